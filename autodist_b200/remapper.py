@@ -1,0 +1,164 @@
+"""Feed / fetch remapping between the user's single-device view and this rank's replica.
+
+Capability parity with ``autodist/remapper.py:29-313``:
+
+* **feed** - a value fed to a placeholder with a polymorphic (``None``) dimension
+  is split along that dimension between the replicas of this node with
+  ``numpy.array_split`` semantics (uneven allowed); this process keeps the chunk
+  of its own replica. Placeholders without such a dimension get the same value
+  on every replica.
+* **fetch** - a ``train_op`` runs on every replica and yields ``None``; a tensor
+  that carries the batch dimension is concatenated over the node's replicas;
+  anything else is replica 0's value (``AUTODIST_FETCH_MODE=local`` returns this
+  replica's own value without communication); a variable yields its full
+  (merged) value.
+"""
+import numpy as np
+import torch
+import torch.fx as fx
+from torch import nn
+
+from autodist_b200.const import ENV
+from autodist_b200.graph_item import TrainOp
+
+
+def _chunk_bounds(n, k, i):
+    q, r = divmod(n, k)
+    start = i * q + min(i, r)
+    return start, start + q + (1 if i < r else 0)
+
+
+class Remapper:
+    def __init__(self, graph_item, plan, device, local_group=None):
+        self._item = graph_item
+        self._plan = plan
+        self._device = torch.device(device)
+        self._local_group = local_group
+        self._num_local = plan.replica.num_local_replicas
+        self._local_index = plan.replica.local_replica_index
+        self._staging = {}
+        self.fetch_mode = ENV.AUTODIST_FETCH_MODE.val
+        if plan.gate_mode != "sync":
+            self.fetch_mode = "local"   # relaxed modes must not add a lock-step collective
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self._last_chunk = {}
+
+    # ------------------------------------------------------------------ feeds
+    def _to_device(self, name, value):
+        if isinstance(value, torch.Tensor):
+            t = value
+        else:
+            t = torch.from_numpy(np.ascontiguousarray(value))
+        if self._device.type == "cpu":
+            return t
+        if t.device.type == "cpu":
+            self.h2d_bytes += t.numel() * t.element_size()
+            if not t.is_pinned():
+                stage = self._staging.get(name)
+                if stage is None or stage.shape != t.shape or stage.dtype != t.dtype:
+                    stage = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                    self._staging[name] = stage
+                stage.copy_(t)
+                t = stage
+            return t.to(self._device, non_blocking=True)
+        return t.to(self._device)
+
+    def remap_feed(self, feed_dict):
+        feeds = {}
+        for key, value in (feed_dict or {}).items():
+            info = self._item.placeholder_of(key)
+            if not isinstance(value, (torch.Tensor, np.ndarray)):
+                value = np.asarray(value)
+            if isinstance(value, np.ndarray) and value.dtype == np.float64 and info.dtype == torch.float32:
+                value = value.astype(np.float32)
+            dim = info.batch_dim
+            if dim is not None and self._num_local > 1:
+                lo, hi = _chunk_bounds(value.shape[dim], self._num_local, self._local_index)
+                index = [slice(None)] * value.ndim
+                index[dim] = slice(lo, hi)
+                value = value[tuple(index)]
+            if dim is not None:
+                self._last_chunk[info.name] = value.shape[dim]
+            t = self._to_device(info.name, value)
+            if t.dtype != info.dtype and t.is_floating_point() and info.dtype.is_floating_point:
+                t = t.to(info.dtype)
+            feeds[info.name] = t
+        return feeds
+
+    # ------------------------------------------------------------------ fetches
+    def flatten_fetches(self, fetches):
+        """Returns (leaves, rebuild) where rebuild(list of values) restores the fetch structure."""
+        leaves = []
+
+        def walk(obj):
+            if isinstance(obj, (list, tuple)):
+                subs = [walk(o) for o in obj]
+                return lambda vals, subs=subs, kind=type(obj): kind(s(vals) for s in subs)
+            if isinstance(obj, dict):
+                subs = {k: walk(v) for k, v in obj.items()}
+                return lambda vals, subs=subs: {k: s(vals) for k, s in subs.items()}
+            leaves.append(obj)
+            idx = len(leaves) - 1
+            return lambda vals, idx=idx: vals[idx]
+
+        rebuild = walk(fetches)
+        return leaves, rebuild
+
+    def classify(self, leaf):
+        if isinstance(leaf, TrainOp):
+            return "train_op"
+        if isinstance(leaf, fx.Proxy):
+            return "tensor"
+        if isinstance(leaf, nn.Parameter):
+            return "variable"
+        if isinstance(leaf, str):
+            name = leaf if leaf.endswith(":0") else leaf + ":0"
+            if name in self._item.variables:
+                return "variable"
+            for n in self._item.tracer.graph.nodes:
+                if n.name == leaf or n.name + ":0" == leaf:
+                    return "tensor"
+        raise TypeError(f"cannot fetch {leaf!r}")
+
+    def node_of(self, leaf):
+        if isinstance(leaf, fx.Proxy):
+            return leaf.node
+        for n in self._item.tracer.graph.nodes:
+            if n.name == leaf or n.name + ":0" == leaf:
+                return n
+        raise KeyError(leaf)
+
+    def _is_batch_tensor(self, value):
+        if not isinstance(value, torch.Tensor) or value.dim() == 0 or not self._last_chunk:
+            return False
+        return value.shape[0] in set(self._last_chunk.values())
+
+    def remap_fetch(self, value, to_numpy=True):
+        """Merge one fetched tensor over the node's replicas and bring it to the host."""
+        if not isinstance(value, torch.Tensor):
+            return value
+        if self._num_local > 1 and self.fetch_mode != "local":
+            import torch.distributed as dist
+            if self._is_batch_tensor(value):
+                counts = [torch.zeros(1, dtype=torch.int64, device=value.device) for _ in range(self._num_local)]
+                dist.all_gather(counts, torch.tensor([value.shape[0]], dtype=torch.int64, device=value.device),
+                                group=self._local_group)
+                counts = [int(c.item()) for c in counts]
+                cap = max(counts)
+                pad = value.new_zeros((cap,) + tuple(value.shape[1:]))
+                pad[:value.shape[0]] = value
+                out = [torch.empty_like(pad) for _ in range(self._num_local)]
+                dist.all_gather(out, pad, group=self._local_group)
+                value = torch.cat([o[:c] for o, c in zip(out, counts)])
+            else:
+                value = value.contiguous().clone()
+                dist.broadcast(value, src=self._plan.replica.local_ranks[0], group=self._local_group)
+        if value.device.type != "cpu":
+            self.d2h_bytes += value.numel() * value.element_size()
+        if not to_numpy:
+            return value.cpu()
+        host = value.detach().cpu()
+        if host.dtype == torch.bfloat16:
+            host = host.float()
+        return host.numpy()

@@ -1,0 +1,129 @@
+"""Session: ``sess.run(fetches, feed_dict)`` on the distributed plan.
+
+Capability parity with ``autodist/runner.py:33-132`` (``WrappedSession``): runs
+under the remapper, initialises variables on construction (replica-0 values on
+every replica) and writes a Chrome trace when tracing is requested through
+``RunOptions``. One session drives one rank; the other ranks execute the same
+script and meet this one in the collectives.
+"""
+import json
+import os
+import time
+
+import torch
+
+from autodist_b200 import const
+from autodist_b200.utils import logging
+
+
+class RunOptions:
+    NO_TRACE = 0
+    SOFTWARE_TRACE = 1
+    HARDWARE_TRACE = 2
+    FULL_TRACE = 3
+
+    def __init__(self, trace_level=0):
+        self.trace_level = trace_level
+
+
+class RunMetadata:
+    def __init__(self):
+        self.step_stats = None
+        self.trace_path = None
+
+
+class WrappedSession:
+    def __init__(self, cluster, graph_item, remapper, engine, coordinator=None, is_built=None):
+        self._cluster = cluster
+        self._graph_item = graph_item
+        self._remapper = remapper
+        self._engine = engine
+        self._coordinator = coordinator
+        self._is_built = is_built or (lambda: True)
+        self._closed = False
+        self._trace_step = 0
+        self.last_step_ms = None
+        logging.debug("session ready on rank %d (%s)", engine.rank, engine.device)
+
+    @property
+    def engine(self):
+        return self._engine
+
+    @property
+    def remapper(self):
+        return self._remapper
+
+    @property
+    def rank(self):
+        return self._engine.rank
+
+    def run(self, fetches, feed_dict=None, options=None, run_metadata=None):
+        if self._closed:
+            raise RuntimeError("session is closed")
+        if not self._is_built():
+            raise RuntimeError("the graph was modified after the distributed session was built")
+        if self._coordinator is not None:
+            self._coordinator.check()
+        tracing = options is not None and options.trace_level > RunOptions.NO_TRACE
+        if tracing:
+            prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU] + (
+                [torch.profiler.ProfilerActivity.CUDA] if self._engine.device.type == "cuda" else []))
+            prof.__enter__()
+        try:
+            result = self._run(fetches, feed_dict)
+        finally:
+            if tracing:
+                prof.__exit__(None, None, None)
+                os.makedirs(const.DEFAULT_TRACE_DIR, exist_ok=True)
+                path = os.path.join(const.DEFAULT_TRACE_DIR, f"timeline_{self._trace_step}.json")
+                prof.export_chrome_trace(path)
+                self._trace_step += 1
+                if run_metadata is not None:
+                    run_metadata.trace_path = path
+                    run_metadata.step_stats = prof.key_averages()
+        return result
+
+    def _run(self, fetches, feed_dict):
+        rm, eng = self._remapper, self._engine
+        single = not isinstance(fetches, (list, tuple, dict))
+        leaves, rebuild = rm.flatten_fetches([fetches] if single else fetches)
+        kinds = [rm.classify(l) for l in leaves]
+        feeds = rm.remap_feed(feed_dict)
+        tensor_idx = [i for i, k in enumerate(kinds) if k == "tensor"]
+        nodes = [rm.node_of(leaves[i]) for i in tensor_idx]
+        train_ops = [leaves[i] for i, k in enumerate(kinds) if k == "train_op"]
+        if len(train_ops) > 1:
+            raise NotImplementedError("one train_op per run() call")
+        if train_ops:
+            values = eng.train_step(train_ops[0], nodes, feeds)
+        elif nodes:
+            eng.before_read()
+            values = eng.forward(nodes, feeds, grad=False)
+        else:
+            values = []
+        out = [None] * len(leaves)
+        for i, v in zip(tensor_idx, values):
+            out[i] = rm.remap_fetch(v)
+        for i, k in enumerate(kinds):
+            if k == "variable":
+                leaf = leaves[i]
+                name = self._graph_item.name_of_parameter(leaf) if not isinstance(leaf, str) else (
+                    leaf if leaf.endswith(":0") else leaf + ":0")
+                out[i] = eng.variable_value(name).cpu().numpy()
+        result = rebuild(out)
+        return result[0] if single else result
+
+    def close(self):
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            self._engine.close()
+        except Exception as e:  # shutting down: peers may already be gone
+            logging.debug("engine close: %s", e)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
