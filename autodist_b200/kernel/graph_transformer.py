@@ -54,7 +54,7 @@ class GraphTransformer:
 
     def transform(self):
         item = self.graph_item
-        logging.info("Transforming the original graph to a distributed plan...")
+        logging.debug("Transforming the original graph to a distributed plan...")
         visualization_util.log_graph(item.graph_text(), "0-original")
 
         shard_plans = VariablePartitioner.apply(self._strategy.node_config, item)
@@ -72,5 +72,5 @@ class GraphTransformer:
         for sync, part in synchronizers:
             sync.between_graph_apply(plan, part)
         visualization_util.log_graph(plan.describe(), "3-transformed")
-        logging.info("Successfully built the distributed plan.")
+        logging.debug("Successfully built the distributed plan.")
         return plan

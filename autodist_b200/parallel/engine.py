@@ -458,21 +458,28 @@ class StepEngine:
             out.update(full)
         return out
 
-    def load_optimizer_slots(self, slots):
+    def load_optimizer_slots(self, slots, default_step=0):
         for info, local, _ in self._local_optimizers:
             if local is None:
                 continue
             names = op_info.slot_names(info.cls)
+            members = {id(p) for g in local.param_groups for p in g["params"]}
             for t in self._targets:
-                st = local.state[t.param]
+                if id(t.param) not in members:
+                    continue
+                loaded = {}
                 for slot in names:
                     key = f"{t.var_name[:-2]}/{slot}"
                     if key in slots:
                         src = slots[key].to(self.device)
-                        st[slot] = (src if t.part is None else t.part.view(src)).clone()
-                key = f"{t.var_name[:-2]}/step"
-                if key in slots:
-                    st["step"] = torch.as_tensor(float(slots[key]))
+                        loaded[slot] = (src if t.part is None else t.part.view(src)).clone()
+                if not loaded:
+                    continue
+                st = local.state[t.param]
+                st.update(loaded)
+                # The writer only knows the step counters of the parts it owned; the rest took as many steps.
+                step = slots.get(f"{t.var_name[:-2]}/step", default_step)
+                st["step"] = torch.as_tensor(float(step))
 
     def close(self):
         if self._async is not None:

@@ -161,4 +161,4 @@ class Remapper:
         host = value.detach().cpu()
         if host.dtype == torch.bfloat16:
             host = host.float()
-        return host.numpy()
+        return np.array(host.numpy(), copy=True) if value.device.type == "cpu" else host.numpy()

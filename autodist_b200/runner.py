@@ -10,6 +10,7 @@ import json
 import os
 import time
 
+import numpy as np
 import torch
 
 from autodist_b200 import const
@@ -109,7 +110,7 @@ class WrappedSession:
                 leaf = leaves[i]
                 name = self._graph_item.name_of_parameter(leaf) if not isinstance(leaf, str) else (
                     leaf if leaf.endswith(":0") else leaf + ":0")
-                out[i] = eng.variable_value(name).cpu().numpy()
+                out[i] = np.array(eng.variable_value(name).float().cpu().numpy() if eng.variable_value(name).dtype == torch.bfloat16 else eng.variable_value(name).cpu().numpy(), copy=True)
         result = rebuild(out)
         return result[0] if single else result
 

@@ -20,7 +20,7 @@ class Strategy:
     def __init__(self, strategy=None):
         self._strategy = strategy if strategy is not None else strategy_pb2.Strategy()
         if strategy is None:
-            self._strategy.id = datetime.datetime.utcnow().strftime("%Y%m%dT%H%M%SM%f")
+            self._strategy.id = datetime.datetime.now(datetime.timezone.utc).strftime("%Y%m%dT%H%M%SM%f")
 
     # -- message access ---------------------------------------------------
     @property

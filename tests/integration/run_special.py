@@ -1,0 +1,181 @@
+"""Multi-rank scenarios that are not plain strategy x case runs: self-launch through the coordinator,
+bounded staleness, asynchronous PS, worker failure, cross-strategy checkpoint reload, ad.function."""
+import os
+import sys
+import tempfile
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, HERE)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from autodist_b200 import AutoDist  # noqa: E402
+from autodist_b200.autodist import _reset_default_autodist  # noqa: E402
+from autodist_b200.checkpoint.saver import Saver  # noqa: E402
+from autodist_b200.resource_spec import ResourceSpec  # noqa: E402
+from autodist_b200.strategy import PS, AllReduce, PartitionedPS  # noqa: E402
+import cases  # noqa: E402
+
+
+def build(ad, case="c0"):
+    factory, _, data_fn, ph_specs, opt_fn, steps = cases.CASES[case]
+    torch.manual_seed(7)
+    model = factory()
+    phs = {k: ad.placeholder(shape, dtype, name=k) for k, (shape, dtype) in ph_specs.items()}
+    loss = model(**phs)
+    opt = opt_fn(list(model.parameters()))
+    return model, phs, loss, opt.minimize(loss), data_fn()
+
+
+def scenario_selflaunch():
+    """No external launcher: the chief re-executes this script for the second replica."""
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=AllReduce(chunk_size=4))
+    ref_state, _ = cases.oracle("c0")
+    with ad.scope():
+        model, phs, loss, train_op, data = build(ad)
+        sess = ad.create_distributed_session()
+        for _ in range(5):
+            sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+        w = sess.run(model.W)
+    assert abs(float(w) - float(ref_state["W"])) < 1e-5, (w, ref_state["W"])
+    print(f"selflaunch rank {sess.rank} ok", flush=True)
+
+
+def scenario_stale():
+    """staleness=2: the fast rank never leads by more than 2 steps, and it does get ahead."""
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=PS(sync=True, staleness=2))
+    with ad.scope():
+        model, phs, loss, train_op, data = build(ad)
+        sess = ad.create_distributed_session()
+        leads = []
+        for step in range(8):
+            if sess.rank == 1:
+                time.sleep(0.3)   # the slow worker
+            sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+            leads.append(sess.engine._async.last_lead)
+        lv = sess.run(loss, {phs[k]: data[k] for k in phs})
+    assert max(leads) <= 2, leads
+    if sess.rank == 0:
+        assert max(leads) >= 1, f"the fast rank never ran ahead: {leads}"
+    assert np.isfinite(lv)
+    print(f"stale rank {sess.rank} leads {leads} ok", flush=True)
+
+
+def scenario_async():
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=PS(sync=False))
+    with ad.scope():
+        model, phs, loss, train_op, data = build(ad)
+        sess = ad.create_distributed_session()
+        first = None
+        for step in range(6 if sess.rank == 0 else 3):   # ranks take different numbers of steps: no lock-step
+            lv, _ = sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+            first = lv if first is None else first
+    assert lv < first
+    print(f"async rank {sess.rank} ok", flush=True)
+
+
+def scenario_failure():
+    """A worker that exits with an error surfaces in the chief as WorkerFailure, not as a hang."""
+    from autodist_b200.coordinator import WorkerFailure
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=AllReduce())
+    with ad.scope():
+        model, phs, loss, train_op, data = build(ad)
+        sess = ad.create_distributed_session()
+        sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+        if sess.rank == 1:
+            os._exit(3)       # dies between steps, nothing in flight
+        caught = None
+        for _ in range(50):
+            try:
+                time.sleep(0.2)
+                sess.run(model.W)        # no collective; the coordinator check raises
+            except WorkerFailure as e:
+                caught = e
+                break
+    assert caught is not None
+    print("failure surfaced ok:", caught, flush=True)
+    os._exit(0)
+
+
+def scenario_crossload():
+    """Save under PartitionedPS, restore under AllReduce in a second session of the same ranks."""
+    tmp = os.environ["AUTODIST_TEST_TMP"]
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2),
+                  strategy_builder=PartitionedPS(num_shards=2, reduction_devices="gpu"))
+    with ad.scope():
+        model, phs, loss, train_op, data = build(ad, "c3")
+        saver = Saver(max_to_keep=2)
+        sess = ad.create_distributed_session()
+        for step in range(1, 4):
+            sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+            path = saver.save(sess, os.path.join(tmp, "m"), global_step=step)
+        after3 = {n: sess.run(n) for n, _ in ad.graph_item.named_parameters()}
+        sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+        after4 = {n: sess.run(n) for n, _ in ad.graph_item.named_parameters()}
+        sess.close()
+    if sess.rank == 0:
+        assert not os.path.exists(os.path.join(tmp, "m-1")) and os.path.exists(os.path.join(tmp, "m-3.index"))
+        plain = torch.load(path, weights_only=False)
+        assert plain["variables"]["emb.weight"].shape == (30, 6)          # merged, original name
+        assert plain["slots"]["emb.weight/exp_avg"].shape == (30, 6)      # optimizer slot merged too
+        assert plain["slices"]["emb.weight"] == [[[0, 0], [15, 6]], [[15, 0], [15, 6]]]
+    _reset_default_autodist()
+    ad2 = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=AllReduce(chunk_size=2))
+    with ad2.scope():
+        torch.manual_seed(99)   # different init: restore must overwrite it
+        model, phs, loss, train_op, data = build(ad2, "c3")
+        torch.manual_seed(123)
+        for p in model.parameters():
+            p.data.normal_()
+        saver2 = Saver()
+        sess2 = ad2.create_distributed_session()
+        saver2.restore(sess2, path)
+        for n, v in after3.items():
+            assert np.allclose(sess2.run(n), v, atol=1e-7), n
+        sess2.run([loss, train_op], {phs[k]: data[k] for k in phs})   # continues exactly (Adam slots restored)
+        for n, v in after4.items():
+            assert np.allclose(sess2.run(n), v, atol=1e-5), (n, np.abs(sess2.run(n) - v).max())
+    print(f"crossload rank {sess2.rank} ok", flush=True)
+
+
+def scenario_function():
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=AllReduce())
+    ref_state, ref_losses = cases.oracle("c0")
+    data = cases.data_linear()
+    with ad.scope():
+        torch.manual_seed(7)
+        model = cases.Linear0()
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+
+        @ad.function
+        def train_step(x, y):
+            loss = model(x, y)
+            return loss, opt.minimize(loss), model.b
+
+        for _ in range(5):
+            loss, _, b = train_step(data["x"], y=data["y"])
+    assert abs(float(b) - float(ref_state["b"])) < 1e-5
+    print(f"function rank {ad.rank} ok", flush=True)
+
+
+def _spawn_ranks(name, nproc=2):
+    """Start the ranks the way an external launcher would (RANK / WORLD_SIZE in the environment)."""
+    import subprocess
+    port = 21000 + (os.getpid() % 20000)
+    procs = [subprocess.Popen([sys.executable, os.path.abspath(__file__), name],
+                              env=dict(os.environ, RANK=str(r), WORLD_SIZE=str(nproc), LOCAL_RANK=str(r),
+                                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port)))
+             for r in range(nproc)]
+    codes = [p.wait(timeout=500) for p in procs]
+    sys.exit(0 if all(c == 0 for c in codes) else 1)
+
+
+if __name__ == "__main__":
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)
+    if sys.argv[1] in ("crossload",) and "RANK" not in os.environ:
+        _spawn_ranks(sys.argv[1])
+    globals()["scenario_" + sys.argv[1]]()
