@@ -1,0 +1,328 @@
+// Python bindings of the sm_100a kernels: tensor-map construction, argument checks, launches on the current stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+
+#include <mutex>
+
+#include "comm.h"
+#include "elementwise.h"
+#include "gemm_tcgen05.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    TORCH_CHECK(e == cudaSuccess && p != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+Tensor as4d(const Tensor& t) {
+  TORCH_CHECK(t.dim() >= 2 && t.dim() <= 4, "operand must have 2 to 4 dimensions");
+  Tensor v = t;
+  while (v.dim() < 4) v = v.unsqueeze(0);
+  return v;
+}
+
+// 4-D bf16 tiled map over a strided view [b_hi, b_lo, outer, inner] (inner stride 1), 128-byte swizzle.
+CUtensorMap make_map(const Tensor& v, int box_outer) {
+  TORCH_CHECK(v.scalar_type() == at::kBFloat16, "GEMM operands must be bf16");
+  TORCH_CHECK(v.stride(3) == 1, "innermost dimension must be contiguous");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(v.data_ptr()) % 16 == 0, "operand base must be 16-byte aligned");
+  cuuint64_t dims[4] = {(cuuint64_t)v.size(3), (cuuint64_t)v.size(2), (cuuint64_t)v.size(1), (cuuint64_t)v.size(0)};
+  cuuint64_t strides[3];
+  int64_t prev = v.size(3);
+  for (int i = 0; i < 3; ++i) {
+    const int d = 2 - i;   // tensor dim of map dim i+1
+    int64_t s = v.size(d) > 1 ? v.stride(d) : prev;
+    TORCH_CHECK((s * 2) % 16 == 0 && s > 0, "operand strides must be positive multiples of 8 elements, got ", s);
+    strides[i] = (cuuint64_t)s * 2;
+    prev = s * v.size(d);
+  }
+  cuuint32_t box[4] = {64, (cuuint32_t)box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap m;
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, v.data_ptr(), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return m;
+}
+
+// D = alpha * A.B^T (+ epilogue). a: [.., M, K] (K-major) or [.., K, M] (a_mn); b: [.., N, K] or [.., K, N] (b_mn);
+// c: [.., M, N] bf16 or fp32 view with unit inner stride.
+void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
+          const optional<Tensor>& c2, const optional<Tensor>& aux, double alpha, double beta, Tensor error_flag, int64_t bn) {
+  const c10::cuda::CUDAGuard guard(a_.device());
+  Tensor a = as4d(a_), b = as4d(b_), c = as4d(c_);
+  const int M = a_mn ? a.size(3) : a.size(2), K = a_mn ? a.size(2) : a.size(3);
+  const int N = b_mn ? b.size(3) : b.size(2), Kb = b_mn ? b.size(2) : b.size(3);
+  TORCH_CHECK(K == Kb, "contraction extents differ: ", K, " vs ", Kb);
+  TORCH_CHECK(a.size(0) == b.size(0) && a.size(1) == b.size(1), "batch dimensions of A and B differ");
+  TORCH_CHECK(c.size(0) == a.size(0) && c.size(1) == a.size(1) && c.size(2) == M && c.size(3) == N, "output shape mismatch");
+  TORCH_CHECK(c.stride(3) == 1, "output inner stride must be 1");
+  if (bn <= 0) bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+  TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "bn must be 64, 128 or 256");
+  CUtensorMap tmA = make_map(a, a_mn ? 64 : 128);
+  CUtensorMap tmB = make_map(b, b_mn ? 64 : (int)bn);
+  adb200::GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.batch_lo = a.size(1); p.batch_hi = a.size(0);
+  p.C = c.data_ptr();
+  p.ldc = c.stride(2);
+  p.strideC_lo = c.size(1) > 1 ? c.stride(1) : 0;
+  p.strideC_hi = c.size(0) > 1 ? c.stride(0) : 0;
+  TORCH_CHECK(c.scalar_type() == at::kFloat || c.scalar_type() == at::kBFloat16, "output must be fp32 or bf16");
+  p.c_is_fp32 = c.scalar_type() == at::kFloat;
+  p.epilogue = (int)epilogue;
+  p.alpha = (float)alpha;
+  p.beta = (float)beta;
+  p.bias = nullptr; p.C2 = nullptr; p.aux = nullptr;
+  if (epilogue == adb200::EPI_BIAS || epilogue == adb200::EPI_BIAS_GELU) {
+    TORCH_CHECK(bias.has_value() && bias->scalar_type() == at::kFloat && bias->numel() >= N, "fp32 bias of N entries needed");
+    p.bias = bias->data_ptr<float>();
+  }
+  if (epilogue == adb200::EPI_BIAS_GELU) {
+    TORCH_CHECK(c2.has_value() && c2->scalar_type() == at::kBFloat16 && !p.c_is_fp32, "bf16 second output needed");
+    Tensor c2v = as4d(*c2);
+    TORCH_CHECK(c2v.strides() == c.strides(), "second output must share the strides of the first");
+    p.C2 = reinterpret_cast<__nv_bfloat16*>(c2v.data_ptr());
+  }
+  if (epilogue == adb200::EPI_MUL_GELU_GRAD) {
+    TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16, "bf16 pre-activation needed");
+    Tensor av = as4d(*aux);
+    TORCH_CHECK(av.strides() == c.strides(), "pre-activation must share the strides of the output");
+    p.aux = reinterpret_cast<const __nv_bfloat16*>(av.data_ptr());
+  }
+  p.error_flag = error_flag.data_ptr<int>();
+  cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
+}
+
+#define BF(t) reinterpret_cast<__nv_bfloat16*>((t).data_ptr())
+#define CBF(t) reinterpret_cast<const __nv_bfloat16*>((t).data_ptr())
+#define OPT_BF(t) ((t).has_value() ? reinterpret_cast<__nv_bfloat16*>((t)->data_ptr()) : nullptr)
+#define OPT_F(t) ((t).has_value() ? (t)->data_ptr<float>() : nullptr)
+#define OPT_I64(t) ((t).has_value() ? (t)->data_ptr<int64_t>() : nullptr)
+#define OPT_LL(t) ((t).has_value() ? reinterpret_cast<const long long*>((t)->data_ptr<int64_t>()) : nullptr)
+#define STREAM at::cuda::getCurrentCUDAStream()
+
+void ln_fwd(const Tensor& x, const optional<Tensor>& res, const Tensor& gamma, const Tensor& beta, const optional<Tensor>& z, Tensor y,
+            Tensor mean, Tensor rstd, double eps, double p_drop, int64_t seed, const optional<Tensor>& step) {
+  const int H = x.size(-1), rows = x.numel() / H;
+  TORCH_CHECK(H % 8 == 0 && H <= 1024, "layernorm width must be a multiple of 8 and at most 1024");
+  adb200::ln_fwd(CBF(x), OPT_BF(res), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(z), BF(y), mean.data_ptr<float>(),
+                 rstd.data_ptr<float>(), rows, H, (float)eps, (float)p_drop, (uint64_t)seed, OPT_LL(step), STREAM);
+}
+void ln_bwd(const Tensor& dy, const Tensor& z, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, const optional<Tensor>& dz_add,
+            Tensor dz, const optional<Tensor>& dx, Tensor part, Tensor dgamma, Tensor dbeta, double p_drop, int64_t seed,
+            const optional<Tensor>& step, bool accumulate) {
+  const int H = dy.size(-1), rows = dy.numel() / H;
+  const int blocks = adb200::ln_bwd_blocks(rows);
+  TORCH_CHECK(part.numel() >= 2LL * blocks * H, "partial buffer too small");
+  adb200::ln_bwd(CBF(dy), CBF(z), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), OPT_BF(dz_add), BF(dz),
+                 OPT_BF(dx), part.data_ptr<float>(), part.data_ptr<float>() + (long long)blocks * H, dgamma.data_ptr<float>(),
+                 dbeta.data_ptr<float>(), rows, H, (float)p_drop, (uint64_t)seed, OPT_LL(step), accumulate ? 1 : 0, STREAM);
+}
+void embed_sum(const Tensor& word, const Tensor& pos, const Tensor& type, const Tensor& ids, const optional<Tensor>& tt, Tensor z, int64_t S) {
+  const int H = word.size(1), rows = ids.numel();
+  adb200::embed_sum(CBF(word), CBF(pos), CBF(type), ids.data_ptr<int64_t>(), OPT_I64(tt), BF(z), rows, (int)S, H, STREAM);
+}
+void scatter_add_rows(Tensor dst, const Tensor& idx, const Tensor& src, double scale) {
+  adb200::scatter_add_rows(dst.data_ptr<float>(), idx.data_ptr<int64_t>(), CBF(src), idx.numel(), src.size(-1), (float)scale, STREAM);
+}
+void strided_rowsum(const Tensor& x, Tensor out, int64_t keys, int64_t stride, int64_t count) {
+  adb200::strided_rowsum(CBF(x), out.data_ptr<float>(), keys, stride, count, x.size(-1), STREAM);
+}
+void keyed_colsum(const Tensor& x, const optional<Tensor>& key, Tensor part, Tensor out, int64_t keys, bool accumulate) {
+  const int H = x.size(-1), rows = x.numel() / H;
+  TORCH_CHECK(H % 8 == 0, "width must be a multiple of 8");
+  TORCH_CHECK(part.numel() >= (long long)adb200::colsum_parts(rows) * keys * H, "partial buffer too small");
+  adb200::keyed_colsum(CBF(x), OPT_I64(key), part.data_ptr<float>(), out.data_ptr<float>(), rows, H, keys, accumulate ? 1 : 0, STREAM);
+}
+void gather_rows(const Tensor& src, const Tensor& idx, Tensor out) {
+  adb200::gather_rows(CBF(src), idx.data_ptr<int64_t>(), BF(out), idx.numel(), src.size(-1), STREAM);
+}
+void scatter_add_rows_bf16(Tensor dst, const Tensor& idx, const Tensor& src) {
+  adb200::scatter_add_rows_bf16(BF(dst), idx.data_ptr<int64_t>(), CBF(src), idx.numel(), src.size(-1), STREAM);
+}
+void softmax_fwd(const Tensor& x, const optional<Tensor>& mask, Tensor p, const optional<Tensor>& p_drop, double scale, double pd,
+                 int64_t seed, const optional<Tensor>& step) {
+  const int S = x.size(-1);
+  TORCH_CHECK(S % 8 == 0 && S <= 1024 && x.dim() == 4, "scores must be [B, heads, S, S] with S a multiple of 8 up to 1024");
+  const long long rows = x.numel() / S;
+  adb200::softmax_fwd(CBF(x), OPT_F(mask), BF(p), OPT_BF(p_drop), rows, S, (int)(x.size(1) * x.size(2)), (float)scale, (float)pd,
+                      (uint64_t)seed, OPT_LL(step), STREAM);
+}
+void softmax_bwd(Tensor dp, const Tensor& p, double scale, double pd, int64_t seed, const optional<Tensor>& step) {
+  const int S = p.size(-1);
+  adb200::softmax_bwd(BF(dp), CBF(p), p.numel() / S, S, (float)scale, (float)pd, (uint64_t)seed, OPT_LL(step), STREAM);
+}
+void xent(Tensor logits, const Tensor& labels, const optional<Tensor>& weights, Tensor denom, Tensor loss_sum, int64_t V, double loss_scale,
+          bool compute_denom, double eps) {
+  const int ld = logits.size(-1), rows = logits.numel() / ld;
+  if (compute_denom) {
+    TORCH_CHECK(weights.has_value(), "weights needed to compute the denominator");
+    adb200::weight_sum(weights->data_ptr<float>(), rows, denom.data_ptr<float>(), (float)eps, STREAM);
+  }
+  adb200::xent(BF(logits), labels.data_ptr<int64_t>(), OPT_F(weights), denom.data_ptr<float>(), loss_sum.data_ptr<float>(), rows, (int)V, ld,
+               (float)loss_scale, STREAM);
+}
+void tanh_bwd(const Tensor& dy, const Tensor& y, Tensor dx) { adb200::tanh_bwd(CBF(dy), CBF(y), BF(dx), y.numel(), STREAM); }
+void add_bf16(const Tensor& a, const Tensor& b, Tensor out) {
+  TORCH_CHECK(a.numel() % 8 == 0, "length must be a multiple of 8");
+  adb200::add_bf16(CBF(a), CBF(b), BF(out), a.numel(), STREAM);
+}
+void adam_update(Tensor p, const Tensor& g, Tensor m, Tensor v, const optional<Tensor>& p16, const Tensor& lr, double b1, double b2, double eps,
+                 double wd, bool decoupled, const Tensor& step, double grad_scale) {
+  adb200::adam_update(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), OPT_BF(p16), p.numel(),
+                      lr.data_ptr<float>(), (float)b1, (float)b2, (float)eps, (float)wd, decoupled ? 1 : 0,
+                      reinterpret_cast<const long long*>(step.data_ptr<int64_t>()), (float)grad_scale, STREAM);
+}
+void sgd_update(Tensor p, const Tensor& g, const optional<Tensor>& mom, const optional<Tensor>& p16, const Tensor& lr, double momentum,
+                double dampening, double wd, bool nesterov, const Tensor& step, double grad_scale) {
+  adb200::sgd_update(p.data_ptr<float>(), g.data_ptr<float>(), OPT_F(mom), OPT_BF(p16), p.numel(), lr.data_ptr<float>(), (float)momentum,
+                     (float)dampening, (float)wd, nesterov ? 1 : 0, reinterpret_cast<const long long*>(step.data_ptr<int64_t>()),
+                     (float)grad_scale, STREAM);
+}
+void adagrad_update(Tensor p, const Tensor& g, Tensor acc, const optional<Tensor>& p16, const Tensor& lr, double eps, double wd, double grad_scale) {
+  adb200::adagrad_update(p.data_ptr<float>(), g.data_ptr<float>(), acc.data_ptr<float>(), OPT_BF(p16), p.numel(), lr.data_ptr<float>(),
+                         (float)eps, (float)wd, (float)grad_scale, STREAM);
+}
+void cast_f32_bf16(const Tensor& x, Tensor y) { adb200::cast_f32_bf16(x.data_ptr<float>(), BF(y), x.numel(), STREAM); }
+void increment(Tensor c) { adb200::increment(reinterpret_cast<long long*>(c.data_ptr<int64_t>()), STREAM); }
+
+// ---------------------------------------------------------------------------------------------- communication
+adb200::SymCtx make_ctx(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s) {
+  adb200::SymCtx c;
+  c.flags = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  c.epochs = reinterpret_cast<uint32_t*>(epochs.data_ptr<int32_t>());
+  c.error = error.data_ptr<int32_t>();
+  c.rank = (int)rank;
+  c.world = (int)world;
+  c.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  TORCH_CHECK(world >= 1 && world <= 8, "1 to 8 ranks supported");
+  TORCH_CHECK(epochs.numel() >= adb200::kMaxCommBlocks, "epoch array too small");
+  return c;
+}
+
+// buf_ptrs: int64 device tensor with every rank's wire-buffer address; mc_ptr: multicast address or 0.
+void allreduce(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s, const Tensor& buf_ptrs,
+               int64_t mc_ptr, int64_t wire, int64_t n, const optional<Tensor>& src32, const optional<Tensor>& residual,
+               const optional<Tensor>& dst32, double scale, int64_t blocks) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  const int vec = wire == adb200::WIRE_F32 ? 4 : 8;
+  TORCH_CHECK(n % vec == 0, "bucket length must be a multiple of ", vec);
+  if (blocks <= 0) blocks = adb200::comm_grid(n / vec / world, adb200::kMaxCommBlocks);
+  TORCH_CHECK(blocks <= adb200::kMaxCommBlocks, "too many blocks");
+  adb200::launch_allreduce(c, reinterpret_cast<void* const*>(buf_ptrs.data_ptr<int64_t>()), reinterpret_cast<void*>(mc_ptr), (int)wire, n,
+                           OPT_F(src32), OPT_F(residual), OPT_F(dst32), (float)scale, (int)blocks, STREAM);
+}
+
+void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
+                           const Tensor& grad_ptrs, const Tensor& p16_ptrs, const optional<Tensor>& p32_ptrs, Tensor master,
+                           const optional<Tensor>& s1, const optional<Tensor>& s2, const Tensor& seg_start, const Tensor& seg_len,
+                           const Tensor& seg_state, const Tensor& owned_prefix, int64_t kind, const Tensor& lr, const Tensor& step, double b1,
+                           double b2, double eps, double wd, double momentum, double grad_scale, bool decoupled, bool nesterov, double scale,
+                           int64_t blocks) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  const int nseg = seg_start.numel();
+  TORCH_CHECK(owned_prefix.numel() == nseg + 1, "owned_prefix must have nseg + 1 entries");
+  TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
+  adb200::launch_reduce_scatter_update(
+      c, reinterpret_cast<float* const*>(grad_ptrs.data_ptr<int64_t>()), reinterpret_cast<__nv_bfloat16* const*>(p16_ptrs.data_ptr<int64_t>()),
+      p32_ptrs.has_value() ? reinterpret_cast<float* const*>(p32_ptrs->data_ptr<int64_t>()) : nullptr, master.data_ptr<float>(), OPT_F(s1),
+      OPT_F(s2), reinterpret_cast<const long long*>(seg_start.data_ptr<int64_t>()), reinterpret_cast<const long long*>(seg_len.data_ptr<int64_t>()),
+      reinterpret_cast<const long long*>(seg_state.data_ptr<int64_t>()), reinterpret_cast<const long long*>(owned_prefix.data_ptr<int64_t>()), nseg,
+      (int)kind, lr.data_ptr<float>(), reinterpret_cast<const long long*>(step.data_ptr<int64_t>()), (float)b1, (float)b2, (float)eps, (float)wd,
+      (float)momentum, (float)grad_scale, decoupled ? 1 : 0, nesterov ? 1 : 0, (float)scale, (int)blocks, STREAM);
+}
+
+void sparse_scatter_add(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
+                        const Tensor& shard_ptrs, const Tensor& ids, const Tensor& vals, int64_t V, double scale, int64_t blocks) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  const int H = vals.size(-1);
+  TORCH_CHECK(H % 4 == 0, "row width must be a multiple of 4");
+  TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
+  adb200::launch_sparse_scatter_add(c, reinterpret_cast<float* const*>(shard_ptrs.data_ptr<int64_t>()), ids.data_ptr<int64_t>(), vals.data_ptr(),
+                                    vals.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), H, V, (float)scale, (int)blocks, STREAM);
+}
+
+void embedding_gather_peers(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
+                            const Tensor& shard_ptrs, const Tensor& ids, Tensor out, int64_t V, bool do_barrier, int64_t blocks) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  TORCH_CHECK(out.size(-1) % 8 == 0, "row width must be a multiple of 8");
+  TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
+  adb200::launch_embedding_gather_peers(c, reinterpret_cast<__nv_bfloat16* const*>(shard_ptrs.data_ptr<int64_t>()), ids.data_ptr<int64_t>(),
+                                        BF(out), ids.numel(), out.size(-1), V, do_barrier ? 1 : 0, (int)blocks, STREAM);
+}
+
+void sym_barrier(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s, int64_t blocks) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  adb200::launch_barrier(c, (int)blocks, STREAM);
+}
+
+void staleness_gate(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
+                    const Tensor& clock_ptrs, int64_t my_step, int64_t staleness) {
+  adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  adb200::launch_staleness_gate(c, reinterpret_cast<uint32_t* const*>(clock_ptrs.data_ptr<int64_t>()), (uint32_t)my_step, (uint32_t)staleness, STREAM);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("ln_fwd", &ln_fwd);
+  m.def("ln_bwd", &ln_bwd);
+  m.def("ln_bwd_blocks", &adb200::ln_bwd_blocks);
+  m.def("colsum_parts", &adb200::colsum_parts);
+  m.def("embed_sum", &embed_sum);
+  m.def("scatter_add_rows", &scatter_add_rows);
+  m.def("strided_rowsum", &strided_rowsum);
+  m.def("keyed_colsum", &keyed_colsum);
+  m.def("gather_rows", &gather_rows);
+  m.def("scatter_add_rows_bf16", &scatter_add_rows_bf16);
+  m.def("softmax_fwd", &softmax_fwd);
+  m.def("softmax_bwd", &softmax_bwd);
+  m.def("xent", &xent);
+  m.def("tanh_bwd", &tanh_bwd);
+  m.def("add_bf16", &add_bf16);
+  m.def("adam_update", &adam_update);
+  m.def("sgd_update", &sgd_update);
+  m.def("adagrad_update", &adagrad_update);
+  m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("increment", &increment);
+  m.def("allreduce", &allreduce);
+  m.def("reduce_scatter_update", &reduce_scatter_update);
+  m.def("sparse_scatter_add", &sparse_scatter_add);
+  m.def("embedding_gather_peers", &embedding_gather_peers);
+  m.def("sym_barrier", &sym_barrier);
+  m.def("staleness_gate", &staleness_gate);
+  m.attr("MAX_COMM_BLOCKS") = adb200::kMaxCommBlocks;
+}

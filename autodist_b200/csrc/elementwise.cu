@@ -1,0 +1,633 @@
+// Bandwidth-bound kernels of the transformer / optimizer path, written for sm_100a (HBM3e-bound: 16-byte
+// vector accesses, one pass over the data, reductions in registers + warp shuffles, statistics in fp32).
+//
+//   layernorm (+ residual add + dropout) forward / backward, embedding sum + layernorm, masked softmax (+dropout)
+//   forward / backward, log-softmax cross-entropy forward+backward in one pass, row gather / scatter-add,
+//   column sums (bias gradients), fused Adam / SGD-momentum / Adagrad updates that also emit the bf16 compute copy.
+//
+// In the reference all of these are TensorFlow library ops (LayerNormalization, softmax, sparse CE, ResourceApply*:
+// examples/benchmark/utils/modeling/layers/transformer.py:133-164, masked_softmax.py:37-56,
+// autodist/kernel/common/op_info.py:24-68).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "elementwise.h"
+
+namespace adb200 {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Counter-based dropout mask: the same (seed, index) gives the same decision in forward and backward.
+__device__ __forceinline__ uint32_t mix(uint64_t seed, uint64_t idx) {
+  uint64_t x = seed + idx * 0x9E3779B97F4A7C15ull;
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return (uint32_t)x;
+}
+__device__ __forceinline__ float keep_scale(uint64_t seed, uint64_t idx, uint32_t thresh, float inv_keep) {
+  return ((mix(seed, idx) >> 8) >= thresh) ? inv_keep : 0.0f;
+}
+__device__ __forceinline__ uint64_t step_seed(uint64_t seed, const long long* step) {
+  return seed + (step ? (uint64_t)(*step) * 0x100000001B3ull : 0ull);
+}
+
+__device__ __forceinline__ void load8(const bf16* p, float* v) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(bf16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ------------------------------------------------------------------------------------------------ LayerNorm
+// One warp per row, H a multiple of 8 and at most 8 * 32 * MAXV. z = dropout(x) + residual is written back (it is
+// what the backward pass needs), y = LN(z) * gamma + beta.
+constexpr int MAXV = 4;   // 8-element vectors per lane -> H <= 1024
+
+__global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const float* __restrict__ gamma,
+                              const float* __restrict__ beta, bf16* __restrict__ z, bf16* __restrict__ y,
+                              float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, float eps,
+                              float p_drop, uint64_t seed, const long long* step) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const int nvec = H / 8;
+  const uint32_t thresh = (uint32_t)(p_drop * 16777216.0f);
+  const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
+  const uint64_t sd = step_seed(seed, step);
+  float v[MAXV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+      const long long off = (long long)warp * H + vec * 8;
+      load8(x + off, v[i]);
+      if (p_drop > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+      }
+      if (res) {
+        float r[8];
+        load8(res + off, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+  }
+  const float mu = warp_sum(s) / H;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; q += d * d; }
+    }
+  const float rs = rsqrtf(warp_sum(q) / H + eps);
+  if (lane == 0) { mean[warp] = mu; rstd[warp] = rs; }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+      const long long off = (long long)warp * H + vec * 8;
+      if (z) store8(z + off, v[i]);
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mu) * rs * gamma[vec * 8 + j] + beta[vec * 8 + j];
+      store8(y + off, o);
+    }
+  }
+}
+
+// dz = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)); dx = dz * dropout mask (only written when p_drop > 0).
+// `dz_add` (optional) is added to dz before it is stored: the gradient arriving over the residual connection.
+__global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ z, const float* __restrict__ mean,
+                              const float* __restrict__ rstd, const float* __restrict__ gamma, const bf16* __restrict__ dz_add,
+                              bf16* __restrict__ dz, bf16* __restrict__ dx, float* __restrict__ part_g, float* __restrict__ part_b,
+                              int rows, int H, float p_drop, uint64_t seed, const long long* step) {
+  extern __shared__ float sm[];   // [warps][H] x 2
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int nvec = H / 8;
+  const uint32_t thresh = (uint32_t)(p_drop * 16777216.0f);
+  const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
+  const uint64_t sd = step_seed(seed, step);
+  float ag[MAXV][8], ab[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { ag[i][j] = 0.f; ab[i][j] = 0.f; }
+  for (int row = blockIdx.x * wpb + wib; row < rows; row += gridDim.x * wpb) {
+    const float mu = mean[row], rs = rstd[row];
+    float g[MAXV][8], xh[MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int vec = lane + 32 * i;
+      if (vec < nvec) {
+        const long long off = (long long)row * H + vec * 8;
+        float d[8], zz[8];
+        load8(dy + off, d);
+        load8(z + off, zz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (zz[j] - mu) * rs;
+          ag[i][j] += d[j] * xh[i][j];
+          ab[i][j] += d[j];
+          g[i][j] = d[j] * gamma[vec * 8 + j];
+          s1 += g[i][j];
+          s2 += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / H;
+    s2 = warp_sum(s2) / H;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int vec = lane + 32 * i;
+      if (vec < nvec) {
+        const long long off = (long long)row * H + vec * 8;
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - s1 - xh[i][j] * s2);
+        if (dz_add) {
+          float a[8];
+          load8(dz_add + off, a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += a[j];
+        }
+        store8(dz + off, o);
+        if (p_drop > 0.f && dx) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+          store8(dx + off, o);
+        }
+      }
+    }
+  }
+  float* sg = sm;
+  float* sb = sm + wpb * H;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { sg[wib * H + vec * 8 + j] = ag[i][j]; sb[wib * H + vec * 8 + j] = ab[i][j]; }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < wpb; ++w) { a += sg[w * H + c]; b += sb[w * H + c]; }
+    part_g[(long long)blockIdx.x * H + c] = a;
+    part_b[(long long)blockIdx.x * H + c] = b;
+  }
+}
+
+// out[c] (+)= sum over `parts` rows of part[r][c]
+__global__ void colsum_f32_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int H, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float a = 0.f;
+  for (int r = 0; r < parts; ++r) a += part[(long long)r * H + c];
+  out[c] = accumulate ? out[c] + a : a;
+}
+
+// ------------------------------------------------------------------------------------------------ embeddings
+// z[row] = word[ids[row]] + pos[row % S] + type[tt[row]]  (bf16 tables), then the layernorm kernel runs on z.
+__global__ void embed_sum_kernel(const bf16* __restrict__ word, const bf16* __restrict__ pos, const bf16* __restrict__ type,
+                                 const int64_t* __restrict__ ids, const int64_t* __restrict__ tt, bf16* __restrict__ z,
+                                 int rows, int S, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const long long w = ids[warp], t = tt ? tt[warp] : 0;
+  const int s = warp % S;
+  for (int vec = lane; vec < H / 8; vec += 32) {
+    float a[8], b[8], c[8];
+    load8(word + w * H + vec * 8, a);
+    load8(pos + (long long)s * H + vec * 8, b);
+    load8(type + t * H + vec * 8, c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] += b[j] + c[j];
+    store8(z + (long long)warp * H + vec * 8, a);
+  }
+}
+
+// dst[idx[r]] += src[r] (fp32 destination, bf16 source rows): dense embedding gradient by vector atomics.
+__global__ void scatter_add_rows_kernel(float* __restrict__ dst, const int64_t* __restrict__ idx, const bf16* __restrict__ src,
+                                        int rows, int H, float scale) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const long long r = idx[warp];
+  for (int vec = lane; vec < H / 8; vec += 32) {
+    float a[8];
+    load8(src + (long long)warp * H + vec * 8, a);
+    float* d = dst + r * H + vec * 8;
+    atomicAdd(reinterpret_cast<float4*>(d), make_float4(a[0] * scale, a[1] * scale, a[2] * scale, a[3] * scale));
+    atomicAdd(reinterpret_cast<float4*>(d + 4), make_float4(a[4] * scale, a[5] * scale, a[6] * scale, a[7] * scale));
+  }
+}
+
+// out[k][c] = sum over rows r = k + j*stride (j < count) of x[r][c]: position-embedding gradient (k = position).
+__global__ void strided_rowsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, int keys, int stride, int count, int H) {
+  const int k = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= H || k >= keys) return;
+  float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < count; ++j) {
+    float v[8];
+    load8(x + ((long long)k + (long long)j * stride) * H + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] += v[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[(long long)k * H + c + i] = a[i];
+}
+
+// part[b][k][c] = sum over this block's rows with key[row]==k of x[row][c]   (keys small: token-type gradient)
+// With key == nullptr every row has key 0: plain column sums (bias gradients).
+__global__ void keyed_colsum_kernel(const bf16* __restrict__ x, const int64_t* __restrict__ key, float* __restrict__ part,
+                                    int rows, int H, int keys, int rows_per_block) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= H) return;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  for (int k = 0; k < keys; ++k) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = r0; r < r1; ++r) {
+      if (key && key[r] != k) continue;
+      float v[8];
+      load8(x + (long long)r * H + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] += v[i];
+    }
+    float* o = part + ((long long)blockIdx.y * keys + k) * H + c;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = a[i];
+  }
+}
+
+// out[r] = src[idx[r]] (bf16 rows)
+__global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx, bf16* __restrict__ out, int rows, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const long long r = idx[warp];
+  for (int vec = lane; vec < H / 8; vec += 32)
+    *reinterpret_cast<uint4*>(out + (long long)warp * H + vec * 8) = *reinterpret_cast<const uint4*>(src + r * H + vec * 8);
+}
+
+// dst[idx[r]] += src[r] for bf16 rows whose indices are unique (MLM positions of one sequence never repeat)
+__global__ void scatter_add_rows_bf16_kernel(bf16* __restrict__ dst, const int64_t* __restrict__ idx, const bf16* __restrict__ src, int rows, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const long long r = idx[warp];
+  for (int vec = lane; vec < H / 8; vec += 32) {
+    float a[8], b[8];
+    load8(src + (long long)warp * H + vec * 8, a);
+    load8(dst + r * H + vec * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] += a[j];
+    store8(dst + r * H + vec * 8, b);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ softmax
+// Rows of length S (<= 1024, multiple of 8) of a [B, heads, S, S] tensor; one warp per row. p = softmax(scale*x + mask[b]);
+// writes p (needed by the backward pass) and, when dropout is on, p_drop = dropout(p) for the P.V product.
+__global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ mask, bf16* __restrict__ p,
+                                   bf16* __restrict__ p_drop, long long rows, int S, int rows_per_batch, float scale,
+                                   float pd, uint64_t seed, const long long* step) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const int b = (int)(warp / rows_per_batch);
+  const int nvec = S / 8;
+  float v[MAXV][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+      load8(x + warp * S + vec * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = v[i][j] * scale + (mask ? mask[(long long)b * S + vec * 8 + j] : 0.f);
+        mx = fmaxf(mx, v[i][j]);
+      }
+    }
+  }
+  mx = warp_max(mx);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[i][j] = __expf(v[i][j] - mx); s += v[i][j]; }
+    }
+  const float inv = 1.0f / warp_sum(s);
+  const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
+  const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
+  const uint64_t sd = step_seed(seed, step);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+      const long long off = warp * S + vec * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] *= inv;
+      store8(p + off, v[i]);
+      if (pd > 0.f && p_drop) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+        store8(p_drop + off, v[i]);
+      }
+    }
+  }
+}
+
+// ds = scale * p * (dp' - sum(dp' * p)) with dp' = dp * dropout mask; written over dp.
+__global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict__ p, long long rows, int S, float scale,
+                                   float pd, uint64_t seed, const long long* step) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const int nvec = S / 8;
+  const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
+  const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
+  const uint64_t sd = step_seed(seed, step);
+  float d[MAXV][8], pr[MAXV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+      const long long off = warp * S + vec * 8;
+      load8(dp + off, d[i]);
+      load8(p + off, pr[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (pd > 0.f) d[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+        s += d[i][j] * pr[i][j];
+      }
+    }
+  }
+  s = warp_sum(s);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int vec = lane + 32 * i;
+    if (vec < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d[i][j] = scale * pr[i][j] * (d[i][j] - s);
+      store8(dp + warp * S + vec * 8, d[i]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ cross-entropy
+// One block per row of logits [rows, ld] (first V columns valid). loss_sum += w * (lse - x[label]); the logits are
+// overwritten by d loss / d logits = w / denom * (softmax - onehot) (zero in the padding columns). denom is read
+// from device memory (sum of weights, computed by weight_sum_kernel) so that the whole step stays on the device.
+__global__ void weight_sum_kernel(const float* __restrict__ w, int n, float* __restrict__ out, float eps) {
+  float a = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) a += w[i];
+  a = warp_sum(a);
+  __shared__ float s[32];
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) t += s[i];
+    *out = t + eps;
+  }
+}
+
+__global__ void xent_kernel(bf16* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ weights,
+                            const float* __restrict__ denom, float* __restrict__ loss_sum, int V, int ld, float loss_scale) {
+  const int row = blockIdx.x;
+  bf16* x = logits + (long long)row * ld;
+  __shared__ float red[32];
+  __shared__ float bc;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) mx = fmaxf(mx, __bfloat162float(x[c]));
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) { float m = red[0]; for (int i = 1; i < (blockDim.x >> 5); ++i) m = fmaxf(m, red[i]); bc = m; }
+  __syncthreads();
+  mx = bc;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) s += __expf(__bfloat162float(x[c]) - mx);
+  s = warp_sum(s);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < (blockDim.x >> 5); ++i) t += red[i]; bc = t; }
+  __syncthreads();
+  const float sum = bc;
+  const float w = weights ? weights[row] : 1.0f;
+  const float dn = *denom;
+  const long long label = labels[row];
+  if (threadIdx.x == 0) atomicAdd(loss_sum, loss_scale * w * (logf(sum) + mx - __bfloat162float(x[label])) / dn);
+  const float g = loss_scale * w / dn;
+  const float inv = 1.0f / sum;
+  for (int c = threadIdx.x; c < ld; c += blockDim.x) {
+    float v = 0.f;
+    if (c < V) v = g * (__expf(__bfloat162float(x[c]) - mx) * inv - (c == label ? 1.0f : 0.0f));
+    x[c] = __float2bfloat16(v);
+  }
+}
+
+__global__ void tanh_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { float t = __bfloat162float(y[i]); dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * (1.0f - t * t)); }
+}
+
+__global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float x[8], y[8];
+  load8(a + i * 8, x);
+  load8(b + i * 8, y);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] += y[j];
+  store8(out + i * 8, x);
+}
+
+// ------------------------------------------------------------------------------------------------ optimizers
+// Flat multi-tensor updates over [n] fp32 master weights; each also writes the bf16 copy the next forward reads.
+// lr and the step counter live in device memory so that a captured CUDA graph follows schedules.
+__global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                            bf16* __restrict__ p16, long long n, const float* __restrict__ lr_ptr, float b1, float b2, float eps,
+                            float wd, int decoupled, const long long* __restrict__ step_ptr, float grad_scale) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  const float lr = *lr_ptr;
+  const float t = (float)(*step_ptr);
+  const float c1 = 1.0f - powf(b1, t), c2 = 1.0f - powf(b2, t);
+  const int cnt = (int)min((long long)4, n - i);
+  float pp[4], gg[4], mm[4], vv[4];
+  if (cnt == 4) {
+    float4 a = *reinterpret_cast<const float4*>(p + i); pp[0] = a.x; pp[1] = a.y; pp[2] = a.z; pp[3] = a.w;
+    a = *reinterpret_cast<const float4*>(g + i); gg[0] = a.x; gg[1] = a.y; gg[2] = a.z; gg[3] = a.w;
+    a = *reinterpret_cast<const float4*>(m + i); mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w;
+    a = *reinterpret_cast<const float4*>(v + i); vv[0] = a.x; vv[1] = a.y; vv[2] = a.z; vv[3] = a.w;
+  } else {
+    for (int j = 0; j < cnt; ++j) { pp[j] = p[i + j]; gg[j] = g[i + j]; mm[j] = m[i + j]; vv[j] = v[i + j]; }
+  }
+  for (int j = 0; j < cnt; ++j) {
+    float gr = gg[j] * grad_scale;
+    if (wd != 0.f) { if (decoupled) pp[j] *= 1.0f - lr * wd; else gr += wd * pp[j]; }
+    mm[j] = b1 * mm[j] + (1.0f - b1) * gr;
+    vv[j] = b2 * vv[j] + (1.0f - b2) * gr * gr;
+    pp[j] -= lr * (mm[j] / c1) / (sqrtf(vv[j] / c2) + eps);
+  }
+  if (cnt == 4) {
+    *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (p16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+      uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      *reinterpret_cast<uint2*>(p16 + i) = u;
+    }
+  } else {
+    for (int j = 0; j < cnt; ++j) { p[i + j] = pp[j]; m[i + j] = mm[j]; v[i + j] = vv[j]; if (p16) p16[i + j] = __float2bfloat16(pp[j]); }
+  }
+}
+
+__global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ mom, bf16* __restrict__ p16,
+                           long long n, const float* __restrict__ lr_ptr, float momentum, float dampening, float wd, int nesterov,
+                           const long long* __restrict__ step_ptr, float grad_scale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float lr = *lr_ptr;
+  float gr = g[i] * grad_scale + wd * p[i];
+  if (momentum != 0.f) {
+    const float b = (*step_ptr <= 1) ? gr : momentum * mom[i] + (1.0f - dampening) * gr;
+    mom[i] = b;
+    gr = nesterov ? gr + momentum * b : b;
+  }
+  const float np = p[i] - lr * gr;
+  p[i] = np;
+  if (p16) p16[i] = __float2bfloat16(np);
+}
+
+__global__ void adagrad_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ acc, bf16* __restrict__ p16,
+                               long long n, const float* __restrict__ lr_ptr, float eps, float wd, float grad_scale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gr = g[i] * grad_scale + wd * p[i];
+  const float a = acc[i] + gr * gr;
+  acc[i] = a;
+  const float np = p[i] - *lr_ptr * gr / (sqrtf(a) + eps);
+  p[i] = np;
+  if (p16) p16[i] = __float2bfloat16(np);
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __float2bfloat16(x[i]);
+}
+
+__global__ void increment_kernel(long long* c) { *c += 1; }
+
+inline int blocks_for(long long n, int per) { return (int)((n + per - 1) / per); }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------- launchers
+void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* beta, bf16* z, bf16* y, float* mean, float* rstd,
+            int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st) {
+  ln_fwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
+}
+int ln_bwd_blocks(int rows) { return rows < 296 * 4 ? (rows + 3) / 4 : 296; }
+void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd, const float* gamma, const bf16* dz_add, bf16* dz,
+            bf16* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
+            const long long* step, int accumulate, cudaStream_t st) {
+  const int blocks = ln_bwd_blocks(rows);
+  ln_bwd_kernel<<<blocks, 128, 2 * 4 * H * sizeof(float), st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part_g, part_b, rows, H,
+                                                                p_drop, seed, step);
+  colsum_f32_kernel<<<blocks_for(H, 256), 256, 0, st>>>(part_g, dgamma, blocks, H, accumulate);
+  colsum_f32_kernel<<<blocks_for(H, 256), 256, 0, st>>>(part_b, dbeta, blocks, H, accumulate);
+}
+void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
+               int H, cudaStream_t st) {
+  embed_sum_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(word, pos, type, ids, tt, z, rows, S, H);
+}
+void scatter_add_rows(float* dst, const int64_t* idx, const bf16* src, int rows, int H, float scale, cudaStream_t st) {
+  scatter_add_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H, scale);
+}
+void strided_rowsum(const bf16* x, float* out, int keys, int stride, int count, int H, cudaStream_t st) {
+  dim3 grid(blocks_for(H / 8, 128), keys);
+  strided_rowsum_kernel<<<grid, 128, 0, st>>>(x, out, keys, stride, count, H);
+}
+int colsum_parts(int rows) { return rows >= 2048 ? 64 : (rows >= 256 ? 16 : 1); }
+void keyed_colsum(const bf16* x, const int64_t* key, float* part, float* out, int rows, int H, int keys, int accumulate, cudaStream_t st) {
+  const int parts = colsum_parts(rows);
+  const int rpb = (rows + parts - 1) / parts;
+  dim3 grid(blocks_for(H / 8, 128), parts);
+  keyed_colsum_kernel<<<grid, 128, 0, st>>>(x, key, part, rows, H, keys, rpb);
+  colsum_f32_kernel<<<blocks_for(keys * H, 256), 256, 0, st>>>(part, out, parts, keys * H, accumulate);
+}
+void gather_rows(const bf16* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
+  gather_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
+}
+void scatter_add_rows_bf16(bf16* dst, const int64_t* idx, const bf16* src, int rows, int H, cudaStream_t st) {
+  scatter_add_rows_bf16_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H);
+}
+void softmax_fwd(const bf16* x, const float* mask, bf16* p, bf16* p_drop, long long rows, int S, int rows_per_batch, float scale,
+                 float pd, uint64_t seed, const long long* step, cudaStream_t st) {
+  softmax_fwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(x, mask, p, p_drop, rows, S, rows_per_batch, scale, pd, seed, step);
+}
+void softmax_bwd(bf16* dp, const bf16* p, long long rows, int S, float scale, float pd, uint64_t seed, const long long* step,
+                 cudaStream_t st) {
+  softmax_bwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dp, p, rows, S, scale, pd, seed, step);
+}
+void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st) { weight_sum_kernel<<<1, 256, 0, st>>>(w, n, out, eps); }
+void xent(bf16* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,
+          float loss_scale, cudaStream_t st) {
+  xent_kernel<<<rows, V >= 4096 ? 1024 : 128, 0, st>>>(logits, labels, weights, denom, loss_sum, V, ld, loss_scale);
+}
+void tanh_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
+  tanh_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, y, dx, n);
+}
+void add_bf16(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t st) {
+  add_bf16_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(a, b, out, n / 8);
+}
+void adam_update(float* p, const float* g, float* m, float* v, bf16* p16, long long n, const float* lr, float b1, float b2,
+                 float eps, float wd, int decoupled, const long long* step, float grad_scale, cudaStream_t st) {
+  adam_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, st>>>(p, g, m, v, p16, n, lr, b1, b2, eps, wd, decoupled, step, grad_scale);
+}
+void sgd_update(float* p, const float* g, float* mom, bf16* p16, long long n, const float* lr, float momentum, float dampening,
+                float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st) {
+  sgd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, mom, p16, n, lr, momentum, dampening, wd, nesterov, step, grad_scale);
+}
+void adagrad_update(float* p, const float* g, float* acc, bf16* p16, long long n, const float* lr, float eps, float wd,
+                    float grad_scale, cudaStream_t st) {
+  adagrad_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, acc, p16, n, lr, eps, wd, grad_scale);
+}
+void cast_f32_bf16(const float* x, bf16* y, long long n, cudaStream_t st) {
+  cast_f32_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(x, y, n);
+}
+void increment(long long* c, cudaStream_t st) { increment_kernel<<<1, 1, 0, st>>>(c); }
+
+}  // namespace adb200

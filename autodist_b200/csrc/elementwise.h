@@ -1,0 +1,40 @@
+// Host-side interface of the bandwidth-bound kernels (see elementwise.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace adb200 {
+typedef __nv_bfloat16 bf16_t;
+void ln_fwd(const bf16_t* x, const bf16_t* res, const float* gamma, const float* beta, bf16_t* z, bf16_t* y, float* mean, float* rstd,
+            int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st);
+int ln_bwd_blocks(int rows);
+void ln_bwd(const bf16_t* dy, const bf16_t* z, const float* mean, const float* rstd, const float* gamma, const bf16_t* dz_add, bf16_t* dz,
+            bf16_t* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
+            const long long* step, int accumulate, cudaStream_t st);
+void embed_sum(const bf16_t* word, const bf16_t* pos, const bf16_t* type, const int64_t* ids, const int64_t* tt, bf16_t* z, int rows, int S,
+               int H, cudaStream_t st);
+void scatter_add_rows(float* dst, const int64_t* idx, const bf16_t* src, int rows, int H, float scale, cudaStream_t st);
+void strided_rowsum(const bf16_t* x, float* out, int keys, int stride, int count, int H, cudaStream_t st);
+int colsum_parts(int rows);
+void keyed_colsum(const bf16_t* x, const int64_t* key, float* part, float* out, int rows, int H, int keys, int accumulate, cudaStream_t st);
+void gather_rows(const bf16_t* src, const int64_t* idx, bf16_t* out, int rows, int H, cudaStream_t st);
+void scatter_add_rows_bf16(bf16_t* dst, const int64_t* idx, const bf16_t* src, int rows, int H, cudaStream_t st);
+void softmax_fwd(const bf16_t* x, const float* mask, bf16_t* p, bf16_t* p_drop, long long rows, int S, int rows_per_batch, float scale,
+                 float pd, uint64_t seed, const long long* step, cudaStream_t st);
+void softmax_bwd(bf16_t* dp, const bf16_t* p, long long rows, int S, float scale, float pd, uint64_t seed, const long long* step,
+                 cudaStream_t st);
+void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st);
+void xent(bf16_t* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,
+          float loss_scale, cudaStream_t st);
+void tanh_bwd(const bf16_t* dy, const bf16_t* y, bf16_t* dx, long long n, cudaStream_t st);
+void add_bf16(const bf16_t* a, const bf16_t* b, bf16_t* out, long long n, cudaStream_t st);
+void adam_update(float* p, const float* g, float* m, float* v, bf16_t* p16, long long n, const float* lr, float b1, float b2,
+                 float eps, float wd, int decoupled, const long long* step, float grad_scale, cudaStream_t st);
+void sgd_update(float* p, const float* g, float* mom, bf16_t* p16, long long n, const float* lr, float momentum, float dampening,
+                float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st);
+void adagrad_update(float* p, const float* g, float* acc, bf16_t* p16, long long n, const float* lr, float eps, float wd,
+                    float grad_scale, cudaStream_t st);
+void cast_f32_bf16(const float* x, bf16_t* y, long long n, cudaStream_t st);
+void increment(long long* c, cudaStream_t st);
+}  // namespace adb200

@@ -1,0 +1,395 @@
+// Batched bf16 GEMM on the 5th-generation tensor cores (sm_100a): D[b][M,N] = A[b][M,K] * B[b][N,K]^T.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0    TMA producer   cp.async.bulk.tensor (4-D tiled maps, 128-byte swizzle) into a ring of smem stages
+//   warp 1    MMA issuer     one lane issues tcgen05.mma (cta_group::1, kind::f16, 128 x BN x 16), accumulators in TMEM
+//   warps 2-5 epilogue       tcgen05.ld of the accumulator (two TMEM buffers, so tile i+1 is multiplied while tile i
+//                            is written), fused bias / GELU / GELU-derivative / scale, direct 32-byte row stores
+//
+// Either operand may be K-major (contraction dimension contiguous in memory) or MN-major (the M or N dimension
+// contiguous): the backward GEMMs of a linear layer (dX = dY W, dW = dY^T X) and of attention read the same
+// tensors as the forward pass without a transpose kernel.
+//
+// Every mbarrier wait is bounded: when a wait gives up the CTA records an error code in `error_flag`, lets its own
+// TMA copies land, frees its TMEM and returns, so a bad launch cannot hang the device.
+//
+// The reference has no counterpart: its matmuls are TensorFlow/cuBLAS library calls
+// (examples/benchmark/utils/modeling/layers/dense_einsum.py:185-191).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_tcgen05.h"
+
+namespace adb200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr long long kWaitLimitCycles = 6000000000LL;   // ~3 s at 1.9 GHz
+
+template <int BN> struct Cfg {
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;              // double-buffered fp32 accumulator
+  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 form, 128-byte swizzle).
+//   K-major : rows of 128 bytes, groups of 8 rows 1024 bytes apart (SBO); LBO unused.
+//   MN-major: chunks of 64 elements along M/N; inside a chunk 8-row groups along K are 1024 bytes apart (SBO),
+//             chunks are BK*128 bytes apart (LBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;    // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;    // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ uint32_t make_idesc(int n, bool a_mn, bool b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;                       // D format: f32
+  d |= 1u << 7;                       // A format: bf16
+  d |= 1u << 10;                      // B format: bf16
+  d |= (a_mn ? 1u : 0u) << 15;        // A major
+  d |= (b_mn ? 1u : 0u) << 16;        // B major
+  d |= (uint32_t)(n >> 3) << 17;      // N / 8
+  d |= (uint32_t)(BM >> 4) << 24;     // M / 16
+  return d;
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;
+  float t = tanhf(k * (x + 0.044715f * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  float t = tanhf(k * (x + 0.044715f * x * x * x));
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k * (1.0f + 3.0f * 0.044715f * x * x);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + C::STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * (A_BYTES + C::B_BYTES));
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* tfull = bars + 2 * C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int per_batch = tiles_m * tiles_n;
+  const long long total = (long long)per_batch * p.batch_lo * p.batch_hi;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
+        const int tn = rem / tiles_m, tm = rem % tiles_m;
+        const int b_lo = b % p.batch_lo, b_hi = b / p.batch_lo;
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], A_BYTES + C::B_BYTES);
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * C::B_BYTES;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_4d(a_dst + j * (BK * 128), &tmA, &full[stage], m0 + 64 * j, k0, b_lo, b_hi);
+          } else {
+            tma_load_4d(a_dst, &tmA, &full[stage], k0, m0, b_lo, b_hi);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_4d(b_dst + j * (BK * 128), &tmB, &full[stage], n0 + 64 * j, k0, b_lo, b_hi);
+          } else {
+            tma_load_4d(b_dst, &tmB, &full[stage], k0, n0, b_lo, b_hi);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (p.error_flag) atomicExch(p.error_flag, 1);
+      }
+      // Let copies that are still in flight land before the CTA goes away (the consumer may have given up).
+      if (*abort_flag) {
+        for (int s = 0; s < C::STAGES; ++s) {
+          const long long t0 = clock64();
+          while (!mbar_try(&full[s], 0) && !mbar_try(&full[s], 1) && clock64() - t0 < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0; int as = 0; uint32_t aphase = 0; bool ok = true;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[as], aphase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_desc(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? make_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                     : make_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+            umma(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);          // frees the smem stage once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[as]);               // accumulator complete -> epilogue
+        if (++as == 2) { as = 0; aphase ^= 1; }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (p.error_flag) atomicExch(p.error_flag, 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 -> TMEM lane quarter warp % 4)
+    const int q = warp & 3;
+    int as = 0; uint32_t aphase = 0; bool ok = true;
+    const bool vec_ok = (p.ldc % 8 == 0);
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
+      const int tn = rem / tiles_m, tm = rem % tiles_m;
+      const int b_lo = b % p.batch_lo, b_hi = b / p.batch_lo;
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const long long coff = (long long)b_hi * p.strideC_hi + (long long)b_lo * p.strideC_lo + (long long)row * p.ldc;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 16; ++c) {
+        float v[16];
+        __syncwarp();                          // tcgen05.ld is warp-collective: reconverge after predicated stores
+        tmem_ld16(t_row + c * 16, v);
+        const int col0 = n0 + c * 16;
+        const int ncols = (row < p.M) ? min(16, p.N - col0) : 0;
+        if (ncols > 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
+        if (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_GELU) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
+        } else if (p.epilogue == EPI_MUL_GELU_GRAD) {
+          const __nv_bfloat16* aux = p.aux + coff + col0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (j < ncols) v[j] *= gelu_tanh_grad(__bfloat162float(aux[j]));
+        }
+        if (p.c_is_fp32) {
+          float* dst = reinterpret_cast<float*>(p.C) + coff + col0;
+          if (p.beta != 0.0f) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < ncols) dst[j] += v[j];
+          } else if (ncols == 16 && (p.ldc % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < ncols) dst[j] = v[j];
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + coff + col0;
+          if (ncols == 16 && vec_ok) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < ncols) dst[j] = __float2bfloat16(v[j]);
+          }
+          if (p.epilogue == EPI_BIAS_GELU) {
+            __nv_bfloat16* dst2 = p.C2 + coff + col0;
+            if (ncols == 16 && vec_ok) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(gelu_tanh(v[2 * j]), gelu_tanh(v[2 * j + 1]));
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(dst2) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(dst2 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) if (j < ncols) dst2[j] = __float2bfloat16(gelu_tanh(v[j]));
+            }
+          }
+        }
+        }  // ncols > 0
+      }
+      __syncwarp();
+      tc_fence_before();
+      mbar_arrive(&tempty[as]);
+      if (++as == 2) { as = 0; aphase ^= 1; }
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      if (p.error_flag) atomicExch(p.error_flag, 3);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch_lo * p.batch_hi;
+  const int grid = (int)(tiles < num_sms ? tiles : num_sms);
+  kern<<<grid, kThreads, C::SMEM, stream>>>(tmA, tmB, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_box_rows_b(int bn, bool b_mn) { return b_mn ? BK : bn; }
+
+cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn, bool a_mn, bool b_mn,
+                        int num_sms, cudaStream_t stream) {
+#define ADB_DISPATCH(BN_)                                                                      \
+  if (bn == BN_) {                                                                             \
+    if (!a_mn && !b_mn) return launch_one<BN_, false, false>(tmA, tmB, p, num_sms, stream);    \
+    if (!a_mn && b_mn) return launch_one<BN_, false, true>(tmA, tmB, p, num_sms, stream);      \
+    if (a_mn && !b_mn) return launch_one<BN_, true, false>(tmA, tmB, p, num_sms, stream);      \
+    return launch_one<BN_, true, true>(tmA, tmB, p, num_sms, stream);                          \
+  }
+  ADB_DISPATCH(256)
+  ADB_DISPATCH(128)
+  ADB_DISPATCH(64)
+#undef ADB_DISPATCH
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace adb200

@@ -1,0 +1,32 @@
+// Host-side interface of the tcgen05 GEMM (see gemm_tcgen05.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace adb200 {
+
+enum GemmEpilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_MUL_GELU_GRAD = 3 };
+
+struct GemmParams {
+  int M, N, K;                 // per batch entry
+  int batch_lo, batch_hi;      // two batch dimensions (1 when unused)
+  void* C;                     // output, bf16 or fp32, row-major with leading dimension ldc (elements)
+  long long ldc, strideC_lo, strideC_hi;
+  int c_is_fp32;
+  __nv_bfloat16* C2;           // EPI_BIAS_GELU: gelu(C) goes here (same strides as C)
+  const float* bias;           // EPI_BIAS*: one value per output column
+  const __nv_bfloat16* aux;    // EPI_MUL_GELU_GRAD: pre-activation, same strides as C
+  int epilogue;
+  float alpha;                 // scale applied to the accumulator first
+  float beta;                  // fp32 output only: 0 = overwrite, otherwise C += result
+  int* error_flag;             // device int, set non-zero when a bounded wait gave up
+};
+
+// `bn` is the N extent of the tile (64, 128 or 256). The tensor maps must be 4-D bf16 maps with 128-byte swizzle:
+//   K-major operand : dims (K, rows, batch_lo, batch_hi), box (64, 128 for A / bn for B, 1, 1)
+//   MN-major operand: dims (rows, K, batch_lo, batch_hi), box (64, 64, 1, 1)
+cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn, bool a_mn,
+                        bool b_mn, int num_sms, cudaStream_t stream);
+
+}  // namespace adb200

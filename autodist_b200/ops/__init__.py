@@ -1,0 +1,38 @@
+"""Python face of the hand-written sm_100a kernels.
+
+``ext()`` returns the compiled extension module. On a machine with a CUDA device
+a missing or stale extension is an error (no silent PyTorch fallback); without a
+device ``ext()`` returns ``None`` and only the host-side logic is usable.
+"""
+import importlib.util
+import os
+import sys
+
+import torch
+
+from autodist_b200.ops import build as _build
+
+_EXT = None
+_TRIED = False
+
+
+def ext(required=None):
+    global _EXT, _TRIED
+    if _EXT is not None:
+        return _EXT
+    if required is None:
+        required = torch.cuda.is_available()
+    if not _TRIED or required:
+        _TRIED = True
+        path = _build.so_path()
+        if not os.path.exists(path) and required:
+            path = _build.build()
+        if os.path.exists(path):
+            spec = importlib.util.spec_from_file_location(_build.NAME, path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            sys.modules[_build.NAME] = mod
+            _EXT = mod
+    if _EXT is None and required:
+        raise RuntimeError("the sm_100a extension is not built: run `python -m autodist_b200.ops.build`")
+    return _EXT

@@ -1,0 +1,267 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 restatements of the same ops."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def E():
+    from autodist_b200 import ops
+    return ops.ext(required=True)
+
+
+@pytest.fixture()
+def err():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _check(out, ref, tol):
+    diff = (out.float() - ref).abs().max().item()
+    bound = tol * max(1.0, ref.abs().max().item())
+    assert diff <= bound, f"max diff {diff} > {bound}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (200, 300, 136), (4096, 1024, 1024), (32, 2, 1024),
+                                   (640, 1000, 1024)])
+def test_gemm_kmajor(E, err, M, N, K):
+    torch.manual_seed(0)
+    a, b = _rand(M, K), _rand(N, K)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    E.gemm(a, b, c, False, False, 0, None, None, None, 1.0, 0.0, err, 0)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(c, a.float() @ b.float().t(), 1e-2)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_widths_fp32_out(E, err, bn):
+    torch.manual_seed(1)
+    M, N, K = 384, 512, 320
+    a, b = _rand(M, K), _rand(N, K)
+    c = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    E.gemm(a, b, c, False, False, 0, None, None, None, 0.5, 0.0, err, bn)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(c, 0.5 * (a.float() @ b.float().t()), 2e-3)
+    c2 = c.clone()
+    E.gemm(a, b, c2, False, False, 0, None, None, None, 0.5, 1.0, err, bn)     # accumulate into fp32
+    torch.cuda.synchronize()
+    _check(c2, 2 * c, 2e-3)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 320, 192), (1024, 4096, 4096)])
+def test_gemm_mn_major(E, err, a_mn, b_mn, M, N, K):
+    """The layouts of the backward GEMMs: dX = dY.W (B is MN-major), dW = dY^T.X (both MN-major)."""
+    torch.manual_seed(2)
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    c = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, 0)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    A = a.float().t() if a_mn else a.float()
+    B = b.float().t() if b_mn else b.float()
+    _check(c, A @ B.t(), 2e-3)
+
+
+def test_gemm_epilogues(E, err):
+    torch.manual_seed(3)
+    M, N, K = 256, 512, 256
+    a, b = _rand(M, K, scale=0.2), _rand(N, K, scale=0.2)
+    bias = torch.randn(N, device="cuda")
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    act = torch.empty_like(pre)
+    E.gemm(a, b, pre, False, False, 2, bias, act, None, 1.0, 0.0, err, 0)
+    ref = a.float() @ b.float().t() + bias
+    _check(pre, ref, 1e-2)
+    _check(act, torch.nn.functional.gelu(pre.float(), approximate="tanh"), 1e-2)
+    # dU = (dG . W) * gelu'(u)
+    dg, w = _rand(M, K, scale=0.2), _rand(K, N, scale=0.2)      # w is [K, N]: MN-major B for the contraction over K
+    du = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    E.gemm(dg, w, du, False, True, 3, None, None, pre, 1.0, 0.0, err, 0)
+    u = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(u, approximate="tanh").backward(dg.float() @ w.float())
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(du, u.grad, 1e-2)
+
+
+def test_gemm_batched_strided_attention_layout(E, err):
+    """Q, K, V are strided views into the fused QKV projection output; the context lands in [B*S, heads*D]."""
+    torch.manual_seed(4)
+    B, S, Hh, D = 2, 128, 4, 64
+    qkv = _rand(B * S, 3 * Hh * D, scale=0.5)
+    v5 = qkv.view(B, S, 3, Hh, D)
+    q, k, v = (v5[:, :, i].permute(0, 2, 1, 3) for i in range(3))       # [B, heads, S, D] views
+    scores = torch.empty(B, Hh, S, S, dtype=torch.bfloat16, device="cuda")
+    E.gemm(q, k, scores, False, False, 0, None, None, None, 1.0, 0.0, err, 128)
+    ref_s = q.float() @ k.float().transpose(-1, -2)
+    _check(scores, ref_s, 1e-2)
+    p = torch.softmax(ref_s / 8, -1).to(torch.bfloat16)
+    ctx = torch.empty(B * S, Hh * D, dtype=torch.bfloat16, device="cuda")
+    ctx_view = ctx.view(B, S, Hh, D).permute(0, 2, 1, 3)
+    E.gemm(p, v, ctx_view, False, True, 0, None, None, None, 1.0, 0.0, err, 64)       # V is [S_k, D]: MN-major B
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(ctx_view, p.float() @ v.float(), 1e-2)
+    # dK = dS^T . Q : both operands MN-major
+    ds = _rand(B, Hh, S, S, scale=0.1)
+    dk = torch.empty(B, Hh, S, D, dtype=torch.bfloat16, device="cuda")
+    E.gemm(ds, q, dk, True, True, 0, None, None, None, 1.0, 0.0, err, 64)
+    torch.cuda.synchronize()
+    _check(dk, ds.float().transpose(-1, -2) @ q.float(), 1e-2)
+
+
+@pytest.mark.parametrize("rows,H,p", [(64, 1024, 0.0), (37, 256, 0.0), (4096, 1024, 0.1)])
+def test_layernorm(E, rows, H, p):
+    torch.manual_seed(5)
+    x, res = _rand(rows, H), _rand(rows, H)
+    gamma, beta = torch.randn(H, device="cuda"), torch.randn(H, device="cuda")
+    z, y = torch.empty_like(x), torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    E.ln_fwd(x, res, gamma, beta, z, y, mean, rstd, 1e-12, p, 1234, None)
+    if p == 0.0:
+        zr = x.float() + res.float()
+        _check(z, zr, 1e-2)
+    else:
+        kept = ((z.float() - res.float()).abs() > 0).float().mean().item()
+        assert abs(kept - (1 - p)) < 0.01
+    zr = z.float().requires_grad_(True)
+    g = gamma.clone().requires_grad_(True)
+    b = beta.clone().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(zr, (H,), g, b, 1e-12)
+    _check(y, yr.detach(), 2e-2)
+    dy = _rand(rows, H)
+    yr.backward(dy.float())
+    dz, dx = torch.empty_like(x), torch.empty_like(x)
+    part = torch.empty(2 * E.ln_bwd_blocks(rows) * H, device="cuda")
+    dg, db = torch.empty(H, device="cuda"), torch.empty(H, device="cuda")
+    E.ln_bwd(dy, z, mean, rstd, gamma, None, dz, dx, part, dg, db, p, 1234, None, False)
+    torch.cuda.synchronize()
+    _check(dz, zr.grad, 2e-2)
+    _check(dg, g.grad, 2e-2)
+    _check(db, b.grad, 2e-2)
+    if p > 0:
+        mask = ((z.float() - res.float()).abs() > 0).float() / (1 - p)
+        _check(dx, dz.float() * mask, 2e-2)
+
+
+@pytest.mark.parametrize("pd", [0.0, 0.1])
+def test_softmax(E, pd):
+    torch.manual_seed(6)
+    B, Hh, S = 3, 4, 128
+    x = _rand(B, Hh, S, S, scale=3)
+    mask = torch.zeros(B, S, device="cuda")
+    mask[:, 100:] = -10000.0
+    p, pdrop = torch.empty_like(x), torch.empty_like(x)
+    E.softmax_fwd(x, mask, p, pdrop, 0.125, pd, 77, None)
+    ref = torch.softmax(x.float() * 0.125 + mask[:, None, None, :], -1)
+    _check(p, ref, 1e-2)
+    dp = _rand(B, Hh, S, S)
+    keep = torch.ones_like(ref)
+    if pd > 0:
+        keep = (pdrop.float() != 0).float() / (1 - pd)
+        keep[p.float() == 0] = 1.0 / (1 - pd)
+        assert abs((pdrop.float() != 0).float().mean().item() / (p.float() != 0).float().mean().item() - (1 - pd)) < 0.02
+    pr = p.float()
+    d = dp.float() * (keep if pd > 0 else 1.0)
+    ref_ds = 0.125 * pr * (d - (d * pr).sum(-1, keepdim=True))
+    E.softmax_bwd(dp, p, 0.125, pd, 77, None)
+    torch.cuda.synchronize()
+    if pd == 0:
+        _check(dp, ref_ds, 2e-2)
+    else:
+        ok = (p.float() != 0)
+        assert ((dp.float() - ref_ds).abs() * ok).max().item() < 5e-2
+
+
+def test_xent(E):
+    torch.manual_seed(7)
+    rows, V, ld = 64, 1003, 1008
+    logits = _rand(rows, ld, scale=2)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    w = (torch.rand(rows, device="cuda") > 0.3).float()
+    xr = logits[:, :V].float().requires_grad_(True)
+    per = torch.nn.functional.cross_entropy(xr, labels, reduction="none")
+    ref = (per * w).sum() / (w.sum() + 1e-5)
+    ref.backward()
+    denom, loss = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    E.xent(logits, labels, w, denom, loss, V, 1.0, True, 1e-5)
+    torch.cuda.synchronize()
+    assert abs(loss.item() - ref.item()) < 2e-2 * abs(ref.item())
+    _check(logits[:, :V], xr.grad, 2e-2)
+    assert logits[:, V:].abs().max().item() == 0
+
+
+def test_embedding_and_row_ops(E):
+    torch.manual_seed(8)
+    V, H, B, S = 500, 256, 4, 32
+    word, pos, typ = _rand(V, H), _rand(64, H), _rand(2, H)
+    ids = torch.randint(0, V, (B * S,), device="cuda")
+    tt = torch.randint(0, 2, (B * S,), device="cuda")
+    z = torch.empty(B * S, H, dtype=torch.bfloat16, device="cuda")
+    E.embed_sum(word, pos, typ, ids, tt, z, S)
+    ref = word.float()[ids] + pos.float()[torch.arange(B * S, device="cuda") % S] + typ.float()[tt]
+    _check(z, ref, 1e-2)
+    dz = _rand(B * S, H)
+    dword = torch.zeros(V, H, device="cuda")
+    E.scatter_add_rows(dword, ids, dz, 1.0)
+    _check(dword, torch.zeros(V, H, device="cuda").index_add_(0, ids, dz.float()), 1e-3)
+    dpos = torch.zeros(S, H, device="cuda")
+    E.strided_rowsum(dz, dpos, S, S, B)
+    _check(dpos, dz.float().view(B, S, H).sum(0), 1e-3)
+    part = torch.empty(E.colsum_parts(B * S) * 2 * H, device="cuda")
+    dtyp = torch.zeros(2, H, device="cuda")
+    E.keyed_colsum(dz, tt, part, dtyp, 2, False)
+    _check(dtyp, torch.zeros(2, H, device="cuda").index_add_(0, tt, dz.float()), 1e-3)
+    dbias = torch.zeros(H, device="cuda")
+    E.keyed_colsum(dz, None, part, dbias, 1, False)
+    _check(dbias, dz.float().sum(0), 1e-3)
+    idx = torch.randperm(B * S, device="cuda")[:20]
+    out = torch.empty(20, H, dtype=torch.bfloat16, device="cuda")
+    E.gather_rows(z, idx, out)
+    assert torch.equal(out, z[idx])
+    base = z.clone()
+    E.scatter_add_rows_bf16(base, idx, out)
+    torch.cuda.synchronize()
+    exp = z.float()
+    exp[idx] += out.float()
+    _check(base, exp, 1e-2)
+
+
+def test_optimizers_match_torch(E):
+    torch.manual_seed(9)
+    n = 10007
+    lr = torch.tensor([1e-2], device="cuda")
+    step = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for name in ("adam", "sgd", "adagrad"):
+        p0 = torch.randn(n, device="cuda")
+        ref_p = p0.clone().requires_grad_(True)
+        opt = {"adam": lambda: torch.optim.Adam([ref_p], lr=1e-2, weight_decay=0.01),
+               "sgd": lambda: torch.optim.SGD([ref_p], lr=1e-2, momentum=0.9, weight_decay=0.01),
+               "adagrad": lambda: torch.optim.Adagrad([ref_p], lr=1e-2, eps=1e-10)}[name]()
+        p, s1, s2 = p0.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        p16 = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        step.zero_()
+        for _ in range(3):
+            g = torch.randn(n, device="cuda")
+            ref_p.grad = g.clone()
+            opt.step()
+            E.increment(step)
+            if name == "adam":
+                E.adam_update(p, g, s1, s2, p16, lr, 0.9, 0.999, 1e-8, 0.01, False, step, 1.0)
+            elif name == "sgd":
+                E.sgd_update(p, g, s1, p16, lr, 0.9, 0.0, 0.01, False, step, 1.0)
+            else:
+                E.adagrad_update(p, g, s1, p16, lr, 1e-10, 0.0, 1.0)
+        torch.cuda.synchronize()
+        assert (p - ref_p.detach()).abs().max().item() < 1e-5, name
+        assert (p16.float() - p).abs().max().item() < 2e-2
