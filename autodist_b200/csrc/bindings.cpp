@@ -104,7 +104,7 @@ void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, i
   p.alpha = (float)alpha;
   p.beta = (float)beta;
   p.bias = nullptr; p.C2 = nullptr; p.aux = nullptr;
-  if (epilogue == adb200::EPI_BIAS || epilogue == adb200::EPI_BIAS_GELU) {
+  if (epilogue == adb200::EPI_BIAS || epilogue == adb200::EPI_BIAS_GELU || epilogue == adb200::EPI_BIAS_TANH) {
     TORCH_CHECK(bias.has_value() && bias->scalar_type() == at::kFloat && bias->numel() >= N, "fp32 bias of N entries needed");
     p.bias = bias->data_ptr<float>();
   }
@@ -114,8 +114,8 @@ void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, i
     TORCH_CHECK(c2v.strides() == c.strides(), "second output must share the strides of the first");
     p.C2 = reinterpret_cast<__nv_bfloat16*>(c2v.data_ptr());
   }
-  if (epilogue == adb200::EPI_MUL_GELU_GRAD) {
-    TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16, "bf16 pre-activation needed");
+  if (epilogue == adb200::EPI_MUL_GELU_GRAD || epilogue == adb200::EPI_ADD) {
+    TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16 && !p.c_is_fp32, "bf16 auxiliary operand and bf16 output needed");
     Tensor av = as4d(*aux);
     TORCH_CHECK(av.strides() == c.strides(), "pre-activation must share the strides of the output");
     p.aux = reinterpret_cast<const __nv_bfloat16*>(av.data_ptr());
@@ -194,6 +194,7 @@ void xent(Tensor logits, const Tensor& labels, const optional<Tensor>& weights, 
   adb200::xent(BF(logits), labels.data_ptr<int64_t>(), OPT_F(weights), denom.data_ptr<float>(), loss_sum.data_ptr<float>(), rows, (int)V, ld,
                (float)loss_scale, STREAM);
 }
+void gelu_bwd(const Tensor& dy, const Tensor& u, Tensor dx) { adb200::gelu_bwd(CBF(dy), CBF(u), BF(dx), u.numel(), STREAM); }
 void tanh_bwd(const Tensor& dy, const Tensor& y, Tensor dx) { adb200::tanh_bwd(CBF(dy), CBF(y), BF(dx), y.numel(), STREAM); }
 void add_bf16(const Tensor& a, const Tensor& b, Tensor out) {
   TORCH_CHECK(a.numel() % 8 == 0, "length must be a multiple of 8");
@@ -312,6 +313,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("softmax_bwd", &softmax_bwd);
   m.def("xent", &xent);
   m.def("tanh_bwd", &tanh_bwd);
+  m.def("gelu_bwd", &gelu_bwd);
   m.def("add_bf16", &add_bf16);
   m.def("adam_update", &adam_update);
   m.def("sgd_update", &sgd_update);

@@ -461,6 +461,16 @@ __global__ void tanh_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restr
   if (i < n) { float t = __bfloat162float(y[i]); dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * (1.0f - t * t)); }
 }
 
+__global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ u, bf16* __restrict__ dx, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float x = __bfloat162float(u[i]);
+  const float k = 0.7978845608028654f;
+  const float t = tanhf(k * (x + 0.044715f * x * x * x));
+  const float d = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k * (1.0f + 3.0f * 0.044715f * x * x);
+  dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * d);
+}
+
 __global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n8) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
@@ -606,6 +616,9 @@ void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st) {
 void xent(bf16* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,
           float loss_scale, cudaStream_t st) {
   xent_kernel<<<rows, V >= 4096 ? 1024 : 128, 0, st>>>(logits, labels, weights, denom, loss_sum, V, ld, loss_scale);
+}
+void gelu_bwd(const bf16* dy, const bf16* u, bf16* dx, long long n, cudaStream_t st) {
+  gelu_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, u, dx, n);
 }
 void tanh_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
   tanh_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, y, dx, n);

@@ -27,6 +27,7 @@ void softmax_bwd(bf16_t* dp, const bf16_t* p, long long rows, int S, float scale
 void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st);
 void xent(bf16_t* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,
           float loss_scale, cudaStream_t st);
+void gelu_bwd(const bf16_t* dy, const bf16_t* u, bf16_t* dx, long long n, cudaStream_t st);
 void tanh_bwd(const bf16_t* dy, const bf16_t* y, bf16_t* dx, long long n, cudaStream_t st);
 void add_bf16(const bf16_t* a, const bf16_t* b, bf16_t* out, long long n, cudaStream_t st);
 void adam_update(float* p, const float* g, float* m, float* v, bf16_t* p16, long long n, const float* lr, float b1, float b2,

