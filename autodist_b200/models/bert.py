@@ -88,7 +88,7 @@ class BertPretrainer(nn.Module):
             return nn.Parameter(torch.ones(*shape))
 
         P = nn.ParameterDict
-        self.emb = P({"word": w(c.vocab_size, H), "pos": w(c.max_position_embeddings, H), "type": w(c.type_vocab_size, H),
+        self.emb = P({"word": w(c.vocab_size, H), "pos": w(c.max_position_embeddings, H), "tok_type": w(c.type_vocab_size, H),
                       "ln_g": ones(H), "ln_b": zeros(H)})
         self.layers = nn.ModuleList([
             P({"qkv_w": w(3 * H, H), "qkv_b": zeros(3 * H), "out_w": w(H, H), "out_b": zeros(H),
@@ -118,7 +118,7 @@ class BertPretrainer(nn.Module):
         H, nh = c.hidden_size, c.num_attention_heads
         D = H // nh
         e = self.emb
-        x = e["word"][input_ids] + e["pos"][:S][None] + e["type"][segment_ids]
+        x = e["word"][input_ids] + e["pos"][:S][None] + e["tok_type"][segment_ids]
         x = F.layer_norm(x, (H,), e["ln_g"], e["ln_b"], c.layer_norm_eps)
         add_mask = (1.0 - input_mask.to(x.dtype))[:, None, None, :] * -10000.0
         pd_h = c.hidden_dropout_prob if dropout else 0.0
@@ -241,7 +241,7 @@ class BertPretrainer(nn.Module):
             return t.view(B, S, nh, D).permute(0, 2, 1, 3)
 
         # ------------------------------ forward
-        E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.type"], ids, tts, ws["z0"], S)
+        E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S)
         E.ln_fwd(ws["z0"], None, w32["emb.ln_g"], w32["emb.ln_b"], None, ws["x0"], ws["m0"], ws["r0"], eps, 0.0, 0, None)
         x = ws["x0"]
         for l, A in enumerate(ws["layers"]):
@@ -363,7 +363,7 @@ class BertPretrainer(nn.Module):
             E.scatter_add_rows(g["emb.word"], ids, dz0, 1.0)
         g["emb.pos"].zero_()
         E.strided_rowsum(dz0, g["emb.pos"], S, S, B)
-        E.keyed_colsum(dz0, tts, ws["part"], g["emb.type"], c.type_vocab_size, False)
+        E.keyed_colsum(dz0, tts, ws["part"], g["emb.tok_type"], c.type_vocab_size, False)
         ready(0, fl.offsets["layers.0.qkv_w"])
         return ws["loss"]
 

@@ -14,6 +14,32 @@ from autodist_b200.ops import build as _build
 
 _EXT = None
 _TRIED = False
+launch_count = 0      # kernels launched through the extension by this process (a graph replay re-launches its capture)
+
+
+class _Counting:
+    """Thin proxy over the extension module that counts kernel-launching calls."""
+    _NO_LAUNCH = {"ln_bwd_blocks", "colsum_parts", "MAX_COMM_BLOCKS"}
+    _MULTI = {"ln_bwd": 3, "keyed_colsum": 2}
+
+    def __init__(self, mod):
+        self._mod = mod
+        for name in dir(mod):
+            if name.startswith("_"):
+                continue
+            attr = getattr(mod, name)
+            if callable(attr) and name not in self._NO_LAUNCH:
+                setattr(self, name, self._wrap(attr, self._MULTI.get(name, 1)))
+            else:
+                setattr(self, name, attr)
+
+    @staticmethod
+    def _wrap(fn, n):
+        def call(*args):
+            global launch_count
+            launch_count += n
+            return fn(*args)
+        return call
 
 
 def ext(required=None):
@@ -32,7 +58,7 @@ def ext(required=None):
             mod = importlib.util.module_from_spec(spec)
             spec.loader.exec_module(mod)
             sys.modules[_build.NAME] = mod
-            _EXT = mod
+            _EXT = _Counting(mod)
     if _EXT is None and required:
         raise RuntimeError("the sm_100a extension is not built: run `python -m autodist_b200.ops.build`")
     return _EXT

@@ -186,6 +186,7 @@ class FusedStepEngine(StepEngine):
         self._use_graph = os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0"
         self._warm_steps = 0
         self.launches_per_step = 0
+        self.graph_kernels = 0
         module.grad_ready = self._on_grad_ready
         if self.world_size > 1:
             torch.cuda.synchronize()
@@ -339,8 +340,11 @@ class FusedStepEngine(StepEngine):
             if self.world_size > 1:
                 dist.barrier(group=self.backend.group)
             graph = torch.cuda.CUDAGraph()
+            from autodist_b200 import ops
+            before = ops.launch_count
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 out = self._run_model(train_op, nodes, static)
+            self.graph_kernels = ops.launch_count - before   # kernels of this extension per replay
             self._graph = (key, graph, static, out)
             torch.cuda.synchronize()
             if self.world_size > 1:

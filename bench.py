@@ -1,0 +1,216 @@
+"""Headline benchmark: BERT-large pre-training throughput (sequences/s), seq 128, batch 32 per GPU.
+
+``python bench.py --gpus N --steps K --warmup W`` (N > 1: launched by ``torch.distributed.run``, one rank
+per GPU). Runs the training step through the framework's public API (``AutoDist`` -> ``scope`` ->
+``create_distributed_session`` -> ``sess.run``) on synthetic data with random-initialised weights and prints
+ONE JSON line on rank 0. ``value`` is device-timed with inputs resident on the device; ``e2e`` repeats the
+measurement with every step's inputs copied from pinned host memory and the loss read back to the host.
+``--impl reference`` reports why the reference itself cannot run here.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# per-GPU examples/s of the reference's "AutoDist AllReduce" BERT-large bars (T4, read off docs/usage/figure1.png)
+PUBLISHED_PER_GPU = {1: 11.1, 2: 8.0, 4: 7.8, 8: 3.2}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, power and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self._stop_evt = index, [], threading.Event()
+        self.proc = None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            for line in self.proc.stdout:
+                self.samples.append([x.strip() for x in line.split(",")])
+                if self._stop_evt.is_set():
+                    break
+        except (OSError, ValueError):
+            pass
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.proc is not None:
+            self.proc.terminate()     # the exact process this thread started
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[1]))
+                mx.append(float(s[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "petuum/autodist needs TensorFlow 1.15-2.2 (CUDA 10, no sm_100 code) and protoc at install time; "
+                       "neither is present offline: pip install of /root/reference fails in setup.py generate_proto"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="bert-large", choices=["bert-large", "bert-base", "bert-tiny"])
+    ap.add_argument("--strategy", default="allreduce", choices=["allreduce", "allreduce_ef", "parallax", "ps", "partitioned_ps"])
+    ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
+    ap.add_argument("--seq", type=int, default=128)
+    ap.add_argument("--comm", default=None, help="fused (own kernels) or nccl (baseline)")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.comm:
+        os.environ["AUTODIST_COMM"] = args.comm
+    if args.no_graph:
+        os.environ["AUTODIST_CUDA_GRAPH"] = "0"
+    os.environ.setdefault("AUTODIST_MIN_LOG_LEVEL", "WARNING")
+    os.environ.setdefault("AUTODIST_FETCH_MODE", "local")
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from autodist_b200 import AutoDist, ops
+    from autodist_b200.models.bert import BertConfig, BertPretrainer, synthetic_batch
+    from autodist_b200.resource_spec import ResourceSpec
+    from autodist_b200 import strategy as S
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    n_gpus = args.gpus
+    if world != n_gpus and world > 1:
+        n_gpus = world
+    builders = {
+        "allreduce": lambda: S.AllReduce(chunk_size=256),
+        "allreduce_ef": lambda: S.AllReduce(chunk_size=256, compressor="HorovodCompressorEF"),
+        "parallax": lambda: S.Parallax(chunk_size=256, reduction_devices="gpu"),
+        "ps": lambda: S.PSLoadBalancing(reduction_devices="gpu", local_proxy_variable=True),
+        "partitioned_ps": lambda: S.PartitionedPS(num_shards=n_gpus, reduction_devices="gpu", local_proxy_variable=True),
+    }
+    cfg = {"bert-large": BertConfig.large, "bert-base": BertConfig.base, "bert-tiny": BertConfig.tiny}[args.model]()
+    max_pred = 20
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=n_gpus), strategy_builder=builders[args.strategy]())
+    host_batches = [synthetic_batch(cfg, args.batch, args.seq, max_pred, seed=1000 * rank + i, pin=True) for i in range(4)]
+    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    with ad.scope():
+        torch.manual_seed(0)
+        model = BertPretrainer(cfg)
+        phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in host_batches[0].items()}
+        loss = model(**phs)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-4)
+        train_op = opt.minimize(loss)
+        sess = ad.create_distributed_session()
+        dev = sess.engine.device
+        dev_batches = [{k: v.to(dev) for k, v in b.items()} for b in host_batches]
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def feed(batches, i):
+            b = batches[i % len(batches)]
+            return {phs[k]: b[k] for k in phs}
+
+        # ---- warm-up (also builds workspaces and captures the CUDA graph)
+        for i in range(args.warmup + 3):
+            sess.run(train_op, feed(dev_batches, i))
+        sess.engine.check_errors() if hasattr(sess.engine, "check_errors") else None
+
+        sampler = ClockSampler(dev.index or 0) if rank == 0 else None
+        if sampler:
+            sampler.start()
+            time.sleep(0.3)
+        # ---- device-timed region: K steps, inputs resident on the device
+        launches0 = ops.launch_count
+        per_step_launches = getattr(sess.engine, "launches_per_step", 0)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            sess.run(train_op, feed(dev_batches, i))
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        eager_launches = ops.launch_count - launches0
+        # ---- end-to-end region: pinned host inputs copied every step, loss read back every step
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        last = None
+        for i in range(args.steps):
+            last, _ = sess.run([loss, train_op], feed(host_batches, i))
+        f1.record()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+        if sampler:
+            sampler.stop()
+        if hasattr(sess.engine, "check_errors"):
+            sess.engine.check_errors()
+
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+
+    if rank != 0:
+        return 0
+    global_batch = args.batch * n_gpus
+    value = global_batch * args.steps / (ms / 1e3)
+    e2e = global_batch * args.steps / (ms_e2e / 1e3)
+    graph_launches = getattr(sess.engine, "graph_kernels", 0)
+    launches = eager_launches if eager_launches > 0 else graph_launches * args.steps
+    published = PUBLISHED_PER_GPU.get(n_gpus)
+    out = {
+        "metric": "BERT-large pre-training sequences/sec (seq 128), max over ranks",
+        "value": round(value, 2), "unit": "sequences/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / (published * n_gpus), 2) if published and args.model == "bert-large" else None,
+        "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM positions, random-init weights)",
+        "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq, "max_predictions": max_pred,
+                   "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute",
+                   "comm": os.environ.get("AUTODIST_COMM", "fused"),
+                   "cuda_graph": os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0",
+                   "l2": "per-step working set (activations + weights > 4 GB) is far larger than the 126 MB L2",
+                   "engine": type(sess.engine).__name__},
+        "clocks": sampler.summary() if sampler else None,
+        "e2e": {"value": round(e2e, 2), "unit": "sequences/s", "ms_per_step": round(ms_e2e / args.steps, 3),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": float(last)},
+        "gpu_launches": int(launches),
+        "impl": "ours",
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
