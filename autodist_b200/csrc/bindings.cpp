@@ -175,7 +175,7 @@ void scatter_add_rows_bf16(Tensor dst, const Tensor& idx, const Tensor& src) {
 void softmax_fwd(const Tensor& x, const optional<Tensor>& mask, Tensor p, const optional<Tensor>& p_drop, double scale, double pd,
                  int64_t seed, const optional<Tensor>& step) {
   const int S = x.size(-1);
-  TORCH_CHECK(S % 8 == 0 && S <= 1024 && x.dim() == 4, "scores must be [B, heads, S, S] with S a multiple of 8 up to 1024");
+  TORCH_CHECK(adb200::softmax_supported(S) && x.dim() == 4, "scores must be [B, heads, S, S] with S in {64, 128, 256, 512, 1024}");
   const long long rows = x.numel() / S;
   adb200::softmax_fwd(CBF(x), OPT_F(mask), BF(p), OPT_BF(p_drop), rows, S, (int)(x.size(1) * x.size(2)), (float)scale, (float)pd,
                       (uint64_t)seed, OPT_LL(step), STREAM);

@@ -204,13 +204,21 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
   }
 }
 
-// out[c] (+)= sum over `parts` rows of part[r][c]
+// out[c] (+)= sum over `parts` rows of part[r][c]. A block covers 32 columns; its 8 warps split the partial rows.
 __global__ void colsum_f32_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int H, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
   float a = 0.f;
-  for (int r = 0; r < parts; ++r) a += part[(long long)r * H + c];
-  out[c] = accumulate ? out[c] + a : a;
+  if (c < H)
+    for (int r = w; r < parts; r += 8) a += part[(long long)r * H + c];
+  sm[w][threadIdx.x & 31] = a;
+  __syncthreads();
+  if (w == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ embeddings
@@ -264,25 +272,35 @@ __global__ void strided_rowsum_kernel(const bf16* __restrict__ x, float* __restr
   for (int i = 0; i < 8; ++i) out[(long long)k * H + c + i] = a[i];
 }
 
-// part[b][k][c] = sum over this block's rows with key[row]==k of x[row][c]   (keys small: token-type gradient)
-// With key == nullptr every row has key 0: plain column sums (bias gradients).
+// part[y][k][c] = sum over row chunk y of the rows with key[row]==k of x[row][c]   (keys small: token-type gradient).
+// With key == nullptr every row has key 0: plain column sums (bias gradients). A block covers 64 columns (8 vectors)
+// with 32 row lanes per vector; the lanes' sums meet in shared memory.
 __global__ void keyed_colsum_kernel(const bf16* __restrict__ x, const int64_t* __restrict__ key, float* __restrict__ part,
                                     int rows, int H, int keys, int rows_per_block) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c >= H) return;
+  __shared__ float sm[32][65];
+  const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + vec * 8;
   const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
   for (int k = 0; k < keys; ++k) {
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = r0; r < r1; ++r) {
-      if (key && key[r] != k) continue;
-      float v[8];
-      load8(x + (long long)r * H + c, v);
+    if (c < H)
+      for (int r = r0 + rl; r < r1; r += 32) {
+        if (key && key[r] != k) continue;
+        float v[8];
+        load8(x + (long long)r * H + c, v);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] += v[i];
+        for (int i = 0; i < 8; ++i) a[i] += v[i];
+      }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm[rl][vec * 8 + i] = a[i];
+    __syncthreads();
+    if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < H) {
+      float t = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) t += sm[i][threadIdx.x];
+      part[((long long)blockIdx.y * keys + k) * H + blockIdx.x * 64 + threadIdx.x] = t;
     }
-    float* o = part + ((long long)blockIdx.y * keys + k) * H + c;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = a[i];
+    __syncthreads();
   }
 }
 
@@ -313,92 +331,100 @@ __global__ void scatter_add_rows_bf16_kernel(bf16* __restrict__ dst, const int64
 // ------------------------------------------------------------------------------------------------ softmax
 // Rows of length S (<= 1024, multiple of 8) of a [B, heads, S, S] tensor; one warp per row. p = softmax(scale*x + mask[b]);
 // writes p (needed by the backward pass) and, when dropout is on, p_drop = dropout(p) for the P.V product.
+template <int TPR> __device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = TPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <int TPR> __device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+  for (int o = TPR / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// TPR threads per row, VPT 8-element vectors per thread: S = 8 * TPR * VPT. (S = 128 -> 16 threads, two rows per warp.)
+template <int TPR, int VPT>
 __global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ mask, bf16* __restrict__ p,
                                    bf16* __restrict__ p_drop, long long rows, int S, int rows_per_batch, float scale,
                                    float pd, uint64_t seed, const long long* step) {
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= rows) return;
-  const int b = (int)(warp / rows_per_batch);
-  const int nvec = S / 8;
-  float v[MAXV][8];
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / TPR;
+  const int t = (int)(gt % TPR);
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
+  const int b = (int)(rr / rows_per_batch);
+  float v[VPT][8];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-      load8(x + warp * S + vec * 8, v[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        v[i][j] = v[i][j] * scale + (mask ? mask[(long long)b * S + vec * 8 + j] : 0.f);
-        mx = fmaxf(mx, v[i][j]);
-      }
+  for (int i = 0; i < VPT; ++i) {
+    const int col = (t + TPR * i) * 8;
+    load8(x + rr * S + col, v[i]);
+    float mk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (mask) {
+      const float4 m0 = *reinterpret_cast<const float4*>(mask + (long long)b * S + col);
+      const float4 m1 = *reinterpret_cast<const float4*>(mask + (long long)b * S + col + 4);
+      mk[0] = m0.x; mk[1] = m0.y; mk[2] = m0.z; mk[3] = m0.w; mk[4] = m1.x; mk[5] = m1.y; mk[6] = m1.z; mk[7] = m1.w;
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[i][j] = v[i][j] * scale + mk[j]; mx = fmaxf(mx, v[i][j]); }
   }
-  mx = warp_max(mx);
+  mx = group_max<TPR>(mx);
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i)
-    if (lane + 32 * i < nvec) {
+  for (int i = 0; i < VPT; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { v[i][j] = __expf(v[i][j] - mx); s += v[i][j]; }
-    }
-  const float inv = 1.0f / warp_sum(s);
+    for (int j = 0; j < 8; ++j) { v[i][j] = __expf(v[i][j] - mx); s += v[i][j]; }
+  const float inv = 1.0f / group_sum<TPR>(s);
+  if (!live) return;
   const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
   const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-      const long long off = warp * S + vec * 8;
+  for (int i = 0; i < VPT; ++i) {
+    const long long off = row * S + (t + TPR * i) * 8;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] *= inv;
-      store8(p + off, v[i]);
-      if (pd > 0.f && p_drop) {
+    for (int j = 0; j < 8; ++j) v[i][j] *= inv;
+    store8(p + off, v[i]);
+    if (pd > 0.f && p_drop) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
-        store8(p_drop + off, v[i]);
-      }
+      for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+      store8(p_drop + off, v[i]);
     }
   }
 }
 
 // ds = scale * p * (dp' - sum(dp' * p)) with dp' = dp * dropout mask; written over dp.
+template <int TPR, int VPT>
 __global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict__ p, long long rows, int S, float scale,
                                    float pd, uint64_t seed, const long long* step) {
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= rows) return;
-  const int nvec = S / 8;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / TPR;
+  const int t = (int)(gt % TPR);
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
   const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
   const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
-  float d[MAXV][8], pr[MAXV][8];
+  float d[VPT][8], pr[VPT][8];
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-      const long long off = warp * S + vec * 8;
-      load8(dp + off, d[i]);
-      load8(p + off, pr[i]);
+  for (int i = 0; i < VPT; ++i) {
+    const long long off = rr * S + (t + TPR * i) * 8;
+    load8(dp + off, d[i]);
+    load8(p + off, pr[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (pd > 0.f) d[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
-        s += d[i][j] * pr[i][j];
-      }
+    for (int j = 0; j < 8; ++j) {
+      if (pd > 0.f) d[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+      s += d[i][j] * pr[i][j];
     }
   }
-  s = warp_sum(s);
+  s = group_sum<TPR>(s);
+  if (!live) return;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
+  for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) d[i][j] = scale * pr[i][j] * (d[i][j] - s);
-      store8(dp + warp * S + vec * 8, d[i]);
-    }
+    for (int j = 0; j < 8; ++j) d[i][j] = scale * pr[i][j] * (d[i][j] - s);
+    store8(dp + row * S + (t + TPR * i) * 8, d[i]);
   }
 }
 
@@ -576,8 +602,8 @@ void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd,
   const int blocks = ln_bwd_blocks(rows);
   ln_bwd_kernel<<<blocks, 128, 2 * 4 * H * sizeof(float), st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part_g, part_b, rows, H,
                                                                 p_drop, seed, step);
-  colsum_f32_kernel<<<blocks_for(H, 256), 256, 0, st>>>(part_g, dgamma, blocks, H, accumulate);
-  colsum_f32_kernel<<<blocks_for(H, 256), 256, 0, st>>>(part_b, dbeta, blocks, H, accumulate);
+  colsum_f32_kernel<<<blocks_for(H, 32), 256, 0, st>>>(part_g, dgamma, blocks, H, accumulate);
+  colsum_f32_kernel<<<blocks_for(H, 32), 256, 0, st>>>(part_b, dbeta, blocks, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
                int H, cudaStream_t st) {
@@ -590,13 +616,13 @@ void strided_rowsum(const bf16* x, float* out, int keys, int stride, int count, 
   dim3 grid(blocks_for(H / 8, 128), keys);
   strided_rowsum_kernel<<<grid, 128, 0, st>>>(x, out, keys, stride, count, H);
 }
-int colsum_parts(int rows) { return rows >= 2048 ? 64 : (rows >= 256 ? 16 : 1); }
+int colsum_parts(int rows) { return rows >= 2048 ? 16 : (rows >= 256 ? 4 : 1); }
 void keyed_colsum(const bf16* x, const int64_t* key, float* part, float* out, int rows, int H, int keys, int accumulate, cudaStream_t st) {
   const int parts = colsum_parts(rows);
   const int rpb = (rows + parts - 1) / parts;
-  dim3 grid(blocks_for(H / 8, 128), parts);
-  keyed_colsum_kernel<<<grid, 128, 0, st>>>(x, key, part, rows, H, keys, rpb);
-  colsum_f32_kernel<<<blocks_for(keys * H, 256), 256, 0, st>>>(part, out, parts, keys * H, accumulate);
+  dim3 grid(blocks_for(H, 64), parts);
+  keyed_colsum_kernel<<<grid, 256, 0, st>>>(x, key, part, rows, H, keys, rpb);
+  colsum_f32_kernel<<<blocks_for(keys * H, 32), 256, 0, st>>>(part, out, parts, keys * H, accumulate);
 }
 void gather_rows(const bf16* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
   gather_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
@@ -604,13 +630,23 @@ void gather_rows(const bf16* src, const int64_t* idx, bf16* out, int rows, int H
 void scatter_add_rows_bf16(bf16* dst, const int64_t* idx, const bf16* src, int rows, int H, cudaStream_t st) {
   scatter_add_rows_bf16_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H);
 }
+#define ADB_SOFTMAX_DISPATCH(KERNEL, ...)                                                              \
+  do {                                                                                                 \
+    const int threads = S / 8;                                                                         \
+    if (threads == 8) KERNEL<8, 1><<<blocks_for(rows * 8, 256), 256, 0, st>>>(__VA_ARGS__);            \
+    else if (threads == 16) KERNEL<16, 1><<<blocks_for(rows * 16, 256), 256, 0, st>>>(__VA_ARGS__);    \
+    else if (threads == 32) KERNEL<32, 1><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);    \
+    else if (threads == 64) KERNEL<32, 2><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);    \
+    else if (threads == 128) KERNEL<32, 4><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);   \
+  } while (0)
+bool softmax_supported(int S) { return S == 64 || S == 128 || S == 256 || S == 512 || S == 1024; }
 void softmax_fwd(const bf16* x, const float* mask, bf16* p, bf16* p_drop, long long rows, int S, int rows_per_batch, float scale,
                  float pd, uint64_t seed, const long long* step, cudaStream_t st) {
-  softmax_fwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(x, mask, p, p_drop, rows, S, rows_per_batch, scale, pd, seed, step);
+  ADB_SOFTMAX_DISPATCH(softmax_fwd_kernel, x, mask, p, p_drop, rows, S, rows_per_batch, scale, pd, seed, step);
 }
 void softmax_bwd(bf16* dp, const bf16* p, long long rows, int S, float scale, float pd, uint64_t seed, const long long* step,
                  cudaStream_t st) {
-  softmax_bwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dp, p, rows, S, scale, pd, seed, step);
+  ADB_SOFTMAX_DISPATCH(softmax_bwd_kernel, dp, p, rows, S, scale, pd, seed, step);
 }
 void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st) { weight_sum_kernel<<<1, 256, 0, st>>>(w, n, out, eps); }
 void xent(bf16* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,

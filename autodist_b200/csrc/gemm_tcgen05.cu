@@ -290,14 +290,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = tanhf(v[j]);
           }
-        } else if (p.epilogue == EPI_ADD) {
+        } else if (p.epilogue == EPI_ADD || p.epilogue == EPI_MUL_GELU_GRAD) {
           const __nv_bfloat16* aux = p.aux + coff + col0;
+          float x[16];
+          if (ncols == 16 && vec_ok) {
+            const uint4 u0 = *reinterpret_cast<const uint4*>(aux), u1 = *reinterpret_cast<const uint4*>(aux + 8);
+            const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
+            const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) if (j < ncols) v[j] += __bfloat162float(aux[j]);
-        } else if (p.epilogue == EPI_MUL_GELU_GRAD) {
-          const __nv_bfloat16* aux = p.aux + coff + col0;
+            for (int j = 0; j < 4; ++j) {
+              const float2 f0 = __bfloat1622float2(h0[j]), f1 = __bfloat1622float2(h1[j]);
+              x[2 * j] = f0.x; x[2 * j + 1] = f0.y; x[8 + 2 * j] = f1.x; x[8 + 2 * j + 1] = f1.y;
+            }
+          } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) if (j < ncols) v[j] *= gelu_tanh_grad(__bfloat162float(aux[j]));
+            for (int j = 0; j < 16; ++j) x[j] = (j < ncols) ? __bfloat162float(aux[j]) : 0.f;
+          }
+          if (p.epilogue == EPI_ADD) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += x[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= gelu_tanh_grad(x[j]);
+          }
         }
         if (p.c_is_fp32) {
           float* dst = reinterpret_cast<float*>(p.C) + coff + col0;

@@ -1,0 +1,100 @@
+"""Micro-benchmarks of the hand-written kernels against the measured peaks.
+
+``python -m autodist_b200.ops.bench_ops [--json out.json]`` times the tcgen05 GEMM at the shapes of the BERT-large
+step (forward, dX and dW layouts) with CUDA events (warm-up, L2 flushed between iterations by streaming a 256 MB
+buffer) and reports TFLOP/s next to ``torch.matmul`` (cuBLAS) at the same shape, plus the bandwidth-bound kernels
+in GB/s.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+
+def _time(fn, iters=10, flush=None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default="")
+    ap.add_argument("--small", action="store_true")
+    args = ap.parse_args()
+    from autodist_b200 import ops
+    E = ops.ext(required=True)
+    dev = "cuda"
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peaks = {}
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peaks = json.load(open(path))
+    rows = []
+    T = 4096
+    shapes = [("qkv fwd", T, 3072, 1024, False, False), ("ffn1 fwd", T, 4096, 1024, False, False),
+              ("ffn2 fwd", T, 1024, 4096, False, False), ("out fwd", T, 1024, 1024, False, False),
+              ("ffn1 dX", T, 1024, 4096, False, True), ("ffn2 dX", T, 4096, 1024, False, True),
+              ("ffn1 dW", 4096, 1024, T, True, True), ("ffn2 dW", 1024, 4096, T, True, True),
+              ("square 8192", 8192, 8192, 8192, False, False)]
+    if args.small:
+        shapes = shapes[:2]
+    for name, M, N, K, a_mn, b_mn in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device=dev).to(torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        for bn in (256, 128):
+            ms = _time(lambda: E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, bn), flush=flush)
+            A = a.t() if a_mn else a
+            B = b if b_mn else b.t()
+            ms_lib = _time(lambda: torch.matmul(A, B, out=c), flush=flush)
+            fl = 2.0 * M * N * K
+            rows.append({"kernel": f"gemm {name} {M}x{N}x{K} bn{bn}", "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                         "cublas_ms": round(ms_lib, 4), "cublas_tflops": round(fl / ms_lib / 1e9, 1),
+                         "frac_of_measured_peak": round(fl / ms / 1e9 / peaks.get("bf16_tflops", 1656.4), 3)})
+    # bandwidth-bound kernels
+    H = 1024
+    x = torch.randn(T * 8, H, device=dev).to(torch.bfloat16)
+    res = torch.randn_like(x.float()).to(torch.bfloat16)
+    g, bta = torch.ones(H, device=dev), torch.zeros(H, device=dev)
+    z, y = torch.empty_like(x), torch.empty_like(x)
+    mean, rstd = torch.empty(T * 8, device=dev), torch.empty(T * 8, device=dev)
+    ms = _time(lambda: E.ln_fwd(x, res, g, bta, z, y, mean, rstd, 1e-12, 0.1, 1, None), flush=flush)
+    rows.append({"kernel": "ln_fwd 32768x1024 (+res+dropout)", "ms": round(ms, 4), "gbs": round(4 * x.numel() * 2 / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(4 * x.numel() * 2 / ms / 1e6 / peaks.get("hbm_gbs", 6518.6), 3)})
+    part = torch.empty(2 * E.ln_bwd_blocks(T * 8) * H, device=dev)
+    dg, db = torch.empty(H, device=dev), torch.empty(H, device=dev)
+    ms = _time(lambda: E.ln_bwd(y, z, mean, rstd, g, None, x, res, part, dg, db, 0.1, 1, None, False), flush=flush)
+    rows.append({"kernel": "ln_bwd 32768x1024 (+dropout)", "ms": round(ms, 4), "gbs": round(4 * x.numel() * 2 / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(4 * x.numel() * 2 / ms / 1e6 / peaks.get("hbm_gbs", 6518.6), 3)})
+    n = 128 << 20
+    p, gr, m, v = (torch.zeros(n, device=dev) for _ in range(4))
+    p16 = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    lr = torch.tensor([1e-3], device=dev)
+    st = torch.ones(1, dtype=torch.int64, device=dev)
+    ms = _time(lambda: E.adam_update(p, gr, m, v, p16, lr, 0.9, 0.999, 1e-8, 0.0, False, st, 1.0))
+    rows.append({"kernel": "adam 128M params", "ms": round(ms, 4), "gbs": round(n * 30 / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(n * 30 / ms / 1e6 / peaks.get("hbm_gbs", 6518.6), 3)})
+    for r in rows:
+        print(json.dumps(r))
+    assert err.item() == 0
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump(rows, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
