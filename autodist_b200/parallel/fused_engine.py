@@ -141,8 +141,6 @@ class FusedStepEngine(StepEngine):
                     return False
                 if any(p.part_index is not None for p in b.parts):
                     return False
-            if plan.sparse_all_reduce:
-                return False
             if plan.ps_entries:
                 return False
         return True
@@ -241,14 +239,23 @@ class FusedStepEngine(StepEngine):
         if self.world_size <= 1:
             return
         need16 = False
+        per_var = []
         for b in self.plan.ordered_buckets():
-            names = [p.var_name for p in b.parts]
-            lo = min(fl.offsets[n] for n in names)
-            hi = max(fl.range_of([n])[1] for n in names)
             wd = None if b.compressor_type == "NoneCompressor" else wire_dtype()
             ef = b.compressor_type == "HorovodCompressorEF"
             need16 |= wd is not None
-            self.range_wire.append((lo, hi, wd, ef, set(names)))
+            for part in b.parts:
+                per_var.append((fl.offsets[part.var_name], fl.range_of([part.var_name])[1], wd, ef))
+        # Row-sparse variables under an all-reduce strategy: this model writes their gradient densely into the flat
+        # buffer, so the mean over replicas is the same all-reduce, uncompressed.
+        for part, _, _ in self.plan.sparse_all_reduce:
+            per_var.append((fl.offsets[part.var_name], fl.range_of([part.var_name])[1], None, False))
+        per_var.sort()
+        for lo, hi, wd, ef in per_var:
+            if self.range_wire and self.range_wire[-1][1] == lo and self.range_wire[-1][2:4] == (wd, ef):
+                self.range_wire[-1] = (self.range_wire[-1][0], hi, wd, ef, None)
+            else:
+                self.range_wire.append((lo, hi, wd, ef, None))
         if need16:
             self._wire, self._wire_ptrs, self._wire_mc = self.arena.alloc(fl.total, wire_dtype())
             self._residual = torch.zeros(fl.total, dtype=torch.float32, device=self.device)

@@ -77,7 +77,8 @@ def main():
             E.allreduce(*ctx(), wptrs, mcast, code, n, gg, rr, gg, 1.0 / world, 0)
             torch.cuda.synchronize()
             arena.check()
-            check(f"allreduce {wire_dtype} EF {label} value", gg, ref, 2e-4 if wire_dtype is torch.bfloat16 else 2e-5)
+            check(f"allreduce {wire_dtype} EF {label} value", gg, ref,
+                  (5e-4 if wire_dtype is torch.bfloat16 else 5e-5) if label == "nvls" else (2e-4 if wire_dtype is torch.bfloat16 else 2e-5))
             check(f"allreduce {wire_dtype} EF {label} residual", rr, ref_res, 1e-7)
             dist.barrier()
 
