@@ -240,16 +240,17 @@ class FusedStepEngine(StepEngine):
             return
         need16 = False
         per_var = []
+        flat_name = {self.item.name_of_parameter(p): n for n, p in zip(fl.names, fl.params)}   # "x:0" -> flat key
         for b in self.plan.ordered_buckets():
             wd = None if b.compressor_type == "NoneCompressor" else wire_dtype()
             ef = b.compressor_type == "HorovodCompressorEF"
             need16 |= wd is not None
             for part in b.parts:
-                per_var.append((fl.offsets[part.var_name], fl.range_of([part.var_name])[1], wd, ef))
+                per_var.append((fl.offsets[flat_name[part.var_name]], fl.range_of([flat_name[part.var_name]])[1], wd, ef))
         # Row-sparse variables under an all-reduce strategy: this model writes their gradient densely into the flat
         # buffer, so the mean over replicas is the same all-reduce, uncompressed.
         for part, _, _ in self.plan.sparse_all_reduce:
-            per_var.append((fl.offsets[part.var_name], fl.range_of([part.var_name])[1], None, False))
+            per_var.append((fl.offsets[flat_name[part.var_name]], fl.range_of([flat_name[part.var_name]])[1], None, False))
         per_var.sort()
         for lo, hi, wd, ef in per_var:
             if self.range_wire and self.range_wire[-1][1] == lo and self.range_wire[-1][2:4] == (wd, ef):
