@@ -33,6 +33,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--only", default="", help="run only the GEMM shapes whose label contains this text")
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     from autodist_b200 import ops
     E = ops.ext(required=True)
@@ -52,19 +54,25 @@ def main():
               ("square 8192", 8192, 8192, 8192, False, False)]
     if args.small:
         shapes = shapes[:2]
+    if args.only:
+        shapes = [s for s in shapes if args.only in s[0]]
     for name, M, N, K, a_mn, b_mn in shapes:
         a = torch.randn((K, M) if a_mn else (M, K), device=dev).to(torch.bfloat16)
         b = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
         c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         for bn in (256, 128):
-            ms = _time(lambda: E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, bn), flush=flush)
+            ms = _time(lambda: E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, bn), iters=args.iters, flush=flush)
             A = a.t() if a_mn else a
             B = b if b_mn else b.t()
-            ms_lib = _time(lambda: torch.matmul(A, B, out=c), flush=flush)
+            ms_lib = _time(lambda: torch.matmul(A, B, out=c), iters=args.iters, flush=flush)
             fl = 2.0 * M * N * K
             rows.append({"kernel": f"gemm {name} {M}x{N}x{K} bn{bn}", "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
                          "cublas_ms": round(ms_lib, 4), "cublas_tflops": round(fl / ms_lib / 1e9, 1),
                          "frac_of_measured_peak": round(fl / ms / 1e9 / peaks.get("bf16_tflops", 1656.4), 3)})
+    if args.only:
+        for r in rows:
+            print(json.dumps(r))
+        return
     # bandwidth-bound kernels
     H = 1024
     x = torch.randn(T * 8, H, device=dev).to(torch.bfloat16)
