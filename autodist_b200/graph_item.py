@@ -421,7 +421,7 @@ class GraphItem:
     def prepare(self):
         """Freeze the naming registry and detect sparse-gradient variables."""
         self._refresh_module_registry()
-        for m in self.root.modules():
+        for m in list(self.root.modules()):
             if isinstance(m, nn.Embedding) and m.sparse:
                 self._sparse_params.add(id(m.weight))
             for p in getattr(m, "sparse_grad_parameters", lambda: [])():

@@ -1,0 +1,183 @@
+"""ImageNet-shape CNNs of the reference's benchmark driver (``examples/benchmark/imagenet.py:232-249`` builds
+``tf.keras.applications.{ResNet101, VGG16, InceptionV3, DenseNet121}`` with random weights).
+
+ResNet-101 (v1.5 bottlenecks), VGG-16, DenseNet-121 and a small Inception-style network are defined here from
+scratch. Convolutions, batch-norm and pooling run on PyTorch's cuDNN path in channels-last bf16 (library compute: the
+baseline these models are measured with until the implicit-GEMM convolution kernels land); the fully connected
+layers - 25088x4096, 4096x4096, 4096x1000 for VGG-16 - run on the tcgen05 GEMM. ``ImageClassifier`` wraps a backbone
+and the loss into one leaf module.
+"""
+import torch
+from torch import nn
+import torch.nn.functional as F
+
+from autodist_b200.ops.functional import Linear
+
+
+def _conv_bn(cin, cout, k, stride=1, padding=0):
+    return nn.Sequential(nn.Conv2d(cin, cout, k, stride, padding, bias=False), nn.BatchNorm2d(cout), nn.ReLU(inplace=True))
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, cin, width, stride):
+        super().__init__()
+        cout = width * self.expansion
+        self.a = _conv_bn(cin, width, 1)
+        self.b = _conv_bn(width, width, 3, stride, 1)
+        self.c = nn.Sequential(nn.Conv2d(width, cout, 1, bias=False), nn.BatchNorm2d(cout))
+        self.down = None
+        if stride != 1 or cin != cout:
+            self.down = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.BatchNorm2d(cout))
+
+    def forward(self, x):
+        idn = x if self.down is None else self.down(x)
+        return F.relu(self.c(self.b(self.a(x))) + idn)
+
+
+class ResNet(nn.Module):
+    def __init__(self, blocks=(3, 4, 23, 3), num_classes=1000, width=64):
+        super().__init__()
+        self.stem = nn.Sequential(_conv_bn(3, width, 7, 2, 3), nn.MaxPool2d(3, 2, 1))
+        layers, cin = [], width
+        for i, n in enumerate(blocks):
+            w = width * 2 ** i
+            for j in range(n):
+                layers.append(Bottleneck(cin, w, 2 if (j == 0 and i > 0) else 1))
+                cin = w * Bottleneck.expansion
+        self.layers = nn.Sequential(*layers)
+        self.fc = Linear(cin, num_classes)
+
+    def forward(self, x):
+        x = self.layers(self.stem(x))
+        return self.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
+
+
+def resnet101(num_classes=1000):
+    return ResNet((3, 4, 23, 3), num_classes)
+
+
+def resnet50(num_classes=1000):
+    return ResNet((3, 4, 6, 3), num_classes)
+
+
+class VGG16(nn.Module):
+    CFG = (64, 64, "M", 128, 128, "M", 256, 256, 256, "M", 512, 512, 512, "M", 512, 512, 512, "M")
+
+    def __init__(self, num_classes=1000, image_size=224):
+        super().__init__()
+        layers, cin = [], 3
+        for v in self.CFG:
+            if v == "M":
+                layers.append(nn.MaxPool2d(2, 2))
+            else:
+                layers += [nn.Conv2d(cin, v, 3, padding=1), nn.ReLU(inplace=True)]
+                cin = v
+        self.features = nn.Sequential(*layers)
+        side = image_size // 32
+        self.fc1 = Linear(512 * side * side, 4096)
+        self.fc2 = Linear(4096, 4096)
+        self.fc3 = Linear(4096, num_classes)
+
+    def forward(self, x):
+        x = torch.flatten(self.features(x), 1)
+        return self.fc3(F.relu(self.fc2(F.relu(self.fc1(x)))))
+
+
+class _DenseLayer(nn.Module):
+    def __init__(self, cin, growth):
+        super().__init__()
+        self.f = nn.Sequential(nn.BatchNorm2d(cin), nn.ReLU(inplace=True), nn.Conv2d(cin, 4 * growth, 1, bias=False),
+                               nn.BatchNorm2d(4 * growth), nn.ReLU(inplace=True), nn.Conv2d(4 * growth, growth, 3, padding=1, bias=False))
+
+    def forward(self, x):
+        return torch.cat([x, self.f(x)], 1)
+
+
+class DenseNet121(nn.Module):
+    def __init__(self, num_classes=1000, growth=32, blocks=(6, 12, 24, 16)):
+        super().__init__()
+        c = 2 * growth
+        mods = [nn.Conv2d(3, c, 7, 2, 3, bias=False), nn.BatchNorm2d(c), nn.ReLU(inplace=True), nn.MaxPool2d(3, 2, 1)]
+        for i, n in enumerate(blocks):
+            for _ in range(n):
+                mods.append(_DenseLayer(c, growth))
+                c += growth
+            if i + 1 < len(blocks):
+                mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True), nn.Conv2d(c, c // 2, 1, bias=False), nn.AvgPool2d(2, 2)]
+                c //= 2
+        mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True)]
+        self.features = nn.Sequential(*mods)
+        self.fc = Linear(c, num_classes)
+
+    def forward(self, x):
+        return self.fc(torch.flatten(F.adaptive_avg_pool2d(self.features(x), 1), 1))
+
+
+class _InceptionBlock(nn.Module):
+    def __init__(self, cin, c1, c3r, c3, c5r, c5, cp):
+        super().__init__()
+        self.b1 = _conv_bn(cin, c1, 1)
+        self.b3 = nn.Sequential(_conv_bn(cin, c3r, 1), _conv_bn(c3r, c3, 3, 1, 1))
+        self.b5 = nn.Sequential(_conv_bn(cin, c5r, 1), _conv_bn(c5r, c5, 3, 1, 1), _conv_bn(c5, c5, 3, 1, 1))
+        self.bp = nn.Sequential(nn.AvgPool2d(3, 1, 1), _conv_bn(cin, cp, 1))
+
+    def forward(self, x):
+        return torch.cat([self.b1(x), self.b3(x), self.b5(x), self.bp(x)], 1)
+
+
+class InceptionNet(nn.Module):
+    """Inception-style network (factorised 5x5 branches, batch-norm everywhere) at Inception-V3's depth class."""
+
+    def __init__(self, num_classes=1000):
+        super().__init__()
+        self.stem = nn.Sequential(_conv_bn(3, 32, 3, 2), _conv_bn(32, 32, 3), _conv_bn(32, 64, 3, 1, 1), nn.MaxPool2d(3, 2),
+                                  _conv_bn(64, 80, 1), _conv_bn(80, 192, 3), nn.MaxPool2d(3, 2))
+        blocks, cin = [], 192
+        for spec in [(64, 48, 64, 64, 96, 32), (64, 48, 64, 64, 96, 64), (64, 48, 64, 64, 96, 64)]:
+            blocks.append(_InceptionBlock(cin, *spec))
+            cin = spec[0] + spec[2] + spec[4] + spec[5]
+        blocks.append(nn.MaxPool2d(3, 2))
+        for spec in [(192, 128, 192, 128, 192, 192)] * 4:
+            blocks.append(_InceptionBlock(cin, *spec))
+            cin = spec[0] + spec[2] + spec[4] + spec[5]
+        blocks.append(nn.MaxPool2d(3, 2))
+        for spec in [(320, 384, 768, 448, 384, 192)] * 2:
+            blocks.append(_InceptionBlock(cin, *spec))
+            cin = spec[0] + spec[2] + spec[4] + spec[5]
+        self.blocks = nn.Sequential(*blocks)
+        self.fc = Linear(cin, num_classes)
+
+    def forward(self, x):
+        return self.fc(torch.flatten(F.adaptive_avg_pool2d(self.blocks(self.stem(x)), 1), 1))
+
+
+BACKBONES = {"resnet101": resnet101, "resnet50": resnet50, "vgg16": VGG16, "densenet121": DenseNet121,
+             "inceptionv3": InceptionNet}
+
+
+class ImageClassifier(nn.Module):
+    """Backbone + softmax cross-entropy as one leaf module: ``loss = model(images[N,3,H,W], labels[N])``."""
+    _autodist_leaf = True
+
+    def __init__(self, backbone="resnet101", num_classes=1000, compute_dtype=torch.bfloat16, **kw):
+        super().__init__()
+        self.net = BACKBONES[backbone](num_classes=num_classes, **kw) if isinstance(backbone, str) else backbone
+        self.compute_dtype = compute_dtype
+
+    def forward(self, images, labels):
+        if images.is_cuda:
+            images = images.contiguous(memory_format=torch.channels_last)
+            with torch.autocast("cuda", dtype=self.compute_dtype):
+                logits = self.net(images)
+        else:
+            logits = self.net(images)
+        return F.cross_entropy(logits.float(), labels)
+
+
+def synthetic_images(batch, image_size=224, num_classes=1000, seed=0):
+    """Images ~ N(0, 1) and uniform labels (the benchmark's synthetic input)."""
+    g = torch.Generator().manual_seed(seed)
+    return {"images": torch.randn(batch, 3, image_size, image_size, generator=g),
+            "labels": torch.randint(0, num_classes, (batch,), generator=g)}

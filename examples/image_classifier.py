@@ -1,0 +1,35 @@
+"""Getting-started CNN on Fashion-MNIST-shaped synthetic data with the default strategy
+(reference: ``examples/image_classifier.py``)."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from autodist_b200 import AutoDist  # noqa: E402
+from autodist_b200.models.simple import FashionCNN  # noqa: E402
+from autodist_b200.resource_spec import ResourceSpec  # noqa: E402
+
+
+def main():
+    spec = ResourceSpec(sys.argv[1]) if len(sys.argv) > 1 else ResourceSpec.local(num_cpus=2)
+    ad = AutoDist(resource_spec=spec)                     # default builder: PSLoadBalancing
+    rng = np.random.RandomState(0)
+    images = rng.rand(256, 1, 28, 28).astype(np.float32)
+    labels = rng.randint(0, 10, size=256).astype(np.int64)
+    with ad.scope():
+        model = FashionCNN()
+        x = ad.placeholder((None, 1, 28, 28), torch.float32, name="images")
+        y = ad.placeholder((None,), torch.int64, name="labels")
+        loss = model(x, y)
+        train_op = torch.optim.SGD(model.parameters(), lr=0.05).minimize(loss)
+        sess = ad.create_distributed_session()
+        for epoch in range(5):
+            lv, _ = sess.run([loss, train_op], {x: images, y: labels})
+            if sess.rank == 0:
+                print(f"epoch {epoch} loss {float(lv):.4f}")
+
+
+if __name__ == "__main__":
+    main()
