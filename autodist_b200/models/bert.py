@@ -150,10 +150,10 @@ class BertPretrainer(nn.Module):
         return mlm_loss + nsp_loss
 
     # ------------------------------------------------------------------ fused path
-    def materialize(self, device, grad_alloc=None):
+    def materialize(self, device, grad_alloc=None, master_alloc=None, p16_alloc=None):
         """Move the parameters into flat master / bf16 / gradient buffers on ``device``."""
         named = [(n, p) for n, p in self.named_parameters()]
-        self.flat = FlatParams(named, device, grad_alloc)
+        self.flat = FlatParams(named, device, grad_alloc, master_alloc=master_alloc, p16_alloc=p16_alloc)
         self._ws = None
         return self.flat
 

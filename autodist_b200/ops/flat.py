@@ -13,7 +13,7 @@ def _round_up(n, m):
 
 
 class FlatParams:
-    def __init__(self, named_params, device, grad_alloc=None, align=8):
+    def __init__(self, named_params, device, grad_alloc=None, align=8, master_alloc=None, p16_alloc=None):
         self.names, self.params, self.offsets, self.numels = [], [], {}, {}
         off = 0
         for name, p in named_params:
@@ -24,8 +24,10 @@ class FlatParams:
             off = _round_up(off + p.numel(), align)
         self.total = _round_up(off, 64)
         self.device = torch.device(device)
-        self.master = torch.zeros(self.total, dtype=torch.float32, device=device)
-        self.p16 = torch.zeros(self.total, dtype=torch.bfloat16, device=device)
+        self.master = master_alloc(self.total) if master_alloc is not None else \
+            torch.zeros(self.total, dtype=torch.float32, device=device)
+        self.p16 = p16_alloc(self.total) if p16_alloc is not None else \
+            torch.zeros(self.total, dtype=torch.bfloat16, device=device)
         self.grad = grad_alloc(self.total) if grad_alloc is not None else \
             torch.zeros(self.total, dtype=torch.float32, device=device)
         self.w32, self.w16, self.g = {}, {}, {}

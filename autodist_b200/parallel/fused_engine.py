@@ -141,8 +141,9 @@ class FusedStepEngine(StepEngine):
                     return False
                 if any(p.part_index is not None for p in b.parts):
                     return False
-            if plan.ps_entries:
-                return False
+            for e in plan.ps_entries.values():
+                if e.gate != "sync" or (e.part.part_index is not None and e.part.axis != 0):
+                    return False
         return True
 
     def __init__(self, graph_item, plan, backend, device, module):
@@ -169,7 +170,22 @@ class FusedStepEngine(StepEngine):
                 t.zero_()
                 self._grad_sym = {"ptrs": ptrs, "mc": mc}
                 return t
-        self.flat = module.materialize(self.device, grad_alloc)
+        master_alloc = p16_alloc = None
+        self._p32_sym = self._p16_sym = None
+        if self.world_size > 1 and plan.ps_entries:
+            # owners write updated parameters straight into every rank's copies: those live in symmetric memory too
+            def master_alloc(n):
+                t, ptrs, _ = self.arena.alloc(n, torch.float32)
+                t.zero_()
+                self._p32_sym = ptrs
+                return t
+
+            def p16_alloc(n):
+                t, ptrs, _ = self.arena.alloc(n, torch.bfloat16)
+                t.zero_()
+                self._p16_sym = ptrs
+                return t
+        self.flat = module.materialize(self.device, grad_alloc, master_alloc, p16_alloc)
         self._params = {name: p for name, p in graph_item.named_parameters()}
         if self.world_size > 1:
             backend.broadcast_(self.flat.master, 0)
@@ -234,7 +250,7 @@ class FusedStepEngine(StepEngine):
         """Which compressor applies to which range of the flat gradient buffer."""
         fl = self.flat
         self.range_wire = []     # (lo, hi, wire dtype or None, error feedback?)
-        self.sparse_vars = {}
+        self.ps_segments = []
         self._wire = self._wire_ptrs = self._residual = None
         if self.world_size <= 1:
             return
@@ -260,10 +276,78 @@ class FusedStepEngine(StepEngine):
         if need16:
             self._wire, self._wire_ptrs, self._wire_mc = self.arena.alloc(fl.total, wire_dtype())
             self._residual = torch.zeros(fl.total, dtype=torch.float32, device=self.device)
+        self._setup_ps_segments(flat_name)
+
+    def _setup_ps_segments(self, flat_name):
+        """Parameter-server parts as owned segments of the flat buffers (kernel ``reduce_scatter_update``)."""
+        fl = self.flat
+        self.ps_segments = []            # (start, length, owner) sorted by start; 4-element aligned
+        self._ps_tables = {}
+        by_var = {}
         for e in self.plan.ps_entries.values():
-            self.sparse_vars[e.part.var_name] = e
-        if self.sparse_vars:
-            self._setup_sparse()
+            by_var.setdefault(e.part.var_name, []).append(e)
+        for var_name, entries in by_var.items():
+            name = flat_name[var_name]
+            base, end = fl.offsets[name], fl.range_of([name])[1]
+            p = fl.params[fl.names.index(name)]
+            row = p.numel() // p.shape[0] if p.dim() > 0 and p.shape[0] > 0 else 1
+            entries.sort(key=lambda e: e.part.offset)
+            starts = [base + (e.part.offset * row if e.part.part_index is not None else 0) for e in entries]
+            if any(st % 4 for st in starts):
+                # shards of a tiny variable that do not start on 16-byte boundaries: the first owner takes all of it
+                self.ps_segments.append((base, end - base, entries[0].owner))
+                continue
+            for i, e in enumerate(entries):
+                stop = starts[i + 1] if i + 1 < len(entries) else end
+                self.ps_segments.append((starts[i], stop - starts[i], e.owner))
+        self.ps_segments.sort()
+        if not self.ps_segments:
+            return
+        dev = self.device
+        mine = [(st, ln) for st, ln, ow in self.ps_segments if ow == self.rank]
+        self._state_offset = {}
+        off = 0
+        for st, ln in mine:
+            self._state_offset[st] = off
+            off += ln
+        n = max(off, 4)
+        self.ps_master = torch.zeros(n, dtype=torch.float32, device=dev)
+        for st, ln in mine:
+            o = self._state_offset[st]
+            self.ps_master[o:o + ln].copy_(fl.master[st:st + ln])
+        self.ps_s1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
+        self.ps_s2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
+
+    def _ps_table(self, lo, hi):
+        """Device tables of this rank's owned segments inside [lo, hi) (cached per flight)."""
+        key = (lo, hi)
+        if key not in self._ps_tables:
+            inside = [(st, ln, ow) for st, ln, ow in self.ps_segments if st >= lo and st + ln <= hi]
+            mine = [(st, ln) for st, ln, ow in inside if ow == self.rank]
+            starts = [st for st, _ in mine] or [0]
+            lens = [ln for _, ln in mine] or [0]
+            state = [self._state_offset[st] for st, _ in mine] or [0]
+            prefix = [0]
+            for ln in lens:
+                prefix.append(prefix[-1] + ln)
+            t = lambda v: torch.tensor(v, dtype=torch.int64, device=self.device)   # noqa: E731
+            total = sum(ln for _, ln, _ in inside)
+            self._ps_tables[key] = (bool(inside), t(starts), t(lens), t(state), t(prefix), total)
+        return self._ps_tables[key]
+
+    def _ps_update_range(self, lo, hi):
+        any_inside, starts, lens, state, prefix, total = self._ps_table(lo, hi)
+        if not any_inside:
+            return 0
+        g = self.opt_info.optimizer.param_groups[0]
+        kind = {"SGD": 0, "Adam": 1, "AdamW": 1, "Adagrad": 2}[self.opt_kind]
+        b1, b2 = g.get("betas", (0.0, 0.0))
+        blocks = max(8, min(self.E.MAX_COMM_BLOCKS, total // (4 * 512 * self.world_size) + 1))
+        self.E.reduce_scatter_update(*self.arena.ctx(), self._grad_sym["ptrs"], self._p16_sym, self._p32_sym, self.ps_master,
+                                     self.ps_s1, self.ps_s2, starts, lens, state, prefix, kind, self.lr, self.opt_step,
+                                     b1, b2, g.get("eps", 1e-8), g.get("weight_decay", 0.0), g.get("momentum", 0.0), 1.0,
+                                     self.opt_kind == "AdamW", bool(g.get("nesterov", False)), 1.0 / self.world_size, blocks)
+        return 1
 
     def _policy_for(self, lo, hi):
         """Split [lo, hi) by the bucket policies that cover it."""
@@ -284,6 +368,7 @@ class FusedStepEngine(StepEngine):
                 for a, b, wd, ef in self._policy_for(lo, hi):
                     self._all_reduce_range(a, b, wd, ef)
                 covered = self._policy_for(lo, hi)
+                self.launches_per_step += self._ps_update_range(lo, hi)
             else:
                 covered = [(lo, hi, None, False)]
             for a, b, _, _ in covered:
@@ -303,12 +388,6 @@ class FusedStepEngine(StepEngine):
             mc = self._wire_mc + lo * 2 if self._wire_mc else 0
             g = self.flat.grad[lo:hi]
             self.E.allreduce(*ctx, ptrs, mc, WIRE[wd], n, g, self._residual[lo:hi] if ef else None, g, scale, 0)
-
-    # ------------------------------------------------------------------ sparse parameter-server path (K4 / K5)
-    def _setup_sparse(self):
-        """Row-sparse variables: each rank owns the rows the even/uneven split rule gives it; gradients are added
-        into the owner's shard through peer memory, the owner updates, lookups read rows from the owners."""
-        raise NotImplementedError("sparse parameter-server variables run on the generic engine for now")
 
     # ------------------------------------------------------------------ step
     def _run_model(self, train_op, nodes, feeds):
@@ -383,10 +462,31 @@ class FusedStepEngine(StepEngine):
         names = {"Adam": ("exp_avg", "exp_avg_sq"), "AdamW": ("exp_avg", "exp_avg_sq"), "SGD": ("momentum_buffer",),
                  "Adagrad": ("sum",)}[self.opt_kind]
         out = {}
+        bufs = [self.slot1, self.slot2]
+        if self.ps_segments:
+            # slots of parameter-server segments live with their owners: gather them into full-size buffers
+            merged = []
+            for local, owned in zip(bufs, (self.ps_s1, self.ps_s2)):
+                if local is None:
+                    merged.append(None)
+                    continue
+                full_buf = local.clone()
+                for st, ln, ow in self.ps_segments:
+                    full_buf[st:st + ln].zero_()
+                    if ow == self.rank:
+                        o = self._state_offset[st]
+                        full_buf[st:st + ln].copy_(owned[o:o + ln])
+                mask = torch.zeros_like(full_buf)
+                for st, ln, ow in self.ps_segments:
+                    mask[st:st + ln] = 1
+                part = full_buf * mask
+                dist.all_reduce(part, group=self.backend.group)
+                merged.append(torch.where(mask.bool(), part, full_buf))
+            bufs = merged
         for name, p in zip(self.flat.names, self.flat.params):
             full = self.item.name_of_parameter(p)[:-2]
             o, n = self.flat.offsets[name], p.numel()
-            for slot, buf in zip(names, (self.slot1, self.slot2)):
+            for slot, buf in zip(names, bufs):
                 if buf is not None:
                     out[f"{full}/{slot}"] = buf[o:o + n].view(p.shape).clone()
             out[f"{full}/step"] = torch.as_tensor(float(self.global_step))

@@ -19,3 +19,14 @@ def test_comm_kernels(nvls):
            "--master-port", "29611", os.path.join(HERE, "integration", "run_comm_gpu.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "ALL COMM CHECKS PASSED" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_engine_matches_nccl_engine():
+    import torch
+    n = min(torch.cuda.device_count(), 4)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29612", os.path.join(HERE, "integration", "run_fused_gpu.py")]
+    r = subprocess.run(cmd, env=dict(os.environ), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "FUSED ENGINE CHECKS PASSED" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
