@@ -6,6 +6,7 @@
 #include <torch/extension.h>
 
 #include <mutex>
+#include <vector>
 
 #include "comm.h"
 #include "elementwise.h"
@@ -90,8 +91,11 @@ void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, i
   if (bn <= 0) bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
   TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "bn must be 64, 128 or 256");
   CUtensorMap tmA = make_map(a, a_mn ? 64 : 128);
-  CUtensorMap tmB = make_map(b, b_mn ? 64 : (int)bn);
+  adb200::TmapArray tmB;
+  tmB.m[0] = make_map(b, b_mn ? 64 : (int)bn);
+  for (int i = 1; i < 8; ++i) tmB.m[i] = tmB.m[0];
   adb200::GemmParams p{};
+  p.b_shard_rows = 0;
   p.M = M; p.N = N; p.K = K;
   p.batch_lo = a.size(1); p.batch_hi = a.size(0);
   p.C = c.data_ptr();
@@ -122,6 +126,53 @@ void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, i
   }
   p.error_flag = error_flag.data_ptr<int>();
   cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
+}
+
+// Y = A . W^T (+ bias) where W [N, K] is split by rows into `world` equal shards that live in the owners' symmetric
+// memory: every B tile is fetched from its owner by a TMA load over NVLink inside the GEMM (no gathered copy of W).
+// shard_ptrs: one device address per owner (host list), each a contiguous bf16 [N / world, K] block.
+void gemm_gathered_b(const Tensor& a_, const std::vector<int64_t>& shard_ptrs, int64_t rows_per_shard, Tensor c_, int64_t epilogue,
+                     const optional<Tensor>& bias, Tensor error_flag, int64_t bn) {
+  const c10::cuda::CUDAGuard guard(a_.device());
+  Tensor a = as4d(a_), c = as4d(c_);
+  const int world = (int)shard_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8, "1 to 8 shards");
+  const int M = a.size(2), K = a.size(3);
+  const int N = (int)rows_per_shard * world;
+  TORCH_CHECK(a.size(0) == 1 && a.size(1) == 1, "the gathered-weight GEMM is not batched");
+  TORCH_CHECK(c.size(2) == M && c.size(3) == N && c.stride(3) == 1, "output shape mismatch");
+  if (bn <= 0) bn = rows_per_shard % 256 == 0 ? 256 : (rows_per_shard % 128 == 0 ? 128 : 64);
+  TORCH_CHECK(rows_per_shard % bn == 0, "rows per shard must be a multiple of the tile width ", bn);
+  TORCH_CHECK(K % 8 == 0, "K must be a multiple of 8");
+  CUtensorMap tmA = make_map(a, 128);
+  adb200::TmapArray tmB;
+  for (int s = 0; s < 8; ++s) {
+    const int src = s < world ? s : 0;
+    cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows_per_shard, 1, 1};
+    cuuint64_t strides[3] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * rows_per_shard, (cuuint64_t)K * 2 * rows_per_shard};
+    cuuint32_t box[4] = {64, (cuuint32_t)bn, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode_fn()(&tmB.m[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, reinterpret_cast<void*>(shard_ptrs[src]), dims, strides, box,
+                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for shard ", s, " with code ", (int)r);
+  }
+  adb200::GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.batch_lo = 1; p.batch_hi = 1;
+  p.C = c.data_ptr(); p.ldc = c.stride(2); p.strideC_lo = 0; p.strideC_hi = 0;
+  p.c_is_fp32 = c.scalar_type() == at::kFloat;
+  p.epilogue = (int)epilogue; p.alpha = 1.0f; p.beta = 0.0f;
+  p.bias = nullptr; p.C2 = nullptr; p.aux = nullptr;
+  if (epilogue == adb200::EPI_BIAS) {
+    TORCH_CHECK(bias.has_value() && bias->scalar_type() == at::kFloat && bias->numel() >= N, "fp32 bias of N entries needed");
+    p.bias = bias->data_ptr<float>();
+  } else {
+    TORCH_CHECK(epilogue == adb200::EPI_NONE, "only the plain and bias epilogues are offered here");
+  }
+  p.error_flag = error_flag.data_ptr<int>();
+  p.b_shard_rows = (int)rows_per_shard;
+  cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, false, false, num_sms(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
 }
 
@@ -299,6 +350,7 @@ void staleness_gate(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_gathered_b", &gemm_gathered_b);
   m.def("ln_fwd", &ln_fwd);
   m.def("ln_bwd", &ln_bwd);
   m.def("ln_bwd_blocks", &adb200::ln_bwd_blocks);

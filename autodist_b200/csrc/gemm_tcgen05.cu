@@ -143,7 +143,7 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmapArray tmBs, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -203,11 +203,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } else {
             tma_load_4d(a_dst, &tmA, &full[stage], k0, m0, b_lo, b_hi);
           }
+          // Row-sharded B: the tile's rows live in one owner's memory; its map addresses that peer directly.
+          const int shard = p.b_shard_rows > 0 ? n0 / p.b_shard_rows : 0;
+          const int nb = n0 - shard * p.b_shard_rows;
+          const CUtensorMap* tmB = &tmBs.m[shard];
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_4d(b_dst + j * (BK * 128), &tmB, &full[stage], n0 + 64 * j, k0, b_lo, b_hi);
+            for (int j = 0; j < BN / 64; ++j) tma_load_4d(b_dst + j * (BK * 128), tmB, &full[stage], nb + 64 * j, k0, b_lo, b_hi);
           } else {
-            tma_load_4d(b_dst, &tmB, &full[stage], k0, n0, b_lo, b_hi);
+            tma_load_4d(b_dst, tmB, &full[stage], k0, nb, b_lo, b_hi);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -380,7 +384,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 template <int BN, bool A_MN, bool B_MN>
-cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int num_sms, cudaStream_t stream) {
+cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int num_sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -397,9 +401,7 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 
 }  // namespace
 
-int gemm_box_rows_b(int bn, bool b_mn) { return b_mn ? BK : bn; }
-
-cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn, bool a_mn, bool b_mn,
+cudaError_t launch_gemm(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int bn, bool a_mn, bool b_mn,
                         int num_sms, cudaStream_t stream) {
 #define ADB_DISPATCH(BN_)                                                                      \
   if (bn == BN_) {                                                                             \

@@ -21,12 +21,19 @@ struct GemmParams {
   float alpha;                 // scale applied to the accumulator first
   float beta;                  // fp32 output only: 0 = overwrite, otherwise C += result
   int* error_flag;             // device int, set non-zero when a bounded wait gave up
+  int b_shard_rows;            // > 0: B is split by rows into shards of this many rows, shard s read through tmB.m[s]
+};
+
+// B operand maps: one for an ordinary GEMM; one per owner rank when the rows of B (a weight matrix sharded along
+// axis 0) live in the owners' memories and are fetched tile by tile over NVLink by (non-multicast) TMA loads.
+struct TmapArray {
+  CUtensorMap m[8];
 };
 
 // `bn` is the N extent of the tile (64, 128 or 256). The tensor maps must be 4-D bf16 maps with 128-byte swizzle:
 //   K-major operand : dims (K, rows, batch_lo, batch_hi), box (64, 128 for A / bn for B, 1, 1)
 //   MN-major operand: dims (rows, K, batch_lo, batch_hi), box (64, 64, 1, 1)
-cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn, bool a_mn,
+cudaError_t launch_gemm(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int bn, bool a_mn,
                         bool b_mn, int num_sms, cudaStream_t stream);
 
 }  // namespace adb200

@@ -118,8 +118,10 @@ def main():
     cfg = {"bert-large": BertConfig.large, "bert-base": BertConfig.base, "bert-tiny": BertConfig.tiny}[args.model]()
     max_pred = 20
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=n_gpus), strategy_builder=builders[args.strategy]())
-    host_batches = [synthetic_batch(cfg, args.batch, args.seq, max_pred, seed=1000 * rank + i, pin=True) for i in range(4)]
-    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    # Every process feeds its node's whole batch (batch per GPU x GPUs of the node), as a user of the API does; the
+    # remapper keeps this replica's slice, so only that slice crosses PCIe.
+    host_batches = [synthetic_batch(cfg, args.batch * n_gpus, args.seq, max_pred, seed=i, pin=True) for i in range(4)]
+    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values()) // n_gpus
     with ad.scope():
         torch.manual_seed(0)
         model = BertPretrainer(cfg)

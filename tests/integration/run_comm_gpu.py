@@ -160,6 +160,26 @@ def main():
     check("sparse_scatter_add owner shard", shard32[:my_rows * H].view(my_rows, H), dense[my_off:my_off + my_rows], 1e-4)
     dist.barrier()
 
+    # ---- K3: weight rows sharded over the ranks, gathered tile by tile inside the consuming GEMM
+    rows_per, Kd, Md = 256, 512, 384
+    wshard, wptrs, _ = arena.alloc(rows_per * Kd, torch.bfloat16)
+    torch.manual_seed(21)
+    w_full = (torch.randn(rows_per * world, Kd, device=dev) * 0.1).to(torch.bfloat16)
+    wshard.copy_(w_full[rank * rows_per:(rank + 1) * rows_per].reshape(-1))
+    xin = (torch.randn(Md, Kd, device=dev) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(rows_per * world, device=dev)
+    yout = torch.empty(Md, rows_per * world, dtype=torch.bfloat16, device=dev)
+    gerr = torch.zeros(1, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize(); dist.barrier()
+    E.sym_barrier(*ctx(), 1)                       # every owner's shard is in place
+    E.gemm_gathered_b(xin, [int(p) for p in wptrs.tolist()], rows_per, yout, 1, bias, gerr, 0)
+    E.sym_barrier(*ctx(), 1)                       # nobody overwrites a shard that a peer still reads
+    torch.cuda.synchronize()
+    arena.check()
+    assert gerr.item() == 0
+    check("all-gather fused into the GEMM (peer TMA tiles)", yout, xin.float() @ w_full.float().t() + bias, 3e-2)
+    dist.barrier()
+
     # ---- K20: a wait that nothing answers runs out, reports a status, and the context stays usable
     arena.timeout_s = 0.5
     if rank == 0:
