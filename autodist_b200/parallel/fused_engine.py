@@ -79,6 +79,9 @@ class GenericFusedModelEngine(StepEngine):
         all_nodes = list(nodes)
         if train_op.loss_node not in all_nodes:
             all_nodes.append(train_op.loss_node)
+        fl = self.module.flat
+        for name, p in zip(fl.names, fl.params):
+            p.grad = fl.g[name]          # the generic sparse paths replace .grad; the model always writes the flat views
         values = self.forward(all_nodes, feeds, grad=True)
         self.sync_and_update(train_op)
         self.module.flat.refresh_bf16()
