@@ -74,6 +74,11 @@ class GenericFusedModelEngine(StepEngine):
             self.backend.broadcast_(self.module.flat.master, 0)
         self.module.flat.refresh_bf16()
 
+    def before_read(self):
+        if self._pending_pull:
+            super().before_read()
+            self.module.flat.refresh_bf16()      # lazily pulled parameter-server values reach the compute copy too
+
     def train_step(self, train_op, nodes, feeds):
         self.before_read()
         all_nodes = list(nodes)

@@ -56,7 +56,7 @@ def main():
     for name in ("AllReduce", "AllReduce_EF", "PSLoadBalancing_gpu", "PartitionedPS_gpu", "Parallax_gpu"):
         ref, _, ref_losses, ref_engine = run(name, "nccl", world, rank)
         got, p16, losses, engine = run(name, "fused", world, rank)
-        tol = 2e-3 if name == "AllReduce_EF" else 2e-5      # fp16 wire vs fp32 wire
+        tol = 2e-3 if name == "AllReduce_EF" else 1e-4      # fp16 wire vs fp32 wire; summation order differs from NCCL's
         diff = (got - ref).abs().max().item()
         d16 = (p16 - got).abs().max().item()
         ok = diff <= tol and d16 < 1e-2 and engine == "FusedStepEngine" and ref_engine == "GenericFusedModelEngine"
