@@ -514,39 +514,59 @@ __global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restri
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                             bf16* __restrict__ p16, long long n, const float* __restrict__ lr_ptr, float b1, float b2, float eps,
                             float wd, int decoupled, const long long* __restrict__ step_ptr, float grad_scale) {
-  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (i >= n) return;
   const float lr = *lr_ptr;
   const float t = (float)(*step_ptr);
   const float c1 = 1.0f - powf(b1, t), c2 = 1.0f - powf(b2, t);
-  const int cnt = (int)min((long long)4, n - i);
-  float pp[4], gg[4], mm[4], vv[4];
-  if (cnt == 4) {
-    float4 a = *reinterpret_cast<const float4*>(p + i); pp[0] = a.x; pp[1] = a.y; pp[2] = a.z; pp[3] = a.w;
-    a = *reinterpret_cast<const float4*>(g + i); gg[0] = a.x; gg[1] = a.y; gg[2] = a.z; gg[3] = a.w;
-    a = *reinterpret_cast<const float4*>(m + i); mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w;
-    a = *reinterpret_cast<const float4*>(v + i); vv[0] = a.x; vv[1] = a.y; vv[2] = a.z; vv[3] = a.w;
-  } else {
-    for (int j = 0; j < cnt; ++j) { pp[j] = p[i + j]; gg[j] = g[i + j]; mm[j] = m[i + j]; vv[j] = v[i + j]; }
-  }
-  for (int j = 0; j < cnt; ++j) {
-    float gr = gg[j] * grad_scale;
-    if (wd != 0.f) { if (decoupled) pp[j] *= 1.0f - lr * wd; else gr += wd * pp[j]; }
-    mm[j] = b1 * mm[j] + (1.0f - b1) * gr;
-    vv[j] = b2 * vv[j] + (1.0f - b2) * gr * gr;
-    pp[j] -= lr * (mm[j] / c1) / (sqrtf(vv[j] / c2) + eps);
-  }
-  if (cnt == 4) {
-    *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
-    *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    if (p16) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
-      uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-      *reinterpret_cast<uint2*>(p16 + i) = u;
+  const float inv_c1 = 1.0f / c1, inv_c2 = 1.0f / c2;
+  const long long nvec = n / 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // two independent 16-byte groups per iteration keep eight loads in flight per thread
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < nvec; q += 2 * stride) {
+    float4 P[2], G[2], M[2], V[2];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const long long i = (q + u * stride) * 4;
+      live[u] = (q + u * stride) < nvec;
+      if (live[u]) {
+        P[u] = *reinterpret_cast<const float4*>(p + i);
+        G[u] = __ldcs(reinterpret_cast<const float4*>(g + i));
+        M[u] = *reinterpret_cast<const float4*>(m + i);
+        V[u] = *reinterpret_cast<const float4*>(v + i);
+      }
     }
-  } else {
-    for (int j = 0; j < cnt; ++j) { p[i + j] = pp[j]; m[i + j] = mm[j]; v[i + j] = vv[j]; if (p16) p16[i + j] = __float2bfloat16(pp[j]); }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (!live[u]) continue;
+      const long long i = (q + u * stride) * 4;
+      float pp[4] = {P[u].x, P[u].y, P[u].z, P[u].w}, gg[4] = {G[u].x, G[u].y, G[u].z, G[u].w};
+      float mm[4] = {M[u].x, M[u].y, M[u].z, M[u].w}, vv[4] = {V[u].x, V[u].y, V[u].z, V[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float gr = gg[j] * grad_scale;
+        if (wd != 0.f) { if (decoupled) pp[j] *= 1.0f - lr * wd; else gr += wd * pp[j]; }
+        mm[j] = b1 * mm[j] + (1.0f - b1) * gr;
+        vv[j] = b2 * vv[j] + (1.0f - b2) * gr * gr;
+        pp[j] -= lr * (mm[j] * inv_c1) / (sqrtf(vv[j] * inv_c2) + eps);
+      }
+      *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      if (p16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+        *reinterpret_cast<uint2*>(p16 + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      }
+    }
+  }
+  // tail (n not a multiple of 4)
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    const long long i = nvec * 4 + threadIdx.x;
+    float gr = g[i] * grad_scale, pp = p[i];
+    if (wd != 0.f) { if (decoupled) pp *= 1.0f - lr * wd; else gr += wd * pp; }
+    const float mm = b1 * m[i] + (1.0f - b1) * gr, vv = b2 * v[i] + (1.0f - b2) * gr * gr;
+    pp -= lr * (mm * inv_c1) / (sqrtf(vv * inv_c2) + eps);
+    p[i] = pp; m[i] = mm; v[i] = vv;
+    if (p16) p16[i] = __float2bfloat16(pp);
   }
 }
 
@@ -595,7 +615,7 @@ void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* bet
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st) {
   ln_fwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
 }
-int ln_bwd_blocks(int rows) { return rows < 296 * 4 ? (rows + 3) / 4 : 296; }
+int ln_bwd_blocks(int rows) { return rows < 1184 * 4 ? (rows + 3) / 4 : 1184; }
 void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd, const float* gamma, const bf16* dz_add, bf16* dz,
             bf16* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
             const long long* step, int accumulate, cudaStream_t st) {
@@ -664,7 +684,9 @@ void add_bf16(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t
 }
 void adam_update(float* p, const float* g, float* m, float* v, bf16* p16, long long n, const float* lr, float b1, float b2,
                  float eps, float wd, int decoupled, const long long* step, float grad_scale, cudaStream_t st) {
-  adam_kernel<<<blocks_for((n + 3) / 4, 256), 256, 0, st>>>(p, g, m, v, p16, n, lr, b1, b2, eps, wd, decoupled, step, grad_scale);
+  const long long groups = (n / 4 + 1) / 2 + 1;
+  const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
+  adam_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(p, g, m, v, p16, n, lr, b1, b2, eps, wd, decoupled, step, grad_scale);
 }
 void sgd_update(float* p, const float* g, float* mom, bf16* p16, long long n, const float* lr, float momentum, float dampening,
                 float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st) {
