@@ -20,6 +20,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 # per-GPU examples/s of the reference's "AutoDist AllReduce" BERT-large bars (T4, read off docs/usage/figure1.png)
 PUBLISHED_PER_GPU = {1: 11.1, 2: 8.0, 4: 7.8, 8: 3.2}
+PUBLISHED_RESNET101 = {1: 62.0, 2: 59.5, 4: 59.0, 8: 52.0}     # images/s/GPU, "AutoDist AllReduce" bars
 
 
 class ClockSampler(threading.Thread):
@@ -79,9 +80,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default="bert-large", choices=["bert-large", "bert-base", "bert-tiny"])
+    ap.add_argument("--model", default="bert-large", choices=["bert-large", "bert-base", "bert-tiny", "resnet101", "vgg16",
+                                                              "resnet50", "densenet121", "inceptionv3"])
     ap.add_argument("--strategy", default="allreduce", choices=["allreduce", "allreduce_ef", "parallax", "ps", "partitioned_ps"])
-    ap.add_argument("--batch", type=int, default=32, help="sequences per GPU")
+    ap.add_argument("--batch", type=int, default=0, help="samples per GPU (default: 32 sequences, 64 images, 32 for vgg16)")
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--comm", default=None, help="fused (own kernels) or nccl (baseline)")
     ap.add_argument("--no-graph", action="store_true")
@@ -115,19 +117,29 @@ def main():
         "ps": lambda: S.PSLoadBalancing(reduction_devices="gpu", local_proxy_variable=True),
         "partitioned_ps": lambda: S.PartitionedPS(num_shards=n_gpus, reduction_devices="gpu", local_proxy_variable=True),
     }
-    cfg = {"bert-large": BertConfig.large, "bert-base": BertConfig.base, "bert-tiny": BertConfig.tiny}[args.model]()
+    is_bert = args.model.startswith("bert")
+    if not args.batch:
+        args.batch = 32 if is_bert or args.model == "vgg16" else 64
     max_pred = 20
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=n_gpus), strategy_builder=builders[args.strategy]())
     # Every process feeds its node's whole batch (batch per GPU x GPUs of the node), as a user of the API does; the
     # remapper keeps this replica's slice, so only that slice crosses PCIe.
-    host_batches = [synthetic_batch(cfg, args.batch * n_gpus, args.seq, max_pred, seed=i, pin=True) for i in range(4)]
+    if is_bert:
+        cfg = {"bert-large": BertConfig.large, "bert-base": BertConfig.base, "bert-tiny": BertConfig.tiny}[args.model]()
+        host_batches = [synthetic_batch(cfg, args.batch * n_gpus, args.seq, max_pred, seed=i, pin=True) for i in range(4)]
+    else:
+        from autodist_b200.models.cnn import ImageClassifier, synthetic_images
+        host_batches = [{k: v.pin_memory() for k, v in synthetic_images(args.batch * n_gpus, 224, 1000, seed=i).items()}
+                        for i in range(2)]
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values()) // n_gpus
     with ad.scope():
         torch.manual_seed(0)
-        model = BertPretrainer(cfg)
+        model = BertPretrainer(cfg) if is_bert else (ImageClassifier(args.model, image_size=224) if args.model == "vgg16"
+                                                     else ImageClassifier(args.model))
         phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in host_batches[0].items()}
         loss = model(**phs)
-        opt = torch.optim.Adam(model.parameters(), lr=1e-4)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-4) if is_bert else \
+            torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
         train_op = opt.minimize(loss)
         sess = ad.create_distributed_session()
         dev = sess.engine.device
@@ -193,19 +205,23 @@ def main():
     launches = eager_launches if eager_launches > 0 else graph_launches * args.steps
     published = PUBLISHED_PER_GPU.get(n_gpus)
     out = {
-        "metric": "BERT-large pre-training sequences/sec (seq 128), max over ranks",
-        "value": round(value, 2), "unit": "sequences/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+        "metric": "BERT-large pre-training sequences/sec (seq 128), max over ranks" if is_bert
+        else f"{args.model} ImageNet-shape training images/sec, max over ranks",
+        "value": round(value, 2), "unit": "sequences/s" if is_bert else "images/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(value / (published * n_gpus), 2) if published and args.model == "bert-large" else None,
+        "vs_baseline": round(value / (published * n_gpus), 2) if published and args.model == "bert-large" else (
+            round(value / (PUBLISHED_RESNET101.get(n_gpus, 0) * n_gpus), 2) if args.model == "resnet101" and n_gpus in PUBLISHED_RESNET101 else None),
         "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM positions, random-init weights)",
-        "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq, "max_predictions": max_pred,
-                   "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute",
+        "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq if is_bert else None,
+                   "max_predictions": max_pred if is_bert else None,
+                   "compute": "hand-written sm_100a kernels" if is_bert else "cuDNN convolutions (library) + tcgen05 GEMM for fully connected layers",
+                   "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute" if is_bert else "SGD momentum 0.9, fp32 master + bf16 autocast",
                    "comm": os.environ.get("AUTODIST_COMM", "fused"),
                    "cuda_graph": os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0",
                    "l2": "per-step working set (activations + weights > 4 GB) is far larger than the 126 MB L2",
                    "engine": type(sess.engine).__name__},
         "clocks": sampler.summary() if sampler else None,
-        "e2e": {"value": round(e2e, 2), "unit": "sequences/s", "ms_per_step": round(ms_e2e / args.steps, 3),
+        "e2e": {"value": round(e2e, 2), "unit": "sequences/s" if is_bert else "images/s", "ms_per_step": round(ms_e2e / args.steps, 3),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": float(last)},
         "gpu_launches": int(launches),
         "impl": "ours",
