@@ -194,6 +194,7 @@ class BertPretrainer(nn.Module):
             # heads
             "pooled": bf(B, H), "nsp_logits": bf(B, 8), "d_pooled": bf(B, H), "d_pre": bf(B, H),
             "flat_pos": torch.empty(B * P, dtype=torch.int64, device=dev),
+            "row_index": torch.arange(T, dtype=torch.int64, device=dev),
             "xm": bf(B * P, H), "hm_u": bf(B * P, H), "hm": bf(B * P, H), "hl": bf(B * P, H), "mm": f32(B * P),
             "mr": f32(B * P), "logits": bf(B * P, Vp), "d_hl": bf(B * P, H), "d_hm": bf(B * P, H), "d_hu": bf(B * P, H),
             "d_xm": bf(B * P, H), "d_bias": f32(Vp),
@@ -241,7 +242,12 @@ class BertPretrainer(nn.Module):
             return t.view(B, S, nh, D).permute(0, 2, 1, 3)
 
         # ------------------------------ forward
-        E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S)
+        if self._word_lookup_hook is not None:
+            # sharded table: the rows of this batch are fetched from the shards that own them (peer memory)
+            rows = self._word_lookup_hook(ids)
+            E.embed_sum(rows, w16["emb.pos"], w16["emb.tok_type"], ws["row_index"], tts, ws["z0"], S)
+        else:
+            E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S)
         E.ln_fwd(ws["z0"], None, w32["emb.ln_g"], w32["emb.ln_b"], None, ws["x0"], ws["m0"], ws["r0"], eps, 0.0, 0, None)
         x = ws["x0"]
         for l, A in enumerate(ws["layers"]):
@@ -368,6 +374,7 @@ class BertPretrainer(nn.Module):
         return ws["loss"]
 
     _word_grad_hook = None
+    _word_lookup_hook = None
 
     # ------------------------------------------------------------------ module call
     def forward(self, input_ids, input_mask, segment_ids, mlm_positions, mlm_ids, mlm_weights, nsp_labels):

@@ -109,6 +109,10 @@ class SymmetricArena:
         self.flags, self.flag_ptrs, _ = self.alloc(nflags, torch.int32)
         self.flags.zero_()
         self.epochs = torch.zeros(self.E.MAX_COMM_BLOCKS, dtype=torch.int32, device=device)
+        # a second, independent set of flags for kernels issued from another stream (barrier epochs are per channel)
+        self.flags_b, self.flag_ptrs_b, _ = self.alloc(nflags, torch.int32)
+        self.flags_b.zero_()
+        self.epochs_b = torch.zeros(self.E.MAX_COMM_BLOCKS, dtype=torch.int32, device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
         self.timeout_s = float(os.environ.get("AUTODIST_KERNEL_TIMEOUT", "20"))
         torch.cuda.synchronize()
@@ -127,7 +131,9 @@ class SymmetricArena:
                 mc = 0
         return t, ptrs, mc
 
-    def ctx(self):
+    def ctx(self, channel=0):
+        if channel:
+            return (self.flag_ptrs_b, self.epochs_b, self.error, self.rank, self.world, self.timeout_s)
         return (self.flag_ptrs, self.epochs, self.error, self.rank, self.world, self.timeout_s)
 
     def check(self):
@@ -294,8 +300,11 @@ class FusedStepEngine(StepEngine):
         by_var = {}
         for e in self.plan.ps_entries.values():
             by_var.setdefault(e.part.var_name, []).append(e)
+        self.sharded_rows = {}
         for var_name, entries in by_var.items():
             name = flat_name[var_name]
+            if self._try_row_sharding(var_name, name, entries):
+                continue
             base, end = fl.offsets[name], fl.range_of([name])[1]
             p = fl.params[fl.names.index(name)]
             row = p.numel() // p.shape[0] if p.dim() > 0 and p.shape[0] > 0 else 1
@@ -325,6 +334,70 @@ class FusedStepEngine(StepEngine):
             self.ps_master[o:o + ln].copy_(fl.master[st:st + ln])
         self.ps_s1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
         self.ps_s2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
+
+    # ---- row-sparse variables sharded over all ranks: K4 (scatter-add to owners) / K5 (gather from owners) ----------
+    def _try_row_sharding(self, var_name, name, entries):
+        """A sparse variable split along axis 0 into one shard per rank, shard i owned by rank i, is not replicated at
+        all: lookups read rows from the owners and gradients are added into the owners' shards."""
+        hooks = hasattr(self.module, "_word_lookup_hook") and name == "emb.word"
+        if not (hooks and len(entries) == self.world_size and all(e.part.sparse for e in entries)):
+            return False
+        entries.sort(key=lambda e: e.part.offset)
+        if [e.owner for e in entries] != list(range(self.world_size)) or os.environ.get("AUTODIST_SPARSE_ROWS", "1") == "0":
+            return False
+        fl = self.flat
+        p = fl.params[fl.names.index(name)]
+        V, H = p.shape
+        q, rem = divmod(V, self.world_size)
+        if [e.part.size for e in entries] != [q + (1 if i < rem else 0) for i in range(self.world_size)] or H % 8:
+            return False
+        cap = q + 1
+        my_rows, my_off = entries[self.rank].part.size, entries[self.rank].part.offset
+        shard16, s16ptrs, _ = self.arena.alloc(cap * H, torch.bfloat16)
+        grad32, g32ptrs, _ = self.arena.alloc(cap * H, torch.float32)
+        master = fl.w32[name][my_off:my_off + my_rows].reshape(-1).clone()
+        shard16.zero_()
+        shard16[:my_rows * H].copy_(master)
+        st = {"V": V, "H": H, "rows": my_rows, "off": my_off, "shard16": shard16, "s16ptrs": s16ptrs, "grad32": grad32,
+              "g32ptrs": g32ptrs, "master": master, "name": name, "var": var_name,
+              "s1": torch.zeros_like(master) if self._needs_slot1() else None,
+              "s2": torch.zeros_like(master) if self.opt_kind in ("Adam", "AdamW") else None}
+        self.sharded_rows[name] = st
+        self.module._word_lookup_hook = lambda ids: self._lookup_rows(st, ids)
+        self.module._word_grad_hook = lambda ids, rows: self._push_rows(st, ids, rows)
+        return True
+
+    def _lookup_rows(self, st, ids):
+        out = torch.empty(ids.numel(), st["H"], dtype=torch.bfloat16, device=self.device)
+        self.E.embedding_gather_peers(*self.arena.ctx(1), st["s16ptrs"], ids, out, st["V"], True, 32)
+        return out
+
+    def _push_rows(self, st, ids, rows):
+        st["grad32"].zero_()
+        self.E.sparse_scatter_add(*self.arena.ctx(1), st["g32ptrs"], ids, rows, st["V"], 1.0 / self.world_size, 32)
+        n = st["rows"] * st["H"]
+        g = self.opt_info.optimizer.param_groups[0]
+        p, gr, p16 = st["master"], st["grad32"][:n], st["shard16"][:n]
+        if self.opt_kind in ("Adam", "AdamW"):
+            b1, b2 = g["betas"]
+            self.E.adam_update(p, gr, st["s1"], st["s2"], p16, self.lr, b1, b2, g["eps"], g["weight_decay"],
+                               self.opt_kind == "AdamW", self.opt_step, 1.0)
+        elif self.opt_kind == "SGD":
+            self.E.sgd_update(p, gr, st["s1"], p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"],
+                              self.opt_step, 1.0)
+        else:
+            self.E.adagrad_update(p, gr, st["s1"], p16, self.lr, g["eps"], g["weight_decay"], 1.0)
+
+    def _gather_sharded(self, st, local_flat):
+        """Full [V, H] tensor from every owner's rows (checkpoints, variable fetches)."""
+        cap = st["V"] // self.world_size + 1
+        pad = torch.zeros(cap * st["H"], dtype=torch.float32, device=self.device)
+        pad[:local_flat.numel()].copy_(local_flat)
+        parts = [torch.empty_like(pad) for _ in range(self.world_size)]
+        dist.all_gather(parts, pad, group=self.backend.group)
+        q, rem = divmod(st["V"], self.world_size)
+        rows = [q + (1 if i < rem else 0) for i in range(self.world_size)]
+        return torch.cat([parts[i][:rows[i] * st["H"]] for i in range(self.world_size)]).view(st["V"], st["H"])
 
     def _ps_table(self, lo, hi):
         """Device tables of this rank's owned segments inside [lo, hi) (cached per flight)."""
@@ -464,6 +537,9 @@ class FusedStepEngine(StepEngine):
 
     # ------------------------------------------------------------------ state
     def variable_value(self, name):
+        for st in self.sharded_rows.values() if hasattr(self, "sharded_rows") else ():
+            if st["var"] == name:
+                return self._gather_sharded(st, st["master"])
         return self._params[name].detach()
 
     def optimizer_slots(self):
@@ -498,6 +574,11 @@ class FusedStepEngine(StepEngine):
                 if buf is not None:
                     out[f"{full}/{slot}"] = buf[o:o + n].view(p.shape).clone()
             out[f"{full}/step"] = torch.as_tensor(float(self.global_step))
+        for st in getattr(self, "sharded_rows", {}).values():
+            full = st["var"][:-2]
+            for slot, buf in zip(names, (st["s1"], st["s2"])):
+                if buf is not None:
+                    out[f"{full}/{slot}"] = self._gather_sharded(st, buf)
         return out
 
     def load_optimizer_slots(self, slots, default_step=0):
@@ -515,6 +596,14 @@ class FusedStepEngine(StepEngine):
     def after_restore(self):
         self.flat.refresh_bf16()
         self.opt_step.fill_(self.global_step)
+        for st in getattr(self, "sharded_rows", {}).values():
+            n = st["rows"] * st["H"]
+            st["master"].copy_(self.flat.w32[st["name"]][st["off"]:st["off"] + st["rows"]].reshape(-1))
+            st["shard16"][:n].copy_(st["master"])
+        for st_, ln, ow in getattr(self, "ps_segments", []):
+            if ow == self.rank:
+                o = self._state_offset[st_]
+                self.ps_master[o:o + ln].copy_(self.flat.master[st_:st_ + ln])
 
     def close(self):
         return

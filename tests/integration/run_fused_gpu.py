@@ -43,6 +43,10 @@ def run(strategy_name, comm, world, rank, opt_name="sgd"):
         if hasattr(sess.engine, "check_errors"):
             sess.engine.check_errors()
         torch.cuda.synchronize()
+        # variables are read back through the engine: a row-sharded embedding is gathered from its owners
+        word = sess.engine.variable_value("emb.word:0").float()
+        model.flat.w32["emb.word"].copy_(word)
+        model.flat.w16["emb.word"].copy_(word)
         state = model.flat.master.clone()
         p16 = model.flat.p16.float().clone()
         engine = type(sess.engine).__name__
