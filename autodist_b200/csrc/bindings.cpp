@@ -267,6 +267,19 @@ void adagrad_update(Tensor p, const Tensor& g, Tensor acc, const optional<Tensor
   adb200::adagrad_update(p.data_ptr<float>(), g.data_ptr<float>(), acc.data_ptr<float>(), OPT_BF(p16), p.numel(), lr.data_ptr<float>(),
                          (float)eps, (float)wd, (float)grad_scale, STREAM);
 }
+void lstm_cell_fwd(const Tensor& gates, const Tensor& c_prev, Tensor c, Tensor h, double forget_bias) {
+  const int B = c_prev.size(0), S = c_prev.size(1);
+  TORCH_CHECK(gates.scalar_type() == at::kFloat && gates.size(1) == 4 * S && gates.is_contiguous(), "gates must be fp32 [B, 4S]");
+  adb200::lstm_cell_fwd(gates.data_ptr<float>(), c_prev.data_ptr<float>(), c.data_ptr<float>(), BF(h), B, S, (float)forget_bias, STREAM);
+}
+void lstm_cell_bwd(const Tensor& gates, const Tensor& c_prev, const Tensor& c, const Tensor& dh, const optional<Tensor>& dc_next,
+                   Tensor dgates, Tensor dc_prev, double forget_bias) {
+  const int B = c_prev.size(0), S = c_prev.size(1);
+  adb200::lstm_cell_bwd(gates.data_ptr<float>(), c_prev.data_ptr<float>(), c.data_ptr<float>(), dh.data_ptr<float>(), OPT_F(dc_next),
+                        dgates.data_ptr<float>(), dc_prev.data_ptr<float>(), B, S, (float)forget_bias, STREAM);
+}
+void sumsq(const Tensor& x, Tensor acc, double weight) { adb200::sumsq(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)weight, STREAM); }
+void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_scale(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)max_norm, STREAM); }
 void cast_f32_bf16(const Tensor& x, Tensor y) { adb200::cast_f32_bf16(x.data_ptr<float>(), BF(y), x.numel(), STREAM); }
 void increment(Tensor c) { adb200::increment(reinterpret_cast<long long*>(c.data_ptr<int64_t>()), STREAM); }
 
@@ -371,6 +384,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("lstm_cell_fwd", &lstm_cell_fwd);
+  m.def("lstm_cell_bwd", &lstm_cell_bwd);
+  m.def("sumsq", &sumsq);
+  m.def("clip_scale", &clip_scale);
   m.def("increment", &increment);
   m.def("allreduce", &allreduce);
   m.def("reduce_scatter_update", &reduce_scatter_update);

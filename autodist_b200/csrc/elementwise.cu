@@ -599,6 +599,63 @@ __global__ void adagrad_kernel(float* __restrict__ p, const float* __restrict__ 
   if (p16) p16[i] = __float2bfloat16(np);
 }
 
+// ------------------------------------------------------------------------------------------------ LSTM cell (K17)
+// gates [B, 4S] in the order i, j, f, o (fp32); c = sigmoid(f + fb) * c_prev + sigmoid(i) * tanh(j); h = sigmoid(o) * tanh(c)
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+__global__ void lstm_cell_fwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_prev, float* __restrict__ c,
+                                     bf16* __restrict__ h, int B, int S, float forget_bias) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * S) return;
+  const int b = (int)(idx / S), s = (int)(idx % S);
+  const float* g = gates + (long long)b * 4 * S;
+  const float i = g[s], j = g[S + s], f = g[2 * S + s], o = g[3 * S + s];
+  const float cn = sigmoidf_(f + forget_bias) * c_prev[idx] + sigmoidf_(i) * tanhf(j);
+  c[idx] = cn;
+  h[idx] = __float2bfloat16(sigmoidf_(o) * tanhf(cn));
+}
+
+__global__ void lstm_cell_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_prev, const float* __restrict__ c,
+                                     const float* __restrict__ dh, const float* __restrict__ dc_next, float* __restrict__ dgates,
+                                     float* __restrict__ dc_prev, int B, int S, float forget_bias) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * S) return;
+  const int b = (int)(idx / S), s = (int)(idx % S);
+  const float* g = gates + (long long)b * 4 * S;
+  float* dg = dgates + (long long)b * 4 * S;
+  const float si = sigmoidf_(g[s]), tj = tanhf(g[S + s]), sf = sigmoidf_(g[2 * S + s] + forget_bias), so = sigmoidf_(g[3 * S + s]);
+  const float tc = tanhf(c[idx]);
+  const float d_h = dh[idx];
+  const float dct = (dc_next ? dc_next[idx] : 0.f) + d_h * so * (1.0f - tc * tc);
+  dg[s] = dct * tj * si * (1.0f - si);
+  dg[S + s] = dct * si * (1.0f - tj * tj);
+  dg[2 * S + s] = dct * c_prev[idx] * sf * (1.0f - sf);
+  dg[3 * S + s] = d_h * tc * so * (1.0f - so);
+  dc_prev[idx] = dct * sf;
+}
+
+// ------------------------------------------------------------------------------------------------ global-norm clip (K19)
+// acc += weight * sum(x^2); later x *= min(1, max_norm / (sqrt(acc) + 1e-6)). The norm never visits the host.
+__global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ acc, float weight) {
+  float a = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) a += x[i] * x[i];
+  a = warp_sum(a);
+  __shared__ float sm[32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) t += sm[i];
+    atomicAdd(acc, t * weight);
+  }
+}
+__global__ void clip_scale_kernel(float* __restrict__ x, long long n, const float* __restrict__ acc, float max_norm) {
+  const float norm = sqrtf(*acc);
+  if (norm <= max_norm) return;
+  const float sc = max_norm / (norm + 1e-6f);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= sc;
+}
+
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = __float2bfloat16(x[i]);
@@ -695,6 +752,21 @@ void sgd_update(float* p, const float* g, float* mom, bf16* p16, long long n, co
 void adagrad_update(float* p, const float* g, float* acc, bf16* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st) {
   adagrad_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, acc, p16, n, lr, eps, wd, grad_scale);
+}
+void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16* h, int B, int S, float fb, cudaStream_t st) {
+  lstm_cell_fwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, h, B, S, fb);
+}
+void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, const float* dh, const float* dc_next, float* dgates,
+                   float* dc_prev, int B, int S, float fb, cudaStream_t st) {
+  lstm_cell_bwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, dh, dc_next, dgates, dc_prev, B, S, fb);
+}
+void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st) {
+  const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
+  sumsq_kernel<<<blocks, 256, 0, st>>>(x, n, acc, weight);
+}
+void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st) {
+  const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
+  clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
 }
 void cast_f32_bf16(const float* x, bf16* y, long long n, cudaStream_t st) {
   cast_f32_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(x, y, n);

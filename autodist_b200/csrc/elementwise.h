@@ -37,6 +37,11 @@ void sgd_update(float* p, const float* g, float* mom, bf16_t* p16, long long n, 
                 float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st);
 void adagrad_update(float* p, const float* g, float* acc, bf16_t* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st);
+void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16_t* h, int B, int S, float fb, cudaStream_t st);
+void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, const float* dh, const float* dc_next, float* dgates,
+                   float* dc_prev, int B, int S, float fb, cudaStream_t st);
+void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st);
+void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
 void cast_f32_bf16(const float* x, bf16_t* y, long long n, cudaStream_t st);
 void increment(long long* c, cudaStream_t st);
 }  // namespace adb200

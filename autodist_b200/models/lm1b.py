@@ -12,7 +12,7 @@ import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import linear
+from autodist_b200.ops.functional import linear, lstm_cell
 
 
 @dataclass
@@ -75,10 +75,9 @@ class LM1B(nn.Module):
         cell = torch.zeros(Bsz, c.state_size, dtype=torch.float32, device=x.device)
         outs = []
         for t in range(T):
-            gates = linear(torch.cat([inputs[:, t], h], 1), self.W, self.B).float()
-            i, j, f, o = gates.chunk(4, 1)
-            cell = torch.sigmoid(f + 1.0) * cell + torch.sigmoid(i) * torch.tanh(j)
-            h = linear((torch.sigmoid(o) * torch.tanh(cell)).to(dt), self.W_P)
+            gates = linear(torch.cat([inputs[:, t], h], 1), self.W, self.B)
+            cell, hidden = lstm_cell(gates, cell, 1.0)
+            h = linear(hidden.to(dt), self.W_P)
             outs.append(h)
         out = torch.stack(outs, 1).reshape(Bsz * T, c.projected_size)
         if self.training and c.keep_prob < 1.0:

@@ -93,3 +93,51 @@ class Linear(torch.nn.Linear):
 
     def forward(self, x):
         return linear(x, self.weight, self.bias)
+
+
+class _LSTMCellFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gates, c_prev, forget_bias):
+        E = ops.ext(required=True)
+        gates = gates.float().contiguous()
+        c_prev = c_prev.float().contiguous()
+        c = torch.empty_like(c_prev)
+        h = torch.empty(c_prev.shape, dtype=torch.bfloat16, device=c_prev.device)
+        E.lstm_cell_fwd(gates, c_prev, c, h, forget_bias)
+        ctx.save_for_backward(gates, c_prev, c)
+        ctx.fb = forget_bias
+        return c, h
+
+    @staticmethod
+    def backward(ctx, dc_next, dh):
+        E = ops.ext(required=True)
+        gates, c_prev, c = ctx.saved_tensors
+        dh = torch.zeros_like(c) if dh is None else dh.float().contiguous()
+        dgates = torch.empty_like(gates)
+        dc_prev = torch.empty_like(c)
+        E.lstm_cell_bwd(gates, c_prev, c, dh, None if dc_next is None else dc_next.float().contiguous(), dgates, dc_prev, ctx.fb)
+        return dgates, dc_prev, None
+
+
+def lstm_cell(gates, c_prev, forget_bias=1.0):
+    """Pointwise part of an LSTM step: ``gates`` [B, 4S] in the order i, j, f, o -> ``(c_new fp32, h bf16)``."""
+    if gates.is_cuda:
+        return _LSTMCellFn.apply(gates, c_prev, forget_bias)
+    i, j, f, o = gates.float().chunk(4, 1)
+    c = torch.sigmoid(f + forget_bias) * c_prev + torch.sigmoid(i) * torch.tanh(j)
+    return c, torch.sigmoid(o) * torch.tanh(c)
+
+
+def clip_by_global_norm_(grads, max_norm, weights=None, all_reduce=None):
+    """Scale fp32 CUDA gradients in place so that their joint L2 norm is at most ``max_norm``; the norm stays on the
+    device. ``weights`` weighs each tensor's squared sum (replicated tensors count once across ranks);
+    ``all_reduce`` (optional callable) sums the squared norm over ranks."""
+    E = ops.ext(required=True)
+    acc = torch.zeros(1, dtype=torch.float32, device=grads[0].device)
+    for k, g in enumerate(grads):
+        E.sumsq(g, acc, 1.0 if weights is None else weights[k])
+    if all_reduce is not None:
+        all_reduce(acc)
+    for g in grads:
+        E.clip_scale(g, acc, max_norm)
+    return acc

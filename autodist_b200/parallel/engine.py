@@ -333,6 +333,8 @@ class StepEngine:
             return
         max_norm, params = train_op.clip_global_norm
         ids = {id(p) for p in params}
+        if self.device.type == "cuda":
+            return self._clip_on_device(max_norm, ids)
         sq = torch.zeros((), dtype=torch.float64, device=self.device)
         touched = []
         for t in self._targets:
@@ -348,6 +350,28 @@ class StepEngine:
         if norm > max_norm:
             for g in touched:
                 g.mul_(max_norm / (norm + 1e-6))
+
+    def _clip_on_device(self, max_norm, ids):
+        """Global-norm clip with the sum-of-squares and scale kernels: the norm never visits the host."""
+        from autodist_b200.ops.functional import clip_by_global_norm_
+        ps_vars = {e.part.var_name for e in self.plan.ps_entries.values()}
+        grads, weights = [], []
+        for t in self._targets:
+            if id(t.full_param) not in ids or t.full_param.grad is None:
+                continue
+            g = t.grad_view(self._dense_grad(t.full_param))
+            if g.dtype != torch.float32 or not g.is_contiguous():
+                continue
+            replicated = t.part is None or t.var_name not in ps_vars
+            grads.append(g)
+            weights.append(1.0 / self.world_size if (replicated and self.world_size > 1) else 1.0)
+        if not grads:
+            return
+        reduce = None
+        if self.world_size > 1:
+            import torch.distributed as dist
+            reduce = lambda acc: dist.all_reduce(acc, group=getattr(self.backend, "group", None))   # noqa: E731
+        clip_by_global_norm_(grads, max_norm, weights, reduce)
 
     def _apply_local(self, train_op):
         info, local, group_map = self._local_optimizers[train_op.optimizer_index]

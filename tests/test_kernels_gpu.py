@@ -270,3 +270,60 @@ def test_optimizers_match_torch(E):
         torch.cuda.synchronize()
         assert (p - ref_p.detach()).abs().max().item() < 1e-5, name
         assert (p16.float() - p).abs().max().item() < 2e-2
+
+
+def test_functional_linear_matches_torch():
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(10)
+    x = (torch.randn(3, 40, 256, device="cuda") * 0.5).requires_grad_(True)
+    w = (torch.randn(512, 256, device="cuda") * 0.05).requires_grad_(True)
+    b = torch.randn(512, device="cuda").requires_grad_(True)
+    for act in (None, "gelu"):
+        for t in (x, w, b):
+            t.grad = None
+        y = Fn.linear(x.to(torch.bfloat16), w, b, activation=act)
+        dy = torch.randn_like(y.float())
+        y.float().backward(dy)
+        gx, gw, gb = x.grad.clone(), w.grad.clone(), b.grad.clone()
+        for t in (x, w, b):
+            t.grad = None
+        ref = torch.nn.functional.linear(x, w, b)
+        if act == "gelu":
+            ref = torch.nn.functional.gelu(ref, approximate="tanh")
+        ref.backward(dy)
+        _check(y, ref.detach(), 2e-2)
+        _check(gx, x.grad, 3e-2)
+        _check(gw, w.grad, 3e-2)
+        _check(gb, b.grad, 3e-2)
+    Fn.check_errors()
+
+
+def test_lstm_cell_and_clip(E):
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(11)
+    B, S = 16, 96
+    gates = torch.randn(B, 4 * S, device="cuda", requires_grad=True)
+    c_prev = torch.randn(B, S, device="cuda", requires_grad=True)
+    c, h = Fn.lstm_cell(gates, c_prev, 1.0)
+    dh, dc = torch.randn(B, S, device="cuda"), torch.randn(B, S, device="cuda")
+    (c * dc).sum().backward(retain_graph=True)
+    (h.float() * dh).sum().backward()
+    got = (gates.grad.clone(), c_prev.grad.clone())
+    gates.grad = c_prev.grad = None
+    i, j, f, o = gates.chunk(4, 1)
+    c_ref = torch.sigmoid(f + 1.0) * c_prev + torch.sigmoid(i) * torch.tanh(j)
+    h_ref = torch.sigmoid(o) * torch.tanh(c_ref)
+    ((c_ref * dc).sum() + (h_ref * dh).sum()).backward()
+    _check(c, c_ref.detach(), 1e-5)
+    _check(h, h_ref.detach(), 1e-2)
+    _check(got[0], gates.grad, 1e-2)      # h is rounded to bf16 on the way out; its gradient path is exact
+    _check(got[1], c_prev.grad, 1e-4)
+    gs = [torch.randn(1000, device="cuda") * 3, torch.randn(77, 13, device="cuda")]
+    ref_norm = torch.sqrt(sum((g ** 2).sum() for g in gs))
+    expect = [g * (5.0 / (ref_norm + 1e-6)) for g in gs]
+    Fn.clip_by_global_norm_(gs, 5.0)
+    for g, e in zip(gs, expect):
+        _check(g, e, 1e-5)
+    small = [torch.ones(4, device="cuda") * 0.1]
+    Fn.clip_by_global_norm_(small, 5.0)
+    assert torch.equal(small[0], torch.ones(4, device="cuda") * 0.1)
