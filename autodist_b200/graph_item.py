@@ -19,8 +19,7 @@ records, with a proto round-trip), rebuilt over ``torch.fx``:
 import contextlib
 import functools
 import json
-import operator
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -635,19 +634,13 @@ def patch_optimizers():
     torch.optim.Optimizer.__init__ = wrapped_init
 
     def minimize(self, loss, var_list=None, clip_global_norm=None):
+        """``train_op`` for ``loss``; ``clip_global_norm=(max_norm, [parameters])`` clips those gradients jointly."""
         item = get_default_graph_item()
-        if item is None:
-            for info_item in _items_holding(self):
-                item = info_item
         if item is None:
             raise RuntimeError("optimizer.minimize(loss) must be called inside ad.scope()")
         return item.extend_gradient_info(self, loss, var_list, clip_global_norm)
 
     torch.optim.Optimizer.minimize = minimize
-
-
-def _items_holding(optimizer):
-    return []
 
 
 def _patch_module_capture(item):
@@ -675,11 +668,3 @@ def _patch_module_capture(item):
         nn.Module.__call__ = orig_call
 
     return unpatch
-
-
-# Small symbolic helpers that read better than raw operator calls in user code.
-def reduce_mean(x):
-    return x.mean()
-
-
-getitem = operator.getitem

@@ -310,7 +310,6 @@ class BertPretrainer(nn.Module):
         gm(ws["d_pre"], cls, g["pooler.w"], a_mn=True, b_mn=True, bn=128)
         d_cls = d_seq.view(B, S, H)[:, 0]
         gm(ws["d_pre"], w16["pooler.w"], d_cls, b_mn=True, epi=EPI_ADD, aux=d_cls, bn=128)
-        names = fl.names
         ready(fl.offsets["pooler.w"], fl.total)
 
         d_out = d_seq
@@ -348,15 +347,10 @@ class BertPretrainer(nn.Module):
             gm(ws["d_qkv"], x_in, g[n + "qkv_w"], a_mn=True, b_mn=True)                 # dWqkv
             d_prev = dctx
             gm(ws["d_qkv"], w16[n + "qkv_w"], d_prev, b_mn=True, epi=EPI_ADD, aux=dz1)  # dx = dqkv . Wqkv + dz1
-            d_out = d_prev
-            if ph > 0:
-                pass
+            d_out = d_prev           # always ws["d_a"]: the two spare buffers hold this layer's dz / dropped copies
             lo = fl.offsets[n + "qkv_w"]
             hi = fl.offsets[f"layers.{l + 1}.qkv_w"] if l + 1 < c.num_hidden_layers else fl.offsets["pooler.w"]
             ready(lo, hi)
-            # keep d_out distinct from the two spare buffers for the next layer
-            if d_out is spare[0] or d_out is spare[1]:
-                raise AssertionError("buffer rotation broke")
         # embeddings
         dz0 = spare[0]
         E.ln_bwd(d_out, ws["z0"], ws["m0"], ws["r0"], w32["emb.ln_g"], None, dz0, None, ws["part"], g["emb.ln_g"], g["emb.ln_b"],

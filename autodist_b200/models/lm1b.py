@@ -68,7 +68,7 @@ class LM1B(nn.Module):
         c = self.config
         Bsz, T = x.shape
         dt = torch.bfloat16 if x.is_cuda else torch.float32
-        inputs = F.embedding(x, self.emb, sparse=x.is_cuda is False and False).to(dt)
+        inputs = F.embedding(x, self.emb).to(dt)
         if self.training and c.keep_prob < 1.0:
             inputs = F.dropout(inputs, 1.0 - c.keep_prob)
         h = torch.zeros(Bsz, c.projected_size, dtype=dt, device=x.device)

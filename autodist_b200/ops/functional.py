@@ -76,10 +76,6 @@ class _LinearFn(torch.autograd.Function):
         return dx.view(ctx.shape).to(dy.dtype), dw.to(ctx.w_dtype), db, None
 
 
-def _aligned(x, weight):
-    return x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 or (x.shape[-1] % 8 == 0 and weight.shape[0] >= 1)
-
-
 def linear(x, weight, bias=None, activation=None):
     """``activation(x @ weight.T + bias)`` with ``activation`` in ``{None, "gelu"}`` (tanh form)."""
     if x.is_cuda and x.shape[-1] % 8 == 0 and (weight.shape[0] % 8 == 0):
