@@ -50,11 +50,14 @@ def _fused_module(graph_item):
 
 def make_engine(graph_item, plan, backend, device):
     module = _fused_module(graph_item)
-    if module is not None and ENV.AUTODIST_COMM.val != "nccl" and FusedStepEngine.supports(graph_item, plan, module):
+    fused_comm = ENV.AUTODIST_COMM.val != "nccl"
+    if module is not None and fused_comm and FusedStepEngine.supports(graph_item, plan, module):
         return FusedStepEngine(graph_item, plan, backend, device, module)
     if module is not None:
         logging.info("fused model on the generic engine (communication through %s)", backend.name)
         return GenericFusedModelEngine(graph_item, plan, backend, device, module)
+    if fused_comm and FlatAutogradEngine.supports_autograd(graph_item, plan):
+        return FlatAutogradEngine(graph_item, plan, backend, device)
     return StepEngine(graph_item, plan, backend, device)
 
 
@@ -146,6 +149,9 @@ class FusedStepEngine(StepEngine):
     @staticmethod
     def supports(graph_item, plan, module):
         if len(graph_item.optimizers) != 1:
+            return False
+        if os.environ.get("AUTODIST_CLIP_UNSUPPORTED_IN_FUSED", "1") == "1" and any(
+                op.clip_global_norm for op in graph_item.train_ops):
             return False
         if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
             return False
@@ -607,3 +613,107 @@ class FusedStepEngine(StepEngine):
 
     def close(self):
         return
+
+
+class _AutogradModel:
+    """Adapter that gives an ordinary autograd program the flat-buffer face the fused engine expects."""
+
+    def __init__(self, graph_item):
+        self.item = graph_item
+        self.flat = None
+        self.grad_ready = None
+
+    def materialize(self, device, grad_alloc=None, master_alloc=None, p16_alloc=None):
+        from autodist_b200.ops.flat import FlatParams
+        with torch.no_grad():
+            for b in self.item.root.buffers():
+                b.data = b.data.to(device)
+        named = [(n[:-2], p) for n, p in self.item.named_parameters()]
+        frozen = [p for _, p in named if not p.requires_grad]
+        with torch.no_grad():
+            for p in frozen:
+                p.data = p.data.to(device)
+        self.flat = FlatParams([(n, p) for n, p in named if p.requires_grad], device, grad_alloc,
+                               master_alloc=master_alloc, p16_alloc=p16_alloc)
+        return self.flat
+
+    def check_error(self):
+        from autodist_b200.ops.functional import check_errors
+        check_errors()
+
+
+class FlatAutogradEngine(FusedStepEngine):
+    """Any ``torch.autograd`` program on the fused communication path.
+
+    Parameters and gradients are re-homed into flat buffers (gradients in symmetric memory); autograd accumulates
+    into those views in place, post-accumulate hooks report finished parameters, and as soon as a *flight* (a run
+    of consecutive parameters, at least ``AUTODIST_FLIGHT_MB`` of gradients) is complete its all-reduce /
+    reduce-scatter kernel and the fused optimizer kernel run on the communication stream while autograd continues.
+    This is how the CNN benchmarks (cuDNN convolutions) use the same synchronisation kernels as the fused models.
+    """
+
+    @staticmethod
+    def supports_autograd(graph_item, plan):
+        if len(graph_item.optimizers) != 1 or len(graph_item.optimizers[0].optimizer.param_groups) != 1:
+            return False
+        params = [p for _, p in graph_item.named_parameters() if p.requires_grad]
+        if not params or any(p.dtype != torch.float32 for p in params):
+            return False
+        if any(v.sparse_grad for v in graph_item.variables.values()):
+            return False
+        updated = graph_item.updated_variable_names()
+        if any(graph_item.name_of_parameter(p) not in updated for p in params):
+            return False
+        return FusedStepEngine.supports(graph_item, plan, None)
+
+    def __init__(self, graph_item, plan, backend, device):
+        super().__init__(graph_item, plan, backend, device, _AutogradModel(graph_item))
+        self._use_graph = False
+        fl = self.flat
+        limit = int(float(os.environ.get("AUTODIST_FLIGHT_MB", "32")) * (1 << 20) / 4)
+        # flights in backward order: consecutive parameters from the end of the flat buffer
+        self._flight_of, self._flights = {}, []
+        hi = fl.total
+        names = list(fl.names)
+        members = []
+        for name in reversed(names):
+            members.append(name)
+            lo = fl.offsets[name]
+            if hi - lo >= limit or name == names[0]:
+                self._flights.append({"lo": lo, "hi": hi, "need": len(members), "have": 0, "sent": False})
+                for m in members:
+                    self._flight_of[m] = len(self._flights) - 1
+                members, hi = [], lo
+        for name, p in zip(fl.names, fl.params):
+            p.register_post_accumulate_grad_hook(self._make_hook(name))
+
+    def _make_hook(self, name):
+        def hook(param):
+            f = self._flights[self._flight_of[name]]
+            f["have"] += 1
+            if f["have"] == f["need"] and not f["sent"]:
+                f["sent"] = True
+                self._on_grad_ready(f["lo"], f["hi"])
+        return hook
+
+    def _run_model(self, train_op, nodes, feeds):
+        all_nodes = list(nodes)
+        if train_op.loss_node not in all_nodes:
+            all_nodes.append(train_op.loss_node)
+        self.E.increment(self.opt_step)
+        self.launches_per_step = 0
+        fl = self.flat
+        fl.grad.zero_()
+        for f in self._flights:
+            f["have"], f["sent"] = 0, False
+        for name, p in zip(fl.names, fl.params):
+            p.grad = fl.g[name]                      # autograd adds into the flat views in place
+        values = self.forward(all_nodes, feeds, grad=True)
+        values[all_nodes.index(train_op.loss_node)].backward()
+        for f in self._flights:                      # parameters that received no gradient this step: still synchronised
+            if not f["sent"]:
+                f["sent"] = True
+                self._on_grad_ready(f["lo"], f["hi"])
+        self._done_event.record(self.comm_stream)
+        torch.cuda.current_stream().wait_event(self._done_event)
+        return values

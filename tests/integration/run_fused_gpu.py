@@ -54,9 +54,52 @@ def run(strategy_name, comm, world, rank, opt_name="sgd"):
     return state, p16, losses, engine
 
 
+def run_cnn(strategy_name, comm, world, rank):
+    """An ordinary autograd model (cuDNN convolutions + batch-norm + tcgen05 linear) on both engines."""
+    os.environ["AUTODIST_COMM"] = comm
+    from autodist_b200 import AutoDist, strategy as S
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.models.cnn import ImageClassifier, synthetic_images
+    from autodist_b200.resource_spec import ResourceSpec
+    _reset_default_autodist()
+    builders = {
+        "AllReduce": lambda: S.AllReduce(chunk_size=8),
+        "AllReduce_EF": lambda: S.AllReduce(chunk_size=8, compressor="HorovodCompressorEF"),
+        "PartitionedPS_gpu": lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu", local_proxy_variable=True),
+    }
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builders[strategy_name]())
+    data = synthetic_images(4 * world, 32, 16, seed=5)
+    with ad.scope():
+        torch.manual_seed(0)
+        model = ImageClassifier("vgg16", num_classes=16, image_size=32, compute_dtype=torch.float32)
+        images = ad.placeholder((None, 3, 32, 32), torch.float32, name="images")
+        labels = ad.placeholder((None,), torch.int64, name="labels")
+        loss = model(images, labels)
+        train_op = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9).minimize(loss)
+        sess = ad.create_distributed_session()
+        losses = [float(sess.run([loss, train_op], {images: data["images"], labels: data["labels"]})[0]) for _ in range(4)]
+        if hasattr(sess.engine, "check_errors"):
+            sess.engine.check_errors()
+        torch.cuda.synchronize()
+        state = torch.cat([sess.engine.variable_value(n).reshape(-1).float() for n, _ in ad.graph_item.named_parameters()])
+        engine = type(sess.engine).__name__
+        sess.close()
+    return state, losses, engine
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     failures = 0
+    for name in ("AllReduce", "AllReduce_EF", "PartitionedPS_gpu"):
+        ref, ref_losses, ref_engine = run_cnn(name, "nccl", world, rank)
+        got, losses, engine = run_cnn(name, "fused", world, rank)
+        diff = (got - ref).abs().max().item()
+        tol = 5e-3 if name == "AllReduce_EF" else 2e-3       # bf16 tensor-core linears + cuDNN reductions are not bitwise stable
+        ok = diff <= tol and engine == "FlatAutogradEngine" and ref_engine == "StepEngine" and all(l == l for l in losses)
+        failures += 0 if ok else 1
+        if rank == 0:
+            print(f"cnn {name}: engines {ref_engine} vs {engine}, max |param diff| {diff:.2e} (tol {tol}), "
+                  f"loss {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
     for name in ("AllReduce", "AllReduce_EF", "PSLoadBalancing_gpu", "PartitionedPS_gpu", "Parallax_gpu"):
         ref, _, ref_losses, ref_engine = run(name, "nccl", world, rank)
         got, p16, losses, engine = run(name, "fused", world, rank)
