@@ -280,6 +280,20 @@ void lstm_cell_bwd(const Tensor& gates, const Tensor& c_prev, const Tensor& c, c
 }
 void sumsq(const Tensor& x, Tensor acc, double weight) { adb200::sumsq(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)weight, STREAM); }
 void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_scale(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)max_norm, STREAM); }
+void psgd_p(Tensor M, const optional<Tensor>& err, const Tensor& Q, Tensor P) {
+  const int m = M.size(0), n = M.size(1), r = Q.size(1);
+  TORCH_CHECK(r >= 1 && r <= 4 && M.is_contiguous() && Q.is_contiguous() && P.is_contiguous(), "rank 1..4, contiguous fp32 operands");
+  adb200::psgd_p(M.data_ptr<float>(), OPT_F(err), Q.data_ptr<float>(), P.data_ptr<float>(), m, n, r, STREAM);
+}
+void psgd_q(const Tensor& M, const Tensor& P, Tensor Qn) {
+  const int m = M.size(0), n = M.size(1), r = P.size(1);
+  TORCH_CHECK(r >= 1 && r <= 4 && M.is_contiguous() && P.is_contiguous() && Qn.is_contiguous(), "rank 1..4, contiguous fp32 operands");
+  adb200::psgd_q(M.data_ptr<float>(), P.data_ptr<float>(), Qn.data_ptr<float>(), m, n, r, STREAM);
+}
+void psgd_d(Tensor M, Tensor err, const Tensor& P, const Tensor& Q) {
+  const int m = M.size(0), n = M.size(1), r = P.size(1);
+  adb200::psgd_d(M.data_ptr<float>(), err.data_ptr<float>(), P.data_ptr<float>(), Q.data_ptr<float>(), m, n, r, STREAM);
+}
 void cast_f32_bf16(const Tensor& x, Tensor y) { adb200::cast_f32_bf16(x.data_ptr<float>(), BF(y), x.numel(), STREAM); }
 void increment(Tensor c) { adb200::increment(reinterpret_cast<long long*>(c.data_ptr<int64_t>()), STREAM); }
 
@@ -384,6 +398,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("psgd_p", &psgd_p);
+  m.def("psgd_q", &psgd_q);
+  m.def("psgd_d", &psgd_d);
   m.def("lstm_cell_fwd", &lstm_cell_fwd);
   m.def("lstm_cell_bwd", &lstm_cell_bwd);
   m.def("sumsq", &sumsq);

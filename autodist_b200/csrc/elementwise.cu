@@ -656,6 +656,61 @@ __global__ void clip_scale_kernel(float* __restrict__ x, long long n, const floa
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= sc;
 }
 
+// ------------------------------------------------------------------------------------------------ PowerSGD (K8)
+// Rank-r (r <= 4) factors of an fp32 matrix M [m, n]; all three kernels are bandwidth-bound passes over M.
+//   psgd_p : M += err (in place); P[i, :] = M[i, :] . Q          one warp per row
+//   psgd_q : Qn[j, :] = sum_i M[i, j] * P[i, :]                  blocks own 32 columns, their warps split the rows
+//   psgd_d : err = M - P Q^T;  M = P Q^T                          elementwise
+constexpr int PSGD_MAXR = 4;
+
+__global__ void psgd_p_kernel(float* __restrict__ M, const float* __restrict__ err, const float* __restrict__ Q, float* __restrict__ P,
+                              int m, int n, int r) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= m) return;
+  float acc[PSGD_MAXR] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = lane; j < n; j += 32) {
+    const long long idx = (long long)row * n + j;
+    float v = M[idx];
+    if (err) { v += err[idx]; M[idx] = v; }
+    for (int k = 0; k < r; ++k) acc[k] += v * Q[(long long)j * r + k];
+  }
+  for (int k = 0; k < r; ++k) {
+    const float t = warp_sum(acc[k]);
+    if (lane == 0) P[(long long)row * r + k] = t;
+  }
+}
+
+__global__ void psgd_q_kernel(const float* __restrict__ M, const float* __restrict__ P, float* __restrict__ Qn, int m, int n, int r) {
+  __shared__ float sm[8][32][PSGD_MAXR];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
+  float acc[PSGD_MAXR] = {0.f, 0.f, 0.f, 0.f};
+  if (col < n)
+    for (int i = w; i < m; i += 8) {
+      const float v = M[(long long)i * n + col];
+      for (int k = 0; k < r; ++k) acc[k] += v * P[(long long)i * r + k];
+    }
+  for (int k = 0; k < PSGD_MAXR; ++k) sm[w][lane][k] = acc[k];
+  __syncthreads();
+  if (w == 0 && col < n)
+    for (int k = 0; k < r; ++k) {
+      float t = 0.f;
+      for (int i = 0; i < 8; ++i) t += sm[i][lane][k];
+      Qn[(long long)col * r + k] = t;
+    }
+}
+
+__global__ void psgd_d_kernel(float* __restrict__ M, float* __restrict__ err, const float* __restrict__ P, const float* __restrict__ Q,
+                              int m, int n, int r) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)m * n) return;
+  const int i = (int)(idx / n), j = (int)(idx % n);
+  float a = 0.f;
+  for (int k = 0; k < r; ++k) a += P[(long long)i * r + k] * Q[(long long)j * r + k];
+  err[idx] = M[idx] - a;
+  M[idx] = a;
+}
+
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = __float2bfloat16(x[i]);
@@ -767,6 +822,15 @@ void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t s
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st) {
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
+}
+void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st) {
+  psgd_p_kernel<<<blocks_for(m, 4), 128, 0, st>>>(M, err, Q, P, m, n, r);
+}
+void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st) {
+  psgd_q_kernel<<<blocks_for(n, 32), 256, 0, st>>>(M, P, Qn, m, n, r);
+}
+void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st) {
+  psgd_d_kernel<<<blocks_for((long long)m * n, 256), 256, 0, st>>>(M, err, P, Q, m, n, r);
 }
 void cast_f32_bf16(const float* x, bf16* y, long long n, cudaStream_t st) {
   cast_f32_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(x, y, n);

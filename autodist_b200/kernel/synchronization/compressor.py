@@ -146,6 +146,8 @@ class PowerSGDCompressor(CompressorEF):
     def reduce(self, flat, backend):
         layout = self._plan(flat)
         err = self._residual(flat)
+        if flat.is_cuda and flat.dtype == torch.float32 and self.rank <= 4:
+            return self._reduce_cuda(flat, err, layout, backend)
         flat.add_(err)
         mats = [(i, off, numel, mat) for i, (off, numel, mat) in enumerate(layout) if mat is not None]
         vecs = [(off, numel) for off, numel, mat in layout if mat is None]
@@ -183,6 +185,49 @@ class PowerSGDCompressor(CompressorEF):
             approx = pv @ qv.t()
             err[off:off + numel].view(m, n).copy_(M - approx)
             M.copy_(approx)
+            self.q[i] = qv.clone()
+        cursor = sum(p_sizes)
+        for off, numel in vecs:
+            flat[off:off + numel].copy_(msg1[cursor:cursor + numel])
+            cursor += numel
+        return flat
+
+    def _reduce_cuda(self, flat, err, layout, backend):
+        """Same algorithm on the hand-written kernels: three bandwidth-bound passes per matrix (P, Q, decompress)."""
+        from autodist_b200 import ops
+        E = ops.ext(required=True)
+        mats = [(i, off, numel, mat) for i, (off, numel, mat) in enumerate(layout) if mat is not None]
+        vecs = [(off, numel) for off, numel, mat in layout if mat is None]
+        r = self.rank
+        p_sizes = [mat[0] * r for _, _, _, mat in mats]
+        msg1 = flat.new_empty(sum(p_sizes) + sum(n for _, n in vecs))
+        cursor, p_views = 0, []
+        for (i, off, numel, (m, n)), psz in zip(mats, p_sizes):
+            M = flat[off:off + numel].view(m, n)
+            pv = msg1[cursor:cursor + psz].view(m, r)
+            E.psgd_p(M, err[off:off + numel].view(m, n), self._q_for(i, n, flat).contiguous(), pv)
+            p_views.append(pv)
+            cursor += psz
+        for off, numel in vecs:
+            flat[off:off + numel].add_(err[off:off + numel])
+            msg1[cursor:cursor + numel].copy_(flat[off:off + numel])
+            cursor += numel
+        backend.compressed_all_reduce_mean_(msg1, None, None)
+        q_sizes = [mat[1] * r for _, _, _, mat in mats]
+        msg2 = flat.new_empty(max(sum(q_sizes), 1))
+        cursor, q_views = 0, []
+        for (i, off, numel, (m, n)), pv, qsz in zip(mats, p_views, q_sizes):
+            orthogonalize_(pv)
+            qv = msg2[cursor:cursor + qsz].view(n, r)
+            E.psgd_q(flat[off:off + numel].view(m, n), pv, qv)
+            q_views.append(qv)
+            cursor += qsz
+        if mats:
+            backend.compressed_all_reduce_mean_(msg2[:sum(q_sizes)], None, None)
+        for off, numel in vecs:
+            err[off:off + numel].zero_()
+        for (i, off, numel, (m, n)), pv, qv in zip(mats, p_views, q_views):
+            E.psgd_d(flat[off:off + numel].view(m, n), err[off:off + numel].view(m, n), pv.contiguous(), qv.contiguous())
             self.q[i] = qv.clone()
         cursor = sum(p_sizes)
         for off, numel in vecs:

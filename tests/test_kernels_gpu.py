@@ -327,3 +327,24 @@ def test_lstm_cell_and_clip(E):
     small = [torch.ones(4, device="cuda") * 0.1]
     Fn.clip_by_global_norm_(small, 5.0)
     assert torch.equal(small[0], torch.ones(4, device="cuda") * 0.1)
+
+
+def test_power_sgd_kernels_match_the_torch_compressor():
+    from autodist_b200.kernel.synchronization.compressor import Compressor
+    from autodist_b200.parallel.comm import LocalBackend
+
+    class Bucket:
+        def member_shapes(self):
+            return [(96, 80), (80,), (33, 7, 5)]
+
+    torch.manual_seed(12)
+    flat = torch.randn(96 * 80 + 80 + 33 * 35)
+    for rank in (1, 2):
+        cpu = Compressor.create("PowerSGDCompressor", Bucket(), rank=rank)
+        gpu = Compressor.create("PowerSGDCompressor", Bucket(), rank=rank)
+        for step in range(3):
+            g = flat * (step + 1)
+            a = cpu.reduce(g.clone(), LocalBackend())
+            b = gpu.reduce(g.clone().cuda(), LocalBackend())
+            _check(b.cpu(), a, 1e-4)
+            _check(gpu.error.cpu(), cpu.error, 1e-4)
