@@ -68,7 +68,7 @@ class LM1B(nn.Module):
         c = self.config
         Bsz, T = x.shape
         dt = torch.bfloat16 if x.is_cuda else torch.float32
-        inputs = F.embedding(x, self.emb).to(dt)
+        inputs = F.embedding(x, self.emb, sparse=True).to(dt)     # row-sparse gradient: only the looked-up rows travel
         if self.training and c.keep_prob < 1.0:
             inputs = F.dropout(inputs, 1.0 - c.keep_prob)
         h = torch.zeros(Bsz, c.projected_size, dtype=dt, device=x.device)
@@ -88,10 +88,10 @@ class LM1B(nn.Module):
             self._gen = torch.Generator(device=x.device)
             self._gen.manual_seed(1234)
         neg = log_uniform_sample(c.num_sampled, c.vocab_size, self._gen, x.device)
-        true_w = F.embedding(targets, self.softmax_w).to(dt)
+        true_w = F.embedding(targets, self.softmax_w, sparse=True).to(dt)
         true_logit = (out * true_w).sum(1).float() + self.softmax_b[targets] - torch.log(
             c.num_sampled * log_uniform_prob(targets, c.vocab_size))
-        neg_w = F.embedding(neg, self.softmax_w).to(dt)
+        neg_w = F.embedding(neg, self.softmax_w, sparse=True).to(dt)
         neg_logit = (out @ neg_w.t()).float() + self.softmax_b[neg] - torch.log(c.num_sampled * log_uniform_prob(neg, c.vocab_size))
         neg_logit = neg_logit.masked_fill(neg[None, :] == targets[:, None], -1e9)     # remove accidental hits
         logits = torch.cat([true_logit[:, None], neg_logit], 1)
