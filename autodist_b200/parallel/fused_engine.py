@@ -462,6 +462,13 @@ class FusedStepEngine(StepEngine):
                 self._update_range(a, b)
             self.launches_per_step += 2 * len(covered)
 
+    def _comm_blocks(self, n_elems, nvls):
+        """Blocks of one all-reduce launch: enough to fill the links, few enough to leave the SMs to the GEMMs that
+        run next to it (the in-switch reduction needs far fewer threads than peer loads/stores)."""
+        forced = int(os.environ.get("AUTODIST_COMM_BLOCKS", "0"))
+        cap = forced or (32 if nvls else 96)
+        return max(1, min(cap, n_elems // (4 * 512 * self.world_size) + 1))
+
     def _all_reduce_range(self, lo, hi, wd, ef):
         n = hi - lo
         scale = 1.0 / self.world_size
@@ -469,12 +476,13 @@ class FusedStepEngine(StepEngine):
         if wd is None:
             ptrs = self._grad_sym["ptrs"] + lo * 4
             mc = self._grad_sym["mc"] + lo * 4 if self._grad_sym["mc"] else 0
-            self.E.allreduce(*ctx, ptrs, mc, 0, n, None, None, None, scale, 0)
+            self.E.allreduce(*ctx, ptrs, mc, 0, n, None, None, None, scale, self._comm_blocks(n, bool(mc)))
         else:
             ptrs = self._wire_ptrs + lo * 2
             mc = self._wire_mc + lo * 2 if self._wire_mc else 0
             g = self.flat.grad[lo:hi]
-            self.E.allreduce(*ctx, ptrs, mc, WIRE[wd], n, g, self._residual[lo:hi] if ef else None, g, scale, 0)
+            self.E.allreduce(*ctx, ptrs, mc, WIRE[wd], n, g, self._residual[lo:hi] if ef else None, g, scale,
+                             self._comm_blocks(n, bool(mc)))
 
     # ------------------------------------------------------------------ step
     def _run_model(self, train_op, nodes, feeds):
