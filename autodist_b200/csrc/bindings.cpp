@@ -307,7 +307,7 @@ adb200::SymCtx make_ctx(const Tensor& flag_ptrs, Tensor epochs, Tensor error, in
   c.world = (int)world;
   c.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   TORCH_CHECK(world >= 1 && world <= 8, "1 to 8 ranks supported");
-  TORCH_CHECK(epochs.numel() >= adb200::kMaxCommBlocks, "epoch array too small");
+  TORCH_CHECK(epochs.numel() >= adb200::kMaxCommBlocks + 2, "epoch array too small (blocks + 2 words)");
   return c;
 }
 

@@ -80,6 +80,40 @@ __device__ bool sym_barrier(const SymCtx& c) {
   return s_ok != 0;
 }
 
+// Grid-wide barrier among the blocks of this launch on this GPU (arrival count + generation word in device memory).
+// The cross-GPU barrier above pairs block b with the peers' block b only; where a phase reads data that *any* block
+// of a rank produced (the packed wire buffer, the reduced result), the blocks of that rank meet here first.
+// All blocks of a communication launch are resident at once (at most kMaxCommBlocks of 512 threads); the wait is bounded.
+__device__ bool grid_barrier(const SymCtx& c) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    uint32_t* count = c.epochs + kMaxCommBlocks;
+    volatile uint32_t* gen_p = c.epochs + kMaxCommBlocks + 1;
+    __threadfence();
+    const uint32_t gen = *gen_p;
+    if (atomicAdd(count, 1u) == gridDim.x - 1) {
+      atomicExch(count, 0u);
+      __threadfence();
+      atomicAdd(const_cast<uint32_t*>(gen_p), 1u);
+    } else {
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t it = 0;
+      while (*gen_p == gen) {
+        if (((++it) & 63u) == 0 && globaltimer_ns() - t0 > c.timeout_ns) {
+          s_ok = 0;
+          atomicExch(c.error, 300);
+          break;
+        }
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
 template <typename T> struct Wire;
 template <> struct Wire<float> {
   static constexpr int VEC = 4;
@@ -187,6 +221,7 @@ __global__ void __launch_bounds__(512) allreduce_kernel(SymCtx c, T* const* bufs
       }
       Wire<T>::store(mine + i * VEC, w);
     }
+    if (!grid_barrier(c)) return;      // every block of this rank has packed before any block tells the peers
   }
   if (!sym_barrier(c)) return;
   const long long chunk = (nvec + c.world - 1) / c.world;
@@ -220,6 +255,7 @@ __global__ void __launch_bounds__(512) allreduce_kernel(SymCtx c, T* const* bufs
   }
   if (!sym_barrier(c)) return;
   if (dst32) {
+    if (!grid_barrier(c)) return;      // every peer block has delivered its slice (all local blocks passed their barrier)
     for (long long i = tid; i < nvec; i += nthr) {
       float w[VEC];
       Wire<T>::load(mine + i * VEC, w);

@@ -11,7 +11,8 @@ constexpr int kMaxCommBlocks = 128;
 
 struct SymCtx {
   uint32_t* const* flags;      // device array [world]: rank r's flag words, laid out [block][sender]
-  uint32_t* epochs;            // local device array [kMaxCommBlocks]: barriers this block index has passed
+  uint32_t* epochs;            // local device array [kMaxCommBlocks + 2]: barriers each block index has passed, then the
+                               // two words (arrival count, generation) of the local grid-wide barrier
   int* error;                  // local device int: 0 = fine, 100+peer / 200+peer = a bounded wait gave up
   int rank, world;
   unsigned long long timeout_ns;

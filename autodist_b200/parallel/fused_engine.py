@@ -111,11 +111,11 @@ class SymmetricArena:
         nflags = self.E.MAX_COMM_BLOCKS * 8
         self.flags, self.flag_ptrs, _ = self.alloc(nflags, torch.int32)
         self.flags.zero_()
-        self.epochs = torch.zeros(self.E.MAX_COMM_BLOCKS, dtype=torch.int32, device=device)
+        self.epochs = torch.zeros(self.E.MAX_COMM_BLOCKS + 8, dtype=torch.int32, device=device)
         # a second, independent set of flags for kernels issued from another stream (barrier epochs are per channel)
         self.flags_b, self.flag_ptrs_b, _ = self.alloc(nflags, torch.int32)
         self.flags_b.zero_()
-        self.epochs_b = torch.zeros(self.E.MAX_COMM_BLOCKS, dtype=torch.int32, device=device)
+        self.epochs_b = torch.zeros(self.E.MAX_COMM_BLOCKS + 8, dtype=torch.int32, device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
         self.timeout_s = float(os.environ.get("AUTODIST_KERNEL_TIMEOUT", "20"))
         torch.cuda.synchronize()
