@@ -466,7 +466,7 @@ class FusedStepEngine(StepEngine):
         """Blocks of one all-reduce launch: enough to fill the links, few enough to leave the SMs to the GEMMs that
         run next to it (the in-switch reduction needs far fewer threads than peer loads/stores)."""
         forced = int(os.environ.get("AUTODIST_COMM_BLOCKS", "0"))
-        cap = forced or (32 if nvls else 96)
+        cap = forced or (64 if nvls else 96)
         return max(1, min(cap, n_elems // (4 * 512 * self.world_size) + 1))
 
     def _all_reduce_range(self, lo, hi, wd, ef):
@@ -509,14 +509,18 @@ class FusedStepEngine(StepEngine):
         return [v.detach() if isinstance(v, torch.Tensor) else v for v in values[:len(nodes)]]
 
     def _graphed_step(self, train_op, nodes, feeds):
-        key = (id(train_op), tuple(id(n) for n in nodes), tuple((k, tuple(v.shape)) for k, v in sorted(feeds.items())))
+        if any(n is not train_op.loss_node for n in nodes):
+            return self._run_model(train_op, nodes, feeds)       # fetches beyond the loss: run eagerly
+        # one capture serves both `run(train_op)` and `run([loss, train_op])`: the loss is always computed
+        requested, nodes = len(nodes), [train_op.loss_node]
+        key = (id(train_op), tuple((k, tuple(v.shape)) for k, v in sorted(feeds.items())))
         if self._graph is not None and self._graph[0] != key:
             self._graph = None
         if self._graph is None:
             if self._warm_steps < 2:
                 # run eagerly first: lazy initialisation (workspaces, kernel attributes) must not happen during capture
                 self._warm_steps += 1
-                return self._run_model(train_op, nodes, feeds)
+                return self._run_model(train_op, nodes, feeds)[:requested]
             static = {k: v.clone() for k, v in feeds.items()}
             torch.cuda.synchronize()
             if self.world_size > 1:
@@ -536,7 +540,7 @@ class FusedStepEngine(StepEngine):
         for k, v in feeds.items():
             static[k].copy_(v, non_blocking=True)
         graph.replay()
-        return out
+        return out[:requested]
 
     def sync_and_update(self, train_op):
         return

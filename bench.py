@@ -158,6 +158,8 @@ def main():
         # ---- warm-up (also builds workspaces and captures the CUDA graph)
         for i in range(args.warmup + 3):
             sess.run(train_op, feed(dev_batches, i))
+        for i in range(2):                                   # the end-to-end form of the call is warmed up as well
+            sess.run([loss, train_op], feed(host_batches, i))
         sess.engine.check_errors() if hasattr(sess.engine, "check_errors") else None
 
         sampler = ClockSampler(dev.index or 0) if rank == 0 else None
