@@ -87,6 +87,61 @@ def run_cnn(strategy_name, comm, world, rank):
     return state, losses, engine
 
 
+def check_checkpoint(world, rank):
+    """Save under PartitionedPS on the fused engine (owner segments + row-sharded embedding), restore under AllReduce:
+    the file holds full tensors under the original names and training continues from the same state."""
+    import tempfile
+    import torch.distributed as dist
+    os.environ["AUTODIST_COMM"] = "fused"
+    from autodist_b200 import AutoDist, strategy as S
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.checkpoint.saver import Saver
+    from autodist_b200.models.bert import BertConfig, BertPretrainer, synthetic_batch
+    from autodist_b200.resource_spec import ResourceSpec
+    cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    batch = synthetic_batch(cfg, 4, 128, 8, seed=10 + rank)
+    tmp = [tempfile.mkdtemp(prefix="adb_ckpt_") if rank == 0 else None]
+    path = None
+    states = []
+    for phase, builder in (("save", lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu")),
+                           ("restore", lambda: S.AllReduce(chunk_size=16))):
+        _reset_default_autodist()
+        ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builder())
+        with ad.scope():
+            torch.manual_seed(0 if phase == "save" else 5)
+            model = BertPretrainer(cfg)
+            phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in batch.items()}
+            loss = model(**phs)
+            train_op = torch.optim.Adam(model.parameters(), lr=1e-3).minimize(loss)
+            saver = Saver()
+            sess = ad.create_distributed_session()
+            feed = {phs[k]: batch[k] for k in phs}
+            if phase == "save":
+                dist.broadcast_object_list(tmp, src=0)
+                for _ in range(3):
+                    sess.run([loss, train_op], feed)
+                path = saver.save(sess, os.path.join(tmp[0], "m"), global_step=3)
+                states.append({n: sess.engine.variable_value(n).float().cpu().clone() for n, _ in ad.graph_item.named_parameters()})
+                dist.barrier()
+            else:
+                saver.restore(sess, path)
+                got = {n: sess.engine.variable_value(n).float().cpu() for n, _ in ad.graph_item.named_parameters()}
+                worst = max((got[n] - states[0][n]).abs().max().item() for n in got)
+                plain = torch.load(path, map_location="cpu", weights_only=False)
+                ok = worst == 0.0 and tuple(plain["variables"]["emb.word"].shape) == (cfg.vocab_size, cfg.hidden_size) \
+                    and tuple(plain["slots"]["emb.word/exp_avg"].shape) == (cfg.vocab_size, cfg.hidden_size) \
+                    and float(plain["slots"]["emb.word/exp_avg"].abs().sum()) > 0
+                lv, _ = sess.run([loss, train_op], feed)
+                ok = ok and lv == lv
+                if rank == 0:
+                    print(f"checkpoint PartitionedPS -> AllReduce: max |restored - saved| {worst:.1e}, next loss {float(lv):.4f} "
+                          f"{'ok' if ok else 'FAIL'}", flush=True)
+                sess.close()
+                return ok
+            sess.close()
+    return False
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     failures = 0
@@ -117,6 +172,8 @@ def main():
     failures += 0 if ok else 1
     if rank == 0:
         print(f"PartitionedPS_gpu adam: {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
+    failures += 0 if check_checkpoint(world, rank) else 1
+    if rank == 0:
         print("FUSED ENGINE CHECKS PASSED" if failures == 0 else "FUSED ENGINE CHECKS FAILED", flush=True)
     import torch.distributed as dist
     if dist.is_initialized():
