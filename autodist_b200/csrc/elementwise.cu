@@ -30,16 +30,23 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Counter-based dropout mask: the same (seed, index) gives the same decision in forward and backward.
-__device__ __forceinline__ uint32_t mix(uint64_t seed, uint64_t idx) {
+// Counter-based dropout mask: the same (seed, index) gives the same decision in forward and backward. One 64-bit
+// hash decides four neighbouring elements (16 bits each), so a vector of eight costs two hashes.
+__device__ __forceinline__ uint64_t mix(uint64_t seed, uint64_t idx) {
   uint64_t x = seed + idx * 0x9E3779B97F4A7C15ull;
   x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
   x ^= x >> 27; x *= 0x94D049BB133111EBull;
   x ^= x >> 31;
-  return (uint32_t)x;
+  return x;
 }
-__device__ __forceinline__ float keep_scale(uint64_t seed, uint64_t idx, uint32_t thresh, float inv_keep) {
-  return ((mix(seed, idx) >> 8) >= thresh) ? inv_keep : 0.0f;
+// Scales (0 or 1 / keep probability) of the eight elements starting at `base` (a multiple of 8).
+__device__ __forceinline__ void keep_scale8(uint64_t seed, uint64_t base, uint32_t thresh16, float inv_keep, float* out) {
+  const uint64_t h0 = mix(seed, base >> 2), h1 = mix(seed, (base >> 2) + 1);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    out[j] = (((uint32_t)(h0 >> (16 * j)) & 0xFFFFu) >= thresh16) ? inv_keep : 0.0f;
+    out[4 + j] = (((uint32_t)(h1 >> (16 * j)) & 0xFFFFu) >= thresh16) ? inv_keep : 0.0f;
+  }
 }
 __device__ __forceinline__ uint64_t step_seed(uint64_t seed, const long long* step) {
   return seed + (step ? (uint64_t)(*step) * 0x100000001B3ull : 0ull);
@@ -71,7 +78,7 @@ __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const int nvec = H / 8;
-  const uint32_t thresh = (uint32_t)(p_drop * 16777216.0f);
+  const uint32_t thresh = (uint32_t)(p_drop * 65536.0f);
   const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
   float v[MAXV][8];
@@ -83,8 +90,10 @@ __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict
       const long long off = (long long)warp * H + vec * 8;
       load8(x + off, v[i]);
       if (p_drop > 0.f) {
+        float ks[8];
+        keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+        for (int j = 0; j < 8; ++j) v[i][j] *= ks[j];
       }
       if (res) {
         float r[8];
@@ -129,7 +138,7 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
   extern __shared__ float sm[];   // [warps][H] x 2
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   const int nvec = H / 8;
-  const uint32_t thresh = (uint32_t)(p_drop * 16777216.0f);
+  const uint32_t thresh = (uint32_t)(p_drop * 65536.0f);
   const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
   float ag[MAXV][8], ab[MAXV][8];
@@ -178,8 +187,10 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
         }
         store8(dz + off, o);
         if (p_drop > 0.f && dx) {
+          float ks[8];
+          keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+          for (int j = 0; j < 8; ++j) o[j] *= ks[j];
           store8(dx + off, o);
         }
       }
@@ -376,7 +387,7 @@ __global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __re
     for (int j = 0; j < 8; ++j) { v[i][j] = __expf(v[i][j] - mx); s += v[i][j]; }
   const float inv = 1.0f / group_sum<TPR>(s);
   if (!live) return;
-  const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
+  const uint32_t thresh = (uint32_t)(pd * 65536.0f);
   const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
 #pragma unroll
@@ -386,8 +397,10 @@ __global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __re
     for (int j = 0; j < 8; ++j) v[i][j] *= inv;
     store8(p + off, v[i]);
     if (pd > 0.f && p_drop) {
+      float ks[8];
+      keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
+      for (int j = 0; j < 8; ++j) v[i][j] *= ks[j];
       store8(p_drop + off, v[i]);
     }
   }
@@ -402,7 +415,7 @@ __global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict
   const int t = (int)(gt % TPR);
   const bool live = row < rows;
   const long long rr = live ? row : rows - 1;
-  const uint32_t thresh = (uint32_t)(pd * 16777216.0f);
+  const uint32_t thresh = (uint32_t)(pd * 65536.0f);
   const float inv_keep = pd > 0.f ? 1.0f / (1.0f - pd) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
   float d[VPT][8], pr[VPT][8];
@@ -412,11 +425,14 @@ __global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict
     const long long off = rr * S + (t + TPR * i) * 8;
     load8(dp + off, d[i]);
     load8(p + off, pr[i]);
+    if (pd > 0.f) {
+      float ks[8];
+      keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (pd > 0.f) d[i][j] *= keep_scale(sd, (uint64_t)off + j, thresh, inv_keep);
-      s += d[i][j] * pr[i][j];
+      for (int j = 0; j < 8; ++j) d[i][j] *= ks[j];
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += d[i][j] * pr[i][j];
   }
   s = group_sum<TPR>(s);
   if (!live) return;
