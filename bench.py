@@ -67,6 +67,8 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0                      # one line per job, from rank 0
     print(json.dumps({
         "impl": "reference",
         "unavailable": "petuum/autodist needs TensorFlow 1.15-2.2 (CUDA 10, no sm_100 code) and protoc at install time; "
