@@ -72,7 +72,7 @@ def reference_arm(args):
     print(json.dumps({
         "impl": "reference",
         "unavailable": "petuum/autodist needs TensorFlow 1.15-2.2 (CUDA 10, no sm_100 code) and protoc at install time; "
-                       "neither is present offline: pip install of /root/reference fails in setup.py generate_proto"}))
+                       "neither is present offline: the offline pip install of the reference stops in its setup.py generate_proto step"}))
     return 0
 
 

@@ -41,10 +41,10 @@ def test_remote_command_dry_run(monkeypatch):
     rs = ResourceSpec(os.path.join(SPECS, "r4.yml"))
     c = SSHCluster(rs)
     c._ssh_conf = {"10.20.41.146": SSHConfig(username="root", port=12345, python_venv="source /opt/venv/bin/activate",
-                                             key_file="/root/.ssh/id_rsa", env={"LD_LIBRARY_PATH": "/usr/local/cuda/lib64"})}
+                                             key_file="/home/u/.ssh/id_rsa", env={"LD_LIBRARY_PATH": "/usr/local/cuda/lib64"})}
     cmd = c.remote_command(["python", "/abs/train.py", "--x", "1"], "10.20.41.146", {"AUTODIST_WORKER": "10.20.41.146:GPU:0"})
     joined = " ".join(cmd)
-    assert cmd[0] == "ssh" and "-p 12345" in joined and "-i /root/.ssh/id_rsa" in joined and "root@10.20.41.146" in joined
+    assert cmd[0] == "ssh" and "-p 12345" in joined and "-i /home/u/.ssh/id_rsa" in joined and "root@10.20.41.146" in joined
     assert "source /opt/venv/bin/activate" in joined and "AUTODIST_WORKER=10.20.41.146:GPU:0" in joined
     assert "LD_LIBRARY_PATH=/usr/local/cuda/lib64" in joined and "/abs/train.py" in joined
     assert c.remote_exec(["true"], "10.20.41.146") is None          # dry run: nothing is started
