@@ -2,20 +2,52 @@
 ``tf.keras.applications.{ResNet101, VGG16, InceptionV3, DenseNet121}`` with random weights).
 
 ResNet-101 (v1.5 bottlenecks), VGG-16, DenseNet-121 and a small Inception-style network are defined here from
-scratch. Convolutions, batch-norm and pooling run on PyTorch's cuDNN path in channels-last bf16 (library compute: the
-baseline these models are measured with until the implicit-GEMM convolution kernels land); the fully connected
+scratch. Pointwise (1x1) convolutions - two of the three convolutions of every ResNet bottleneck - and the fully connected
+layers run on the tcgen05 GEMM (`Conv1x1`, `Linear`); spatial convolutions, batch-norm and pooling run on PyTorch's cuDNN
+path in channels-last bf16 (library compute, labelled as such in the benchmark output). The fully connected
 layers - 25088x4096, 4096x4096, 4096x1000 for VGG-16 - run on the tcgen05 GEMM. ``ImageClassifier`` wraps a backbone
 and the loss into one leaf module.
 """
+import os
+
 import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import Linear
+from autodist_b200.ops.functional import Linear, linear
+
+
+class Conv1x1(nn.Conv2d):
+    """Pointwise convolution as a GEMM on the tcgen05 kernel: in channels-last memory a 1x1 convolution is
+    ``[N*H*W, Cin] x [Cout, Cin]^T``, forward, input gradient and weight gradient alike (a strided one subsamples first).
+    Falls back to the library convolution on CPU or for channel counts that are not multiples of 8."""
+
+    def __init__(self, cin, cout, stride=1, bias=False):
+        super().__init__(cin, cout, 1, stride, 0, bias=bias)
+
+    def forward(self, x):
+        cin, cout = self.in_channels, self.out_channels
+        if not (x.is_cuda and USE_TCGEN05_CONV1X1 and cin % 8 == 0 and cout % 8 == 0):
+            return super().forward(x)
+        if self.stride[0] > 1:
+            x = x[:, :, ::self.stride[0], ::self.stride[1]]
+        x = x.contiguous(memory_format=torch.channels_last)
+        n, _, h, w = x.shape
+        y = linear(x.permute(0, 2, 3, 1).reshape(n * h * w, cin), self.weight.view(cout, cin), self.bias)
+        return y.view(n, h, w, cout).permute(0, 3, 1, 2)
+
+
+USE_TCGEN05_CONV1X1 = os.environ.get("AUTODIST_CONV1X1", "tcgen05") == "tcgen05"
+
+
+def _conv(cin, cout, k, stride=1, padding=0, bias=False):
+    if k == 1 and padding == 0:
+        return Conv1x1(cin, cout, stride, bias=bias)
+    return nn.Conv2d(cin, cout, k, stride, padding, bias=bias)
 
 
 def _conv_bn(cin, cout, k, stride=1, padding=0):
-    return nn.Sequential(nn.Conv2d(cin, cout, k, stride, padding, bias=False), nn.BatchNorm2d(cout), nn.ReLU(inplace=True))
+    return nn.Sequential(_conv(cin, cout, k, stride, padding), nn.BatchNorm2d(cout), nn.ReLU(inplace=True))
 
 
 class Bottleneck(nn.Module):
@@ -26,10 +58,10 @@ class Bottleneck(nn.Module):
         cout = width * self.expansion
         self.a = _conv_bn(cin, width, 1)
         self.b = _conv_bn(width, width, 3, stride, 1)
-        self.c = nn.Sequential(nn.Conv2d(width, cout, 1, bias=False), nn.BatchNorm2d(cout))
+        self.c = nn.Sequential(_conv(width, cout, 1), nn.BatchNorm2d(cout))
         self.down = None
         if stride != 1 or cin != cout:
-            self.down = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.BatchNorm2d(cout))
+            self.down = nn.Sequential(_conv(cin, cout, 1, stride), nn.BatchNorm2d(cout))
 
     def forward(self, x):
         idn = x if self.down is None else self.down(x)
@@ -88,7 +120,7 @@ class VGG16(nn.Module):
 class _DenseLayer(nn.Module):
     def __init__(self, cin, growth):
         super().__init__()
-        self.f = nn.Sequential(nn.BatchNorm2d(cin), nn.ReLU(inplace=True), nn.Conv2d(cin, 4 * growth, 1, bias=False),
+        self.f = nn.Sequential(nn.BatchNorm2d(cin), nn.ReLU(inplace=True), _conv(cin, 4 * growth, 1),
                                nn.BatchNorm2d(4 * growth), nn.ReLU(inplace=True), nn.Conv2d(4 * growth, growth, 3, padding=1, bias=False))
 
     def forward(self, x):
@@ -105,7 +137,7 @@ class DenseNet121(nn.Module):
                 mods.append(_DenseLayer(c, growth))
                 c += growth
             if i + 1 < len(blocks):
-                mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True), nn.Conv2d(c, c // 2, 1, bias=False), nn.AvgPool2d(2, 2)]
+                mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True), _conv(c, c // 2, 1), nn.AvgPool2d(2, 2)]
                 c //= 2
         mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True)]
         self.features = nn.Sequential(*mods)

@@ -348,3 +348,22 @@ def test_power_sgd_kernels_match_the_torch_compressor():
             b = gpu.reduce(g.clone().cuda(), LocalBackend())
             _check(b.cpu(), a, 1e-4)
             _check(gpu.error.cpu(), cpu.error, 1e-4)
+
+
+def test_conv1x1_on_the_gemm_matches_the_library_convolution():
+    from autodist_b200.models.cnn import Conv1x1
+    torch.manual_seed(13)
+    for stride in (1, 2):
+        conv = Conv1x1(64, 128, stride).cuda()
+        x = torch.randn(4, 64, 14, 14, device="cuda").to(memory_format=torch.channels_last).requires_grad_(True)
+        y = conv(x.to(torch.bfloat16))
+        dy = torch.randn_like(y.float())
+        y.float().backward(dy)
+        gx, gw = x.grad.clone(), conv.weight.grad.clone()
+        x.grad = conv.weight.grad = None
+        ref = torch.nn.functional.conv2d(x, conv.weight, None, stride)
+        ref.backward(dy)
+        assert y.shape == ref.shape
+        _check(y, ref.detach(), 2e-2)
+        _check(gx, x.grad, 3e-2)
+        _check(gw, conv.weight.grad, 3e-2)
