@@ -351,7 +351,9 @@ def test_power_sgd_kernels_match_the_torch_compressor():
 
 
 def test_conv1x1_on_the_gemm_matches_the_library_convolution():
+    from autodist_b200.models import cnn
     from autodist_b200.models.cnn import Conv1x1
+    cnn.USE_TCGEN05_CONV1X1 = True
     torch.manual_seed(13)
     for stride in (1, 2):
         conv = Conv1x1(64, 128, stride).cuda()
