@@ -16,11 +16,15 @@ implements ``materialize`` / ``fused_forward_backward`` (e.g.
   learning rate) lives in device memory.
 
 Strategies this engine executes natively: all-reduce buckets with
-``NoneCompressor`` / ``HorovodCompressor`` / ``HorovodCompressorEF`` and
-(Parallax) row-sparse embedding variables on the sparse parameter-server path
-(``sparse_scatter_add`` to the owner shard, owner-side update, peer-shard
-gather). Anything else falls back to the generic engine over NCCL, which is
-also the measured baseline (``AUTODIST_COMM=nccl``).
+``NoneCompressor`` / ``HorovodCompressor`` / ``HorovodCompressorEF``
+(``allreduce_kernel``); parameter-server variables and shards with GPU owners as
+owned segments of the flat buffers (``reduce_scatter_update``: reduce to the
+owner, optimizer on the owner's state, parameter write-back to every rank); and
+row-sparse variables sharded one shard per rank, which are not replicated at all
+(``embedding_gather_peers`` for lookups, ``sparse_scatter_add`` into the owners'
+shards, owner-side update). Anything else (PowerSGD, relaxed parameter-server
+gates, clipping, partition axes other than 0) runs on the generic engine over
+NCCL, which is also the measured baseline (``AUTODIST_COMM=nccl``).
 """
 import os
 
@@ -150,9 +154,8 @@ class FusedStepEngine(StepEngine):
     def supports(graph_item, plan, module):
         if len(graph_item.optimizers) != 1:
             return False
-        if os.environ.get("AUTODIST_CLIP_UNSUPPORTED_IN_FUSED", "1") == "1" and any(
-                op.clip_global_norm for op in graph_item.train_ops):
-            return False
+        if any(op.clip_global_norm for op in graph_item.train_ops):
+            return False      # global-norm clipping sits between reduction and update: the generic engine does it
         if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
             return False
         if plan.replica.world_size > 1:
