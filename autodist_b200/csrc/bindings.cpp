@@ -78,8 +78,9 @@ CUtensorMap make_map(const Tensor& v, int box_outer) {
 
 // D = alpha * A.B^T (+ epilogue). a: [.., M, K] (K-major) or [.., K, M] (a_mn); b: [.., N, K] or [.., K, N] (b_mn);
 // c: [.., M, N] bf16 or fp32 view with unit inner stride.
-void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
-          const optional<Tensor>& c2, const optional<Tensor>& aux, double alpha, double beta, Tensor error_flag, int64_t bn) {
+void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
+               const optional<Tensor>& c2, const optional<Tensor>& aux, double alpha, double beta, Tensor error_flag, int64_t bn,
+               const optional<Tensor>& mask, double drop_p, int64_t drop_seed, const optional<Tensor>& drop_step) {
   const c10::cuda::CUDAGuard guard(a_.device());
   Tensor a = as4d(a_), b = as4d(b_), c = as4d(c_);
   const int M = a_mn ? a.size(3) : a.size(2), K = a_mn ? a.size(2) : a.size(3);
@@ -124,9 +125,47 @@ void gemm(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, i
     TORCH_CHECK(av.strides() == c.strides(), "pre-activation must share the strides of the output");
     p.aux = reinterpret_cast<const __nv_bfloat16*>(av.data_ptr());
   }
+  p.mask = nullptr; p.drop_p = 0.f; p.drop_seed = 0; p.drop_step = nullptr;
+  if (epilogue == adb200::EPI_SOFTMAX || epilogue == adb200::EPI_SOFTMAX_GRAD) {
+    TORCH_CHECK(bn == 128 && N == 128 && !p.c_is_fp32 && c.stride(2) == 128, "the softmax epilogues need N == 128 and a contiguous bf16 output row");
+    if (mask.has_value()) {
+      TORCH_CHECK(mask->scalar_type() == at::kFloat && mask->numel() == a.size(0) * 128, "fp32 mask [batch_hi, 128] needed");
+      p.mask = mask->data_ptr<float>();
+    }
+    p.drop_p = (float)drop_p;
+    p.drop_seed = (unsigned long long)drop_seed;
+    p.drop_step = drop_step.has_value() ? reinterpret_cast<const long long*>(drop_step->data_ptr<int64_t>()) : nullptr;
+    if (epilogue == adb200::EPI_SOFTMAX && c2.has_value()) {
+      Tensor c2v = as4d(*c2);
+      TORCH_CHECK(c2v.scalar_type() == at::kBFloat16 && c2v.strides() == c.strides(), "dropped copy must share the strides of the output");
+      p.C2 = reinterpret_cast<__nv_bfloat16*>(c2v.data_ptr());
+    }
+    if (epilogue == adb200::EPI_SOFTMAX_GRAD) {
+      TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16, "probabilities needed");
+      Tensor av = as4d(*aux);
+      TORCH_CHECK(av.strides() == c.strides(), "probabilities must share the strides of the output");
+      p.aux = reinterpret_cast<const __nv_bfloat16*>(av.data_ptr());
+    }
+  }
   p.error_flag = error_flag.data_ptr<int>();
   cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
+}
+
+void gemm(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
+          const optional<Tensor>& c2, const optional<Tensor>& aux, double alpha, double beta, Tensor error_flag, int64_t bn) {
+  TORCH_CHECK(epilogue <= adb200::EPI_BIAS_TANH, "use gemm_softmax for the softmax epilogues");
+  gemm_impl(a, b, c, a_mn, b_mn, epilogue, bias, c2, aux, alpha, beta, error_flag, bn, c10::nullopt, 0.0, 0, c10::nullopt);
+}
+
+// Attention products with the row softmax in the epilogue (rows of 128):
+//   grad == false: c = softmax(alpha * a.b^T + mask), c2 (optional) = dropout(c)
+//   grad == true : c = alpha * P * (d - sum(d * P)) with d = (a.b^T) * dropout mask and P = aux
+void gemm_softmax(const Tensor& a, const Tensor& b, Tensor c, const optional<Tensor>& c2, const optional<Tensor>& mask,
+                  const optional<Tensor>& aux, bool grad, double alpha, double drop_p, int64_t seed, const optional<Tensor>& step,
+                  Tensor error_flag) {
+  gemm_impl(a, b, c, false, false, grad ? adb200::EPI_SOFTMAX_GRAD : adb200::EPI_SOFTMAX, c10::nullopt, c2, aux, alpha, 0.0, error_flag,
+            128, mask, drop_p, seed, step);
 }
 
 // Y = A . W^T (+ bias) where W [N, K] is split by rows into `world` equal shards that live in the owners' symmetric
@@ -377,6 +416,7 @@ void staleness_gate(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_softmax", &gemm_softmax);
   m.def("gemm_gathered_b", &gemm_gathered_b);
   m.def("ln_fwd", &ln_fwd);
   m.def("ln_bwd", &ln_bwd);

@@ -130,6 +130,39 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Dropout decisions: the same counter-based function as the layernorm / softmax kernels (elementwise.cu), so a mask
+// drawn in a fused epilogue is reproduced by any other kernel from (seed, element offset).
+__device__ __forceinline__ uint64_t mix64(uint64_t seed, uint64_t idx) {
+  uint64_t x = seed + idx * 0x9E3779B97F4A7C15ull;
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return x;
+}
+__device__ __forceinline__ void keep_scale8(uint64_t seed, uint64_t base, uint32_t thresh16, float inv_keep, float* out) {
+  const uint64_t h0 = mix64(seed, base >> 2), h1 = mix64(seed, (base >> 2) + 1);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    out[j] = (((uint32_t)(h0 >> (16 * j)) & 0xFFFFu) >= thresh16) ? inv_keep : 0.0f;
+    out[4 + j] = (((uint32_t)(h1 >> (16 * j)) & 0xFFFFu) >= thresh16) ? inv_keep : 0.0f;
+  }
+}
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* src, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k = 0.7978845608028654f;
   float t = tanhf(k * (x + 0.044715f * x * x * x));
@@ -277,8 +310,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
       tc_fence_after();
       const long long coff = (long long)b_hi * p.strideC_hi + (long long)b_lo * p.strideC_lo + (long long)row * p.ldc;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+      bool handled = false;
+      if constexpr (BN == 128) {
+        if (p.epilogue == EPI_SOFTMAX || p.epilogue == EPI_SOFTMAX_GRAD) {
+          // One thread holds its whole row (128 columns): the row reduction needs no communication.
+          handled = true;
+          float x[128];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            __syncwarp();
+            tmem_ld16(t_row + c * 16, x + c * 16);
+          }
+          const uint32_t thresh = (uint32_t)(p.drop_p * 65536.0f);
+          const float inv_keep = p.drop_p > 0.f ? 1.0f / (1.0f - p.drop_p) : 1.0f;
+          const uint64_t sd = p.drop_seed + (p.drop_step ? (uint64_t)(*p.drop_step) * 0x100000001B3ull : 0ull);
+          if (row < p.M) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + coff;
+            if (p.epilogue == EPI_SOFTMAX) {
+              float mx = -INFINITY;
+#pragma unroll
+              for (int j = 0; j < 128; ++j) {
+                x[j] = x[j] * p.alpha + (p.mask ? __ldg(p.mask + (long long)b_hi * 128 + j) : 0.f);
+                mx = fmaxf(mx, x[j]);
+              }
+              float sum = 0.f;
+#pragma unroll
+              for (int j = 0; j < 128; ++j) { x[j] = __expf(x[j] - mx); sum += x[j]; }
+              const float inv = 1.0f / sum;
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[c * 8 + j] *= inv;
+                store8_bf16(out + c * 8, x + c * 8);
+                if (p.C2 != nullptr && p.drop_p > 0.f) {
+                  float ks[8], y[8];
+                  keep_scale8(sd, (uint64_t)(coff + c * 8), thresh, inv_keep, ks);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) y[j] = x[c * 8 + j] * ks[j];
+                  store8_bf16(p.C2 + coff + c * 8, y);
+                }
+              }
+            } else {
+              float s = 0.f;
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                float pr[8];
+                load8_bf16(p.aux + coff + c * 8, pr);
+                if (p.drop_p > 0.f) {
+                  float ks[8];
+                  keep_scale8(sd, (uint64_t)(coff + c * 8), thresh, inv_keep, ks);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) x[c * 8 + j] *= ks[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s += x[c * 8 + j] * pr[j];
+              }
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                float pr[8], y[8];
+                load8_bf16(p.aux + coff + c * 8, pr);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) y[j] = p.alpha * pr[j] * (x[c * 8 + j] - s);
+                store8_bf16(out + c * 8, y);
+              }
+            }
+          }
+        }
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
+      for (int c = 0; c < (handled ? 0 : BN / 16); ++c) {
         float v[16];
         __syncwarp();                          // tcgen05.ld is warp-collective: reconverge after predicated stores
         tmem_ld16(t_row + c * 16, v);

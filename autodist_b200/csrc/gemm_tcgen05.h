@@ -6,7 +6,8 @@
 
 namespace adb200 {
 
-enum GemmEpilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_MUL_GELU_GRAD = 3, EPI_ADD = 4, EPI_BIAS_TANH = 5 };
+enum GemmEpilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_MUL_GELU_GRAD = 3, EPI_ADD = 4, EPI_BIAS_TANH = 5,
+                    EPI_SOFTMAX = 6, EPI_SOFTMAX_GRAD = 7 };
 
 struct GemmParams {
   int M, N, K;                 // per batch entry
@@ -21,6 +22,13 @@ struct GemmParams {
   float alpha;                 // scale applied to the accumulator first
   float beta;                  // fp32 output only: 0 = overwrite, otherwise C += result
   int* error_flag;             // device int, set non-zero when a bounded wait gave up
+  // Row softmax fused into the epilogue (attention, N == 128 == tile width; one thread owns one row):
+  //   EPI_SOFTMAX      C = softmax(alpha * acc + mask[b_hi][col]); C2 (optional) = dropout(C)
+  //   EPI_SOFTMAX_GRAD C = alpha * P * (d - sum(d * P)), d = acc * dropout mask, P read from aux
+  const float* mask;           // additive fp32 mask [batch_hi, N] or null
+  float drop_p;                // dropout probability of the attention probabilities (0 = off)
+  unsigned long long drop_seed;
+  const long long* drop_step;  // device step counter mixed into the seed (null = none)
   int b_shard_rows;            // > 0: B is split by rows into shards of this many rows, shard s read through tmB.m[s]
 };
 

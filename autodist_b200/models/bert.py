@@ -105,6 +105,7 @@ class BertPretrainer(nn.Module):
         self._ws = None
         self._seed = 0x5EED
         self.training_dropout = True
+        self.fused_attention_softmax = True     # S == 128: softmax inside the QK^T / dP GEMM epilogues
 
     def sparse_grad_parameters(self):
         """Variables whose gradient is row-sparse (only when the output projection is untied)."""
@@ -228,6 +229,7 @@ class BertPretrainer(nn.Module):
         gm = lambda *a, **k: self._gemm(ws, *a, **k)   # noqa: E731
         seed = lambda l, site: self._seed + 64 * l + site   # noqa: E731
         scale = 1.0 / math.sqrt(D)
+        fused_sm = S == 128 and self.fused_attention_softmax
 
         ids = input_ids.reshape(-1)
         tts = segment_ids.reshape(-1)
@@ -254,8 +256,11 @@ class BertPretrainer(nn.Module):
             n = f"layers.{l}."
             gm(x, w16[n + "qkv_w"], A["qkv"], epi=EPI_BIAS, bias=w32[n + "qkv_b"])
             q, k, v = (heads_view(A["qkv"], i) for i in range(3))
-            gm(q, k, ws["scores"], bn=128)
-            E.softmax_fwd(ws["scores"], ws["mask"], A["p"], A["pd"] if pa > 0 else None, scale, pa, seed(l, 1), step)
+            if fused_sm:      # scores never leave the SM: scale, mask, softmax and dropout run in the GEMM epilogue
+                E.gemm_softmax(q, k, A["p"], A["pd"] if pa > 0 else None, ws["mask"], None, False, scale, pa, seed(l, 1), step, ws["err"])
+            else:
+                gm(q, k, ws["scores"], bn=128)
+                E.softmax_fwd(ws["scores"], ws["mask"], A["p"], A["pd"] if pa > 0 else None, scale, pa, seed(l, 1), step)
             gm(A["pd"] if pa > 0 else A["p"], v, ctx_view(A["ctx"]), b_mn=True, bn=64)
             gm(A["ctx"], w16[n + "out_w"], ws["tmp"], epi=EPI_BIAS, bias=w32[n + "out_b"])
             E.ln_fwd(ws["tmp"], x, w32[n + "ln1_g"], w32[n + "ln1_b"], A["z1"], A["x1"], A["m1"], A["r1"], eps, ph, seed(l, 2), step)
@@ -338,9 +343,12 @@ class BertPretrainer(nn.Module):
             q, k, v = (heads_view(A["qkv"], i) for i in range(3))
             dq, dk, dv = (heads_view(ws["d_qkv"], i) for i in range(3))
             pdrop = A["pd"] if pa > 0 else A["p"]
-            gm(ctx_view(dctx), v, ws["d_p"], bn=128)                                    # dP = dctx . V^T
             gm(pdrop, ctx_view(dctx), dv, a_mn=True, b_mn=True, bn=64)                  # dV = P^T . dctx
-            E.softmax_bwd(ws["d_p"], A["p"], scale, pa, seed(l, 1), step)               # dS (in place)
+            if fused_sm:      # dS = scale * P * (dP - sum(dP * P)) in the epilogue of dP = dctx . V^T
+                E.gemm_softmax(ctx_view(dctx), v, ws["d_p"], None, None, A["p"], True, scale, pa, seed(l, 1), step, ws["err"])
+            else:
+                gm(ctx_view(dctx), v, ws["d_p"], bn=128)                                # dP = dctx . V^T
+                E.softmax_bwd(ws["d_p"], A["p"], scale, pa, seed(l, 1), step)           # dS (in place)
             gm(ws["d_p"], k, dq, b_mn=True, bn=64)                                      # dQ = dS . K
             gm(ws["d_p"], q, dk, a_mn=True, b_mn=True, bn=64)                           # dK = dS^T . Q
             E.keyed_colsum(ws["d_qkv"], None, ws["part"], g[n + "qkv_b"], 1, False)

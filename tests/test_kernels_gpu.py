@@ -369,3 +369,34 @@ def test_conv1x1_on_the_gemm_matches_the_library_convolution():
         _check(y, ref.detach(), 2e-2)
         _check(gx, x.grad, 3e-2)
         _check(gw, conv.weight.grad, 3e-2)
+
+
+@pytest.mark.parametrize("pd", [0.0, 0.1])
+def test_softmax_fused_into_the_attention_gemms(E, err, pd):
+    """QK^T with scale + mask + softmax (+ dropout) in the epilogue, and dP -> dS likewise, against the two-kernel path."""
+    torch.manual_seed(14)
+    B, Hh, S, D = 2, 3, 128, 64
+    q, k, v = _rand(B, Hh, S, D, scale=0.7), _rand(B, Hh, S, D, scale=0.7), _rand(B, Hh, S, D)
+    mask = torch.zeros(B, S, device="cuda")
+    mask[:, 120:] = -10000.0
+    step = torch.full((1,), 3, dtype=torch.int64, device="cuda")
+    scores = torch.empty(B, Hh, S, S, dtype=torch.bfloat16, device="cuda")
+    p_ref, pd_ref = torch.empty_like(scores), torch.empty_like(scores)
+    E.gemm(q, k, scores, False, False, 0, None, None, None, 1.0, 0.0, err, 128)
+    E.softmax_fwd(scores, mask, p_ref, pd_ref if pd > 0 else None, 0.125, pd, 99, step)
+    p, pdrop = torch.empty_like(scores), torch.empty_like(scores)
+    E.gemm_softmax(q, k, p, pdrop if pd > 0 else None, mask, None, False, 0.125, pd, 99, step, err)
+    exact = torch.softmax((q.float() @ k.float().transpose(-1, -2)) * 0.125 + mask[:, None, None, :], -1)
+    _check(p, exact, 1e-2)                      # the fused form never rounds the scores to bf16
+    _check(p, p_ref.float(), 2e-2)
+    if pd > 0:
+        assert torch.equal(pdrop == 0, pd_ref == 0)          # the same dropout decisions as the stand-alone kernel
+    dctx = _rand(B, Hh, S, D, scale=0.3)
+    ds_ref = torch.empty_like(scores)
+    E.gemm(dctx, v, ds_ref, False, False, 0, None, None, None, 1.0, 0.0, err, 128)
+    E.softmax_bwd(ds_ref, p, 0.125, pd, 99, step)
+    ds = torch.empty_like(scores)
+    E.gemm_softmax(dctx, v, ds, None, None, p, True, 0.125, pd, 99, step, err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(ds, ds_ref.float(), 3e-2)
