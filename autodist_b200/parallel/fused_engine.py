@@ -531,8 +531,14 @@ class FusedStepEngine(StepEngine):
             graph = torch.cuda.CUDAGraph()
             from autodist_b200 import ops
             before = ops.launch_count
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                out = self._run_model(train_op, nodes, static)
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    out = self._run_model(train_op, nodes, static)
+            except Exception as e:       # a program that cannot be captured keeps running eagerly
+                logging.warning("CUDA graph capture failed (%s); continuing with eager launches", e)
+                self._use_graph = False
+                torch.cuda.synchronize()
+                return self._run_model(train_op, nodes, feeds)[:requested]
             self.graph_kernels = ops.launch_count - before   # kernels of this extension per replay
             self._graph = (key, graph, static, out)
             torch.cuda.synchronize()
@@ -683,7 +689,9 @@ class FlatAutogradEngine(FusedStepEngine):
 
     def __init__(self, graph_item, plan, backend, device):
         super().__init__(graph_item, plan, backend, device, _AutogradModel(graph_item))
-        self._use_graph = False
+        # Whole-step capture of an autograd program (forward, backward, flights) is opt-in: AUTODIST_AUTOGRAD_GRAPH=1.
+        self._use_graph = os.environ.get("AUTODIST_AUTOGRAD_GRAPH", "0") == "1"
+        self._warm_needed = 3
         fl = self.flat
         limit = int(float(os.environ.get("AUTODIST_FLIGHT_MB", "32")) * (1 << 20) / 4)
         # flights in backward order: consecutive parameters from the end of the flat buffer
