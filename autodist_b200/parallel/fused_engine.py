@@ -689,8 +689,10 @@ class FlatAutogradEngine(FusedStepEngine):
 
     def __init__(self, graph_item, plan, backend, device):
         super().__init__(graph_item, plan, backend, device, _AutogradModel(graph_item))
-        # Whole-step capture of an autograd program (forward, backward, flights) is opt-in: AUTODIST_AUTOGRAD_GRAPH=1.
-        self._use_graph = os.environ.get("AUTODIST_AUTOGRAD_GRAPH", "0") == "1"
+        # The whole step of an autograd program (forward, backward, hooks and their flights) is captured into one CUDA
+        # graph after two eager steps; AUTODIST_AUTOGRAD_GRAPH=0 keeps eager launches (needed for programs whose
+        # control flow depends on data). A capture that fails falls back to eager launches by itself.
+        self._use_graph = os.environ.get("AUTODIST_AUTOGRAD_GRAPH", "1") == "1"
         self._warm_needed = 3
         fl = self.flat
         limit = int(float(os.environ.get("AUTODIST_FLIGHT_MB", "32")) * (1 << 20) / 4)

@@ -215,7 +215,8 @@ def main():
         "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(value / (published * n_gpus), 2) if published and args.model == "bert-large" else (
             round(value / (PUBLISHED_RESNET101.get(n_gpus, 0) * n_gpus), 2) if args.model == "resnet101" and n_gpus in PUBLISHED_RESNET101 else None),
-        "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM positions, random-init weights)",
+        "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM positions, random-init weights)" if is_bert
+        else "synthetic (images ~ N(0,1), uniform labels over 1000 classes, random-init weights)",
         "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq if is_bert else None,
                    "max_predictions": max_pred if is_bert else None,
                    "compute": "hand-written sm_100a kernels" if is_bert else "cuDNN convolutions (library) + tcgen05 GEMM for fully connected layers",
