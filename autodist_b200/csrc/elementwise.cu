@@ -232,6 +232,26 @@ __global__ void colsum_f32_kernel(const float* __restrict__ part, float* __restr
   }
 }
 
+// Two reductions in one launch (layernorm's dgamma and dbeta): blockIdx.y picks the pair.
+__global__ void colsum2_f32_kernel(const float* __restrict__ part_a, float* __restrict__ out_a, const float* __restrict__ part_b,
+                                   float* __restrict__ out_b, int parts, int H, int accumulate) {
+  __shared__ float sm[8][33];
+  const float* part = blockIdx.y ? part_b : part_a;
+  float* out = blockIdx.y ? out_b : out_a;
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
+  float a = 0.f;
+  if (c < H)
+    for (int r = w; r < parts; r += 8) a += part[(long long)r * H + c];
+  sm[w][threadIdx.x & 31] = a;
+  __syncthreads();
+  if (w == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ embeddings
 // z[row] = word[ids[row]] + pos[row % S] + type[tt[row]]  (bf16 tables), then the layernorm kernel runs on z.
 __global__ void embed_sum_kernel(const bf16* __restrict__ word, const bf16* __restrict__ pos, const bf16* __restrict__ type,
@@ -750,8 +770,7 @@ void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd,
   const int blocks = ln_bwd_blocks(rows);
   ln_bwd_kernel<<<blocks, 128, 2 * 4 * H * sizeof(float), st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part_g, part_b, rows, H,
                                                                 p_drop, seed, step);
-  colsum_f32_kernel<<<blocks_for(H, 32), 256, 0, st>>>(part_g, dgamma, blocks, H, accumulate);
-  colsum_f32_kernel<<<blocks_for(H, 32), 256, 0, st>>>(part_b, dbeta, blocks, H, accumulate);
+  colsum2_f32_kernel<<<dim3(blocks_for(H, 32), 2), 256, 0, st>>>(part_g, dgamma, part_b, dbeta, blocks, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
                int H, cudaStream_t st) {
