@@ -319,6 +319,21 @@ void lstm_cell_bwd(const Tensor& gates, const Tensor& c_prev, const Tensor& c, c
 }
 void sumsq(const Tensor& x, Tensor acc, double weight) { adb200::sumsq(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)weight, STREAM); }
 void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_scale(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)max_norm, STREAM); }
+// x: channels-last activations viewed as [N, H, W, C] bf16 contiguous; cols: [N*Ho*Wo, KH*KW*C]
+void im2col(const Tensor& x, Tensor cols, int64_t KH, int64_t KW, int64_t stride, int64_t pad) {
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.size(3) % 8 == 0, "x must be contiguous bf16 [N, H, W, C], C % 8 == 0");
+  const int N = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);
+  const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
+  TORCH_CHECK(cols.numel() == (int64_t)N * Ho * Wo * KH * KW * C, "cols has the wrong size");
+  adb200::im2col(CBF(x), BF(cols), N, H, W, C, KH, KW, stride, pad, Ho, Wo, STREAM);
+}
+void col2im(const Tensor& dcols, Tensor dx, int64_t KH, int64_t KW, int64_t stride, int64_t pad) {
+  TORCH_CHECK(dx.dim() == 4 && dx.is_contiguous() && dx.scalar_type() == at::kBFloat16 && dx.size(3) % 8 == 0, "dx must be contiguous bf16 [N, H, W, C]");
+  const int N = dx.size(0), H = dx.size(1), W = dx.size(2), C = dx.size(3);
+  const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
+  TORCH_CHECK(dcols.numel() == (int64_t)N * Ho * Wo * KH * KW * C, "dcols has the wrong size");
+  adb200::col2im(CBF(dcols), BF(dx), N, H, W, C, KH, KW, stride, pad, Ho, Wo, STREAM);
+}
 void psgd_p(Tensor M, const optional<Tensor>& err, const Tensor& Q, Tensor P) {
   const int m = M.size(0), n = M.size(1), r = Q.size(1);
   TORCH_CHECK(r >= 1 && r <= 4 && M.is_contiguous() && Q.is_contiguous() && P.is_contiguous(), "rank 1..4, contiguous fp32 operands");
@@ -438,6 +453,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("im2col", &im2col);
+  m.def("col2im", &col2im);
   m.def("psgd_p", &psgd_p);
   m.def("psgd_q", &psgd_q);
   m.def("psgd_d", &psgd_d);

@@ -692,6 +692,57 @@ __global__ void clip_scale_kernel(float* __restrict__ x, long long n, const floa
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= sc;
 }
 
+// ------------------------------------------------------------------------------------------------ convolution as GEMM (K10)
+// Channels-last activations x [N, H, W, C] (C a multiple of 8). im2col lays the receptive fields out as the rows of the
+// GEMM operand cols [N*Ho*Wo, KH*KW*C] (tap-major, channel-minor, matching a weight reshaped to [Cout, KH, KW, C]);
+// col2im is its adjoint in gather form: every input pixel sums the taps that read it, so no atomics are needed.
+__global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, int N, int H, int W, int C, int KH, int KW,
+                              int stride, int pad, int Ho, int Wo) {
+  const int c8 = C / 8;
+  const long long total = (long long)N * Ho * Wo * KH * KW * c8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % c8);
+  long long r = idx / c8;
+  const int tap = (int)(r % (KH * KW));
+  r /= (KH * KW);
+  const int wo = (int)(r % Wo), ho = (int)((r / Wo) % Ho), n = (int)(r / ((long long)Wo * Ho));
+  const int hi = ho * stride - pad + tap / KW, wi = wo * stride - pad + tap % KW;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (hi >= 0 && hi < H && wi >= 0 && wi < W)
+    v = *reinterpret_cast<const uint4*>(x + (((long long)n * H + hi) * W + wi) * C + cv * 8);
+  *reinterpret_cast<uint4*>(cols + idx * 8) = v;
+}
+
+__global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__ dx, int N, int H, int W, int C, int KH, int KW,
+                              int stride, int pad, int Ho, int Wo) {
+  const int c8 = C / 8;
+  const long long total = (long long)N * H * W * c8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int cv = (int)(idx % c8);
+  long long r = idx / c8;
+  const int wi = (int)(r % W), hi = (int)((r / W) % H), n = (int)(r / ((long long)W * H));
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int kh = 0; kh < KH; ++kh) {
+    const int hn = hi + pad - kh;
+    if (hn < 0 || hn % stride) continue;
+    const int ho = hn / stride;
+    if (ho >= Ho) continue;
+    for (int kw = 0; kw < KW; ++kw) {
+      const int wn = wi + pad - kw;
+      if (wn < 0 || wn % stride) continue;
+      const int wo = wn / stride;
+      if (wo >= Wo) continue;
+      float v[8];
+      load8(dcols + ((((long long)n * Ho + ho) * Wo + wo) * (KH * KW) + kh * KW + kw) * C + cv * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+  store8(dx + idx * 8, acc);
+}
+
 // ------------------------------------------------------------------------------------------------ PowerSGD (K8)
 // Rank-r (r <= 4) factors of an fp32 matrix M [m, n]; all three kernels are bandwidth-bound passes over M.
 //   psgd_p : M += err (in place); P[i, :] = M[i, :] . Q          one warp per row
@@ -857,6 +908,14 @@ void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t s
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st) {
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
+}
+void im2col(const bf16* x, bf16* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
+  const long long total = (long long)N * Ho * Wo * KH * KW * (C / 8);
+  im2col_kernel<<<blocks_for(total, 256), 256, 0, st>>>(x, cols, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
+}
+void col2im(const bf16* dcols, bf16* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
+  const long long total = (long long)N * H * W * (C / 8);
+  col2im_kernel<<<blocks_for(total, 256), 256, 0, st>>>(dcols, dx, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
 }
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st) {
   psgd_p_kernel<<<blocks_for(m, 4), 128, 0, st>>>(M, err, Q, P, m, n, r);

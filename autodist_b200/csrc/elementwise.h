@@ -42,6 +42,8 @@ void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, cons
                    float* dc_prev, int B, int S, float fb, cudaStream_t st);
 void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st);
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
+void im2col(const bf16_t* x, bf16_t* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
+void col2im(const bf16_t* dcols, bf16_t* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st);
 void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st);
 void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st);

@@ -14,7 +14,7 @@ import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import Linear, linear
+from autodist_b200.ops.functional import Linear, conv2d, linear
 
 
 class Conv1x1(nn.Conv2d):
@@ -42,10 +42,25 @@ class Conv1x1(nn.Conv2d):
 USE_TCGEN05_CONV1X1 = os.environ.get("AUTODIST_CONV1X1", "cudnn") == "tcgen05"
 
 
+class ConvGemm(nn.Conv2d):
+    """k x k convolution as im2col + tcgen05 GEMM (``ops.functional.conv2d``): forward, input gradient and weight gradient
+    on the hand-written kernels. Selected with ``AUTODIST_CONV=gemm``; the default stays the library convolution, which
+    is faster today (the im2col matrix is materialised)."""
+
+    def forward(self, x):
+        if x.is_cuda and USE_GEMM_CONV and self.groups == 1 and self.dilation == (1, 1) and self.stride[0] == self.stride[1] \
+                and self.padding[0] == self.padding[1]:
+            return conv2d(x, self.weight, self.bias, self.stride[0], self.padding[0])
+        return super().forward(x)
+
+
+USE_GEMM_CONV = os.environ.get("AUTODIST_CONV", "cudnn") == "gemm"
+
+
 def _conv(cin, cout, k, stride=1, padding=0, bias=False):
     if k == 1 and padding == 0:
         return Conv1x1(cin, cout, stride, bias=bias)
-    return nn.Conv2d(cin, cout, k, stride, padding, bias=bias)
+    return ConvGemm(cin, cout, k, stride, padding, bias=bias)
 
 
 def _conv_bn(cin, cout, k, stride=1, padding=0):
@@ -106,7 +121,7 @@ class VGG16(nn.Module):
             if v == "M":
                 layers.append(nn.MaxPool2d(2, 2))
             else:
-                layers += [nn.Conv2d(cin, v, 3, padding=1), nn.ReLU(inplace=True)]
+                layers += [_conv(cin, v, 3, 1, 1, bias=True), nn.ReLU(inplace=True)]
                 cin = v
         self.features = nn.Sequential(*layers)
         side = image_size // 32
@@ -123,7 +138,7 @@ class _DenseLayer(nn.Module):
     def __init__(self, cin, growth):
         super().__init__()
         self.f = nn.Sequential(nn.BatchNorm2d(cin), nn.ReLU(inplace=True), _conv(cin, 4 * growth, 1),
-                               nn.BatchNorm2d(4 * growth), nn.ReLU(inplace=True), nn.Conv2d(4 * growth, growth, 3, padding=1, bias=False))
+                               nn.BatchNorm2d(4 * growth), nn.ReLU(inplace=True), _conv(4 * growth, growth, 3, 1, 1))
 
     def forward(self, x):
         return torch.cat([x, self.f(x)], 1)

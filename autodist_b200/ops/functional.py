@@ -137,3 +137,57 @@ def clip_by_global_norm_(grads, max_norm, weights=None, all_reduce=None):
     for g in grads:
         E.clip_scale(g, acc, max_norm)
     return acc
+
+
+class _ConvGemmFn(torch.autograd.Function):
+    """2-D convolution as im2col + tcgen05 GEMM (forward, input gradient, weight gradient), channels-last bf16."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding):
+        E = ops.ext(required=True)
+        cout, cin, kh, kw = weight.shape
+        xh = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()            # [N, H, W, C]
+        n, h, w, _ = xh.shape
+        ho, wo = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
+        w2 = weight.permute(0, 2, 3, 1).reshape(cout, kh * kw * cin).to(torch.bfloat16).contiguous()
+        cols = torch.empty(n * ho * wo, kh * kw * cin, dtype=torch.bfloat16, device=x.device)
+        E.im2col(xh, cols, kh, kw, stride, padding)
+        y = torch.empty(n * ho * wo, cout, dtype=torch.bfloat16, device=x.device)
+        err = _error_flag(x.device)
+        if bias is not None:
+            E.gemm(cols, w2, y, False, False, 1, bias.float().contiguous(), None, None, 1.0, 0.0, err, 0)
+        else:
+            E.gemm(cols, w2, y, False, False, 0, None, None, None, 1.0, 0.0, err, 0)
+        ctx.save_for_backward(xh, w2)
+        ctx.geom = (kh, kw, stride, padding, ho, wo, cin, cout)
+        ctx.has_bias = bias is not None
+        ctx.w_dtype, ctx.x_dtype = weight.dtype, x.dtype
+        return y.view(n, ho, wo, cout).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        E = ops.ext(required=True)
+        xh, w2 = ctx.saved_tensors
+        kh, kw, stride, padding, ho, wo, cin, cout = ctx.geom
+        n = xh.shape[0]
+        err = _error_flag(dy.device)
+        dy2 = dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous().view(n * ho * wo, cout)
+        cols = torch.empty(n * ho * wo, kh * kw * cin, dtype=torch.bfloat16, device=dy.device)
+        E.im2col(xh, cols, kh, kw, stride, padding)                            # recomputed: cheaper than keeping it
+        dw2 = torch.empty(cout, kh * kw * cin, dtype=torch.float32, device=dy.device)
+        E.gemm(dy2, cols, dw2, True, True, 0, None, None, None, 1.0, 0.0, err, 0)      # dW = dY^T . cols
+        dcols = cols                                                            # reuse the buffer
+        E.gemm(dy2, w2, dcols, False, True, 0, None, None, None, 1.0, 0.0, err, 0)     # dcols = dY . W
+        dx = torch.empty_like(xh)
+        E.col2im(dcols, dx, kh, kw, stride, padding)
+        dw = dw2.view(cout, kh, kw, cin).permute(0, 3, 1, 2).to(ctx.w_dtype)
+        db = dy2.float().sum(0) if ctx.has_bias else None
+        return dx.permute(0, 3, 1, 2).to(ctx.x_dtype), dw, db, None, None
+
+
+def conv2d(x, weight, bias=None, stride=1, padding=0):
+    """Convolution on the hand-written kernels when the channel counts allow it (multiples of 8), else the library."""
+    cout, cin = weight.shape[0], weight.shape[1]
+    if x.is_cuda and cin % 8 == 0 and cout % 8 == 0:
+        return _ConvGemmFn.apply(x, weight, bias, int(stride), int(padding))
+    return F.conv2d(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype), stride, padding)

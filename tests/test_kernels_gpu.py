@@ -400,3 +400,25 @@ def test_softmax_fused_into_the_attention_gemms(E, err, pd):
     torch.cuda.synchronize()
     assert err.item() == 0
     _check(ds, ds_ref.float(), 3e-2)
+
+
+@pytest.mark.parametrize("k,stride,pad", [(3, 1, 1), (3, 2, 1), (7, 2, 3), (1, 1, 0)])
+def test_convolution_as_im2col_gemm_matches_the_library(k, stride, pad):
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(15)
+    x = torch.randn(3, 16, 13, 15, device="cuda").to(memory_format=torch.channels_last).requires_grad_(True)
+    w = (torch.randn(24, 16, k, k, device="cuda") * 0.1).requires_grad_(True)
+    b = torch.randn(24, device="cuda").requires_grad_(True)
+    y = Fn.conv2d(x.to(torch.bfloat16), w, b, stride, pad)
+    dy = torch.randn_like(y.float())
+    y.float().backward(dy)
+    gx, gw, gb = x.grad.clone(), w.grad.clone(), b.grad.clone()
+    x.grad = w.grad = b.grad = None
+    ref = torch.nn.functional.conv2d(x, w, b, stride, pad)
+    ref.backward(dy)
+    assert y.shape == ref.shape
+    _check(y, ref.detach(), 2e-2)
+    _check(gx, x.grad, 3e-2)
+    _check(gw, w.grad, 3e-2)
+    _check(gb, b.grad, 3e-2)
+    Fn.check_errors()
