@@ -92,7 +92,8 @@ class LM1B(nn.Module):
         true_logit = (out * true_w).sum(1).float() + self.softmax_b[targets] - torch.log(
             c.num_sampled * log_uniform_prob(targets, c.vocab_size))
         neg_w = F.embedding(neg, self.softmax_w, sparse=True).to(dt)
-        neg_logit = (out @ neg_w.t()).float() + self.softmax_b[neg] - torch.log(c.num_sampled * log_uniform_prob(neg, c.vocab_size))
+        neg_logit = linear(out, neg_w).float() + self.softmax_b[neg]        # [B*T, 512] x [8192, 512]^T on the tcgen05 GEMM
+        neg_logit = neg_logit - torch.log(c.num_sampled * log_uniform_prob(neg, c.vocab_size))
         neg_logit = neg_logit.masked_fill(neg[None, :] == targets[:, None], -1e9)     # remove accidental hits
         logits = torch.cat([true_logit[:, None], neg_logit], 1)
         loss = F.cross_entropy(logits, torch.zeros_like(targets))
