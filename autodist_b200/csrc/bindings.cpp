@@ -319,6 +319,32 @@ void lstm_cell_bwd(const Tensor& gates, const Tensor& c_prev, const Tensor& c, c
 }
 void sumsq(const Tensor& x, Tensor acc, double weight) { adb200::sumsq(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)weight, STREAM); }
 void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_scale(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)max_norm, STREAM); }
+// Batch-norm over a channels-last matrix x [rows, C] (training mode statistics), optional fused ReLU.
+void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor y, Tensor mean, Tensor rstd, double eps, bool relu) {
+  const int C = x.size(-1), rows = x.numel() / C;
+  TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [.., C], C % 8 == 0");
+  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows) * 2 * C}, x.options().dtype(at::kFloat));
+  Tensor sums = at::empty({2 * C}, x.options().dtype(at::kFloat));
+  adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                 part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, STREAM);
+}
+// Returns [dbeta, dgamma] stacked as a [2, C] fp32 tensor; writes dx.
+Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
+              bool relu) {
+  const int C = x.size(-1), rows = x.numel() / C;
+  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows) * 2 * C}, x.options().dtype(at::kFloat));
+  Tensor sums = at::empty({2, C}, x.options().dtype(at::kFloat));
+  adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx),
+                 part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, relu ? 1 : 0, STREAM);
+  return sums;
+}
+void maxpool_fwd(const Tensor& x, Tensor y, int64_t k, int64_t stride, int64_t pad) {
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.size(3) % 8 == 0, "x must be contiguous bf16 [N, H, W, C]");
+  adb200::maxpool_fwd(CBF(x), BF(y), x.size(0), x.size(1), x.size(2), x.size(3), k, stride, pad, y.size(1), y.size(2), STREAM);
+}
+void maxpool_bwd(const Tensor& x, const Tensor& y, const Tensor& dy, Tensor dx, int64_t k, int64_t stride, int64_t pad) {
+  adb200::maxpool_bwd(CBF(x), CBF(y), CBF(dy), BF(dx), x.size(0), x.size(1), x.size(2), x.size(3), k, stride, pad, y.size(1), y.size(2), STREAM);
+}
 // x: channels-last activations viewed as [N, H, W, C] bf16 contiguous; cols: [N*Ho*Wo, KH*KW*C]
 void im2col(const Tensor& x, Tensor cols, int64_t KH, int64_t KW, int64_t stride, int64_t pad) {
   TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.size(3) % 8 == 0, "x must be contiguous bf16 [N, H, W, C], C % 8 == 0");
@@ -453,6 +479,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("bn_fwd", &bn_fwd);
+  m.def("bn_bwd", &bn_bwd);
+  m.def("maxpool_fwd", &maxpool_fwd);
+  m.def("maxpool_bwd", &maxpool_bwd);
   m.def("im2col", &im2col);
   m.def("col2im", &col2im);
   m.def("psgd_p", &psgd_p);

@@ -743,6 +743,177 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__
   store8(dx + idx * 8, acc);
 }
 
+// ------------------------------------------------------------------------------------------------ batch-norm (K14), pooling (K15)
+// Channels-last activations seen as a matrix [rows = N*H*W, C] (C a multiple of 8).
+// Statistics: part[y][0][c] = sum x, part[y][1][c] = sum x^2 over row chunk y (then colsum_f32 over the chunks).
+__global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int rows, int C, int rows_per_block) {
+  __shared__ float s1[32][65], s2[32][65];
+  const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + vec * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < C)
+    for (int r = r0 + rl; r < r1; r += 32) {
+      float v[8];
+      load8(x + (long long)r * C + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { a[i] += v[i]; b[i] += v[i] * v[i]; }
+    }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { s1[rl][vec * 8 + i] = a[i]; s2[rl][vec * 8 + i] = b[i]; }
+  __syncthreads();
+  if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < C) {
+    float t1 = 0.f, t2 = 0.f;
+    for (int i = 0; i < 32; ++i) { t1 += s1[i][threadIdx.x]; t2 += s2[i][threadIdx.x]; }
+    part[((long long)blockIdx.y * 2 + 0) * C + blockIdx.x * 64 + threadIdx.x] = t1;
+    part[((long long)blockIdx.y * 2 + 1) * C + blockIdx.x * 64 + threadIdx.x] = t2;
+  }
+}
+
+// y = relu?((x - mean) * rstd * gamma + beta); sums = [sum x, sum x^2] per channel; also writes mean / rstd.
+__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ sums, const float* __restrict__ gamma,
+                                const float* __restrict__ beta, bf16* __restrict__ y, float* __restrict__ mean_out,
+                                float* __restrict__ rstd_out, long long rows, int C, float eps, int relu) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = C / 8;
+  if (idx >= rows * c8) return;
+  const int c = (int)(idx % c8) * 8;
+  float v[8];
+  load8(x + idx * 8, v);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float mu = sums[c + j] / rows;
+    const float var = fmaxf(sums[C + c + j] / rows - mu * mu, 0.f);
+    const float rs = rsqrtf(var + eps);
+    if (idx < c8) { mean_out[c + j] = mu; rstd_out[c + j] = rs; }
+    float o = (v[j] - mu) * rs * gamma[c + j] + beta[c + j];
+    v[j] = relu ? fmaxf(o, 0.f) : o;
+  }
+  store8(y + idx * 8, v);
+}
+
+// Backward statistics: part[y][0][c] = sum dy', part[y][1][c] = sum dy' * xhat, dy' = dy masked by the ReLU (y > 0).
+__global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
+                                    const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ part,
+                                    int rows, int C, int rows_per_block, int relu) {
+  __shared__ float s1[32][65], s2[32][65];
+  const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + vec * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < C)
+    for (int r = r0 + rl; r < r1; r += 32) {
+      float d[8], xv[8], yv[8];
+      load8(dy + (long long)r * C + c, d);
+      load8(x + (long long)r * C + c, xv);
+      if (relu) load8(y + (long long)r * C + c, yv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float g = (relu && yv[i] <= 0.f) ? 0.f : d[i];
+        a[i] += g;
+        b[i] += g * (xv[i] - mean[c + i]) * rstd[c + i];
+      }
+    }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { s1[rl][vec * 8 + i] = a[i]; s2[rl][vec * 8 + i] = b[i]; }
+  __syncthreads();
+  if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < C) {
+    float t1 = 0.f, t2 = 0.f;
+    for (int i = 0; i < 32; ++i) { t1 += s1[i][threadIdx.x]; t2 += s2[i][threadIdx.x]; }
+    part[((long long)blockIdx.y * 2 + 0) * C + blockIdx.x * 64 + threadIdx.x] = t1;
+    part[((long long)blockIdx.y * 2 + 1) * C + blockIdx.x * 64 + threadIdx.x] = t2;
+  }
+}
+
+// dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M); sums = [dbeta, dgamma]
+__global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
+                                    const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                    const float* __restrict__ sums, bf16* __restrict__ dx, long long rows, int C, int relu) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = C / 8;
+  if (idx >= rows * c8) return;
+  const int c = (int)(idx % c8) * 8;
+  float d[8], xv[8], yv[8];
+  load8(dy + idx * 8, d);
+  load8(x + idx * 8, xv);
+  if (relu) load8(y + idx * 8, yv);
+  const float inv_m = 1.0f / rows;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float g = (relu && yv[j] <= 0.f) ? 0.f : d[j];
+    const float xh = (xv[j] - mean[c + j]) * rstd[c + j];
+    d[j] = gamma[c + j] * rstd[c + j] * (g - sums[c + j] * inv_m - xh * sums[C + c + j] * inv_m);
+  }
+  store8(dx + idx * 8, d);
+}
+
+// Max pooling over [N, H, W, C] windows (k x k, stride, pad); the backward pass recomputes the arg-max (first maximum wins).
+__global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int k, int stride,
+                                   int pad, int Ho, int Wo) {
+  const int c8 = C / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)N * Ho * Wo * c8) return;
+  const int cv = (int)(idx % c8);
+  long long r = idx / c8;
+  const int wo = (int)(r % Wo), ho = (int)((r / Wo) % Ho), n = (int)(r / ((long long)Wo * Ho));
+  float m[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) m[j] = -INFINITY;
+  for (int kh = 0; kh < k; ++kh)
+    for (int kw = 0; kw < k; ++kw) {
+      const int hi = ho * stride - pad + kh, wi = wo * stride - pad + kw;
+      if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
+      float v[8];
+      load8(x + (((long long)n * H + hi) * W + wi) * C + cv * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[j] = fmaxf(m[j], v[j]);
+    }
+  store8(y + idx * 8, m);
+}
+
+__global__ void maxpool_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ dy,
+                                   bf16* __restrict__ dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo) {
+  const int c8 = C / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)N * H * W * c8) return;
+  const int cv = (int)(idx % c8);
+  long long r = idx / c8;
+  const int wi = (int)(r % W), hi = (int)((r / W) % H), n = (int)(r / ((long long)W * H));
+  float xv[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  load8(x + idx * 8, xv);
+  for (int kh = 0; kh < k; ++kh) {
+    const int hn = hi + pad - kh;
+    if (hn < 0 || hn % stride) continue;
+    const int ho = hn / stride;
+    if (ho >= Ho) continue;
+    for (int kw = 0; kw < k; ++kw) {
+      const int wn = wi + pad - kw;
+      if (wn < 0 || wn % stride) continue;
+      const int wo = wn / stride;
+      if (wo >= Wo) continue;
+      const long long o = ((((long long)n * Ho + ho) * Wo + wo) * C) + cv * 8;
+      float yv[8], dv[8];
+      load8(y + o, yv);
+      load8(dy + o, dv);
+      // the gradient goes to the first maximum of the window in scan order (ties are common after a ReLU)
+      bool first[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) first[j] = xv[j] == yv[j];
+      for (int t = 0; t < kh * k + kw; ++t) {
+        const int h2 = ho * stride - pad + t / k, w2 = wo * stride - pad + t % k;
+        if (h2 < 0 || h2 >= H || w2 < 0 || w2 >= W) continue;
+        float ev[8];
+        load8(x + (((long long)n * H + h2) * W + w2) * C + cv * 8, ev);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (ev[j] == yv[j]) first[j] = false;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (first[j]) acc[j] += dv[j];
+    }
+  }
+  store8(dx + idx * 8, acc);
+}
+
 // ------------------------------------------------------------------------------------------------ PowerSGD (K8)
 // Rank-r (r <= 4) factors of an fp32 matrix M [m, n]; all three kernels are bandwidth-bound passes over M.
 //   psgd_p : M += err (in place); P[i, :] = M[i, :] . Q          one warp per row
@@ -908,6 +1079,28 @@ void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t s
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st) {
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
+}
+int bn_parts(int rows) { return rows >= 4096 ? 32 : (rows >= 256 ? 4 : 1); }
+void bn_fwd(const bf16* x, const float* gamma, const float* beta, bf16* y, float* mean, float* rstd, float* part, float* sums,
+            int rows, int C, float eps, int relu, cudaStream_t st) {
+  const int parts = bn_parts(rows), rpb = (rows + parts - 1) / parts;
+  bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
+  colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
+  bn_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(x, sums, gamma, beta, y, mean, rstd, rows, C, eps, relu);
+}
+void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx,
+            float* part, float* sums, int rows, int C, int relu, cudaStream_t st) {
+  const int parts = bn_parts(rows), rpb = (rows + parts - 1) / parts;
+  bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
+  colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
+  bn_bwd_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(dy, x, y, mean, rstd, gamma, sums, dx, rows, C, relu);
+}
+void maxpool_fwd(const bf16* x, bf16* y, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
+  maxpool_fwd_kernel<<<blocks_for((long long)N * Ho * Wo * (C / 8), 256), 256, 0, st>>>(x, y, N, H, W, C, k, stride, pad, Ho, Wo);
+}
+void maxpool_bwd(const bf16* x, const bf16* y, const bf16* dy, bf16* dx, int N, int H, int W, int C, int k, int stride, int pad,
+                 int Ho, int Wo, cudaStream_t st) {
+  maxpool_bwd_kernel<<<blocks_for((long long)N * H * W * (C / 8), 256), 256, 0, st>>>(x, y, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
 }
 void im2col(const bf16* x, bf16* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
   const long long total = (long long)N * Ho * Wo * KH * KW * (C / 8);

@@ -14,7 +14,7 @@ import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import Linear, conv2d, linear
+from autodist_b200.ops.functional import Linear, batch_norm, conv2d, linear, max_pool2d
 
 
 class Conv1x1(nn.Conv2d):
@@ -63,8 +63,33 @@ def _conv(cin, cout, k, stride=1, padding=0, bias=False):
     return ConvGemm(cin, cout, k, stride, padding, bias=bias)
 
 
+class BatchNormAct(nn.BatchNorm2d):
+    """Batch-norm with an optional fused ReLU. With ``AUTODIST_NORM_POOL=own`` the training-mode statistics, the
+    normalisation (+ ReLU) and both backward passes run on the hand-written kernels; default is the library."""
+
+    def __init__(self, channels, relu=False):
+        super().__init__(channels)
+        self.relu = relu
+
+    def forward(self, x):
+        if x.is_cuda and USE_OWN_NORM_POOL and self.training and x.shape[1] % 8 == 0:
+            return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, True, self.momentum, self.eps, self.relu)
+        y = super().forward(x)
+        return F.relu(y, inplace=True) if self.relu else y
+
+
+class MaxPool(nn.MaxPool2d):
+    def forward(self, x):
+        if x.is_cuda and USE_OWN_NORM_POOL and x.shape[1] % 8 == 0:
+            return max_pool2d(x, self.kernel_size, self.stride, self.padding)
+        return super().forward(x)
+
+
+USE_OWN_NORM_POOL = os.environ.get("AUTODIST_NORM_POOL", "library") == "own"
+
+
 def _conv_bn(cin, cout, k, stride=1, padding=0):
-    return nn.Sequential(_conv(cin, cout, k, stride, padding), nn.BatchNorm2d(cout), nn.ReLU(inplace=True))
+    return nn.Sequential(_conv(cin, cout, k, stride, padding), BatchNormAct(cout, relu=True))
 
 
 class Bottleneck(nn.Module):
@@ -75,10 +100,10 @@ class Bottleneck(nn.Module):
         cout = width * self.expansion
         self.a = _conv_bn(cin, width, 1)
         self.b = _conv_bn(width, width, 3, stride, 1)
-        self.c = nn.Sequential(_conv(width, cout, 1), nn.BatchNorm2d(cout))
+        self.c = nn.Sequential(_conv(width, cout, 1), BatchNormAct(cout))
         self.down = None
         if stride != 1 or cin != cout:
-            self.down = nn.Sequential(_conv(cin, cout, 1, stride), nn.BatchNorm2d(cout))
+            self.down = nn.Sequential(_conv(cin, cout, 1, stride), BatchNormAct(cout))
 
     def forward(self, x):
         idn = x if self.down is None else self.down(x)
@@ -88,7 +113,7 @@ class Bottleneck(nn.Module):
 class ResNet(nn.Module):
     def __init__(self, blocks=(3, 4, 23, 3), num_classes=1000, width=64):
         super().__init__()
-        self.stem = nn.Sequential(_conv_bn(3, width, 7, 2, 3), nn.MaxPool2d(3, 2, 1))
+        self.stem = nn.Sequential(_conv_bn(3, width, 7, 2, 3), MaxPool(3, 2, 1))
         layers, cin = [], width
         for i, n in enumerate(blocks):
             w = width * 2 ** i
@@ -119,7 +144,7 @@ class VGG16(nn.Module):
         layers, cin = [], 3
         for v in self.CFG:
             if v == "M":
-                layers.append(nn.MaxPool2d(2, 2))
+                layers.append(MaxPool(2, 2))
             else:
                 layers += [_conv(cin, v, 3, 1, 1, bias=True), nn.ReLU(inplace=True)]
                 cin = v

@@ -191,3 +191,78 @@ def conv2d(x, weight, bias=None, stride=1, padding=0):
     if x.is_cuda and cin % 8 == 0 and cout % 8 == 0:
         return _ConvGemmFn.apply(x, weight, bias, int(stride), int(padding))
     return F.conv2d(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype), stride, padding)
+
+
+class _BatchNormFn(torch.autograd.Function):
+    """Training-mode batch-norm (+ optional ReLU) over channels-last activations on the hand-written kernels."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, relu):
+        E = ops.ext(required=True)
+        xh = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()            # [N, H, W, C]
+        c = xh.shape[-1]
+        y = torch.empty_like(xh)
+        mean = torch.empty(c, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
+        E.bn_fwd(xh, g32, b32, y, mean, rstd, eps, relu)
+        ctx.save_for_backward(xh, y, mean, rstd, g32)
+        ctx.relu = relu
+        ctx.dtypes = (x.dtype, gamma.dtype)
+        ctx.mark_non_differentiable(mean, rstd)
+        return y.permute(0, 3, 1, 2), mean, rstd
+
+    @staticmethod
+    def backward(ctx, dy, _dm, _dr):
+        E = ops.ext(required=True)
+        xh, y, mean, rstd, g32 = ctx.saved_tensors
+        dyh = dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+        dx = torch.empty_like(xh)
+        sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, ctx.relu)
+        return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), None, None
+
+
+def batch_norm(x, gamma, beta, running_mean=None, running_var=None, training=True, momentum=0.1, eps=1e-5, relu=False):
+    """Batch-norm (+ ReLU) of an NCHW / channels-last tensor; updates the running statistics like ``F.batch_norm``."""
+    if not (x.is_cuda and training and x.shape[1] % 8 == 0):
+        y = F.batch_norm(x, running_mean, running_var, gamma.to(x.dtype) if x.dtype != gamma.dtype and not x.is_cuda else gamma,
+                         beta, training, momentum, eps)
+        return F.relu(y) if relu else y
+    y, mean, rstd = _BatchNormFn.apply(x, gamma, beta, eps, relu)
+    if running_mean is not None:
+        with torch.no_grad():
+            n = x.numel() // x.shape[1]
+            var = (1.0 / (rstd * rstd) - eps).clamp_(min=0) * (n / max(n - 1, 1))
+            running_mean.mul_(1 - momentum).add_(mean.to(running_mean.dtype), alpha=momentum)
+            running_var.mul_(1 - momentum).add_(var.to(running_var.dtype), alpha=momentum)
+    return y
+
+
+class _MaxPoolFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, k, stride, pad):
+        E = ops.ext(required=True)
+        xh = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+        n, h, w, c = xh.shape
+        ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        y = torch.empty(n, ho, wo, c, dtype=torch.bfloat16, device=x.device)
+        E.maxpool_fwd(xh, y, k, stride, pad)
+        ctx.save_for_backward(xh, y)
+        ctx.geom = (k, stride, pad)
+        ctx.x_dtype = x.dtype
+        return y.permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        E = ops.ext(required=True)
+        xh, y = ctx.saved_tensors
+        dx = torch.empty_like(xh)
+        E.maxpool_bwd(xh, y, dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous(), dx, *ctx.geom)
+        return dx.permute(0, 3, 1, 2).to(ctx.x_dtype), None, None, None
+
+
+def max_pool2d(x, kernel_size, stride=None, padding=0):
+    stride = stride or kernel_size
+    if x.is_cuda and x.shape[1] % 8 == 0:
+        return _MaxPoolFn.apply(x, int(kernel_size), int(stride), int(padding))
+    return F.max_pool2d(x, kernel_size, stride, padding)

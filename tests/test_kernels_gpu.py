@@ -422,3 +422,46 @@ def test_convolution_as_im2col_gemm_matches_the_library(k, stride, pad):
     _check(gw, w.grad, 3e-2)
     _check(gb, b.grad, 3e-2)
     Fn.check_errors()
+
+
+@pytest.mark.parametrize("relu", [False, True])
+def test_batch_norm_kernels_match_the_library(relu):
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(16)
+    x = (torch.randn(6, 32, 9, 11, device="cuda") * 2 + 0.5).to(memory_format=torch.channels_last).requires_grad_(True)
+    g = (torch.rand(32, device="cuda") + 0.5).requires_grad_(True)
+    b = torch.randn(32, device="cuda").requires_grad_(True)
+    rm, rv = torch.zeros(32, device="cuda"), torch.ones(32, device="cuda")
+    y = Fn.batch_norm(x.to(torch.bfloat16), g, b, rm, rv, True, 0.1, 1e-5, relu)
+    dy = torch.randn_like(y.float())
+    y.float().backward(dy)
+    got = (x.grad.clone(), g.grad.clone(), b.grad.clone())
+    x.grad = g.grad = b.grad = None
+    rm2, rv2 = torch.zeros(32, device="cuda"), torch.ones(32, device="cuda")
+    xq = x.detach().to(torch.bfloat16).float().requires_grad_(True)            # the kernels see the bf16-rounded input
+    ref = torch.nn.functional.batch_norm(xq, rm2, rv2, g, b, True, 0.1, 1e-5)
+    ref = torch.relu(ref) if relu else ref
+    ref.backward(dy)
+    _check(y, ref.detach(), 2e-2)
+    _check(got[0], xq.grad, 3e-2)
+    _check(got[1], g.grad, 3e-2)
+    _check(got[2], b.grad, 3e-2)
+    _check(rm, rm2, 1e-2)
+    _check(rv, rv2, 1e-2)
+
+
+@pytest.mark.parametrize("k,stride,pad", [(3, 2, 1), (2, 2, 0)])
+def test_max_pool_kernels_match_the_library(k, stride, pad):
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(17)
+    x = torch.relu(torch.randn(4, 16, 13, 14, device="cuda")).to(torch.bfloat16).to(memory_format=torch.channels_last)   # many ties at 0
+    x = x.float().requires_grad_(True)
+    y = Fn.max_pool2d(x.to(torch.bfloat16), k, stride, pad)
+    dy = torch.randn_like(y.float())
+    y.float().backward(dy)
+    gx = x.grad.clone()
+    x.grad = None
+    ref = torch.nn.functional.max_pool2d(x, k, stride, pad)
+    ref.backward(dy.to(torch.bfloat16).float())
+    assert torch.equal(y.float(), ref.detach())
+    _check(gx, x.grad, 2e-2)
