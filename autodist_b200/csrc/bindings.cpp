@@ -323,7 +323,7 @@ void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_sca
 void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor y, Tensor mean, Tensor rstd, double eps, bool relu) {
   const int C = x.size(-1), rows = x.numel() / C;
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [.., C], C % 8 == 0");
-  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows) * 2 * C}, x.options().dtype(at::kFloat));
+  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({2 * C}, x.options().dtype(at::kFloat));
   adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
                  part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, STREAM);
@@ -332,7 +332,7 @@ void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor y, 
 Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
               bool relu) {
   const int C = x.size(-1), rows = x.numel() / C;
-  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows) * 2 * C}, x.options().dtype(at::kFloat));
+  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({2, C}, x.options().dtype(at::kFloat));
   adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx),
                  part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, relu ? 1 : 0, STREAM);

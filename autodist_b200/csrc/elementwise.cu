@@ -1080,17 +1080,24 @@ void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStr
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
 }
-int bn_parts(int rows) { return rows >= 4096 ? 32 : (rows >= 256 ? 4 : 1); }
+// Row chunks per channel block: enough blocks to fill the SMs (~4 per SM) while each chunk keeps >= 64 rows.
+int bn_parts(int rows, int C) {
+  const int cb = (C + 63) / 64;
+  int parts = (592 + cb - 1) / cb;
+  if (parts > rows / 64) parts = rows / 64;
+  if (parts > 256) parts = 256;
+  return parts < 1 ? 1 : parts;
+}
 void bn_fwd(const bf16* x, const float* gamma, const float* beta, bf16* y, float* mean, float* rstd, float* part, float* sums,
             int rows, int C, float eps, int relu, cudaStream_t st) {
-  const int parts = bn_parts(rows), rpb = (rows + parts - 1) / parts;
+  const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
   colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
   bn_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(x, sums, gamma, beta, y, mean, rstd, rows, C, eps, relu);
 }
 void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx,
             float* part, float* sums, int rows, int C, int relu, cudaStream_t st) {
-  const int parts = bn_parts(rows), rpb = (rows + parts - 1) / parts;
+  const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
   colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
   bn_bwd_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(dy, x, y, mean, rstd, gamma, sums, dx, rows, C, relu);

@@ -42,7 +42,7 @@ void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, cons
                    float* dc_prev, int B, int S, float fb, cudaStream_t st);
 void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st);
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
-int bn_parts(int rows);
+int bn_parts(int rows, int C);
 void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, bf16_t* y, float* mean, float* rstd, float* part, float* sums,
             int rows, int C, float eps, int relu, cudaStream_t st);
 void bn_bwd(const bf16_t* dy, const bf16_t* x, const bf16_t* y, const float* mean, const float* rstd, const float* gamma, bf16_t* dx,
