@@ -259,6 +259,10 @@ void keyed_colsum(const Tensor& x, const optional<Tensor>& key, Tensor part, Ten
 void gather_rows(const Tensor& src, const Tensor& idx, Tensor out) {
   adb200::gather_rows(CBF(src), idx.data_ptr<int64_t>(), BF(out), idx.numel(), src.size(-1), STREAM);
 }
+void gather_rows_f32(const Tensor& src, const Tensor& idx, Tensor out) {
+  TORCH_CHECK(src.scalar_type() == at::kFloat && src.is_contiguous() && src.size(-1) % 8 == 0, "fp32 contiguous table, width a multiple of 8");
+  adb200::gather_rows_f32(src.data_ptr<float>(), idx.data_ptr<int64_t>(), BF(out), idx.numel(), src.size(-1), STREAM);
+}
 void scatter_add_rows_bf16(Tensor dst, const Tensor& idx, const Tensor& src) {
   adb200::scatter_add_rows_bf16(BF(dst), idx.data_ptr<int64_t>(), CBF(src), idx.numel(), src.size(-1), STREAM);
 }
@@ -468,6 +472,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("strided_rowsum", &strided_rowsum);
   m.def("keyed_colsum", &keyed_colsum);
   m.def("gather_rows", &gather_rows);
+  m.def("gather_rows_f32", &gather_rows_f32);
   m.def("scatter_add_rows_bf16", &scatter_add_rows_bf16);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);

@@ -344,6 +344,19 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* 
     *reinterpret_cast<uint4*>(out + (long long)warp * H + vec * 8) = *reinterpret_cast<const uint4*>(src + r * H + vec * 8);
 }
 
+// Row gather from an fp32 table with the bf16 cast fused (sampled-softmax / embedding lookups of master weights).
+__global__ void gather_rows_f32_kernel(const float* __restrict__ src, const int64_t* __restrict__ idx, bf16* __restrict__ out, int rows, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const long long r = idx[warp];
+  for (int vec = lane; vec < H / 8; vec += 32) {
+    const float4 a = *reinterpret_cast<const float4*>(src + r * H + vec * 8);
+    const float4 b = *reinterpret_cast<const float4*>(src + r * H + vec * 8 + 4);
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    store8(out + (long long)warp * H + vec * 8, v);
+  }
+}
+
 // dst[idx[r]] += src[r] for bf16 rows whose indices are unique (MLM positions of one sequence never repeat)
 __global__ void scatter_add_rows_bf16_kernel(bf16* __restrict__ dst, const int64_t* __restrict__ idx, const bf16* __restrict__ src, int rows, int H) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -1015,6 +1028,9 @@ void keyed_colsum(const bf16* x, const int64_t* key, float* part, float* out, in
 }
 void gather_rows(const bf16* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
   gather_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
+}
+void gather_rows_f32(const float* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
+  gather_rows_f32_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
 }
 void scatter_add_rows_bf16(bf16* dst, const int64_t* idx, const bf16* src, int rows, int H, cudaStream_t st) {
   scatter_add_rows_bf16_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H);

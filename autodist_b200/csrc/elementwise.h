@@ -19,6 +19,7 @@ void strided_rowsum(const bf16_t* x, float* out, int keys, int stride, int count
 int colsum_parts(int rows);
 void keyed_colsum(const bf16_t* x, const int64_t* key, float* part, float* out, int rows, int H, int keys, int accumulate, cudaStream_t st);
 void gather_rows(const bf16_t* src, const int64_t* idx, bf16_t* out, int rows, int H, cudaStream_t st);
+void gather_rows_f32(const float* src, const int64_t* idx, bf16_t* out, int rows, int H, cudaStream_t st);
 void scatter_add_rows_bf16(bf16_t* dst, const int64_t* idx, const bf16_t* src, int rows, int H, cudaStream_t st);
 bool softmax_supported(int S);
 void softmax_fwd(const bf16_t* x, const float* mask, bf16_t* p, bf16_t* p_drop, long long rows, int S, int rows_per_batch, float scale,

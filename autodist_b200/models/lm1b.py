@@ -12,7 +12,7 @@ import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import linear, lstm_cell
+from autodist_b200.ops.functional import linear, lstm_cell, sparse_lookup
 
 
 @dataclass
@@ -68,7 +68,7 @@ class LM1B(nn.Module):
         c = self.config
         Bsz, T = x.shape
         dt = torch.bfloat16 if x.is_cuda else torch.float32
-        inputs = F.embedding(x, self.emb, sparse=True).to(dt)     # row-sparse gradient: only the looked-up rows travel
+        inputs = sparse_lookup(self.emb, x).to(dt)               # row-sparse gradient: only the looked-up rows travel
         if self.training and c.keep_prob < 1.0:
             inputs = F.dropout(inputs, 1.0 - c.keep_prob)
         h = torch.zeros(Bsz, c.projected_size, dtype=dt, device=x.device)
@@ -88,10 +88,10 @@ class LM1B(nn.Module):
             self._gen = torch.Generator(device=x.device)
             self._gen.manual_seed(1234)
         neg = log_uniform_sample(c.num_sampled, c.vocab_size, self._gen, x.device)
-        true_w = F.embedding(targets, self.softmax_w, sparse=True).to(dt)
+        true_w = sparse_lookup(self.softmax_w, targets).to(dt)
         true_logit = (out * true_w).sum(1).float() + self.softmax_b[targets] - torch.log(
             c.num_sampled * log_uniform_prob(targets, c.vocab_size))
-        neg_w = F.embedding(neg, self.softmax_w, sparse=True).to(dt)
+        neg_w = sparse_lookup(self.softmax_w, neg).to(dt)
         neg_logit = linear(out, neg_w).float() + self.softmax_b[neg]        # [B*T, 512] x [8192, 512]^T on the tcgen05 GEMM
         neg_logit = neg_logit - torch.log(c.num_sampled * log_uniform_prob(neg, c.vocab_size))
         neg_logit = neg_logit.masked_fill(neg[None, :] == targets[:, None], -1e9)     # remove accidental hits

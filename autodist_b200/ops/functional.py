@@ -266,3 +266,31 @@ def max_pool2d(x, kernel_size, stride=None, padding=0):
     if x.is_cuda and x.shape[1] % 8 == 0:
         return _MaxPoolFn.apply(x, int(kernel_size), int(stride), int(padding))
     return F.max_pool2d(x, kernel_size, stride, padding)
+
+
+class _SparseLookupFn(torch.autograd.Function):
+    """Rows ``ids`` of an fp32 table as bf16 (gather with the cast fused); the gradient is row-sparse like
+    ``F.embedding(sparse=True)`` so only the looked-up rows travel to the table's owner."""
+
+    @staticmethod
+    def forward(ctx, table, ids):
+        E = ops.ext(required=True)
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty(flat.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
+        E.gather_rows_f32(table.detach(), flat, out)
+        ctx.save_for_backward(flat)
+        ctx.shape = tuple(table.shape)
+        return out.view(*ids.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat,) = ctx.saved_tensors
+        vals = dy.reshape(flat.numel(), -1).float()
+        return torch.sparse_coo_tensor(flat[None], vals, ctx.shape), None
+
+
+def sparse_lookup(table, ids):
+    """``F.embedding(ids, table, sparse=True)`` returning bf16 on CUDA (fp32 elsewhere)."""
+    if table.is_cuda and table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] % 8 == 0:
+        return _SparseLookupFn.apply(table, ids)
+    return F.embedding(ids, table, sparse=True)

@@ -465,3 +465,22 @@ def test_max_pool_kernels_match_the_library(k, stride, pad):
     ref.backward(dy.to(torch.bfloat16).float())
     assert torch.equal(y.float(), ref.detach())
     _check(gx, x.grad, 2e-2)
+
+
+def test_sparse_lookup_matches_embedding_with_sparse_gradient():
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(18)
+    table = torch.randn(500, 64, device="cuda", requires_grad=True)
+    ids = torch.randint(0, 500, (7, 9), device="cuda")
+    ids[0, :4] = 3                                                             # repeated rows accumulate
+    out = Fn.sparse_lookup(table, ids)
+    assert out.dtype == torch.bfloat16 and out.shape == (7, 9, 64)
+    dy = torch.randn(7, 9, 64, device="cuda")
+    out.float().backward(dy)
+    assert table.grad.is_sparse
+    got = table.grad.to_dense()
+    table.grad = None
+    ref = torch.nn.functional.embedding(ids, table)
+    ref.backward(dy.to(torch.bfloat16).float())
+    _check(out, ref.detach(), 1e-2)
+    _check(got, table.grad, 1e-2)
