@@ -27,7 +27,8 @@ parameter-server path, which the reference's tied head makes dense
 (``networks/masked_lm.py:56,76-78``).
 """
 import math
-from dataclasses import dataclass
+import json
+from dataclasses import asdict, dataclass, fields
 
 import torch
 from torch import nn
@@ -56,6 +57,24 @@ class BertConfig:
     @classmethod
     def large(cls, **kw):
         return cls(**kw)
+
+    # JSON round trip in the layout of the published ``bert_config.json`` files
+    # (reference: ``examples/benchmark/utils/bert_modeling.py:86-108``); unknown keys are ignored.
+    @classmethod
+    def from_dict(cls, obj):
+        known = {f.name for f in fields(cls)}
+        return cls(**{k: v for k, v in obj.items() if k in known})
+
+    @classmethod
+    def from_json_file(cls, path):
+        with open(path) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self):
+        return asdict(self)
+
+    def to_json_string(self):
+        return json.dumps(self.to_dict(), indent=2, sort_keys=True) + "\n"
 
     @classmethod
     def base(cls, **kw):

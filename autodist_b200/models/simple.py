@@ -34,6 +34,12 @@ class SentimentClassifier(nn.Module):
         return F.binary_cross_entropy_with_logits(logit, labels)
 
 
+def NeuMF(num_users, num_items, mf_dim=64, layers=(256, 256, 128, 64), sparse=True):
+    """Neural matrix factorisation with positional arguments; the model itself lives in ``models.ncf``."""
+    from autodist_b200.models.ncf import NeuMF as _NeuMF, NeuMFConfig
+    return _NeuMF(NeuMFConfig(num_users, num_items, mf_dim, list(layers), dense_gradient=not sparse))
+
+
 class NeuMF(nn.Module):
     """Neural matrix factorisation (``examples/benchmark/utils/recommendation/neumf_model.py:200-251``): user / item
     embeddings of width ``mf_dim + layers[0] / 2`` sliced into a GMF part and an MLP part, MLP tower, one logit."""

@@ -4,6 +4,8 @@
 produced in fp32). On CPU tensors the same functions fall back to the plain PyTorch expression, which is also the
 numerics reference of the tests.
 """
+import warnings
+
 import torch
 import torch.nn.functional as F
 
@@ -286,7 +288,9 @@ class _SparseLookupFn(torch.autograd.Function):
     def backward(ctx, dy):
         (flat,) = ctx.saved_tensors
         vals = dy.reshape(flat.numel(), -1).float()
-        return torch.sparse_coo_tensor(flat[None], vals, ctx.shape), None
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")                                   # the library's notice that invariants are unchecked
+            return torch.sparse_coo_tensor(flat[None], vals, ctx.shape, check_invariants=False), None
 
 
 def sparse_lookup(table, ids):

@@ -83,7 +83,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--model", default="bert-large", choices=["bert-large", "bert-base", "bert-tiny", "resnet101", "vgg16",
-                                                              "resnet50", "densenet121", "inceptionv3"])
+                                                              "resnet50", "densenet121", "inceptionv3", "lm1b", "lm1b-tiny"])
     ap.add_argument("--strategy", default="allreduce", choices=["allreduce", "allreduce_ef", "parallax", "ps", "partitioned_ps"])
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU (default: 32 sequences, 64 images, 32 for vgg16)")
     ap.add_argument("--seq", type=int, default=128)
@@ -120,8 +120,9 @@ def main():
         "partitioned_ps": lambda: S.PartitionedPS(num_shards=n_gpus, reduction_devices="gpu", local_proxy_variable=True),
     }
     is_bert = args.model.startswith("bert")
+    is_lm = args.model.startswith("lm1b")
     if not args.batch:
-        args.batch = 32 if is_bert or args.model == "vgg16" else 64
+        args.batch = 128 if is_lm else (32 if is_bert or args.model == "vgg16" else 64)
     max_pred = 20
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=n_gpus), strategy_builder=builders[args.strategy]())
     # Every process feeds its node's whole batch (batch per GPU x GPUs of the node), as a user of the API does; the
@@ -129,6 +130,11 @@ def main():
     if is_bert:
         cfg = {"bert-large": BertConfig.large, "bert-base": BertConfig.base, "bert-tiny": BertConfig.tiny}[args.model]()
         host_batches = [synthetic_batch(cfg, args.batch * n_gpus, args.seq, max_pred, seed=i, pin=True) for i in range(4)]
+    elif is_lm:
+        from autodist_b200.models.lm1b import LM1B, LM1BConfig, zipf_tokens
+        cfg = LM1BConfig.tiny() if args.model == "lm1b-tiny" else LM1BConfig()
+        host_batches = [{k: v.pin_memory() for k, v in zipf_tokens(args.batch * n_gpus, cfg.num_steps, cfg.vocab_size, seed=i).items()}
+                        for i in range(4)]
     else:
         from autodist_b200.models.cnn import ImageClassifier, synthetic_images
         host_batches = [{k: v.pin_memory() for k, v in synthetic_images(args.batch * n_gpus, 224, 1000, seed=i).items()}
@@ -136,13 +142,17 @@ def main():
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values()) // n_gpus
     with ad.scope():
         torch.manual_seed(0)
-        model = BertPretrainer(cfg) if is_bert else (ImageClassifier(args.model, image_size=224) if args.model == "vgg16"
+        model = BertPretrainer(cfg) if is_bert else LM1B(cfg) if is_lm else (ImageClassifier(args.model, image_size=224) if args.model == "vgg16"
                                                      else ImageClassifier(args.model))
         phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in host_batches[0].items()}
         loss = model(**phs)
-        opt = torch.optim.Adam(model.parameters(), lr=1e-4) if is_bert else \
-            torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
-        train_op = opt.minimize(loss)
+        if is_lm:
+            opt = torch.optim.Adagrad(model.parameters(), lr=0.2, initial_accumulator_value=1.0)
+            train_op = opt.minimize(loss, clip_global_norm=(cfg.max_grad_norm, model.dense_parameters()))
+        else:
+            opt = torch.optim.Adam(model.parameters(), lr=1e-4) if is_bert else \
+                torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+            train_op = opt.minimize(loss)
         sess = ad.create_distributed_session()
         dev = sess.engine.device
         dev_batches = [{k: v.to(dev) for k, v in b.items()} for b in host_batches]
@@ -203,30 +213,33 @@ def main():
     if rank != 0:
         return 0
     global_batch = args.batch * n_gpus
-    value = global_batch * args.steps / (ms / 1e3)
-    e2e = global_batch * args.steps / (ms_e2e / 1e3)
+    per_sample = cfg.num_steps if is_lm else 1                 # LM1B counts words: batch x unrolled steps
+    value = global_batch * per_sample * args.steps / (ms / 1e3)
+    e2e = global_batch * per_sample * args.steps / (ms_e2e / 1e3)
+    unit = "sequences/s" if is_bert else "words/s" if is_lm else "images/s"
     graph_launches = getattr(sess.engine, "graph_kernels", 0)
     launches = eager_launches if eager_launches > 0 else graph_launches * args.steps
     published = PUBLISHED_PER_GPU.get(n_gpus)
     out = {
         "metric": "BERT-large pre-training sequences/sec (seq 128), max over ranks" if is_bert
+        else "LM1B big-LSTM training words/sec (20 unrolled steps, sampled softmax 8192), max over ranks" if is_lm
         else f"{args.model} ImageNet-shape training images/sec, max over ranks",
-        "value": round(value, 2), "unit": "sequences/s" if is_bert else "images/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+        "value": round(value, 2), "unit": unit, "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(value / (published * n_gpus), 2) if published and args.model == "bert-large" else (
             round(value / (PUBLISHED_RESNET101.get(n_gpus, 0) * n_gpus), 2) if args.model == "resnet101" and n_gpus in PUBLISHED_RESNET101 else None),
         "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM positions, random-init weights)" if is_bert
-        else "synthetic (images ~ N(0,1), uniform labels over 1000 classes, random-init weights)",
-        "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq if is_bert else None,
+        else "synthetic (Zipf(1.1) token ids over the 793471-word vocabulary, random-init weights)" if is_lm else "synthetic (images ~ N(0,1), uniform labels over 1000 classes, random-init weights)",
+        "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq if is_bert else (cfg.num_steps if is_lm else None),
                    "max_predictions": max_pred if is_bert else None,
-                   "compute": "hand-written sm_100a kernels" if is_bert else "cuDNN convolutions (library) + tcgen05 GEMM for fully connected layers",
-                   "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute" if is_bert else "SGD momentum 0.9, fp32 master + bf16 autocast",
+                   "compute": "hand-written sm_100a kernels" if is_bert else "tcgen05 GEMM + own LSTM-cell / gather kernels, autograd glue" if is_lm else "cuDNN convolutions (library) + tcgen05 GEMM for fully connected layers",
+                   "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute" if is_bert else "Adagrad 0.2, LSTM gradients clipped at norm 10" if is_lm else "SGD momentum 0.9, fp32 master + bf16 autocast",
                    "comm": os.environ.get("AUTODIST_COMM", "fused"),
                    "cuda_graph": os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0",
                    "l2": "per-step working set (activations + weights > 4 GB) is far larger than the 126 MB L2",
                    "engine": type(sess.engine).__name__},
         "clocks": sampler.summary() if sampler else None,
-        "e2e": {"value": round(e2e, 2), "unit": "sequences/s" if is_bert else "images/s", "ms_per_step": round(ms_e2e / args.steps, 3),
+        "e2e": {"value": round(e2e, 2), "unit": unit, "ms_per_step": round(ms_e2e / args.steps, 3),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": float(last)},
         "gpu_launches": int(launches),
         "impl": "ours",
