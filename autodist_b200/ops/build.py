@@ -54,5 +54,50 @@ def build(verbose=False):
     return so_path()
 
 
+HOST_NAME = "_adb200_host"
+
+
+def host_so_path():
+    return os.path.join(EXT_DIR, HOST_NAME + ".so")
+
+
+def build_host(verbose=False):
+    """Host-only extension (no device code): the C++ model of the synchronisation protocol under ``csrc/host``."""
+    from torch.utils import cpp_extension
+    os.makedirs(EXT_DIR, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))
+    h = hashlib.sha1()
+    for path in srcs:
+        with open(path, "rb") as f:
+            h.update(f.read())
+    stamp = os.path.join(EXT_DIR, "host_digest.txt")
+    if os.path.exists(host_so_path()) and os.path.exists(stamp) and open(stamp).read().strip() == h.hexdigest():
+        return host_so_path()
+    build_dir = os.path.join(EXT_DIR, "host")
+    os.makedirs(build_dir, exist_ok=True)
+    cpp_extension.load(name=HOST_NAME, sources=srcs, extra_cflags=["-O2", "-std=c++17", "-pthread"], extra_ldflags=["-pthread"],
+                       build_directory=build_dir, verbose=verbose, is_python_module=False)
+    import shutil
+    shutil.copyfile(os.path.join(build_dir, HOST_NAME + ".so"), host_so_path())
+    with open(stamp, "w") as f:
+        f.write(h.hexdigest())
+    return host_so_path()
+
+
+def load_host():
+    """Import the host-only extension, building it first if needed."""
+    import importlib.util
+    import sys
+    if HOST_NAME in sys.modules:
+        return sys.modules[HOST_NAME]
+    path = build_host()
+    spec = importlib.util.spec_from_file_location(HOST_NAME, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules[HOST_NAME] = mod
+    return mod
+
+
 if __name__ == "__main__":
     print(build(verbose=True))
+    print(build_host(verbose=True))

@@ -34,6 +34,9 @@ class LocalBackend:
     def all_gather_rows(self, indices, values):
         return indices, values
 
+    def all_reduce_sum_(self, tensor):
+        return tensor
+
     def all_gather_counts(self, n):
         return [n]
 
@@ -83,6 +86,11 @@ class TorchDistBackend(LocalBackend):
 
     def broadcast_(self, tensor, src):
         dist.broadcast(tensor, src=src, group=self.group)
+        return tensor
+
+    def all_reduce_sum_(self, tensor):
+        self.bytes_reduced += tensor.numel() * tensor.element_size()
+        dist.all_reduce(tensor, group=self.group)
         return tensor
 
     def all_gather_counts(self, n, device="cpu"):

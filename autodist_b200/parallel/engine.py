@@ -20,12 +20,16 @@ do the reduction, the update and the re-distribution over NVSwitch peer memory.
 """
 from typing import Dict, List, Optional
 
+import warnings
+
 import torch
 from torch import nn
 
 from autodist_b200.kernel.common import op_info
 from autodist_b200.kernel.synchronization.compressor import Compressor
 from autodist_b200.utils import logging
+
+warnings.filterwarnings("ignore", message="Sparse invariant checks")
 
 
 class _Target:
@@ -391,6 +395,13 @@ class StepEngine:
                 continue
             if g is None:
                 t.param.grad = None
+            elif g.is_sparse and sparse_ok and t.part.axis == 0:
+                # rows of this shard only, re-based to the shard: the table's gradient is never made dense
+                g = g.coalesce()
+                rows = g.indices()[0]
+                sel = (rows >= t.part.offset) & (rows < t.part.offset + t.part.size)
+                t.param.grad = torch.sparse_coo_tensor((rows[sel] - t.part.offset).unsqueeze(0), g.values()[sel],
+                                                       t.param.shape).coalesce()
             elif g.is_sparse:
                 dense = g.to_dense()
                 t.full_param.grad = dense
@@ -419,8 +430,55 @@ class StepEngine:
         return out
 
     # -- step 6: owners publish -------------------------------------------------------
+    def _row_publish_vars(self):
+        """Row-sparse parameter-server variables whose optimizer changes only the rows that received a gradient
+        (sparse-capable optimizers): owners publish those rows instead of their whole shard."""
+        cached = getattr(self, "_row_publish_cache", None)
+        if cached is not None:
+            return cached
+        sparse_ok_params = set()
+        for info, local, _ in self._local_optimizers:
+            if op_info.supports_sparse_rows(info.optimizer):
+                for g in info.optimizer.param_groups:
+                    sparse_ok_params.update(id(p) for p in g["params"])
+        by_var: Dict[str, list] = {}
+        for e in self.plan.ps_entries.values():
+            by_var.setdefault(e.part.var_name, []).append(e)
+        out = set()
+        for vname, entries in by_var.items():
+            p = self._params[vname]
+            if id(p) in sparse_ok_params and p.dim() >= 1 and all(
+                    e.part.sparse and (e.part.part_index is None or e.part.axis == 0) for e in entries):
+                out.add(vname)
+        self._row_publish_cache = out
+        return out
+
+    def _publish_rows(self, vname):
+        """Every rank knows the rows touched this step (the gathered indices); each row's owner contributes its new
+        value to a sum over ranks, everybody else contributes zero."""
+        rows = getattr(self, "_touched_rows", {}).get(vname)
+        if rows is None or rows.numel() == 0:
+            return
+        p = self._params[vname]
+        mine = torch.zeros_like(rows, dtype=torch.bool)
+        for e in self.plan.ps_entries.values():
+            if e.part.var_name == vname and e.owner == self.rank:
+                lo = 0 if e.part.part_index is None else e.part.offset
+                hi = p.shape[0] if e.part.part_index is None else e.part.offset + e.part.size
+                mine |= (rows >= lo) & (rows < hi)
+        vals = p.data[rows]
+        vals[~mine] = 0
+        self.backend.all_reduce_sum_(vals)
+        p.data[rows] = vals
+
     def _publish_ps(self):
+        by_rows = self._row_publish_vars()
+        for vname in sorted(by_rows):
+            self._publish_rows(vname)
         for owner, entries in sorted(self.plan.ps_by_owner().items()):
+            entries = [e for e in entries if e.part.var_name not in by_rows]
+            if not entries:
+                continue
             numel = sum(e.part.numel for e in entries)
             dtype = self._params[entries[0].part.var_name].dtype
             flat = self._buffer(("pub", owner), numel, dtype)
