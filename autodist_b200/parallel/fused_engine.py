@@ -125,18 +125,43 @@ class SymmetricArena:
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
+    GUARD_BYTES = 256      # canary words before and after every symmetric buffer (keeps 256-byte alignment)
+
     def alloc(self, numel, dtype):
-        """(local tensor, int64 device tensor of every rank's address, multicast address or 0)."""
-        t = self.symm.empty(numel, dtype=dtype, device=self.device)
-        hdl = self.symm.rendezvous(t, self.group.group_name if hasattr(self.group, "group_name") else self.group)
-        ptrs = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=self.device)
+        """(local tensor, int64 device tensor of every rank's address, multicast address or 0).
+
+        The buffer sits between two guard regions filled with a pattern; ``check_canaries`` tells whether this rank
+        or a peer wrote outside a buffer."""
+        item = torch.empty((), dtype=dtype).element_size()
+        guard = self.GUARD_BYTES // item
+        raw = self.symm.empty(numel + 2 * guard, dtype=dtype, device=self.device)
+        hdl = self.symm.rendezvous(raw, self.group.group_name if hasattr(self.group, "group_name") else self.group)
+        words = raw.view(torch.uint8)
+        words[:self.GUARD_BYTES] = self.CANARY
+        words[self.GUARD_BYTES + numel * item:] = self.CANARY
+        if not hasattr(self, "_guards"):
+            self._guards = []
+        self._guards.append((words, numel * item))
+        t = raw[guard:guard + numel]
+        ptrs = torch.tensor([int(p) + self.GUARD_BYTES for p in hdl.buffer_ptrs], dtype=torch.int64, device=self.device)
         mc = 0
         if os.environ.get("AUTODIST_NVLS", "1") != "0":
             try:
                 mc = int(hdl.multicast_ptr or 0)
             except Exception:  # no multicast support on this fabric / build
                 mc = 0
-        return t, ptrs, mc
+        return t, ptrs, (mc + self.GUARD_BYTES if mc else 0)
+
+    CANARY = 0xA5
+
+    def check_canaries(self):
+        """Raise if any guard byte around a symmetric buffer of this rank changed (an out-of-bounds write, local or
+        from a peer). Synchronises the device; meant for tests and debugging, not for the step loop."""
+        torch.cuda.synchronize()
+        for i, (words, nbytes) in enumerate(getattr(self, "_guards", [])):
+            lo, hi = words[:self.GUARD_BYTES], words[self.GUARD_BYTES + nbytes:]
+            if not (bool((lo == self.CANARY).all()) and bool((hi == self.CANARY).all())):
+                raise RuntimeError(f"rank {self.rank}: guard words of symmetric buffer {i} were overwritten")
 
     def ctx(self, channel=0):
         if channel:

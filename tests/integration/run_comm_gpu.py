@@ -199,6 +199,8 @@ def main():
     E.sym_barrier(*arena.ctx(), 4)
     torch.cuda.synchronize()
     arena.check()
+    dist.barrier()
+    arena.check_canaries()                         # no kernel of this rank or a peer wrote outside a symmetric buffer
     y = torch.ones(4, device=dev)
     dist.all_reduce(y)
     assert y[0].item() == world

@@ -42,6 +42,8 @@ def run(strategy_name, comm, world, rank, opt_name="sgd"):
             losses.append(float(lv))
         if hasattr(sess.engine, "check_errors"):
             sess.engine.check_errors()
+        if getattr(sess.engine, "arena", None) is not None:
+            sess.engine.arena.check_canaries()
         torch.cuda.synchronize()
         # variables are read back through the engine: a row-sharded embedding is gathered from its owners
         word = sess.engine.variable_value("emb.word:0").float()
@@ -80,6 +82,8 @@ def run_cnn(strategy_name, comm, world, rank):
         losses = [float(sess.run([loss, train_op], {images: data["images"], labels: data["labels"]})[0]) for _ in range(4)]
         if hasattr(sess.engine, "check_errors"):
             sess.engine.check_errors()
+        if getattr(sess.engine, "arena", None) is not None:
+            sess.engine.arena.check_canaries()
         torch.cuda.synchronize()
         state = torch.cat([sess.engine.variable_value(n).reshape(-1).float() for n, _ in ad.graph_item.named_parameters()])
         engine = type(sess.engine).__name__

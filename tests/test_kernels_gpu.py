@@ -484,3 +484,66 @@ def test_sparse_lookup_matches_embedding_with_sparse_gradient():
     ref.backward(dy.to(torch.bfloat16).float())
     _check(out, ref.detach(), 1e-2)
     _check(got, table.grad, 1e-2)
+
+
+def test_tail_handling_sweep_of_flat_kernels(E):
+    """Every length from 1 to 257 (vector tails, odd and prime sizes) for the kernels that take a flat element count;
+    guard words after each output buffer must stay untouched."""
+    torch.manual_seed(19)
+    lr = torch.tensor([1e-2], device="cuda")
+    step = torch.ones(1, dtype=torch.int64, device="cuda")
+    guard = 8
+    for n in list(range(1, 258)) + [1021, 4099]:
+        g = torch.randn(n, device="cuda")
+        bufs = [torch.full((n + guard,), 7.0, device="cuda") for _ in range(3)]      # p, m, v each followed by guard words
+        p, m, v = (b[:n] for b in bufs)                                              # each starts at an aligned base
+        p.copy_(torch.randn(n, device="cuda"))
+        m.zero_()
+        v.zero_()
+        p16 = torch.full((n + guard,), 7.0, dtype=torch.bfloat16, device="cuda")
+        ref = p.clone().requires_grad_(True)
+        opt = torch.optim.Adam([ref], lr=1e-2)
+        ref.grad = g.clone()
+        opt.step()
+        E.adam_update(p, g, m, v, p16[:n], lr, 0.9, 0.999, 1e-8, 0.0, False, step, 1.0)
+        assert (p - ref.detach()).abs().max().item() < 1e-5, n
+        assert (p16[:n].float() - p).abs().max().item() < 2e-2, n
+        assert all((b[n:] == 7.0).all() for b in bufs) and (p16[n:] == 7.0).all(), f"write past the end at n={n}"
+    from autodist_b200.ops import functional as Fn
+    for n in (1, 2, 3, 7, 31, 33, 255, 257, 1023, 1025):
+        gs = [torch.randn(n, device="cuda") * 4]
+        norm = gs[0].norm()
+        expect = gs[0] * min(1.0, 2.0 / (norm.item() + 1e-6))
+        Fn.clip_by_global_norm_(gs, 2.0)
+        _check(gs[0], expect, 1e-5)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 31, 127, 257, 1031])
+def test_row_kernels_with_prime_row_counts(E, rows):
+    torch.manual_seed(20)
+    H = 64
+    x = _rand(rows, H)
+    # layer-norm forward over an odd number of rows
+    gamma, beta = torch.randn(H, device="cuda"), torch.randn(H, device="cuda")
+    z, y = torch.empty_like(x), torch.full((rows + 1, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    E.ln_fwd(x, None, gamma, beta, z, y[:rows], mean, rstd, 1e-12, 0.0, 0, None)
+    _check(y[:rows], torch.nn.functional.layer_norm(x.float(), (H,), gamma, beta, 1e-12), 2e-2)
+    assert (y[rows] == 7.0).all()
+    # row gather (bf16 and fp32 tables) with repeated and boundary rows
+    table = torch.randn(rows, H, device="cuda")
+    ids = torch.randint(0, rows, (rows + 2,), device="cuda")
+    ids[0], ids[-1] = 0, rows - 1
+    out = torch.full((rows + 3, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    E.gather_rows_f32(table, ids, out[:rows + 2])
+    _check(out[:rows + 2], table[ids].to(torch.bfloat16).float(), 1e-6)
+    assert (out[rows + 2] == 7.0).all()
+    E.gather_rows(x, ids, out[:rows + 2])
+    assert torch.equal(out[:rows + 2], x[ids]) and (out[rows + 2] == 7.0).all()
+    # batch-norm statistics over a prime number of rows
+    from autodist_b200.ops import functional as Fn
+    xb = x.view(rows, 1, 1, H).permute(0, 3, 1, 2)
+    if rows > 1:
+        yb = Fn.batch_norm(xb, torch.ones(H, device="cuda"), torch.zeros(H, device="cuda"), None, None, True, 0.1, 1e-5, False)
+        ref = torch.nn.functional.batch_norm(xb.float(), None, None, None, None, True, 0.1, 1e-5)
+        _check(yb, ref, 3e-2)
