@@ -56,6 +56,7 @@ class ENV(enum.Enum):
     AUTODIST_RANK = (10, _as_str())                  # set by the launcher on spawned ranks
     AUTODIST_FETCH_MODE = (11, _as_str("replica0"))  # "replica0" (reference rule) or "local"
     AUTODIST_COMM = (12, _as_str("fused"))           # "fused" (own kernels) or "nccl" (baseline)
+    AUTODIST_METRICS_FILE = (13, _as_str())          # JSONL step metrics of rank 0 ("%r" in the name = every rank)
 
     @property
     def val(self):

@@ -33,6 +33,75 @@ class RunMetadata:
         self.trace_path = None
 
 
+class _StepMetrics:
+    """JSONL step metrics: step index, host and device milliseconds, samples per second, bytes all-reduced through
+    the library backend, and the first scalar fetch (the loss). Device time comes from CUDA events that are read one
+    step late, so enabling metrics adds no synchronisation to the step being measured."""
+
+    def __init__(self, path, engine):
+        self._path = path
+        self._engine = engine
+        self._cuda = engine.device.type == "cuda"
+        self._step = 0
+        self._pending = None
+        self._bytes0 = 0
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+
+    @classmethod
+    def from_env(cls, engine):
+        path = const.ENV.AUTODIST_METRICS_FILE.val
+        if not path:
+            return None
+        if "%r" in path:
+            path = path.replace("%r", str(engine.rank))
+        elif engine.rank != 0:
+            return None
+        return cls(path, engine)
+
+    def begin(self):
+        self._flush()
+        self._t0 = time.perf_counter()
+        self._bytes0 = getattr(self._engine.backend, "bytes_reduced", 0)
+        if self._cuda:
+            self._e0 = torch.cuda.Event(enable_timing=True)
+            self._e1 = torch.cuda.Event(enable_timing=True)
+            self._e0.record()
+
+    def end(self, result, feed_dict):
+        rec = {"step": self._step, "host_ms": (time.perf_counter() - self._t0) * 1e3,
+               "bytes_reduced": getattr(self._engine.backend, "bytes_reduced", 0) - self._bytes0}
+        self._step += 1
+        for v in (result if isinstance(result, (list, tuple)) else [result]):
+            if isinstance(v, (float, np.floating)) or (isinstance(v, (np.ndarray, torch.Tensor)) and getattr(v, "size", None) is not None
+                                                       and int(np.prod(tuple(v.shape))) == 1):
+                rec["loss"] = float(v)
+                break
+        batch = next((int(v.shape[0]) for v in (feed_dict or {}).values() if hasattr(v, "shape") and len(v.shape) > 0), None)
+        rec["batch"] = batch
+        if self._cuda:
+            self._e1.record()
+            self._pending = (rec, self._e0, self._e1)
+        else:
+            self._write(rec, rec["host_ms"])
+
+    def _flush(self):
+        if self._pending is not None:
+            rec, e0, e1 = self._pending
+            self._pending = None
+            e1.synchronize()
+            rec["device_ms"] = e0.elapsed_time(e1)
+            self._write(rec, rec["device_ms"])
+
+    def _write(self, rec, ms):
+        if rec.get("batch") and ms > 0:
+            rec["samples_per_sec"] = rec["batch"] / (ms / 1e3)
+        with open(self._path, "a") as f:
+            f.write(json.dumps(rec) + "\n")
+
+    def close(self):
+        self._flush()
+
+
 class WrappedSession:
     def __init__(self, cluster, graph_item, remapper, engine, coordinator=None, is_built=None):
         self._cluster = cluster
@@ -44,6 +113,7 @@ class WrappedSession:
         self._closed = False
         self._trace_step = 0
         self.last_step_ms = None
+        self._metrics = _StepMetrics.from_env(engine)
         logging.debug("session ready on rank %d (%s)", engine.rank, engine.device)
 
     @property
@@ -71,7 +141,11 @@ class WrappedSession:
                 [torch.profiler.ProfilerActivity.CUDA] if self._engine.device.type == "cuda" else []))
             prof.__enter__()
         try:
+            if self._metrics is not None:
+                self._metrics.begin()
             result = self._run(fetches, feed_dict)
+            if self._metrics is not None:
+                self._metrics.end(result, feed_dict)
         finally:
             if tracing:
                 prof.__exit__(None, None, None)
@@ -118,6 +192,8 @@ class WrappedSession:
         if self._closed:
             return
         self._closed = True
+        if self._metrics is not None:
+            self._metrics.close()
         try:
             self._engine.close()
         except Exception as e:  # shutting down: peers may already be gone

@@ -11,3 +11,30 @@ def test_single_instance_per_process():
     with pytest.raises(NotImplementedError):
         AutoDist(resource_spec=ResourceSpec.local(num_cpus=1))
     _reset_default_autodist()
+
+
+def test_step_metrics_file(tmp_path, monkeypatch):
+    import json
+    import torch
+    from autodist_b200 import AutoDist
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.resource_spec import ResourceSpec
+    from autodist_b200.strategy import PS
+    path = tmp_path / "metrics.jsonl"
+    monkeypatch.setenv("AUTODIST_METRICS_FILE", str(path))
+    _reset_default_autodist()
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=PS())
+    with ad.scope():
+        w = torch.nn.Parameter(torch.zeros(3))
+        x = ad.placeholder((None, 3), torch.float32, name="x")
+        loss = ((x * w).sum(1) - 1.0).pow(2).mean()
+        train_op = torch.optim.SGD([w], lr=0.1).minimize(loss)
+        sess = ad.create_distributed_session()
+        for _ in range(3):
+            sess.run([loss, train_op], {x: torch.ones(5, 3)})
+        sess.close()
+    _reset_default_autodist()
+    rows = [json.loads(line) for line in path.read_text().splitlines()]
+    assert [r["step"] for r in rows] == [0, 1, 2]
+    assert all(r["batch"] == 5 and r["host_ms"] > 0 and r["samples_per_sec"] > 0 for r in rows)
+    assert rows[2]["loss"] < rows[0]["loss"]
