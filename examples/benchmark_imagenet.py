@@ -6,7 +6,6 @@
 import argparse
 import os
 import sys
-import time
 
 import torch
 
@@ -14,6 +13,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from autodist_b200 import AutoDist, strategy as S  # noqa: E402
 from autodist_b200.models.cnn import ImageClassifier, synthetic_images  # noqa: E402
 from autodist_b200.resource_spec import ResourceSpec  # noqa: E402
+from autodist_b200.utils import train_utils as tu  # noqa: E402
 
 # variables per collective group used by the reference's driver (imagenet.py:151-158)
 CHUNK = {"vgg16": 25, "resnet101": 200, "inceptionv3": 30}
@@ -44,6 +44,8 @@ def main():
     ap.add_argument("--train_steps", type=int, default=50)
     ap.add_argument("--log_steps", type=int, default=10)
     ap.add_argument("--chunk_size", type=int, default=0)
+    ap.add_argument("--lr_schedule", action="store_true", help="warm-up + piecewise-constant decay (30/60/80 epochs) instead of a fixed rate")
+    ap.add_argument("--benchmark_log", default=None, help="JSONL metrics file")
     args = ap.parse_args()
     spec = ResourceSpec(args.resource_spec) if args.resource_spec else ResourceSpec.local(
         num_gpus=args.gpus if torch.cuda.is_available() else 0, num_cpus=args.gpus)
@@ -60,13 +62,23 @@ def main():
         opt = torch.optim.SGD(model.parameters(), lr=0.01 if args.cnn_model == "vgg16" else 0.1, momentum=0.9)
         train_op = opt.minimize(loss)
         sess = ad.create_distributed_session()
-        t0 = time.time()
+        global_batch = args.batch_size * args.gpus
+        sched = tu.PiecewiseConstantDecayWithWarmup(global_batch, 1281167, 5, [30, 60, 80], [1.0, 0.1, 0.01, 0.001],
+                                                    base_lr=0.01 if args.cnn_model == "vgg16" else 0.1) if args.lr_schedule else None
+        hist = tu.TimeHistory(global_batch, args.log_steps)
+        logger = tu.MetricsLogger(args.benchmark_log) if args.benchmark_log and sess.rank == 0 else None
+        if logger:
+            logger.log_run_info(args.cnn_model, "synthetic ImageNet shape", vars(args))
+        hist.on_train_begin()
         for step in range(1, args.train_steps + 1):
+            if sched is not None:
+                tu.set_learning_rate(opt, sched(step - 1))          # the engines read the captured optimizer's rate every step
             lv, _ = sess.run([loss, train_op], {images: data["images"], labels: data["labels"]})
-            if step % args.log_steps == 0 and sess.rank == 0:
-                dt = time.time() - t0
-                print(f"step {step} loss {float(lv):.4f} {args.log_steps * local / dt:.1f} images/s", flush=True)
-                t0 = time.time()
+            rec = hist.on_step_end()
+            if rec and sess.rank == 0:
+                print(f"step {step} loss {float(lv):.4f} {rec['examples_per_sec']:.1f} images/s", flush=True)
+                if logger:
+                    logger.log_metric("examples_per_sec", rec["examples_per_sec"], "images/s", step, {"loss": float(lv)})
 
 
 if __name__ == "__main__":
