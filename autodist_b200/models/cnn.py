@@ -64,15 +64,19 @@ def _conv(cin, cout, k, stride=1, padding=0, bias=False):
 
 
 class BatchNormAct(nn.BatchNorm2d):
-    """Batch-norm with an optional fused ReLU. With ``AUTODIST_NORM_POOL=own`` the training-mode statistics, the
-    normalisation (+ ReLU) and both backward passes run on the hand-written kernels; default is the library."""
+    """Batch-norm with an optional fused ReLU. For bf16 activations on a GPU (the autocast training path) the
+    training-mode statistics, the normalisation (+ ReLU) and both backward passes run on the hand-written kernels;
+    fp32 activations, evaluation mode and channel counts that are not a multiple of 8 use the library.
+    ``AUTODIST_NORM_POOL=library`` forces the library everywhere, ``=own`` the kernels for fp32 inputs too."""
 
     def __init__(self, channels, relu=False):
         super().__init__(channels)
         self.relu = relu
 
     def forward(self, x):
-        if x.is_cuda and USE_OWN_NORM_POOL and self.training and x.shape[1] % 8 == 0:
+        if _own_norm_pool(x) and self.training and self.momentum is not None:
+            if self.num_batches_tracked is not None:
+                self.num_batches_tracked.add_(1)
             return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, True, self.momentum, self.eps, self.relu)
         y = super().forward(x)
         return F.relu(y, inplace=True) if self.relu else y
@@ -80,12 +84,18 @@ class BatchNormAct(nn.BatchNorm2d):
 
 class MaxPool(nn.MaxPool2d):
     def forward(self, x):
-        if x.is_cuda and USE_OWN_NORM_POOL and x.shape[1] % 8 == 0:
+        if _own_norm_pool(x) and not self.ceil_mode and self.dilation == 1 and isinstance(self.kernel_size, int):
             return max_pool2d(x, self.kernel_size, self.stride, self.padding)
         return super().forward(x)
 
 
-USE_OWN_NORM_POOL = os.environ.get("AUTODIST_NORM_POOL", "library") == "own"
+NORM_POOL_MODE = os.environ.get("AUTODIST_NORM_POOL", "auto")          # auto | own | library
+
+
+def _own_norm_pool(x):
+    if not x.is_cuda or x.dim() != 4 or x.shape[1] % 8 or NORM_POOL_MODE == "library":
+        return False
+    return NORM_POOL_MODE == "own" or x.dtype == torch.bfloat16
 
 
 def _conv_bn(cin, cout, k, stride=1, padding=0):
