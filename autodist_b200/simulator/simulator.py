@@ -15,6 +15,8 @@ from autodist_b200.proto import synchronizers_pb2
 from autodist_b200.simulator.cost_model import NVSwitchCostModel
 
 _WIRE_FACTOR = {"NoneCompressor": 1.0, "HorovodCompressor": 0.5, "HorovodCompressorEF": 0.5}
+# HBM bytes moved by pack + unpack per byte of fp32 gradient
+_PACK_TRAFFIC = {"HorovodCompressor": 1.0 + 0.5 + 0.5 + 1.0, "HorovodCompressorEF": 1.0 + 2.0 + 0.5 + 0.5 + 1.0}
 
 
 class Simulator:
@@ -33,6 +35,11 @@ class Simulator:
 
     def simulate(self, strategy, graph_item, compute_ms=0.0):
         """Predicted step time in milliseconds (``compute_ms`` + exposed synchronisation + optimizer)."""
+        b = self.breakdown(strategy, graph_item)
+        return compute_ms + b["exposed_sync_ms"] + b["optimizer_ms"]
+
+    def breakdown(self, strategy, graph_item):
+        """``{"sync_ms", "exposed_sync_ms", "optimizer_ms"}`` of one step under ``strategy``."""
         m = self.model
         groups = defaultdict(float)
         sync = 0.0
@@ -55,6 +62,10 @@ class Simulator:
                         groups[(cfg.group, comp)] += (var.shape[0] + cols) * r * 4.0 / len(parts)
                     else:
                         groups[(cfg.group, comp)] += share * _WIRE_FACTOR.get(comp, 1.0)
+                        # narrowing is an extra pass over HBM on each side of the collective: read the gradient, (read
+                        # and write the error-feedback residual,) write the wire copy; read it back and widen it
+                        if comp in _PACK_TRAFFIC:
+                            sync += share * _PACK_TRAFFIC[comp] / (m.hbm_gbs * 1e9)
                     opt += m.optimizer(var.numel / len(parts))
                 elif which == "PSSynchronizer":
                     cfg = part.PSSynchronizer
@@ -74,7 +85,7 @@ class Simulator:
                 worst = max(owners.values())
                 sync += m.reduce_to_owner(worst) + m.broadcast_from_owner(worst / 2.0)
         exposed = sync * (1.0 - self.overlap)
-        return compute_ms + (exposed + opt) * 1e3
+        return {"sync_ms": sync * 1e3, "exposed_sync_ms": exposed * 1e3, "optimizer_ms": opt * 1e3}
 
     # ---- dataset records -----------------------------------------------------------------------------
     @staticmethod

@@ -57,3 +57,15 @@ def test_ranking_prefers_sharded_and_sparse_aware_strategies(tmp_path):
     path = Simulator.record(str(tmp_path), "r.yml", s, [0.011, 0.012, 0.010])
     recs = Simulator.load_records(str(tmp_path))
     assert os.path.exists(path) and abs(recs[0]["average"] - 0.011) < 1e-9 and len(recs[0]["runtime"]) == 3
+
+
+def test_predicted_against_measured_table():
+    from autodist_b200.simulator.compare import compare
+    out = compare("bert-tiny", 8, 5.0, {"AllReduce": 5.2, "PartitionedPS": 5.4}, fit_overlap=True)
+    rows = {r["strategy"]: r for r in out["rows"]}
+    assert set(rows) >= {"AllReduce", "AllReduceEF", "Parallax", "PSLoadBalancing", "PartitionedPS"}
+    assert 0.0 <= out["overlap"] <= 1.0
+    assert all(r["predicted_ms"] >= 5.0 and r["sync_ms"] > 0 for r in rows.values())
+    assert rows["AllReduce"]["ratio"] is not None and rows["Parallax"]["ratio"] is None
+    # the compressed wire is narrower but pays pack / unpack passes over HBM
+    assert rows["AllReduceEF"]["sync_ms"] != rows["AllReduce"]["sync_ms"]
