@@ -310,6 +310,19 @@ void adagrad_update(Tensor p, const Tensor& g, Tensor acc, const optional<Tensor
   adb200::adagrad_update(p.data_ptr<float>(), g.data_ptr<float>(), acc.data_ptr<float>(), OPT_BF(p16), p.numel(), lr.data_ptr<float>(),
                          (float)eps, (float)wd, (float)grad_scale, STREAM);
 }
+void sparse_rows_update(Tensor p, const optional<Tensor>& s1, const optional<Tensor>& s2, const optional<Tensor>& p16, const Tensor& rows,
+                        const Tensor& g, int64_t kind, const Tensor& lr, double b1, double b2, double eps, const optional<Tensor>& step,
+                        double grad_scale) {
+  TORCH_CHECK(p.dim() == 2 && p.is_contiguous() && p.scalar_type() == at::kFloat, "parameter must be a contiguous fp32 [V, H] table");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && g.is_contiguous() && g.dim() == 2 && g.size(0) == rows.numel() && g.size(1) == p.size(1),
+              "gradient rows must be fp32 [n, H]");
+  TORCH_CHECK(rows.scalar_type() == at::kLong && rows.is_contiguous(), "row ids must be int64");
+  TORCH_CHECK(kind == 0 || (s1.has_value() && s1->sizes() == p.sizes()), "state 1 must match the table");
+  TORCH_CHECK(kind != 1 || (s2.has_value() && s2->sizes() == p.sizes() && step.has_value()), "lazy Adam needs both moments and the step");
+  adb200::sparse_rows_update(p.data_ptr<float>(), OPT_F(s1), OPT_F(s2), OPT_BF(p16), rows.data_ptr<int64_t>(), g.data_ptr<float>(),
+                             (int)rows.numel(), (int)p.size(1), p.size(0), (int)kind, lr.data_ptr<float>(), (float)b1, (float)b2,
+                             (float)eps, OPT_LL(step), (float)grad_scale, STREAM);
+}
 void lstm_cell_fwd(const Tensor& gates, const Tensor& c_prev, Tensor c, Tensor h, double forget_bias) {
   const int B = c_prev.size(0), S = c_prev.size(1);
   TORCH_CHECK(gates.scalar_type() == at::kFloat && gates.size(1) == 4 * S && gates.is_contiguous(), "gates must be fp32 [B, 4S]");
@@ -483,6 +496,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adam_update", &adam_update);
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
+  m.def("sparse_rows_update", &sparse_rows_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("bn_fwd", &bn_fwd);
   m.def("bn_bwd", &bn_bwd);

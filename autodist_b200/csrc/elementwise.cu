@@ -648,6 +648,44 @@ __global__ void adagrad_kernel(float* __restrict__ p, const float* __restrict__ 
   if (p16) p16[i] = __float2bfloat16(np);
 }
 
+// Row-sparse updates: only the rows that received a gradient are touched (rows must be unique, i.e. a coalesced
+// gradient). kind 0 = SGD, 1 = lazy Adam (moments of untouched rows do not decay), 2 = Adagrad. One warp per row.
+__global__ void sparse_rows_update_kernel(float* __restrict__ p, float* __restrict__ s1, float* __restrict__ s2,
+                                          bf16* __restrict__ p16, const int64_t* __restrict__ rows, const float* __restrict__ g,
+                                          int n, int H, long long V, int kind, const float* __restrict__ lr_ptr, float b1, float b2,
+                                          float eps, const long long* __restrict__ step_ptr, float grad_scale) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n) return;
+  const long long r = rows[warp];
+  if (r < 0 || r >= V) return;                       // out-of-range ids are ignored, never written
+  const float lr = *lr_ptr;
+  float inv_c1 = 1.f, inv_c2 = 1.f;
+  if (kind == 1) {
+    const float t = (float)(*step_ptr);
+    inv_c1 = 1.0f / (1.0f - powf(b1, t));
+    inv_c2 = 1.0f / (1.0f - powf(b2, t));
+  }
+  for (int c = lane; c < H; c += 32) {
+    const long long i = r * H + c;
+    const float gr = g[(long long)warp * H + c] * grad_scale;
+    float np;
+    if (kind == 0) {
+      np = p[i] - lr * gr;
+    } else if (kind == 1) {
+      const float m = b1 * s1[i] + (1.0f - b1) * gr, v = b2 * s2[i] + (1.0f - b2) * gr * gr;
+      s1[i] = m;
+      s2[i] = v;
+      np = p[i] - lr * (m * inv_c1) / (sqrtf(v * inv_c2) + eps);
+    } else {
+      const float a = s1[i] + gr * gr;
+      s1[i] = a;
+      np = p[i] - lr * gr / (sqrtf(a) + eps);
+    }
+    p[i] = np;
+    if (p16) p16[i] = __float2bfloat16(np);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ LSTM cell (K17)
 // gates [B, 4S] in the order i, j, f, o (fp32); c = sigmoid(f + fb) * c_prev + sigmoid(i) * tanh(j); h = sigmoid(o) * tanh(c)
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
@@ -1080,6 +1118,12 @@ void sgd_update(float* p, const float* g, float* mom, bf16* p16, long long n, co
 void adagrad_update(float* p, const float* g, float* acc, bf16* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st) {
   adagrad_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, acc, p16, n, lr, eps, wd, grad_scale);
+}
+void sparse_rows_update(float* p, float* s1, float* s2, bf16* p16, const int64_t* rows, const float* g, int n, int H, long long V,
+                        int kind, const float* lr, float b1, float b2, float eps, const long long* step, float grad_scale,
+                        cudaStream_t st) {
+  if (n <= 0) return;
+  sparse_rows_update_kernel<<<blocks_for(n, 8), 256, 0, st>>>(p, s1, s2, p16, rows, g, n, H, V, kind, lr, b1, b2, eps, step, grad_scale);
 }
 void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16* h, int B, int S, float fb, cudaStream_t st) {
   lstm_cell_fwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, h, B, S, fb);

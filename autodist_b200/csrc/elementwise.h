@@ -36,6 +36,9 @@ void adam_update(float* p, const float* g, float* m, float* v, bf16_t* p16, long
                  float eps, float wd, int decoupled, const long long* step, float grad_scale, cudaStream_t st);
 void sgd_update(float* p, const float* g, float* mom, bf16_t* p16, long long n, const float* lr, float momentum, float dampening,
                 float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st);
+void sparse_rows_update(float* p, float* s1, float* s2, bf16_t* p16, const int64_t* rows, const float* g, int n, int H, long long V,
+                        int kind, const float* lr, float b1, float b2, float eps, const long long* step, float grad_scale,
+                        cudaStream_t st);
 void adagrad_update(float* p, const float* g, float* acc, bf16_t* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st);
 void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16_t* h, int B, int S, float fb, cudaStream_t st);

@@ -298,3 +298,28 @@ def sparse_lookup(table, ids):
     if table.is_cuda and table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] % 8 == 0:
         return _SparseLookupFn.apply(table, ids)
     return F.embedding(ids, table, sparse=True)
+
+
+_SPARSE_KINDS = {"sgd": 0, "lazy_adam": 1, "adagrad": 2}
+
+
+def sparse_rows_update_(kind, table, grad, lr, state1=None, state2=None, step=None, betas=(0.9, 0.999), eps=1e-8,
+                        grad_scale=1.0, table_bf16=None):
+    """Apply a row-sparse gradient to ``table`` in place, touching only the rows that carry a gradient.
+
+    ``kind``: ``"sgd"``, ``"lazy_adam"`` (moments of untouched rows do not decay; ``step`` is the int64 device counter
+    already incremented for this step) or ``"adagrad"``. ``grad`` is a sparse COO tensor (it is coalesced first: the
+    kernel needs unique rows) or a ``(rows, values)`` pair that is already unique. ``lr`` is a float or a device
+    tensor. The reference reaches the same updates through TensorFlow's ``ResourceSparseApply*`` family
+    (``autodist/kernel/common/op_info.py:24-117``)."""
+    E = ops.ext(required=True)
+    if isinstance(grad, tuple):
+        rows, vals = grad
+    else:
+        g = grad.coalesce()
+        rows, vals = g.indices()[0], g.values()
+    if not torch.is_tensor(lr):
+        lr = torch.tensor([float(lr)], dtype=torch.float32, device=table.device)
+    E.sparse_rows_update(table, state1, state2, table_bf16, rows.contiguous(), vals.float().contiguous(), _SPARSE_KINDS[kind], lr,
+                         betas[0], betas[1], eps, step, grad_scale)
+    return table

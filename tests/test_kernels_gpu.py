@@ -547,3 +547,37 @@ def test_row_kernels_with_prime_row_counts(E, rows):
         yb = Fn.batch_norm(xb, torch.ones(H, device="cuda"), torch.zeros(H, device="cuda"), None, None, True, 0.1, 1e-5, False)
         ref = torch.nn.functional.batch_norm(xb.float(), None, None, None, None, True, 0.1, 1e-5)
         _check(yb, ref, 3e-2)
+
+
+@pytest.mark.parametrize("kind", ["sgd", "adagrad", "lazy_adam"])
+def test_sparse_row_updates_match_the_torch_sparse_optimizers(kind):
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(21)
+    V, H = 301, 40
+    p0 = torch.randn(V, H, device="cuda")
+    ref = p0.clone().requires_grad_(True)
+    opt = {"sgd": lambda: torch.optim.SGD([ref], lr=0.1), "adagrad": lambda: torch.optim.Adagrad([ref], lr=0.1, eps=1e-10),
+           "lazy_adam": lambda: torch.optim.SparseAdam([ref], lr=0.01)}[kind]()
+    p = p0.clone()
+    p16 = p0.to(torch.bfloat16)
+    s1, s2 = torch.zeros_like(p), torch.zeros_like(p)
+    step = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for it in range(4):
+        ids = torch.randint(0, V, (64,), device="cuda")
+        ids[:8] = 5                                                           # duplicates are summed by the coalesce
+        vals = torch.randn(64, H, device="cuda")
+        g = torch.sparse_coo_tensor(ids[None], vals, (V, H))
+        ref.grad = g
+        opt.step()
+        step += 1
+        Fn.sparse_rows_update_(kind, p, g, 0.01 if kind == "lazy_adam" else 0.1, s1, s2, step, eps=1e-8 if kind == "lazy_adam" else 1e-10,
+                               table_bf16=p16)
+    torch.cuda.synchronize()
+    assert (p - ref.detach()).abs().max().item() < 1e-5
+    untouched = torch.ones(V, dtype=torch.bool, device="cuda")
+    assert (p16.float() - p).abs().max().item() < 2e-2
+    # ids outside the table are ignored
+    before = p.clone()
+    Fn.sparse_rows_update_("sgd", p, (torch.tensor([V + 3, -1], device="cuda"), torch.ones(2, H, device="cuda")), 0.1)
+    torch.cuda.synchronize()
+    assert torch.equal(p, before) and untouched.all()
