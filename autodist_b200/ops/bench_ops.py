@@ -29,12 +29,68 @@ def _time(fn, iters=10, flush=None):
     return total / iters
 
 
+def _cnn_rows(E, dev, flush, hbm):
+    """Batch-norm (+ReLU), max-pool, fp32 -> bf16 row gather and the row-sparse Adagrad update, each beside the
+    library op of the same shape; bytes are the algorithmic minimum (every tensor read or written once per pass)."""
+    import torch.nn.functional as F
+    from autodist_b200.ops import functional as Fn
+    rows = []
+    N, C, Hh, W = 64, 256, 56, 56                                   # the ResNet stage-1 activation, 103 MB in bf16
+    x = torch.randn(N, C, Hh, W, device=dev).to(torch.bfloat16).to(memory_format=torch.channels_last)
+    xh = x.permute(0, 2, 3, 1).contiguous()
+    gamma, beta = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+    y = torch.empty_like(xh)
+    mean, rstd = torch.empty(C, device=dev), torch.empty(C, device=dev)
+    nbytes = xh.numel() * 2
+    ms = _time(lambda: E.bn_fwd(xh, gamma, beta, y, mean, rstd, 1e-5, True), flush=flush)
+    ms_lib = _time(lambda: F.relu(F.batch_norm(x, None, None, gamma, beta, True, 0.1, 1e-5)), flush=flush)
+    rows.append({"kernel": "bn_fwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(3 * nbytes / ms / 1e6, 1),
+                 "library_ms": round(ms_lib, 4), "frac_of_measured_peak": round(3 * nbytes / ms / 1e6 / hbm, 3)})
+    dy, dx = torch.randn_like(xh), torch.empty_like(xh)
+    ms = _time(lambda: E.bn_bwd(dy, xh, y, mean, rstd, gamma, dx, True), flush=flush)
+    rows.append({"kernel": "bn_bwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(7 * nbytes / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(7 * nbytes / ms / 1e6 / hbm, 3)})
+    N, C, Hh, W = 64, 64, 112, 112                                   # the ResNet stem pool
+    x = torch.randn(N, C, Hh, W, device=dev).to(torch.bfloat16).to(memory_format=torch.channels_last)
+    xh = x.permute(0, 2, 3, 1).contiguous()
+    yo = torch.empty(N, 56, 56, C, dtype=torch.bfloat16, device=dev)
+    nb = (xh.numel() + yo.numel()) * 2
+    ms = _time(lambda: E.maxpool_fwd(xh, yo, 3, 2, 1), flush=flush)
+    ms_lib = _time(lambda: F.max_pool2d(x, 3, 2, 1), flush=flush)
+    rows.append({"kernel": "maxpool_fwd 3x3/2 64x112x112x64", "ms": round(ms, 4), "gbs": round(nb / ms / 1e6, 1),
+                 "library_ms": round(ms_lib, 4), "frac_of_measured_peak": round(nb / ms / 1e6 / hbm, 3)})
+    dyo, dxo = torch.randn_like(yo), torch.empty_like(xh)
+    ms = _time(lambda: E.maxpool_bwd(xh, yo, dyo, dxo, 3, 2, 1), flush=flush)
+    nb = (2 * xh.numel() + 2 * yo.numel()) * 2
+    rows.append({"kernel": "maxpool_bwd 3x3/2 64x112x112x64", "ms": round(ms, 4), "gbs": round(nb / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(nb / ms / 1e6 / hbm, 3)})
+    V, Hd, n = 793471, 512, 128 * 20 + 8192                          # LM1B tables and one step's lookups
+    table = torch.randn(V, Hd, device=dev)
+    ids = torch.randint(0, V, (n,), device=dev)
+    out = torch.empty(n, Hd, dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: E.gather_rows_f32(table, ids, out), flush=flush)
+    ms_lib = _time(lambda: F.embedding(ids, table).to(torch.bfloat16), flush=flush)
+    rows.append({"kernel": f"gather_rows_f32 {n} rows x 512 of 793471", "ms": round(ms, 4), "gbs": round(n * Hd * 6 / ms / 1e6, 1),
+                 "library_ms": round(ms_lib, 4), "frac_of_measured_peak": round(n * Hd * 6 / ms / 1e6 / hbm, 3)})
+    acc = torch.zeros_like(table)
+    uniq = torch.unique(ids)
+    vals = torch.randn(uniq.numel(), Hd, device=dev)
+    lr = torch.tensor([0.2], device=dev)
+    ms = _time(lambda: Fn.sparse_rows_update_("adagrad", table, (uniq, vals), lr, acc), flush=flush)
+    nb = uniq.numel() * Hd * 4 * 5
+    rows.append({"kernel": f"sparse_rows_update adagrad {uniq.numel()} rows x 512", "ms": round(ms, 4), "gbs": round(nb / ms / 1e6, 1),
+                 "frac_of_measured_peak": round(nb / ms / 1e6 / hbm, 3)})
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default="", help="run only the GEMM shapes whose label contains this text")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--group", default="all", choices=["all", "gemm", "bert", "cnn"],
+                    help="gemm: GEMM shapes; bert: LayerNorm / Adam; cnn: batch-norm, max-pool, row gather, sparse-row update")
     args = ap.parse_args()
     from autodist_b200 import ops
     E = ops.ext(required=True)
@@ -56,6 +112,8 @@ def main():
         shapes = shapes[:2]
     if args.only:
         shapes = [s for s in shapes if args.only in s[0]]
+    if args.group in ("bert", "cnn"):
+        shapes = []
     for name, M, N, K, a_mn, b_mn in shapes:
         a = torch.randn((K, M) if a_mn else (M, K), device=dev).to(torch.bfloat16)
         b = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
@@ -72,6 +130,16 @@ def main():
     if args.only:
         for r in rows:
             print(json.dumps(r))
+        return
+    hbm = peaks.get("hbm_gbs", 6518.6)
+    if args.group in ("all", "cnn"):
+        rows += _cnn_rows(E, dev, flush, hbm)
+    if args.group in ("gemm", "cnn"):
+        for r in rows:
+            print(json.dumps(r))
+        if args.json:
+            with open(args.json, "w") as f:
+                json.dump(rows, f, indent=1)
         return
     # bandwidth-bound kernels
     H = 1024
