@@ -340,29 +340,39 @@ void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_sca
 void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor y, Tensor mean, Tensor rstd, double eps, bool relu) {
   const int C = x.size(-1), rows = x.numel() / C;
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [.., C], C % 8 == 0");
+  TORCH_CHECK(y.is_contiguous() && y.numel() == x.numel() && mean.numel() == C && rstd.numel() == C && gamma.numel() == C && beta.numel() == C,
+              "output and per-channel tensors must match x");
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
-  Tensor sums = at::empty({2 * C}, x.options().dtype(at::kFloat));
+  Tensor sums = at::empty({4 * C}, x.options().dtype(at::kFloat));             // [sum x, sum x^2, scale, shift]
   adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                 part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, STREAM);
+                 part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, (float)eps, relu ? 1 : 0, STREAM);
 }
 // Returns [dbeta, dgamma] stacked as a [2, C] fp32 tensor; writes dx.
 Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
               bool relu) {
   const int C = x.size(-1), rows = x.numel() / C;
+  TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
+              "dy, x, dx must be contiguous bf16 [.., C] of one shape, C % 8 == 0");
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
-  Tensor sums = at::empty({2, C}, x.options().dtype(at::kFloat));
+  Tensor sums = at::empty({5, C}, x.options().dtype(at::kFloat));              // [dbeta, dgamma, A, B, K]
   adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx),
-                 part.data_ptr<float>(), sums.data_ptr<float>(), rows, C, relu ? 1 : 0, STREAM);
-  return sums;
+                 part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, relu ? 1 : 0, STREAM);
+  return sums.narrow(0, 0, 2);
 }
-void maxpool_fwd(const Tensor& x, Tensor y, int64_t k, int64_t stride, int64_t pad) {
-  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.size(3) % 8 == 0, "x must be contiguous bf16 [N, H, W, C]");
-  adb200::maxpool_fwd(CBF(x), BF(y), x.size(0), x.size(1), x.size(2), x.size(3), k, stride, pad, y.size(1), y.size(2), STREAM);
+// code: uint8 [N, Ho, Wo, C], the window position of each output's first maximum
+void maxpool_fwd(const Tensor& x, Tensor y, Tensor code, int64_t k, int64_t stride, int64_t pad) {
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.size(3) % 8 == 0 && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [N, H, W, C]");
+  TORCH_CHECK(y.is_contiguous() && code.is_contiguous() && code.scalar_type() == at::kByte && code.numel() == y.numel() && k * k < 255 &&
+              y.size(0) == x.size(0) && y.size(3) == x.size(3), "y / code must be [N, Ho, Wo, C]");
+  adb200::maxpool_fwd(CBF(x), BF(y), code.data_ptr<uint8_t>(), x.size(0), x.size(1), x.size(2), x.size(3), k, stride, pad, y.size(1),
+                      y.size(2), STREAM);
 }
-void maxpool_bwd(const Tensor& x, const Tensor& y, const Tensor& dy, Tensor dx, int64_t k, int64_t stride, int64_t pad) {
-  adb200::maxpool_bwd(CBF(x), CBF(y), CBF(dy), BF(dx), x.size(0), x.size(1), x.size(2), x.size(3), k, stride, pad, y.size(1), y.size(2), STREAM);
+void maxpool_bwd(const Tensor& code, const Tensor& dy, Tensor dx, int64_t k, int64_t stride, int64_t pad) {
+  TORCH_CHECK(dx.dim() == 4 && dx.is_contiguous() && dy.is_contiguous() && code.is_contiguous() && code.numel() == dy.numel() &&
+              dx.size(3) % 8 == 0, "dx [N, H, W, C], dy / code [N, Ho, Wo, C], contiguous");
+  adb200::maxpool_bwd(code.data_ptr<uint8_t>(), CBF(dy), BF(dx), dx.size(0), dx.size(1), dx.size(2), dx.size(3), k, stride, pad, dy.size(1),
+                      dy.size(2), STREAM);
 }
-// x: channels-last activations viewed as [N, H, W, C] bf16 contiguous; cols: [N*Ho*Wo, KH*KW*C]
 void im2col(const Tensor& x, Tensor cols, int64_t KH, int64_t KW, int64_t stride, int64_t pad) {
   TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.size(3) % 8 == 0, "x must be contiguous bf16 [N, H, W, C], C % 8 == 0");
   const int N = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);

@@ -797,6 +797,7 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__
 // ------------------------------------------------------------------------------------------------ batch-norm (K14), pooling (K15)
 // Channels-last activations seen as a matrix [rows = N*H*W, C] (C a multiple of 8).
 // Statistics: part[y][0][c] = sum x, part[y][1][c] = sum x^2 over row chunk y (then colsum_f32 over the chunks).
+// Each thread keeps four independent 16-byte loads in flight.
 __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int rows, int C, int rows_per_block) {
   __shared__ float s1[32][65], s2[32][65];
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
@@ -804,11 +805,22 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
   const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
   float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (c < C)
-    for (int r = r0 + rl; r < r1; r += 32) {
-      float v[8];
-      load8(x + (long long)r * C + c, v);
+    for (int r = r0 + rl; r < r1; r += 128) {
+      float v[4][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { a[i] += v[i]; b[i] += v[i] * v[i]; }
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 32 * u;
+        if (rr < r1) {
+          load8(x + (long long)rr * C + c, v[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { a[i] += v[u][i]; b[i] += v[u][i] * v[u][i]; }
     }
 #pragma unroll
   for (int i = 0; i < 8; ++i) { s1[rl][vec * 8 + i] = a[i]; s2[rl][vec * 8 + i] = b[i]; }
@@ -821,23 +833,37 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
   }
 }
 
-// y = relu?((x - mean) * rstd * gamma + beta); sums = [sum x, sum x^2] per channel; also writes mean / rstd.
-__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ sums, const float* __restrict__ gamma,
-                                const float* __restrict__ beta, bf16* __restrict__ y, float* __restrict__ mean_out,
-                                float* __restrict__ rstd_out, long long rows, int C, float eps, int relu) {
+// Per-channel mean / rstd and the affine form of the normalisation: y = x * scale + shift.
+// coef = [scale (C), shift (C)]; sums = [sum x (C), sum x^2 (C)].
+__global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                   float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ coef, float inv_rows, int C,
+                                   float eps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float mu = sums[c] * inv_rows;
+  const float var = fmaxf(sums[C + c] * inv_rows - mu * mu, 0.f);
+  const float rs = rsqrtf(var + eps);
+  mean[c] = mu;
+  rstd[c] = rs;
+  const float sc = gamma[c] * rs;
+  coef[c] = sc;
+  coef[C + c] = beta[c] - mu * sc;
+}
+
+// y = relu?(x * scale + shift)
+__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ coef, bf16* __restrict__ y, long long total8, int C,
+                                int relu) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c8 = C / 8;
-  if (idx >= rows * c8) return;
-  const int c = (int)(idx % c8) * 8;
+  if (idx >= total8) return;
+  const int c = (int)(idx % (C / 8)) * 8;
   float v[8];
   load8(x + idx * 8, v);
+  const float4 s0 = *reinterpret_cast<const float4*>(coef + c), s1 = *reinterpret_cast<const float4*>(coef + c + 4);
+  const float4 h0 = *reinterpret_cast<const float4*>(coef + C + c), h1 = *reinterpret_cast<const float4*>(coef + C + c + 4);
+  const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w}, sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float mu = sums[c + j] / rows;
-    const float var = fmaxf(sums[C + c + j] / rows - mu * mu, 0.f);
-    const float rs = rsqrtf(var + eps);
-    if (idx < c8) { mean_out[c + j] = mu; rstd_out[c + j] = rs; }
-    float o = (v[j] - mu) * rs * gamma[c + j] + beta[c + j];
+    const float o = fmaf(v[j], sc[j], sh[j]);
     v[j] = relu ? fmaxf(o, 0.f) : o;
   }
   store8(y + idx * 8, v);
@@ -852,19 +878,34 @@ __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __r
   const int c = blockIdx.x * 64 + vec * 8;
   const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
   float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (c < C)
-    for (int r = r0 + rl; r < r1; r += 32) {
-      float d[8], xv[8], yv[8];
-      load8(dy + (long long)r * C + c, d);
-      load8(x + (long long)r * C + c, xv);
-      if (relu) load8(y + (long long)r * C + c, yv);
+  if (c < C) {
+    float mu[8], rs[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float g = (relu && yv[i] <= 0.f) ? 0.f : d[i];
-        a[i] += g;
-        b[i] += g * (xv[i] - mean[c + i]) * rstd[c + i];
+    for (int i = 0; i < 8; ++i) { mu[i] = mean[c + i]; rs[i] = rstd[c + i]; }
+    for (int r = r0 + rl; r < r1; r += 64) {
+      float d[2][8], xv[2][8], yv[2][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int rr = r + 32 * u;
+        if (rr < r1) {
+          load8(dy + (long long)rr * C + c, d[u]);
+          load8(x + (long long)rr * C + c, xv[u]);
+          if (relu) load8(y + (long long)rr * C + c, yv[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { d[u][i] = 0.f; xv[u][i] = 0.f; yv[u][i] = 1.f; }
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float g = (relu && yv[u][i] <= 0.f) ? 0.f : d[u][i];
+          a[i] += g;
+          b[i] += g * (xv[u][i] - mu[i]) * rs[i];
+        }
     }
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) { s1[rl][vec * 8 + i] = a[i]; s2[rl][vec * 8 + i] = b[i]; }
   __syncthreads();
@@ -876,31 +917,41 @@ __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __r
   }
 }
 
-// dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M); sums = [dbeta, dgamma]
+// dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M) = A * dy' + B * x + K per channel; coef = [A (C), B (C), K (C)].
+__global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
+                                       const float* __restrict__ rstd, float* __restrict__ coef, float inv_rows, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float a = gamma[c] * rstd[c];
+  const float k0 = sums[c] * inv_rows, k1 = sums[C + c] * inv_rows;
+  const float bx = -a * rstd[c] * k1;
+  coef[c] = a;
+  coef[C + c] = bx;
+  coef[2 * C + c] = -bx * mean[c] - a * k0;
+}
+
 __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
-                                    const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ gamma,
-                                    const float* __restrict__ sums, bf16* __restrict__ dx, long long rows, int C, int relu) {
+                                    const float* __restrict__ coef, bf16* __restrict__ dx, long long total8, int C, int relu) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c8 = C / 8;
-  if (idx >= rows * c8) return;
-  const int c = (int)(idx % c8) * 8;
+  if (idx >= total8) return;
+  const int c = (int)(idx % (C / 8)) * 8;
   float d[8], xv[8], yv[8];
   load8(dy + idx * 8, d);
   load8(x + idx * 8, xv);
   if (relu) load8(y + idx * 8, yv);
-  const float inv_m = 1.0f / rows;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float g = (relu && yv[j] <= 0.f) ? 0.f : d[j];
-    const float xh = (xv[j] - mean[c + j]) * rstd[c + j];
-    d[j] = gamma[c + j] * rstd[c + j] * (g - sums[c + j] * inv_m - xh * sums[C + c + j] * inv_m);
+    d[j] = fmaf(coef[c + j], g, fmaf(coef[C + c + j], xv[j], coef[2 * C + c + j]));
   }
   store8(dx + idx * 8, d);
 }
 
-// Max pooling over [N, H, W, C] windows (k x k, stride, pad); the backward pass recomputes the arg-max (first maximum wins).
-__global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int k, int stride,
-                                   int pad, int Ho, int Wo) {
+// Max pooling over [N, H, W, C] windows (k x k, stride, pad). The forward pass records, per output element, which
+// window position held the first maximum (kh * k + kw, 255 = empty window); the backward pass routes the gradient
+// with that code, so ties (common after a ReLU) go to exactly one input as in the library.
+__global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ code, int N, int H, int W,
+                                   int C, int k, int stride, int pad, int Ho, int Wo) {
   const int c8 = C / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)N * Ho * Wo * c8) return;
@@ -908,30 +959,35 @@ __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
   long long r = idx / c8;
   const int wo = (int)(r % Wo), ho = (int)((r / Wo) % Ho), n = (int)(r / ((long long)Wo * Ho));
   float m[8];
+  uint32_t pos[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) m[j] = -INFINITY;
+  for (int j = 0; j < 8; ++j) { m[j] = -INFINITY; pos[j] = 255u; }
   for (int kh = 0; kh < k; ++kh)
     for (int kw = 0; kw < k; ++kw) {
       const int hi = ho * stride - pad + kh, wi = wo * stride - pad + kw;
       if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
       float v[8];
       load8(x + (((long long)n * H + hi) * W + wi) * C + cv * 8, v);
+      const uint32_t t = (uint32_t)(kh * k + kw);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m[j] = fmaxf(m[j], v[j]);
+      for (int j = 0; j < 8; ++j)
+        if (pos[j] == 255u || v[j] > m[j]) { m[j] = v[j]; pos[j] = t; }
     }
   store8(y + idx * 8, m);
+  const uint32_t lo = pos[0] | (pos[1] << 8) | (pos[2] << 16) | (pos[3] << 24);
+  const uint32_t hi4 = pos[4] | (pos[5] << 8) | (pos[6] << 16) | (pos[7] << 24);
+  *reinterpret_cast<uint2*>(code + idx * 8) = make_uint2(lo, hi4);
 }
 
-__global__ void maxpool_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ dy,
-                                   bf16* __restrict__ dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo) {
+__global__ void maxpool_bwd_kernel(const uint8_t* __restrict__ code, const bf16* __restrict__ dy, bf16* __restrict__ dx, int N, int H,
+                                   int W, int C, int k, int stride, int pad, int Ho, int Wo) {
   const int c8 = C / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)N * H * W * c8) return;
   const int cv = (int)(idx % c8);
   long long r = idx / c8;
   const int wi = (int)(r % W), hi = (int)((r / W) % H), n = (int)(r / ((long long)W * H));
-  float xv[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  load8(x + idx * 8, xv);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   for (int kh = 0; kh < k; ++kh) {
     const int hn = hi + pad - kh;
     if (hn < 0 || hn % stride) continue;
@@ -943,23 +999,15 @@ __global__ void maxpool_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
       const int wo = wn / stride;
       if (wo >= Wo) continue;
       const long long o = ((((long long)n * Ho + ho) * Wo + wo) * C) + cv * 8;
-      float yv[8], dv[8];
-      load8(y + o, yv);
+      const uint2 packed = *reinterpret_cast<const uint2*>(code + o);
+      const uint32_t t = (uint32_t)(kh * k + kw);
+      float dv[8];
       load8(dy + o, dv);
-      // the gradient goes to the first maximum of the window in scan order (ties are common after a ReLU)
-      bool first[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) first[j] = xv[j] == yv[j];
-      for (int t = 0; t < kh * k + kw; ++t) {
-        const int h2 = ho * stride - pad + t / k, w2 = wo * stride - pad + t % k;
-        if (h2 < 0 || h2 >= H || w2 < 0 || w2 >= W) continue;
-        float ev[8];
-        load8(x + (((long long)n * H + h2) * W + w2) * C + cv * 8, ev);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) if (ev[j] == yv[j]) first[j] = false;
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t p = ((j < 4 ? packed.x : packed.y) >> (8 * (j & 3))) & 0xffu;
+        if (p == t) acc[j] += dv[j];
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (first[j]) acc[j] += dv[j];
     }
   }
   store8(dx + idx * 8, acc);
@@ -1140,34 +1188,40 @@ void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStr
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
 }
-// Row chunks per channel block: enough blocks to fill the SMs (~4 per SM) while each chunk keeps >= 64 rows.
+// Row chunks per channel block: enough blocks to fill the SMs (~8 per SM) while each chunk keeps >= 128 rows.
 int bn_parts(int rows, int C) {
   const int cb = (C + 63) / 64;
-  int parts = (592 + cb - 1) / cb;
-  if (parts > rows / 64) parts = rows / 64;
-  if (parts > 256) parts = 256;
+  int parts = (1184 + cb - 1) / cb;
+  if (parts > rows / 128) parts = rows / 128;
+  if (parts > 512) parts = 512;
   return parts < 1 ? 1 : parts;
 }
+// part: [bn_parts, 2, C]; sums: [2, C]; coef: [2, C] (forward) or [3, C] (backward)
 void bn_fwd(const bf16* x, const float* gamma, const float* beta, bf16* y, float* mean, float* rstd, float* part, float* sums,
-            int rows, int C, float eps, int relu, cudaStream_t st) {
+            float* coef, int rows, int C, float eps, int relu, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
   colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
-  bn_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(x, sums, gamma, beta, y, mean, rstd, rows, C, eps, relu);
+  bn_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, beta, mean, rstd, coef, 1.0f / rows, C, eps);
+  const long long total8 = (long long)rows * (C / 8);
+  bn_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(x, coef, y, total8, C, relu);
 }
 void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx,
-            float* part, float* sums, int rows, int C, int relu, cudaStream_t st) {
+            float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
   colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
-  bn_bwd_apply_kernel<<<blocks_for((long long)rows * (C / 8), 256), 256, 0, st>>>(dy, x, y, mean, rstd, gamma, sums, dx, rows, C, relu);
+  bn_bwd_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, mean, rstd, coef, 1.0f / rows, C);
+  const long long total8 = (long long)rows * (C / 8);
+  bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, total8, C, relu);
 }
-void maxpool_fwd(const bf16* x, bf16* y, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
-  maxpool_fwd_kernel<<<blocks_for((long long)N * Ho * Wo * (C / 8), 256), 256, 0, st>>>(x, y, N, H, W, C, k, stride, pad, Ho, Wo);
+void maxpool_fwd(const bf16* x, bf16* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
+                 cudaStream_t st) {
+  maxpool_fwd_kernel<<<blocks_for((long long)N * Ho * Wo * (C / 8), 256), 256, 0, st>>>(x, y, code, N, H, W, C, k, stride, pad, Ho, Wo);
 }
-void maxpool_bwd(const bf16* x, const bf16* y, const bf16* dy, bf16* dx, int N, int H, int W, int C, int k, int stride, int pad,
-                 int Ho, int Wo, cudaStream_t st) {
-  maxpool_bwd_kernel<<<blocks_for((long long)N * H * W * (C / 8), 256), 256, 0, st>>>(x, y, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+void maxpool_bwd(const uint8_t* code, const bf16* dy, bf16* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
+                 cudaStream_t st) {
+  maxpool_bwd_kernel<<<blocks_for((long long)N * H * W * (C / 8), 256), 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
 }
 void im2col(const bf16* x, bf16* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
   const long long total = (long long)N * Ho * Wo * KH * KW * (C / 8);

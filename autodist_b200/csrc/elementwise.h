@@ -48,12 +48,13 @@ void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t s
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
 int bn_parts(int rows, int C);
 void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, bf16_t* y, float* mean, float* rstd, float* part, float* sums,
-            int rows, int C, float eps, int relu, cudaStream_t st);
+            float* coef, int rows, int C, float eps, int relu, cudaStream_t st);
 void bn_bwd(const bf16_t* dy, const bf16_t* x, const bf16_t* y, const float* mean, const float* rstd, const float* gamma, bf16_t* dx,
-            float* part, float* sums, int rows, int C, int relu, cudaStream_t st);
-void maxpool_fwd(const bf16_t* x, bf16_t* y, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo, cudaStream_t st);
-void maxpool_bwd(const bf16_t* x, const bf16_t* y, const bf16_t* dy, bf16_t* dx, int N, int H, int W, int C, int k, int stride, int pad,
-                 int Ho, int Wo, cudaStream_t st);
+            float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st);
+void maxpool_fwd(const bf16_t* x, bf16_t* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
+                 cudaStream_t st);
+void maxpool_bwd(const uint8_t* code, const bf16_t* dy, bf16_t* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho,
+                 int Wo, cudaStream_t st);
 void im2col(const bf16_t* x, bf16_t* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
 void col2im(const bf16_t* dcols, bf16_t* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st);

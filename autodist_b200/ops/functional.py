@@ -248,18 +248,20 @@ class _MaxPoolFn(torch.autograd.Function):
         n, h, w, c = xh.shape
         ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
         y = torch.empty(n, ho, wo, c, dtype=torch.bfloat16, device=x.device)
-        E.maxpool_fwd(xh, y, k, stride, pad)
-        ctx.save_for_backward(xh, y)
+        code = torch.empty(n, ho, wo, c, dtype=torch.uint8, device=x.device)
+        E.maxpool_fwd(xh, y, code, k, stride, pad)
+        ctx.save_for_backward(code)
         ctx.geom = (k, stride, pad)
+        ctx.x_shape = tuple(xh.shape)
         ctx.x_dtype = x.dtype
         return y.permute(0, 3, 1, 2)
 
     @staticmethod
     def backward(ctx, dy):
         E = ops.ext(required=True)
-        xh, y = ctx.saved_tensors
-        dx = torch.empty_like(xh)
-        E.maxpool_bwd(xh, y, dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous(), dx, *ctx.geom)
+        (code,) = ctx.saved_tensors
+        dx = torch.empty(ctx.x_shape, dtype=torch.bfloat16, device=dy.device)
+        E.maxpool_bwd(code, dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous(), dx, *ctx.geom)
         return dx.permute(0, 3, 1, 2).to(ctx.x_dtype), None, None, None
 
 
