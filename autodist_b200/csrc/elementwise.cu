@@ -939,10 +939,20 @@ __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __r
   load8(dy + idx * 8, d);
   load8(x + idx * 8, xv);
   if (relu) load8(y + idx * 8, yv);
+  float ca[8], cb[8], ck[8];                          // per-channel coefficients, six 16-byte loads
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float4 a4 = *reinterpret_cast<const float4*>(coef + c + 4 * h);
+    const float4 b4 = *reinterpret_cast<const float4*>(coef + C + c + 4 * h);
+    const float4 k4 = *reinterpret_cast<const float4*>(coef + 2 * C + c + 4 * h);
+    ca[4 * h] = a4.x; ca[4 * h + 1] = a4.y; ca[4 * h + 2] = a4.z; ca[4 * h + 3] = a4.w;
+    cb[4 * h] = b4.x; cb[4 * h + 1] = b4.y; cb[4 * h + 2] = b4.z; cb[4 * h + 3] = b4.w;
+    ck[4 * h] = k4.x; ck[4 * h + 1] = k4.y; ck[4 * h + 2] = k4.z; ck[4 * h + 3] = k4.w;
+  }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float g = (relu && yv[j] <= 0.f) ? 0.f : d[j];
-    d[j] = fmaf(coef[c + j], g, fmaf(coef[C + c + j], xv[j], coef[2 * C + c + j]));
+    d[j] = fmaf(ca[j], g, fmaf(cb[j], xv[j], ck[j]));
   }
   store8(dx + idx * 8, d);
 }
