@@ -45,6 +45,11 @@ class Remapper:
         self._last_chunk = {}
 
     # ------------------------------------------------------------------ feeds
+    @property
+    def num_local_replicas(self):
+        """Replicas that this process feeds: a fed batch is split between them along its batch dimension."""
+        return self._num_local
+
     def _to_device(self, name, value):
         if isinstance(value, torch.Tensor):
             t = value
