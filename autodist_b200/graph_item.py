@@ -643,6 +643,12 @@ def patch_optimizers():
     torch.optim.Optimizer.minimize = minimize
 
 
+# Library modules whose forward branches on its inputs (dimension checks, packed sequences, masks): recorded as one
+# node instead of being traced through. User modules opt in with ``_autodist_leaf = True``.
+_AUTO_LEAF_MODULES = (nn.RNNBase, nn.RNNCellBase, nn.MultiheadAttention, nn.TransformerEncoderLayer,
+                      nn.TransformerDecoderLayer, nn.TransformerEncoder, nn.TransformerDecoder, nn.Transformer)
+
+
 def _patch_module_capture(item):
     """While ``item`` is the default: track constructed modules, and record leaf modules as one node."""
     orig_init = nn.Module.__init__
@@ -656,7 +662,8 @@ def _patch_module_capture(item):
 
     @functools.wraps(orig_call)
     def leaf_call(self, *args, **kwargs):
-        if getattr(self, "_autodist_leaf", False) and (_contains_proxy(args) or _contains_proxy(kwargs)):
+        if (getattr(self, "_autodist_leaf", False) or isinstance(self, _AUTO_LEAF_MODULES)) and (
+                _contains_proxy(args) or _contains_proxy(kwargs)):
             return item.tracer.create_proxy("call_module", item.path_of_module(self), args, kwargs)
         return orig_call(self, *args, **kwargs)
 

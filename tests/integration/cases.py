@@ -49,6 +49,39 @@ class SparseNet(nn.Module):
         return ((self.fc2(torch.relu(self.fc1(h))).squeeze(-1) - y) ** 2).mean()
 
 
+class UnrolledLSTM(nn.Module):
+    """Two stacked LSTM cells unrolled over time with nested Python loops and a running state (the reference's
+    while-loop and dynamic-LSTM cases c4 / c6): the tracer records every iteration as straight-line graph nodes."""
+
+    def __init__(self, steps=5):
+        super().__init__()
+        self.cells = nn.ModuleList([nn.LSTMCell(3, 6), nn.LSTMCell(6, 6)])
+        self.peep = nn.Parameter(torch.full((6,), 0.1))
+        self.head = nn.Linear(6, 1)
+        self.steps = steps
+
+    def forward(self, x, y):
+        B = x.shape[0]
+        state = [(x.new_zeros(B, 6), x.new_zeros(B, 6)) for _ in self.cells]
+        total = x.new_zeros(B)
+        t = 0
+        while t < self.steps:                         # python control flow over a static trip count
+            inp = x[:, t]
+            for li, cell in enumerate(self.cells):
+                h, c = cell(inp, state[li])
+                h = h + self.peep * torch.tanh(c)     # peephole-like use of the cell state
+                state[li] = (h, c)
+                inp = h
+            total = total + self.head(inp).squeeze(-1)
+            t += 1
+        return ((total / self.steps - y) ** 2).mean()
+
+
+def _seq_data(n=8, seed=3):
+    rng = np.random.RandomState(seed)
+    return {"x": rng.randn(n, 5, 3).astype(np.float32), "y": rng.randn(n).astype(np.float32)}
+
+
 def _cnn_data(n=8, seed=1):
     rng = np.random.RandomState(seed)
     return {"x": rng.randn(n, 1, 8, 8).astype(np.float32), "y": rng.randint(0, 3, size=n).astype(np.int64)}
@@ -72,6 +105,9 @@ CASES = {
     "c3": (lambda: SparseNet(True), lambda: SparseNet(False), _sparse_data,
            {"ids": ((None, 5), torch.int64), "y": ((None,), torch.float32)},
            lambda ps: torch.optim.Adam(ps, lr=0.01), 4),
+    "c4": (UnrolledLSTM, UnrolledLSTM, _seq_data,
+           {"x": ((None, 5, 3), torch.float32), "y": ((None,), torch.float32)},
+           lambda ps: torch.optim.SGD(ps, lr=0.1, momentum=0.5), 4),
 }
 
 

@@ -38,3 +38,9 @@ def test_matrix_single_rank():
 def test_matrix_four_ranks():
     out = _run("c1", 4, only="AllReduce_chunk512,PartitionedPS_owners,UnevenPartitionedPS_proxy,PSLoadBalancing_proxy")
     assert out.count(" ok") == 16
+
+
+@pytest.mark.integration
+def test_matrix_unrolled_recurrent_case():
+    out = _run("c4", 2, only="PS,AllReduce_None,PartitionedPS_proxy,Parallax_proxy,PartitionedAR,UnevenPartitionedPS_proxy,RandomAxisPartitionAR")
+    assert out.count(" ok") >= 7 and "FAIL" not in out
