@@ -184,7 +184,10 @@ class WrappedSession:
                 leaf = leaves[i]
                 name = self._graph_item.name_of_parameter(leaf) if not isinstance(leaf, str) else (
                     leaf if leaf.endswith(":0") else leaf + ":0")
-                out[i] = np.array(eng.variable_value(name).float().cpu().numpy() if eng.variable_value(name).dtype == torch.bfloat16 else eng.variable_value(name).cpu().numpy(), copy=True)
+                value = eng.variable_value(name)
+                if value.dtype == torch.bfloat16:
+                    value = value.float()                       # numpy has no bfloat16
+                out[i] = np.array(value.cpu().numpy(), copy=True)   # a copy: never a view of live parameter memory
         result = rebuild(out)
         return result[0] if single else result
 
