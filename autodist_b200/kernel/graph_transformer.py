@@ -56,6 +56,8 @@ class GraphTransformer:
         item = self.graph_item
         logging.debug("Transforming the original graph to a distributed plan...")
         visualization_util.log_graph(item.graph_text(), "0-original")
+        if getattr(item, "tracer", None) is not None and getattr(item.tracer, "graph", None) is not None:
+            visualization_util.log_fx_graph(item.tracer.graph, "0-original")
 
         shard_plans = VariablePartitioner.apply(self._strategy.node_config, item)
         visualization_util.log_graph(
