@@ -34,7 +34,7 @@ import torch.distributed as dist
 from autodist_b200.const import ENV
 from autodist_b200.kernel.synchronization.compressor import wire_dtype
 from autodist_b200.parallel.engine import StepEngine
-from autodist_b200.utils import logging
+from autodist_b200.utils import logging, nvtx
 
 WIRE = {None: 0, torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
@@ -478,7 +478,7 @@ class FusedStepEngine(StepEngine):
         compute = torch.cuda.current_stream()
         self._ready_event.record(compute)
         self.comm_stream.wait_event(self._ready_event)
-        with torch.cuda.stream(self.comm_stream):
+        with nvtx.annotate(f"flight [{lo}, {hi})"), torch.cuda.stream(self.comm_stream):
             if self.world_size > 1:
                 for a, b, wd, ef in self._policy_for(lo, hi):
                     self._all_reduce_range(a, b, wd, ef)

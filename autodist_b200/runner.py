@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from autodist_b200 import const
-from autodist_b200.utils import logging
+from autodist_b200.utils import logging, nvtx
 
 
 class RunOptions:
@@ -143,7 +143,8 @@ class WrappedSession:
         try:
             if self._metrics is not None:
                 self._metrics.begin()
-            result = self._run(fetches, feed_dict)
+            with nvtx.annotate(f"step {self._engine.global_step}"):
+                result = self._run(fetches, feed_dict)
             if self._metrics is not None:
                 self._metrics.end(result, feed_dict)
         finally:
