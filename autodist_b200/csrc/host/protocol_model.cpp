@@ -11,6 +11,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -161,6 +162,52 @@ py::tuple simulate_allreduce(int world, int blocks, long long n, int iters, std:
   return py::make_tuple(errors, max_err);
 }
 
+// Bounded-staleness gate: before step s a rank publishes s to every peer and waits until s - (a peer's published step)
+// <= staleness for every peer, or until the time limit. Rank r sleeps delays_us[r] per step (the work of the step), so a
+// slow rank can be modelled without asserting on wall-clock time: the function returns, per rank, the largest lead
+// over the slowest peer that the gate ever let through, and the error codes (200 + the peer waited for).
+py::tuple simulate_staleness(int world, int steps, uint32_t staleness, std::vector<int> delays_us, double timeout_ms,
+                             std::vector<int> stop_after) {
+  if (world < 1 || world > 64 || steps < 1) throw std::invalid_argument("bad sizes");
+  delays_us.resize(world, 0);
+  stop_after.resize(world, steps);                               // a rank that stops early never publishes later steps
+  std::unique_ptr<std::atomic<uint32_t>[]> clocks(new std::atomic<uint32_t>[(size_t)world * world]);   // [owner][sender]
+  for (size_t i = 0; i < (size_t)world * world; ++i) clocks[i].store(0, std::memory_order_relaxed);
+  std::vector<int> max_lead(world, 0), errors(world, 0), reached(world, 0);
+  const long long timeout_ns = (long long)(timeout_ms * 1e6);
+  auto run = [&](int rank) {
+    for (int s = 1; s <= std::min(steps, stop_after[rank]); ++s) {
+      for (int peer = 0; peer < world; ++peer) clocks[(size_t)peer * world + rank].store((uint32_t)s, std::memory_order_release);
+      for (int peer = 0; peer < world; ++peer) {
+        const auto t0 = Clock::now();
+        uint32_t it = 0;
+        while ((int32_t)((uint32_t)s - clocks[(size_t)rank * world + peer].load(std::memory_order_acquire)) > (int32_t)staleness) {
+          if (((++it) & 63u) == 0) {
+            if (expired(t0, timeout_ns)) {
+              errors[rank] = 200 + peer;
+              return;
+            }
+            std::this_thread::yield();
+          }
+        }
+      }
+      int slowest = s;
+      for (int peer = 0; peer < world; ++peer)
+        slowest = std::min(slowest, (int)clocks[(size_t)rank * world + peer].load(std::memory_order_acquire));
+      max_lead[rank] = std::max(max_lead[rank], s - slowest);
+      reached[rank] = s;
+      if (delays_us[rank] > 0) std::this_thread::sleep_for(std::chrono::microseconds(delays_us[rank]));
+    }
+  };
+  {
+    py::gil_scoped_release nogil;
+    std::vector<std::thread> threads;
+    for (int r = 0; r < world; ++r) threads.emplace_back(run, r);
+    for (auto& t : threads) t.join();
+  }
+  return py::make_tuple(max_lead, errors, reached);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(_adb200_host, m) {
@@ -168,4 +215,6 @@ PYBIND11_MODULE(_adb200_host, m) {
   m.def("simulate_allreduce", &simulate_allreduce, py::arg("world"), py::arg("blocks"), py::arg("n"), py::arg("iters") = 1,
         py::arg("absent") = std::vector<int>{}, py::arg("timeout_ms") = 200.0, py::arg("first_epoch") = 0u,
         py::arg("with_grid_barriers") = true);
+  m.def("simulate_staleness", &simulate_staleness, py::arg("world"), py::arg("steps"), py::arg("staleness"),
+        py::arg("delays_us") = std::vector<int>{}, py::arg("timeout_ms") = 500.0, py::arg("stop_after") = std::vector<int>{});
 }

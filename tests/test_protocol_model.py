@@ -33,3 +33,21 @@ def test_size_checks(model):
         model.simulate_allreduce(0, 1, 8)
     with pytest.raises(ValueError):
         model.simulate_allreduce(2, 65, 8)
+
+
+@pytest.mark.parametrize("staleness", [0, 1, 3])
+def test_staleness_gate_bounds_the_lead_of_the_fast_rank(model, staleness):
+    # rank 1 is slow (2 ms of work per step); nothing here asserts on elapsed time, only on how far ahead anyone got
+    lead, errors, reached = model.simulate_staleness(3, 12, staleness, delays_us=[0, 2000, 0], timeout_ms=5000.0)
+    assert errors == [0, 0, 0] and reached == [12, 12, 12]
+    assert max(lead) <= staleness
+    if staleness:
+        assert lead[0] == staleness or lead[2] == staleness        # the fast ranks do use the slack they are given
+
+
+def test_staleness_gate_reports_a_rank_that_stopped(model):
+    # rank 2 stops publishing after step 2 (a process that left between steps): the others get staleness steps further
+    lead, errors, reached = model.simulate_staleness(3, 10, 1, timeout_ms=100.0, stop_after=[10, 10, 2])
+    assert errors[2] == 0 and reached[2] == 2
+    assert errors[0] == 202 and errors[1] == 202
+    assert reached[0] == 3 and reached[1] == 3                      # step 4 would be 2 ahead of rank 2
