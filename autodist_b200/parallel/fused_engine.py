@@ -377,7 +377,11 @@ class FusedStepEngine(StepEngine):
         if not (hooks and len(entries) == self.world_size and all(e.part.sparse for e in entries)):
             return False
         entries.sort(key=lambda e: e.part.offset)
-        if [e.owner for e in entries] != list(range(self.world_size)) or os.environ.get("AUTODIST_SPARSE_ROWS", "1") == "0":
+        # The scatter-add into owner shards uses floating-point atomics, whose order of addition varies from run to
+        # run; AUTODIST_DETERMINISTIC=1 (or AUTODIST_SPARSE_ROWS=0) keeps the table replicated and its gradient on the
+        # dense reduce-scatter path, which adds in a fixed order.
+        if [e.owner for e in entries] != list(range(self.world_size)) or os.environ.get("AUTODIST_SPARSE_ROWS", "1") == "0" \
+                or os.environ.get("AUTODIST_DETERMINISTIC", "0") == "1":
             return False
         fl = self.flat
         p = fl.params[fl.names.index(name)]
