@@ -96,3 +96,22 @@ def test_transformer_writes_all_four_stages(tmp_path, monkeypatch):
     stages = {n.split(".")[0] for n in names}
     assert stages == {"0-original", "1-after-partition", "2-after-in-graph", "3-transformed"}
     assert any(n.endswith(".dot") for n in names)
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE")}
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "3"], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and ("unavailable" in rec or "value" in rec)
+    # a non-zero rank of a multi-process launch stays silent
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"], capture_output=True, text=True,
+                       timeout=300, env=dict(env, RANK="1", WORLD_SIZE="2"))
+    assert r.returncode == 0 and r.stdout.strip() == ""
