@@ -44,7 +44,8 @@ def main():
     ap.add_argument("--train_steps", type=int, default=50)
     ap.add_argument("--log_steps", type=int, default=10)
     ap.add_argument("--chunk_size", type=int, default=0)
-    ap.add_argument("--lr_schedule", action="store_true", help="warm-up + piecewise-constant decay (30/60/80 epochs) instead of a fixed rate")
+    ap.add_argument("--lr_schedule", action="store_true",
+                    help="warm-up + piecewise-constant decay (30/60/80 epochs) instead of a fixed rate")
     ap.add_argument("--benchmark_log", default=None, help="JSONL metrics file")
     args = ap.parse_args()
     spec = ResourceSpec(args.resource_spec) if args.resource_spec else ResourceSpec.local(

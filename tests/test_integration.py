@@ -42,5 +42,6 @@ def test_matrix_four_ranks():
 
 @pytest.mark.integration
 def test_matrix_unrolled_recurrent_case():
-    out = _run("c4", 2, only="PS,AllReduce_None,PartitionedPS_proxy,Parallax_proxy,PartitionedAR,UnevenPartitionedPS_proxy,RandomAxisPartitionAR")
+    out = _run("c4", 2, only="PS,AllReduce_None,PartitionedPS_proxy,Parallax_proxy,PartitionedAR,UnevenPartitionedPS_proxy,"
+                             "RandomAxisPartitionAR")
     assert out.count(" ok") >= 7 and "FAIL" not in out
