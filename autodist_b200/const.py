@@ -57,6 +57,8 @@ class ENV(enum.Enum):
     AUTODIST_FETCH_MODE = (11, _as_str("replica0"))  # "replica0" (reference rule) or "local"
     AUTODIST_COMM = (12, _as_str("fused"))           # "fused" (own kernels) or "nccl" (baseline)
     AUTODIST_METRICS_FILE = (13, _as_str())          # JSONL step metrics of rank 0 ("%r" in the name = every rank)
+    AUTODIST_STEP_TIMEOUT = (14, _as_str())          # seconds a training call may take before the watchdog fires
+    AUTODIST_STEP_TIMEOUT_ACTION = (15, _as_str("report"))   # "report" (log + stack dump) or "abort" (exit code 70)
 
     @property
     def val(self):

@@ -6,8 +6,11 @@ every replica) and writes a Chrome trace when tracing is requested through
 ``RunOptions``. One session drives one rank; the other ranks execute the same
 script and meet this one in the collectives.
 """
+import faulthandler
 import json
 import os
+import sys
+import threading
 import time
 
 import numpy as np
@@ -102,6 +105,70 @@ class _StepMetrics:
         self._flush()
 
 
+class _StepWatchdog:
+    """Host-side step deadline. A daemon thread watches the running training call; when the call outlives
+    ``AUTODIST_STEP_TIMEOUT`` seconds it logs the step, dumps the stack of every thread to stderr and, with
+    ``AUTODIST_STEP_TIMEOUT_ACTION=abort``, ends the process with exit code 70 so that the launcher's watcher tears the
+    job down (a rank stuck in a collective cannot be interrupted from Python in any other way)."""
+
+    EXIT_CODE = 70
+
+    def __init__(self, seconds, action="report", rank=0):
+        self.seconds = float(seconds)
+        self.action = action
+        self.rank = rank
+        self.fired = 0
+        self._cond = threading.Condition()
+        self._deadline = None
+        self._step = None
+        self._stop = False
+        self._thread = threading.Thread(target=self._loop, name="autodist-step-watchdog", daemon=True)
+        self._thread.start()
+
+    @classmethod
+    def from_env(cls, engine):
+        raw = const.ENV.AUTODIST_STEP_TIMEOUT.val
+        if not raw:
+            return None
+        return cls(float(raw), const.ENV.AUTODIST_STEP_TIMEOUT_ACTION.val or "report", engine.rank)
+
+    def arm(self, step):
+        with self._cond:
+            self._deadline = time.monotonic() + self.seconds
+            self._step = step
+            self._cond.notify()
+
+    def disarm(self):
+        with self._cond:
+            self._deadline = None
+            self._cond.notify()
+
+    def close(self):
+        with self._cond:
+            self._stop = True
+            self._cond.notify()
+
+    def _loop(self):
+        with self._cond:
+            while not self._stop:
+                if self._deadline is None:
+                    self._cond.wait()
+                    continue
+                left = self._deadline - time.monotonic()
+                if left > 0:
+                    self._cond.wait(left)
+                    continue
+                self.fired += 1
+                self._deadline = None
+                logging.error("rank %d: step %s exceeded the %.1f s deadline", self.rank, self._step, self.seconds)
+                try:
+                    faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+                except Exception:  # stderr may be closed during shutdown
+                    pass
+                if self.action == "abort":
+                    os._exit(self.EXIT_CODE)
+
+
 class WrappedSession:
     def __init__(self, cluster, graph_item, remapper, engine, coordinator=None, is_built=None):
         self._cluster = cluster
@@ -114,6 +181,7 @@ class WrappedSession:
         self._trace_step = 0
         self.last_step_ms = None
         self._metrics = _StepMetrics.from_env(engine)
+        self._watchdog = _StepWatchdog.from_env(engine)
         logging.debug("session ready on rank %d (%s)", engine.rank, engine.device)
 
     @property
@@ -143,8 +211,14 @@ class WrappedSession:
         try:
             if self._metrics is not None:
                 self._metrics.begin()
-            with nvtx.annotate(f"step {self._engine.global_step}"):
-                result = self._run(fetches, feed_dict)
+            if self._watchdog is not None:
+                self._watchdog.arm(self._engine.global_step)
+            try:
+                with nvtx.annotate(f"step {self._engine.global_step}"):
+                    result = self._run(fetches, feed_dict)
+            finally:
+                if self._watchdog is not None:
+                    self._watchdog.disarm()
             if self._metrics is not None:
                 self._metrics.end(result, feed_dict)
         finally:
@@ -198,6 +272,8 @@ class WrappedSession:
         self._closed = True
         if self._metrics is not None:
             self._metrics.close()
+        if self._watchdog is not None:
+            self._watchdog.close()
         try:
             self._engine.close()
         except Exception as e:  # shutting down: peers may already be gone

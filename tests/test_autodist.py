@@ -70,3 +70,48 @@ def test_function_with_keyword_arguments_and_second_function_refused():
         with pytest.raises(NotImplementedError):
             other(x)
     _reset_default_autodist()
+
+
+def test_step_deadline_watchdog_reports_a_slow_step(monkeypatch, capfd):
+    import time
+    import torch
+    from autodist_b200 import AutoDist
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.resource_spec import ResourceSpec
+    from autodist_b200.strategy import PS
+
+    class Slow(torch.nn.Module):
+        _autodist_leaf = True                        # runs at step time, not at trace time
+
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.zeros(2))
+            self.delay = 0.0
+
+        def forward(self, x):
+            time.sleep(self.delay)
+            return ((x * self.w).sum(1) - 1.0).pow(2).mean()
+
+    monkeypatch.setenv("AUTODIST_STEP_TIMEOUT", "0.3")
+    _reset_default_autodist()
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=PS())
+    with ad.scope():
+        m = Slow()
+        x = ad.placeholder((None, 2), torch.float32, name="x")
+        loss = m(x)
+        train_op = torch.optim.SGD(m.parameters(), lr=0.1).minimize(loss)
+        sess = ad.create_distributed_session()
+        feed = {x: torch.ones(3, 2)}
+        sess.run([loss, train_op], feed)
+        assert sess._watchdog.fired == 0
+        m.delay = 0.8
+        sess.run([loss, train_op], feed)             # the step still completes; the watchdog only reports
+        assert sess._watchdog.fired == 1
+        m.delay = 0.0
+        sess.run([loss, train_op], feed)
+        assert sess._watchdog.fired == 1
+        sess.close()
+    _reset_default_autodist()
+    err = capfd.readouterr().err
+    assert "most recent call first" in err and "time.sleep" not in err.split("most recent call first")[0]
+    assert "forward" in err                            # the stack dump shows where the slow step was
