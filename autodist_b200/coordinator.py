@@ -47,6 +47,11 @@ class Coordinator:
                      ENV.AUTODIST_FETCH_MODE, ENV.AUTODIST_COMM):
             if os.environ.get(flag.name) is not None:
                 env[flag.name] = os.environ[flag.name]
+        # every other AUTODIST_* knob the user set (kernel time-outs, flight size, metrics file, step deadline ...) applies
+        # to the whole job, so it travels too; the per-rank identity variables above are never overwritten
+        for name, value in os.environ.items():
+            if name.startswith("AUTODIST_") and name not in env:
+                env[name] = value
         return env
 
     def launch_clients(self):
