@@ -115,3 +115,43 @@ def test_step_deadline_watchdog_reports_a_slow_step(monkeypatch, capfd):
     err = capfd.readouterr().err
     assert "most recent call first" in err and "time.sleep" not in err.split("most recent call first")[0]
     assert "forward" in err                            # the stack dump shows where the slow step was
+
+
+def test_step_deadline_abort_ends_the_process_with_code_70(tmp_path):
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "slow.py"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script.write_text(f'''
+import sys, time
+sys.path.insert(0, {root!r})
+import torch
+from autodist_b200 import AutoDist
+from autodist_b200.resource_spec import ResourceSpec
+from autodist_b200.strategy import PS
+
+class Stuck(torch.nn.Module):
+    _autodist_leaf = True
+    def __init__(self):
+        super().__init__()
+        self.w = torch.nn.Parameter(torch.zeros(2))
+    def forward(self, x):
+        time.sleep(30)                                # stands for a rank that never comes back from a collective
+        return (x * self.w).sum()
+
+ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=PS())
+with ad.scope():
+    m = Stuck()
+    x = ad.placeholder((None, 2), torch.float32, name="x")
+    loss = m(x)
+    op = torch.optim.SGD(m.parameters(), lr=0.1).minimize(loss)
+    sess = ad.create_distributed_session()
+    sess.run([loss, op], {{x: torch.ones(1, 2)}})
+print("not reached")
+''')
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE")}
+    env.update(AUTODIST_STEP_TIMEOUT="0.5", AUTODIST_STEP_TIMEOUT_ACTION="abort", AUTODIST_MIN_LOG_LEVEL="ERROR")
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 70, r.stderr[-2000:]
+    assert "not reached" not in r.stdout and "exceeded the 0.5 s deadline" in r.stderr
