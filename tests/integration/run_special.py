@@ -161,6 +161,49 @@ def scenario_function():
     print(f"function rank {ad.rank} ok", flush=True)
 
 
+TWO_NODE_SPEC = """
+nodes:
+  - address: 10.0.0.1
+    cpus: [0, 1]
+    chief: true
+  - address: 10.0.0.2
+    cpus: [0, 1]
+    ssh_config: conf
+ssh:
+  conf:
+    username: nobody
+"""
+
+
+def scenario_twonode():
+    """A two-node resource spec (two replicas per node) run as four externally launched ranks on one host: ranks 0-1
+    form node 10.0.0.1, ranks 2-3 node 10.0.0.2. Every process feeds its node's batch, which is split between the two
+    replicas of that node; a hierarchical plan (two workers) must still equal the single-process run."""
+    tmp = os.environ["AUTODIST_TEST_TMP"]
+    path = os.path.join(tmp, f"two_nodes_{os.environ['RANK']}.yml")
+    with open(path, "w") as f:
+        f.write(TWO_NODE_SPEC)
+    results = {}
+    for name, builder in (("AllReduce", AllReduce(chunk_size=1)), ("PartitionedPS", PartitionedPS()), ("PS", PS())):
+        _reset_default_autodist()
+        ad = AutoDist(resource_spec_file=path, strategy_builder=builder)
+        ref_state, _ = cases.oracle("c1")
+        with ad.scope():
+            model, phs, loss, train_op, data = build(ad, "c1")
+            sess = ad.create_distributed_session()
+            info = sess.engine.plan.replica
+            assert info.world_size == 4 and info.num_workers == 2
+            assert info.local_ranks == ([0, 1] if sess.rank < 2 else [2, 3]), info.local_ranks
+            for _ in range(4):
+                sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
+            got = {n: sess.run(p) for n, p in model.named_parameters()}
+            sess.close()
+        diff = max(float(np.abs(got[n] - ref_state[n].numpy()).max()) for n in got)
+        assert diff < 1e-5, (name, diff)
+        results[name] = diff
+    print(f"twonode rank {os.environ['RANK']} ok {results}", flush=True)
+
+
 def _spawn_ranks(name, nproc=2):
     """Start the ranks the way an external launcher would (RANK / WORLD_SIZE in the environment)."""
     import subprocess
@@ -176,6 +219,6 @@ def _spawn_ranks(name, nproc=2):
 if __name__ == "__main__":
     import faulthandler
     faulthandler.dump_traceback_later(240, exit=True)
-    if sys.argv[1] in ("crossload",) and "RANK" not in os.environ:
-        _spawn_ranks(sys.argv[1])
+    if sys.argv[1] in ("crossload", "twonode") and "RANK" not in os.environ:
+        _spawn_ranks(sys.argv[1], 4 if sys.argv[1] == "twonode" else 2)
     globals()["scenario_" + sys.argv[1]]()
