@@ -175,14 +175,11 @@ ssh:
 """
 
 
-def scenario_twonode():
-    """A two-node resource spec (two replicas per node) run as four externally launched ranks on one host: ranks 0-1
-    form node 10.0.0.1, ranks 2-3 node 10.0.0.2. Every process feeds its node's batch, which is split between the two
-    replicas of that node; a hierarchical plan (two workers) must still equal the single-process run."""
+def _run_multi_node(tag, spec_text, world, local_ranks_of):
     tmp = os.environ["AUTODIST_TEST_TMP"]
-    path = os.path.join(tmp, f"two_nodes_{os.environ['RANK']}.yml")
+    path = os.path.join(tmp, f"{tag}_{os.environ['RANK']}.yml")
     with open(path, "w") as f:
-        f.write(TWO_NODE_SPEC)
+        f.write(spec_text)
     results = {}
     for name, builder in (("AllReduce", AllReduce(chunk_size=1)), ("PartitionedPS", PartitionedPS()), ("PS", PS())):
         _reset_default_autodist()
@@ -192,8 +189,8 @@ def scenario_twonode():
             model, phs, loss, train_op, data = build(ad, "c1")
             sess = ad.create_distributed_session()
             info = sess.engine.plan.replica
-            assert info.world_size == 4 and info.num_workers == 2
-            assert info.local_ranks == ([0, 1] if sess.rank < 2 else [2, 3]), info.local_ranks
+            assert info.world_size == world and info.num_workers == 2
+            assert info.local_ranks == local_ranks_of(sess.rank), info.local_ranks
             for _ in range(4):
                 sess.run([loss, train_op], {phs[k]: data[k] for k in phs})
             got = {n: sess.run(p) for n, p in model.named_parameters()}
@@ -201,7 +198,22 @@ def scenario_twonode():
         diff = max(float(np.abs(got[n] - ref_state[n].numpy()).max()) for n in got)
         assert diff < 1e-5, (name, diff)
         results[name] = diff
-    print(f"twonode rank {os.environ['RANK']} ok {results}", flush=True)
+    print(f"{tag} rank {os.environ['RANK']} ok {results}", flush=True)
+
+
+def scenario_twonode():
+    """A two-node resource spec (two replicas per node) run as four externally launched ranks on one host: ranks 0-1
+    form node 10.0.0.1, ranks 2-3 node 10.0.0.2. Every process feeds its node's batch, which is split between the two
+    replicas of that node; a hierarchical plan (two workers) must still equal the single-process run."""
+    _run_multi_node("twonode", TWO_NODE_SPEC, 4, lambda r: [0, 1] if r < 2 else [2, 3])
+
+
+def scenario_hetero():
+    """Nodes of different size (two replicas and one, the shape of the reference's r4 spec): the lone replica of the
+    second node takes that node's whole batch."""
+    spec = TWO_NODE_SPEC.replace("    cpus: [0, 1]\n    ssh_config: conf", "    cpus: [0]\n    ssh_config: conf")
+    assert spec != TWO_NODE_SPEC
+    _run_multi_node("hetero", spec, 3, lambda r: [0, 1] if r < 2 else [2])
 
 
 def _spawn_ranks(name, nproc=2):
@@ -219,6 +231,6 @@ def _spawn_ranks(name, nproc=2):
 if __name__ == "__main__":
     import faulthandler
     faulthandler.dump_traceback_later(240, exit=True)
-    if sys.argv[1] in ("crossload", "twonode") and "RANK" not in os.environ:
-        _spawn_ranks(sys.argv[1], 4 if sys.argv[1] == "twonode" else 2)
+    if sys.argv[1] in ("crossload", "twonode", "hetero") and "RANK" not in os.environ:
+        _spawn_ranks(sys.argv[1], {"twonode": 4, "hetero": 3}.get(sys.argv[1], 2))
     globals()["scenario_" + sys.argv[1]]()
