@@ -175,7 +175,7 @@ ssh:
 """
 
 
-def _run_multi_node(tag, spec_text, world, local_ranks_of):
+def _run_multi_node(tag, spec_text, world, local_ranks_of, case="c1"):
     tmp = os.environ["AUTODIST_TEST_TMP"]
     path = os.path.join(tmp, f"{tag}_{os.environ['RANK']}.yml")
     with open(path, "w") as f:
@@ -184,9 +184,9 @@ def _run_multi_node(tag, spec_text, world, local_ranks_of):
     for name, builder in (("AllReduce", AllReduce(chunk_size=1)), ("PartitionedPS", PartitionedPS()), ("PS", PS())):
         _reset_default_autodist()
         ad = AutoDist(resource_spec_file=path, strategy_builder=builder)
-        ref_state, _ = cases.oracle("c1")
+        ref_state, _ = cases.oracle(case)
         with ad.scope():
-            model, phs, loss, train_op, data = build(ad, "c1")
+            model, phs, loss, train_op, data = build(ad, case)
             sess = ad.create_distributed_session()
             info = sess.engine.plan.replica
             assert info.world_size == world and info.num_workers == 2
@@ -198,7 +198,7 @@ def _run_multi_node(tag, spec_text, world, local_ranks_of):
         diff = max(float(np.abs(got[n] - ref_state[n].numpy()).max()) for n in got)
         assert diff < 1e-5, (name, diff)
         results[name] = diff
-    print(f"{tag} rank {os.environ['RANK']} ok {results}", flush=True)
+    print(f"{tag} {case} rank {os.environ['RANK']} ok {results}", flush=True)
 
 
 def scenario_twonode():
@@ -206,6 +206,8 @@ def scenario_twonode():
     form node 10.0.0.1, ranks 2-3 node 10.0.0.2. Every process feeds its node's batch, which is split between the two
     replicas of that node; a hierarchical plan (two workers) must still equal the single-process run."""
     _run_multi_node("twonode", TWO_NODE_SPEC, 4, lambda r: [0, 1] if r < 2 else [2, 3])
+    # row-sparse embedding + Adagrad: sparse rows are gathered across both nodes, owners publish the touched rows
+    _run_multi_node("twonode", TWO_NODE_SPEC, 4, lambda r: [0, 1] if r < 2 else [2, 3], case="c2")
 
 
 def scenario_hetero():

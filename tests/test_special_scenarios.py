@@ -22,6 +22,6 @@ def _launch(name, tmp_path, expect_ok=2):
 
 @pytest.mark.integration
 @pytest.mark.parametrize("name,oks", [("selflaunch", 2), ("stale", 2), ("async", 2), ("failure", 1),
-                                      ("crossload", 2), ("function", 2), ("twonode", 4), ("hetero", 3)])
+                                      ("crossload", 2), ("function", 2), ("twonode", 8), ("hetero", 3)])
 def test_scenario(name, oks, tmp_path):
     _launch(name, tmp_path, oks)
