@@ -566,3 +566,12 @@ class StepEngine:
     def close(self):
         if self._async is not None:
             self._async.close()
+        # A lazily refreshed parameter-server variable is pulled by a collective the next time any rank reads it. A
+        # rank that is done takes part in that last pull here, so that a peer which still fetches variables after
+        # its final step (the chief printing them, a checkpoint) is not left waiting for it.
+        if self.world_size > 1 and self._pending_pull:
+            try:
+                self.before_read()
+            except Exception as e:  # the peers may already be gone
+                logging.debug("final parameter pull skipped: %s", e)
+                self._pending_pull = False
