@@ -274,6 +274,9 @@ class WrappedSession:
             self._metrics.close()
         if self._watchdog is not None:
             self._watchdog.close()
+        if self._coordinator is not None and getattr(self._coordinator, "failure", None) is not None:
+            # a worker is known to be gone: no collective may be started on the way out
+            self._engine._pending_pull = False
         try:
             self._engine.close()
         except Exception as e:  # shutting down: peers may already be gone
