@@ -14,9 +14,14 @@ class FashionCNN(nn.Module):
         self.drop = nn.Dropout(0.5)
         self.fc = nn.Linear(32 * 13 * 13, num_classes)
 
-    def forward(self, images, labels):
+    def logits(self, images):
         h = F.max_pool2d(F.relu(self.conv(images)), 2).flatten(1)
-        return F.cross_entropy(self.fc(self.drop(h)), labels)
+        return self.fc(self.drop(h))
+
+    def forward(self, images, labels=None):
+        """Loss when ``labels`` are given (session-style programs), logits otherwise (``training.Model``)."""
+        out = self.logits(images)
+        return out if labels is None else F.cross_entropy(out, labels)
 
 
 class SentimentClassifier(nn.Module):

@@ -12,12 +12,27 @@ from autodist_b200.models.simple import FashionCNN  # noqa: E402
 from autodist_b200.resource_spec import ResourceSpec  # noqa: E402
 
 
+def fit_route(ad, images, labels):
+    """The same model through ``compile / fit / evaluate`` (the counterpart of the reference's Keras route)."""
+    from autodist_b200.training import Model
+    model = Model(ad, FashionCNN)
+    model.compile(optimizer=lambda params: torch.optim.SGD(params, lr=0.05), loss=torch.nn.functional.cross_entropy,
+                  metrics={"accuracy": lambda out, y: (out.argmax(1) == y).float().mean()})
+    model.fit(images, labels, batch_size=64, epochs=3, verbose=1)
+    result = model.evaluate(images, labels, batch_size=64)   # every rank takes part: fetches are gathered across replicas
+    if model.session.rank == 0:
+        print("evaluate:", result)
+
+
 def main():
-    spec = ResourceSpec(sys.argv[1]) if len(sys.argv) > 1 else ResourceSpec.local(num_cpus=2)
+    args = [a for a in sys.argv[1:] if a != "--fit"]
+    spec = ResourceSpec(args[0]) if args else ResourceSpec.local(num_cpus=2)
     ad = AutoDist(resource_spec=spec)                     # default builder: PSLoadBalancing
     rng = np.random.RandomState(0)
     images = rng.rand(256, 1, 28, 28).astype(np.float32)
     labels = rng.randint(0, 10, size=256).astype(np.int64)
+    if "--fit" in sys.argv:
+        return fit_route(ad, images, labels)
     with ad.scope():
         model = FashionCNN()
         x = ad.placeholder((None, 1, 28, 28), torch.float32, name="images")
