@@ -75,3 +75,18 @@ def test_fit_matches_plain_pytorch():
     torch.testing.assert_close(torch.as_tensor(got), ref(x).detach(), rtol=1e-5, atol=1e-6)
     model.session.close()
     _reset_default_autodist()
+
+
+@pytest.mark.integration
+def test_fit_route_of_the_example_on_two_self_launched_ranks():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "AUTODIST_WORKER",
+                                                            "AUTODIST_STRATEGY_ID")}
+    env["AUTODIST_MIN_LOG_LEVEL"] = "ERROR"
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "image_classifier.py"), "--fit"], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "epoch 3/3" in r.stdout and "evaluate:" in r.stdout
