@@ -11,14 +11,14 @@ def model():
 
 @pytest.mark.parametrize("world,blocks,n", [(1, 1, 5), (2, 1, 1), (2, 4, 257), (3, 5, 1009), (4, 3, 64), (8, 2, 4099)])
 def test_packed_two_shot_all_reduce_is_exact(model, world, blocks, n):
-    errors, max_err = model.simulate_allreduce(world, blocks, n, iters=4)
+    errors, max_err = model.simulate_allreduce(world, blocks, n, iters=4, timeout_ms=20000.0)
     assert errors == [0] * world
     assert max_err <= 1e-4
 
 
 def test_epochs_survive_wrap_around(model):
     # flags start three steps before 2**32; two barriers per all-reduce carry them across the wrap
-    errors, max_err = model.simulate_allreduce(2, 4, 513, iters=6, first_epoch=0xFFFFFFFD)
+    errors, max_err = model.simulate_allreduce(2, 4, 513, iters=6, first_epoch=0xFFFFFFFD, timeout_ms=20000.0)
     assert errors == [0, 0] and max_err <= 1e-4
 
 
@@ -38,7 +38,7 @@ def test_size_checks(model):
 @pytest.mark.parametrize("staleness", [0, 1, 3])
 def test_staleness_gate_bounds_the_lead_of_the_fast_rank(model, staleness):
     # rank 1 is slow (2 ms of work per step); nothing here asserts on elapsed time, only on how far ahead anyone got
-    lead, errors, reached = model.simulate_staleness(3, 12, staleness, delays_us=[0, 2000, 0], timeout_ms=5000.0)
+    lead, errors, reached = model.simulate_staleness(3, 12, staleness, delays_us=[0, 2000, 0], timeout_ms=20000.0)
     assert errors == [0, 0, 0] and reached == [12, 12, 12]
     assert max(lead) <= staleness
     if staleness:
