@@ -23,7 +23,7 @@ def test_epochs_survive_wrap_around(model):
 
 
 def test_absent_rank_is_reported_not_waited_for(model):
-    errors, _ = model.simulate_allreduce(4, 3, 1001, iters=2, absent=[2], timeout_ms=100.0)
+    errors, _ = model.simulate_allreduce(4, 3, 1001, iters=2, absent=[2], timeout_ms=1500.0)
     assert errors[2] == 0                           # it never ran
     assert all(e == 102 for i, e in enumerate(errors) if i != 2)     # 100 + the peer that never arrived
 
@@ -47,7 +47,7 @@ def test_staleness_gate_bounds_the_lead_of_the_fast_rank(model, staleness):
 
 def test_staleness_gate_reports_a_rank_that_stopped(model):
     # rank 2 stops publishing after step 2 (a process that left between steps): the others get staleness steps further
-    lead, errors, reached = model.simulate_staleness(3, 10, 1, timeout_ms=100.0, stop_after=[10, 10, 2])
+    lead, errors, reached = model.simulate_staleness(3, 10, 1, timeout_ms=1500.0, stop_after=[10, 10, 2])
     assert errors[2] == 0 and reached[2] == 2
     assert errors[0] == 202 and errors[1] == 202
     assert reached[0] == 3 and reached[1] == 3                      # step 4 would be 2 ahead of rank 2
