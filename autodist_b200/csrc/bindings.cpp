@@ -12,6 +12,8 @@
 #include "elementwise.h"
 #include "gemm_tcgen05.h"
 
+void register_conv(pybind11::module& m);
+
 namespace {
 
 using at::Tensor;
@@ -336,26 +338,46 @@ void lstm_cell_bwd(const Tensor& gates, const Tensor& c_prev, const Tensor& c, c
 }
 void sumsq(const Tensor& x, Tensor acc, double weight) { adb200::sumsq(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)weight, STREAM); }
 void clip_scale(Tensor x, const Tensor& acc, double max_norm) { adb200::clip_scale(x.data_ptr<float>(), x.numel(), acc.data_ptr<float>(), (float)max_norm, STREAM); }
-// Batch-norm over a channels-last matrix x [rows, C] (training mode statistics), optional fused ReLU.
-void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor y, Tensor mean, Tensor rstd, double eps, bool relu) {
+// Batch-norm over a channels-last matrix x [rows, C] (training mode statistics), optional residual addend and fused ReLU:
+// y = relu?(bn(x) + res). `sums` (optional, fp32 [2, C]) holds sum x and sum x^2 already (from the convolution's epilogue).
+void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, const optional<Tensor>& res, Tensor y, Tensor mean, Tensor rstd,
+            double eps, bool relu, const optional<Tensor>& sums_in, const optional<Tensor>& run_mean, const optional<Tensor>& run_var,
+            const optional<Tensor>& batches, double momentum) {
   const int C = x.size(-1), rows = x.numel() / C;
+  float* rm = nullptr; float* rv = nullptr; long long* nb = nullptr;
+  if (run_mean.has_value()) {
+    TORCH_CHECK(run_var.has_value() && run_mean->scalar_type() == at::kFloat && run_var->scalar_type() == at::kFloat && run_mean->numel() == C &&
+                run_var->numel() == C && run_mean->is_contiguous() && run_var->is_contiguous(), "running statistics must be fp32 [C]");
+    rm = run_mean->data_ptr<float>(); rv = run_var->data_ptr<float>();
+  }
+  if (batches.has_value()) nb = reinterpret_cast<long long*>(batches->data_ptr<int64_t>());
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be contiguous bf16 [.., C], C % 8 == 0");
   TORCH_CHECK(y.is_contiguous() && y.numel() == x.numel() && mean.numel() == C && rstd.numel() == C && gamma.numel() == C && beta.numel() == C,
               "output and per-channel tensors must match x");
+  if (res.has_value()) TORCH_CHECK(res->is_contiguous() && res->numel() == x.numel() && res->scalar_type() == at::kBFloat16, "residual must match x");
+  Tensor coef = at::empty({2 * C}, x.options().dtype(at::kFloat));              // [scale, shift]
+  if (sums_in.has_value()) {
+    TORCH_CHECK(sums_in->scalar_type() == at::kFloat && sums_in->numel() == 2 * C && sums_in->is_contiguous(), "sums must be fp32 [2, C]");
+    adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(res), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                   nullptr, sums_in->data_ptr<float>(), coef.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, 1, rm, rv, nb, (float)momentum, STREAM);
+    return;
+  }
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
-  Tensor sums = at::empty({4 * C}, x.options().dtype(at::kFloat));             // [sum x, sum x^2, scale, shift]
-  adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                 part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, (float)eps, relu ? 1 : 0, STREAM);
+  Tensor sums = at::empty({2 * C}, x.options().dtype(at::kFloat));
+  adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(res), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                 part.data_ptr<float>(), sums.data_ptr<float>(), coef.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, 0, rm, rv, nb, (float)momentum,
+                 STREAM);
 }
-// Returns [dbeta, dgamma] stacked as a [2, C] fp32 tensor; writes dx.
+// Returns [dbeta, dgamma] stacked as a [2, C] fp32 tensor; writes dx and (optional) dres = dy masked by the ReLU.
 Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
-              bool relu) {
+              const optional<Tensor>& dres, bool relu) {
   const int C = x.size(-1), rows = x.numel() / C;
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
               "dy, x, dx must be contiguous bf16 [.., C] of one shape, C % 8 == 0");
+  if (dres.has_value()) TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel() && dres->scalar_type() == at::kBFloat16, "dres must match x");
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({5, C}, x.options().dtype(at::kFloat));              // [dbeta, dgamma, A, B, K]
-  adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx),
+  adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx), OPT_BF(dres),
                  part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, relu ? 1 : 0, STREAM);
   return sums.narrow(0, 0, 2);
 }
@@ -386,6 +408,19 @@ void col2im(const Tensor& dcols, Tensor dx, int64_t KH, int64_t KW, int64_t stri
   const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
   TORCH_CHECK(dcols.numel() == (int64_t)N * Ho * Wo * KH * KW * C, "dcols has the wrong size");
   adb200::col2im(CBF(dcols), BF(dx), N, H, W, C, KH, KW, stride, pad, Ho, Wo, STREAM);
+}
+// Image [N, C, H, W] (any strides, fp32 or bf16, C <= 8) -> bf16 [N, Hp, Wp, 8] with the pixels at offset (pad, pad) and zeros elsewhere.
+void pad_image8(const Tensor& x, Tensor xp, int64_t pad) {
+  TORCH_CHECK(x.dim() == 4 && x.size(1) <= 8 && (x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16), "x must be [N, C<=8, H, W] fp32 or bf16");
+  TORCH_CHECK(xp.dim() == 4 && xp.size(3) == 8 && xp.is_contiguous() && xp.scalar_type() == at::kBFloat16 && xp.size(0) == x.size(0) &&
+              xp.size(1) >= x.size(2) + pad && xp.size(2) >= x.size(3) + pad, "xp must be contiguous bf16 [N, Hp, Wp, 8]");
+  adb200::pad_image8(x.data_ptr(), x.scalar_type() == at::kFloat ? 1 : 0, x.stride(0), x.stride(1), x.stride(2), x.stride(3), x.size(0),
+                     x.size(1), x.size(2), x.size(3), BF(xp), xp.size(1), xp.size(2), (int)pad, STREAM);
+}
+void relu_bwd(const Tensor& dy, const Tensor& y, Tensor dx) {
+  TORCH_CHECK(dy.is_contiguous() && y.is_contiguous() && dx.is_contiguous() && dy.numel() == y.numel() && dx.numel() == y.numel() && y.numel() % 8 == 0,
+              "contiguous bf16 tensors of one size (a multiple of 8)");
+  adb200::relu_bwd(CBF(dy), CBF(y), BF(dx), y.numel(), STREAM);
 }
 void psgd_p(Tensor M, const optional<Tensor>& err, const Tensor& Q, Tensor P) {
   const int m = M.size(0), n = M.size(1), r = Q.size(1);
@@ -514,6 +549,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("maxpool_bwd", &maxpool_bwd);
   m.def("im2col", &im2col);
   m.def("col2im", &col2im);
+  m.def("pad_image8", &pad_image8);
+  m.def("relu_bwd", &relu_bwd);
   m.def("psgd_p", &psgd_p);
   m.def("psgd_q", &psgd_q);
   m.def("psgd_d", &psgd_d);
@@ -529,4 +566,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sym_barrier", &sym_barrier);
   m.def("staleness_gate", &staleness_gate);
   m.attr("MAX_COMM_BLOCKS") = adb200::kMaxCommBlocks;
+  register_conv(m);
 }

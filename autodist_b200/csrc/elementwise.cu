@@ -531,6 +531,50 @@ __global__ void xent_kernel(bf16* __restrict__ logits, const int64_t* __restrict
   }
 }
 
+// Image with at most 8 channels (any strides) -> bf16 [N, Hp, Wp, 8]: pixels at (pad, pad), zeros in the halo and the spare channels.
+template <typename T>
+__global__ void pad_image8_kernel(const T* __restrict__ x, long long sn, long long sc, long long sh, long long sw, int C, int H, int W,
+                                  bf16* __restrict__ xp, int Hp, int Wp, int pad, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int wp = (int)(i % Wp), hp = (int)((i / Wp) % Hp);
+  const long long n = i / ((long long)Wp * Hp);
+  const int h = hp - pad, w = wp - pad;
+  float v[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) v[c] = 0.f;
+  if (h >= 0 && h < H && w >= 0 && w < W) {
+    const T* src = x + n * sn + h * sh + w * sw;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) if (c < C) v[c] = (float)src[c * sc];
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+    o[c] = *reinterpret_cast<uint32_t*>(&hh);
+  }
+  *reinterpret_cast<uint4*>(xp + i * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void relu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ y, uint4* __restrict__ dx, long long n8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  uint4 d = dy[i];
+  const uint4 yy = y[i];
+  uint32_t* dw = reinterpret_cast<uint32_t*>(&d);
+  const uint32_t* yw = reinterpret_cast<const uint32_t*>(&yy);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    // a bf16 is positive when it is neither zero nor has its sign bit set
+    const uint32_t lo = yw[k] & 0xFFFFu, hi = yw[k] >> 16;
+    const uint32_t keep_lo = (lo != 0u && lo < 0x8000u) ? 0xFFFFu : 0u;
+    const uint32_t keep_hi = (hi != 0u && hi < 0x8000u) ? 0xFFFF0000u : 0u;
+    dw[k] &= (keep_lo | keep_hi);
+  }
+  dx[i] = d;
+}
+
 __global__ void tanh_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) { float t = __bfloat162float(y[i]); dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * (1.0f - t * t)); }
@@ -835,24 +879,31 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
 
 // Per-channel mean / rstd and the affine form of the normalisation: y = x * scale + shift.
 // coef = [scale (C), shift (C)]; sums = [sum x (C), sum x^2 (C)].
+// Also folds the batch statistics into the running mean / variance (unbiased) and counts the batch when those are given.
 __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
                                    float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ coef, float inv_rows, int C,
-                                   float eps) {
+                                   float eps, float* __restrict__ run_mean, float* __restrict__ run_var, long long* __restrict__ batches,
+                                   float momentum, float unbias) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c == 0 && batches != nullptr) *batches += 1;
   if (c >= C) return;
   const float mu = sums[c] * inv_rows;
   const float var = fmaxf(sums[C + c] * inv_rows - mu * mu, 0.f);
   const float rs = rsqrtf(var + eps);
   mean[c] = mu;
   rstd[c] = rs;
+  if (run_mean != nullptr) {
+    run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mu;
+    run_var[c] = (1.0f - momentum) * run_var[c] + momentum * var * unbias;
+  }
   const float sc = gamma[c] * rs;
   coef[c] = sc;
   coef[C + c] = beta[c] - mu * sc;
 }
 
-// y = relu?(x * scale + shift)
-__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ coef, bf16* __restrict__ y, long long total8, int C,
-                                int relu) {
+// y = relu?(x * scale + shift (+ res))
+__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ coef, const bf16* __restrict__ res, bf16* __restrict__ y,
+                                long long total8, int C, int relu) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const int c = (int)(idx % (C / 8)) * 8;
@@ -861,9 +912,11 @@ __global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restr
   const float4 s0 = *reinterpret_cast<const float4*>(coef + c), s1 = *reinterpret_cast<const float4*>(coef + c + 4);
   const float4 h0 = *reinterpret_cast<const float4*>(coef + C + c), h1 = *reinterpret_cast<const float4*>(coef + C + c + 4);
   const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w}, sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+  float rv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (res != nullptr) load8(res + idx * 8, rv);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float o = fmaf(v[j], sc[j], sh[j]);
+    const float o = fmaf(v[j], sc[j], sh[j]) + rv[j];
     v[j] = relu ? fmaxf(o, 0.f) : o;
   }
   store8(y + idx * 8, v);
@@ -931,7 +984,8 @@ __global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const flo
 }
 
 __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
-                                    const float* __restrict__ coef, bf16* __restrict__ dx, long long total8, int C, int relu) {
+                                    const float* __restrict__ coef, bf16* __restrict__ dx, bf16* __restrict__ dres, long long total8, int C,
+                                    int relu) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const int c = (int)(idx % (C / 8)) * 8;
@@ -949,12 +1003,15 @@ __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __r
     cb[4 * h] = b4.x; cb[4 * h + 1] = b4.y; cb[4 * h + 2] = b4.z; cb[4 * h + 3] = b4.w;
     ck[4 * h] = k4.x; ck[4 * h + 1] = k4.y; ck[4 * h + 2] = k4.z; ck[4 * h + 3] = k4.w;
   }
+  float gm[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float g = (relu && yv[j] <= 0.f) ? 0.f : d[j];
+    gm[j] = g;
     d[j] = fmaf(ca[j], g, fmaf(cb[j], xv[j], ck[j]));
   }
   store8(dx + idx * 8, d);
+  if (dres != nullptr) store8(dres + idx * 8, gm);      // gradient of the residual branch: dy masked by the ReLU
 }
 
 // Max pooling over [N, H, W, C] windows (k x k, stride, pad). The forward pass records, per output element, which
@@ -1157,6 +1214,16 @@ void xent(bf16* logits, const int64_t* labels, const float* weights, const float
 void gelu_bwd(const bf16* dy, const bf16* u, bf16* dx, long long n, cudaStream_t st) {
   gelu_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, u, dx, n);
 }
+void pad_image8(const void* x, int is_fp32, long long sn, long long sc, long long sh, long long sw, int N, int C, int H, int W, bf16* xp,
+                int Hp, int Wp, int pad, cudaStream_t st) {
+  const long long total = (long long)N * Hp * Wp;
+  if (is_fp32) pad_image8_kernel<float><<<blocks_for(total, 256), 256, 0, st>>>(reinterpret_cast<const float*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
+  else pad_image8_kernel<bf16><<<blocks_for(total, 256), 256, 0, st>>>(reinterpret_cast<const bf16*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
+}
+void relu_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
+  relu_bwd_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(dy), reinterpret_cast<const uint4*>(y),
+                                                          reinterpret_cast<uint4*>(dx), n / 8);
+}
 void tanh_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
   tanh_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, y, dx, n);
 }
@@ -1207,23 +1274,28 @@ int bn_parts(int rows, int C) {
   return parts < 1 ? 1 : parts;
 }
 // part: [bn_parts, 2, C]; sums: [2, C]; coef: [2, C] (forward) or [3, C] (backward)
-void bn_fwd(const bf16* x, const float* gamma, const float* beta, bf16* y, float* mean, float* rstd, float* part, float* sums,
-            float* coef, int rows, int C, float eps, int relu, cudaStream_t st) {
-  const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
-  bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
-  colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
-  bn_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, beta, mean, rstd, coef, 1.0f / rows, C, eps);
+// sums_given: `sums` already holds the per-channel sum and sum of squares (the convolution's epilogue produced them).
+void bn_fwd(const bf16* x, const float* gamma, const float* beta, const bf16* res, bf16* y, float* mean, float* rstd, float* part, float* sums,
+            float* coef, int rows, int C, float eps, int relu, int sums_given, float* run_mean, float* run_var, long long* batches,
+            float momentum, cudaStream_t st) {
+  if (!sums_given) {
+    const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
+    bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
+    colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
+  }
+  bn_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, beta, mean, rstd, coef, 1.0f / rows, C, eps, run_mean, run_var, batches,
+                                                         momentum, rows > 1 ? (float)rows / (float)(rows - 1) : 1.0f);
   const long long total8 = (long long)rows * (C / 8);
-  bn_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(x, coef, y, total8, C, relu);
+  bn_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(x, coef, res, y, total8, C, relu);
 }
-void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx,
+void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx, bf16* dres,
             float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
   colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
   bn_bwd_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, mean, rstd, coef, 1.0f / rows, C);
   const long long total8 = (long long)rows * (C / 8);
-  bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, total8, C, relu);
+  bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
 }
 void maxpool_fwd(const bf16* x, bf16* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st) {

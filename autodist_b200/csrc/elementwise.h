@@ -47,16 +47,20 @@ void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, cons
 void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st);
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
 int bn_parts(int rows, int C);
-void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, bf16_t* y, float* mean, float* rstd, float* part, float* sums,
-            float* coef, int rows, int C, float eps, int relu, cudaStream_t st);
+void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, const bf16_t* res, bf16_t* y, float* mean, float* rstd, float* part,
+            float* sums, float* coef, int rows, int C, float eps, int relu, int sums_given, float* run_mean, float* run_var,
+            long long* batches, float momentum, cudaStream_t st);
 void bn_bwd(const bf16_t* dy, const bf16_t* x, const bf16_t* y, const float* mean, const float* rstd, const float* gamma, bf16_t* dx,
-            float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st);
+            bf16_t* dres, float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st);
 void maxpool_fwd(const bf16_t* x, bf16_t* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st);
 void maxpool_bwd(const uint8_t* code, const bf16_t* dy, bf16_t* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho,
                  int Wo, cudaStream_t st);
 void im2col(const bf16_t* x, bf16_t* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
 void col2im(const bf16_t* dcols, bf16_t* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
+void pad_image8(const void* x, int is_fp32, long long sn, long long sc, long long sh, long long sw, int N, int C, int H, int W, bf16_t* xp,
+                int Hp, int Wp, int pad, cudaStream_t st);
+void relu_bwd(const bf16_t* dy, const bf16_t* y, bf16_t* dx, long long n, cudaStream_t st);
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st);
 void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st);
 void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st);

@@ -2,84 +2,95 @@
 ``tf.keras.applications.{ResNet101, VGG16, InceptionV3, DenseNet121}`` with random weights).
 
 ResNet-101 (v1.5 bottlenecks), VGG-16, DenseNet-121 and a small Inception-style network are defined here from
-scratch. Convolutions, batch-norm and pooling run on PyTorch's cuDNN path in channels-last bf16 (library compute, labelled as
-such in the benchmark output); pointwise (1x1) convolutions can be switched onto the tcgen05 GEMM with
-``AUTODIST_CONV1X1=tcgen05`` (`Conv1x1`; correct, but not yet faster than the library). The fully connected
-layers - 25088x4096, 4096x4096, 4096x1000 for VGG-16 - run on the tcgen05 GEMM. ``ImageClassifier`` wraps a backbone
-and the loss into one leaf module.
+scratch. On a GPU every convolution (forward, input gradient, weight gradient) is the tcgen05 implicit GEMM of
+``csrc/conv_tcgen05.cu`` over channels-last bf16 activations, with bias / ReLU and the batch-norm statistics in its
+epilogue; batch-norm (+ residual add + ReLU) and max-pooling are hand-written kernels too, and the fully connected
+layers - 25088x4096, 4096x4096, 4096x1000 for VGG-16 - run on the tcgen05 GEMM. ``AUTODIST_CONV=library`` switches the
+convolutions to the library (the comparison baseline). ``ImageClassifier`` wraps a backbone and the loss into one leaf
+module.
 """
+import math
 import os
 
 import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import Linear, batch_norm, conv2d, linear, max_pool2d
+from autodist_b200.ops.functional import Linear, batch_norm, conv2d, max_pool2d
+
+CONV_MODE = os.environ.get("AUTODIST_CONV", "own")                      # own | library
 
 
-class Conv1x1(nn.Conv2d):
-    """Pointwise convolution as a GEMM on the tcgen05 kernel: in channels-last memory a 1x1 convolution is
-    ``[N*H*W, Cin] x [Cout, Cin]^T``, forward, input gradient and weight gradient alike (a strided one subsamples first).
-    Falls back to the library convolution on CPU or for channel counts that are not multiples of 8."""
+class Conv2d(nn.Module):
+    """Square-filter convolution whose weight is stored channels-last, ``[Cout, KH, KW, Cin]`` - the layout the implicit
+    GEMM reads with one TMA box per filter tap and writes its gradient in. Initialised like ``nn.Conv2d``."""
 
-    def __init__(self, cin, cout, stride=1, bias=False):
-        super().__init__(cin, cout, 1, stride, 0, bias=bias)
+    def __init__(self, cin, cout, k, stride=1, padding=0, bias=False, relu=False):
+        super().__init__()
+        self.in_channels, self.out_channels, self.kernel_size, self.stride, self.padding, self.relu = cin, cout, k, stride, padding, relu
+        self.weight = nn.Parameter(torch.empty(cout, k, k, cin))
+        self.bias = nn.Parameter(torch.empty(cout)) if bias else None
+        bound = 1.0 / math.sqrt(cin * k * k)
+        with torch.no_grad():
+            self.weight.uniform_(-bound, bound)            # kaiming_uniform(a=sqrt(5)) reduces to U(-1/sqrt(fan_in), 1/sqrt(fan_in))
+            if bias:
+                self.bias.uniform_(-bound, bound)
 
-    def forward(self, x):
-        cin, cout = self.in_channels, self.out_channels
-        if not (x.is_cuda and USE_TCGEN05_CONV1X1 and cin % 8 == 0 and cout % 8 == 0):
-            return super().forward(x)
-        if self.stride[0] > 1:
-            x = x[:, :, ::self.stride[0], ::self.stride[1]]
-        x = x.contiguous(memory_format=torch.channels_last)
-        n, _, h, w = x.shape
-        y = linear(x.permute(0, 2, 3, 1).reshape(n * h * w, cin), self.weight.view(cout, cin), self.bias)
-        return y.view(n, h, w, cout).permute(0, 3, 1, 2)
+    def forward(self, x, stats=None):
+        if x.is_cuda and CONV_MODE != "library":
+            return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.relu, stats)
+        y = F.conv2d(x, self.weight.permute(0, 3, 1, 2).to(x.dtype), None if self.bias is None else self.bias.to(x.dtype), self.stride,
+                     self.padding)
+        return F.relu(y) if self.relu else y
 
-
-# Measured on ResNet-101 (batch 64): 41.8 ms per step with the pointwise convolutions on the GEMM (per-call casts and
-# copies around it) against 27.1 ms with the library convolution, so the library path stays the default.
-USE_TCGEN05_CONV1X1 = os.environ.get("AUTODIST_CONV1X1", "cudnn") == "tcgen05"
-
-
-class ConvGemm(nn.Conv2d):
-    """k x k convolution as im2col + tcgen05 GEMM (``ops.functional.conv2d``): forward, input gradient and weight gradient
-    on the hand-written kernels. Selected with ``AUTODIST_CONV=gemm``; the default stays the library convolution, which
-    is faster today (the im2col matrix is materialised)."""
-
-    def forward(self, x):
-        if x.is_cuda and USE_GEMM_CONV and self.groups == 1 and self.dilation == (1, 1) and self.stride[0] == self.stride[1] \
-                and self.padding[0] == self.padding[1]:
-            return conv2d(x, self.weight, self.bias, self.stride[0], self.padding[0])
-        return super().forward(x)
+    def extra_repr(self):
+        return f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, padding={self.padding}"
 
 
-USE_GEMM_CONV = os.environ.get("AUTODIST_CONV", "cudnn") == "gemm"
-
-
-def _conv(cin, cout, k, stride=1, padding=0, bias=False):
-    if k == 1 and padding == 0:
-        return Conv1x1(cin, cout, stride, bias=bias)
-    return ConvGemm(cin, cout, k, stride, padding, bias=bias)
+def _conv(cin, cout, k, stride=1, padding=0, bias=False, relu=False):
+    return Conv2d(cin, cout, k, stride, padding, bias=bias, relu=relu)
 
 
 class BatchNormAct(nn.BatchNorm2d):
-    """Batch-norm with an optional fused ReLU. For bf16 activations on a GPU (the autocast training path) the
-    training-mode statistics, the normalisation (+ ReLU) and both backward passes run on the hand-written kernels;
-    fp32 activations, evaluation mode and channel counts that are not a multiple of 8 use the library.
-    ``AUTODIST_NORM_POOL=library`` forces the library everywhere, ``=own`` the kernels for fp32 inputs too."""
+    """Batch-norm with an optional fused residual add and ReLU. For bf16 activations on a GPU (the autocast training path)
+    the training-mode statistics, the normalisation (+ add + ReLU), the running-statistics update and both backward passes
+    run on the hand-written kernels; fp32 activations, evaluation mode and channel counts that are not a multiple of 8 use
+    the library. ``AUTODIST_NORM_POOL=library`` forces the library everywhere, ``=own`` the kernels for fp32 inputs too."""
 
     def __init__(self, channels, relu=False):
         super().__init__(channels)
         self.relu = relu
 
-    def forward(self, x):
+    def forward(self, x, residual=None, sums=None):
         if _own_norm_pool(x) and self.training and self.momentum is not None:
-            if self.num_batches_tracked is not None:
-                self.num_batches_tracked.add_(1)
-            return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, True, self.momentum, self.eps, self.relu)
+            return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, True, self.momentum, self.eps, self.relu,
+                              residual, sums, self.num_batches_tracked)
         y = super().forward(x)
+        if residual is not None:
+            y = y + residual
         return F.relu(y, inplace=True) if self.relu else y
+
+
+class ConvBN(nn.Module):
+    """Convolution followed by batch-norm (+ residual add, + ReLU). On the kernel path the convolution's epilogue already
+    accumulates the per-channel sums the batch-norm needs, so the normalisation reads the activation once."""
+
+    def __init__(self, cin, cout, k, stride=1, padding=0, relu=True):
+        super().__init__()
+        self.conv = _conv(cin, cout, k, stride, padding)
+        self.bn = BatchNormAct(cout, relu=relu)
+
+    def forward(self, x, residual=None):
+        cout = self.conv.out_channels
+        fused = x.is_cuda and x.dim() == 4 and CONV_MODE != "library" and NORM_POOL_MODE != "library" and FUSE_BN_STATS and self.training \
+            and self.bn.momentum is not None and cout % 8 == 0 and cout <= 2048 and (x.dtype == torch.bfloat16 or torch.is_autocast_enabled())
+        if fused:
+            sums = torch.zeros(2, self.conv.out_channels, dtype=torch.float32, device=x.device)
+            return self.bn(self.conv(x, sums), residual, sums)
+        return self.bn(self.conv(x), residual)
+
+
+FUSE_BN_STATS = os.environ.get("AUTODIST_FUSE_BN_STATS", "1") == "1"
 
 
 class MaxPool(nn.MaxPool2d):
@@ -98,8 +109,8 @@ def _own_norm_pool(x):
     return NORM_POOL_MODE == "own" or x.dtype == torch.bfloat16
 
 
-def _conv_bn(cin, cout, k, stride=1, padding=0):
-    return nn.Sequential(_conv(cin, cout, k, stride, padding), BatchNormAct(cout, relu=True))
+def _conv_bn(cin, cout, k, stride=1, padding=0, relu=True):
+    return ConvBN(cin, cout, k, stride, padding, relu=relu)
 
 
 class Bottleneck(nn.Module):
@@ -110,14 +121,14 @@ class Bottleneck(nn.Module):
         cout = width * self.expansion
         self.a = _conv_bn(cin, width, 1)
         self.b = _conv_bn(width, width, 3, stride, 1)
-        self.c = nn.Sequential(_conv(width, cout, 1), BatchNormAct(cout))
+        self.c = _conv_bn(width, cout, 1, relu=True)           # its ReLU comes after the residual add, inside the batch-norm kernel
         self.down = None
         if stride != 1 or cin != cout:
-            self.down = nn.Sequential(_conv(cin, cout, 1, stride), BatchNormAct(cout))
+            self.down = _conv_bn(cin, cout, 1, stride, relu=False)
 
     def forward(self, x):
         idn = x if self.down is None else self.down(x)
-        return F.relu(self.c(self.b(self.a(x))) + idn)
+        return self.c(self.b(self.a(x)), residual=idn)
 
 
 class ResNet(nn.Module):
@@ -156,7 +167,7 @@ class VGG16(nn.Module):
             if v == "M":
                 layers.append(MaxPool(2, 2))
             else:
-                layers += [_conv(cin, v, 3, 1, 1, bias=True), nn.ReLU(inplace=True)]
+                layers.append(_conv(cin, v, 3, 1, 1, bias=True, relu=True))
                 cin = v
         self.features = nn.Sequential(*layers)
         side = image_size // 32
@@ -172,8 +183,8 @@ class VGG16(nn.Module):
 class _DenseLayer(nn.Module):
     def __init__(self, cin, growth):
         super().__init__()
-        self.f = nn.Sequential(nn.BatchNorm2d(cin), nn.ReLU(inplace=True), _conv(cin, 4 * growth, 1),
-                               nn.BatchNorm2d(4 * growth), nn.ReLU(inplace=True), _conv(4 * growth, growth, 3, 1, 1))
+        self.f = nn.Sequential(BatchNormAct(cin, relu=True), _conv(cin, 4 * growth, 1),
+                               BatchNormAct(4 * growth, relu=True), _conv(4 * growth, growth, 3, 1, 1))
 
     def forward(self, x):
         return torch.cat([x, self.f(x)], 1)
@@ -183,15 +194,15 @@ class DenseNet121(nn.Module):
     def __init__(self, num_classes=1000, growth=32, blocks=(6, 12, 24, 16)):
         super().__init__()
         c = 2 * growth
-        mods = [nn.Conv2d(3, c, 7, 2, 3, bias=False), nn.BatchNorm2d(c), nn.ReLU(inplace=True), nn.MaxPool2d(3, 2, 1)]
+        mods = [_conv_bn(3, c, 7, 2, 3), MaxPool(3, 2, 1)]
         for i, n in enumerate(blocks):
             for _ in range(n):
                 mods.append(_DenseLayer(c, growth))
                 c += growth
             if i + 1 < len(blocks):
-                mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True), _conv(c, c // 2, 1), nn.AvgPool2d(2, 2)]
+                mods += [BatchNormAct(c, relu=True), _conv(c, c // 2, 1), nn.AvgPool2d(2, 2)]
                 c //= 2
-        mods += [nn.BatchNorm2d(c), nn.ReLU(inplace=True)]
+        mods += [BatchNormAct(c, relu=True)]
         self.features = nn.Sequential(*mods)
         self.fc = Linear(c, num_classes)
 
@@ -216,17 +227,17 @@ class InceptionNet(nn.Module):
 
     def __init__(self, num_classes=1000):
         super().__init__()
-        self.stem = nn.Sequential(_conv_bn(3, 32, 3, 2), _conv_bn(32, 32, 3), _conv_bn(32, 64, 3, 1, 1), nn.MaxPool2d(3, 2),
-                                  _conv_bn(64, 80, 1), _conv_bn(80, 192, 3), nn.MaxPool2d(3, 2))
+        self.stem = nn.Sequential(_conv_bn(3, 32, 3, 2), _conv_bn(32, 32, 3), _conv_bn(32, 64, 3, 1, 1), MaxPool(3, 2),
+                                  _conv_bn(64, 80, 1), _conv_bn(80, 192, 3), MaxPool(3, 2))
         blocks, cin = [], 192
         for spec in [(64, 48, 64, 64, 96, 32), (64, 48, 64, 64, 96, 64), (64, 48, 64, 64, 96, 64)]:
             blocks.append(_InceptionBlock(cin, *spec))
             cin = spec[0] + spec[2] + spec[4] + spec[5]
-        blocks.append(nn.MaxPool2d(3, 2))
+        blocks.append(MaxPool(3, 2))
         for spec in [(192, 128, 192, 128, 192, 192)] * 4:
             blocks.append(_InceptionBlock(cin, *spec))
             cin = spec[0] + spec[2] + spec[4] + spec[5]
-        blocks.append(nn.MaxPool2d(3, 2))
+        blocks.append(MaxPool(3, 2))
         for spec in [(320, 384, 768, 448, 384, 192)] * 2:
             blocks.append(_InceptionBlock(cin, *spec))
             cin = spec[0] + spec[2] + spec[4] + spec[5]

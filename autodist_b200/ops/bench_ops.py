@@ -42,12 +42,12 @@ def _cnn_rows(E, dev, flush, hbm):
     y = torch.empty_like(xh)
     mean, rstd = torch.empty(C, device=dev), torch.empty(C, device=dev)
     nbytes = xh.numel() * 2
-    ms = _time(lambda: E.bn_fwd(xh, gamma, beta, y, mean, rstd, 1e-5, True), flush=flush)
+    ms = _time(lambda: E.bn_fwd(xh, gamma, beta, None, y, mean, rstd, 1e-5, True, None, None, None, None, 0.1), flush=flush)
     ms_lib = _time(lambda: F.relu(F.batch_norm(x, None, None, gamma, beta, True, 0.1, 1e-5)), flush=flush)
     rows.append({"kernel": "bn_fwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(3 * nbytes / ms / 1e6, 1),
                  "library_ms": round(ms_lib, 4), "frac_of_measured_peak": round(3 * nbytes / ms / 1e6 / hbm, 3)})
     dy, dx = torch.randn_like(xh), torch.empty_like(xh)
-    ms = _time(lambda: E.bn_bwd(dy, xh, y, mean, rstd, gamma, dx, True), flush=flush)
+    ms = _time(lambda: E.bn_bwd(dy, xh, y, mean, rstd, gamma, dx, None, True), flush=flush)
     rows.append({"kernel": "bn_bwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(7 * nbytes / ms / 1e6, 1),
                  "frac_of_measured_peak": round(7 * nbytes / ms / 1e6 / hbm, 3)})
     N, C, Hh, W = 64, 64, 112, 112                                   # the ResNet stem pool

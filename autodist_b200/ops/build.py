@@ -24,7 +24,7 @@ def sources():
 
 def source_digest():
     h = hashlib.sha1()
-    for path in sources() + sorted(glob.glob(os.path.join(CSRC, "*.h"))):
+    for path in sources() + sorted(glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))):
         with open(path, "rb") as f:
             h.update(f.read())
     return h.hexdigest()

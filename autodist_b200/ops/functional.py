@@ -141,76 +141,143 @@ def clip_by_global_norm_(grads, max_norm, weights=None, all_reduce=None):
     return acc
 
 
-class _ConvGemmFn(torch.autograd.Function):
-    """2-D convolution as im2col + tcgen05 GEMM (forward, input gradient, weight gradient), channels-last bf16."""
+def _nhwc(x):
+    """bf16 ``[N, H, W, C]`` contiguous view / copy of a logical ``[N, C, H, W]`` tensor (free for channels-last bf16)."""
+    return x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+
+
+def _bf16_weight(weight):
+    """bf16 copy of a parameter: the engine's flat compute copy when the parameter lives in flat buffers, else a cast."""
+    view = getattr(weight, "_bf16_view", None)
+    if view is not None and view.device == weight.device:
+        return view
+    return weight.detach().to(torch.bfloat16).contiguous()
+
+
+def _colsum(E, dy2):
+    n = dy2.shape[1]
+    db = torch.empty(n, dtype=torch.float32, device=dy2.device)
+    part = torch.empty(E.colsum_parts(dy2.shape[0]) * n, dtype=torch.float32, device=dy2.device)
+    E.keyed_colsum(dy2, None, part, db, 1, False)
+    return db
+
+
+def _rowtap_geometry(h, w, kh, kw, stride, padding):
+    """Padded-image extents of the first-layer path: the halo is written out and rows are long enough for the last
+    64-element read of every output column."""
+    oh, ow = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
+    hp = max(h + 2 * padding, (oh - 1) * stride + kh)
+    wp = max(w + 2 * padding, (ow - 1) * stride + 8)
+    return oh, ow, hp, wp + (wp & 1)
+
+
+class _ConvFn(torch.autograd.Function):
+    """2-D convolution as an implicit GEMM on tcgen05 (``csrc/conv_tcgen05.cu``): forward, input gradient and weight
+    gradient read the channels-last bf16 activations in place through TMA boxes, one per filter tap; bias, ReLU and the
+    per-channel sums a following batch-norm needs are fused into the forward epilogue. ``weight`` is ``[Cout, KH, KW, Cin]``."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, stride, padding):
+    def forward(ctx, x, weight, bias, stride, padding, relu, stats):
         E = ops.ext(required=True)
-        cout, cin, kh, kw = weight.shape
-        xh = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()            # [N, H, W, C]
-        n, h, w, _ = xh.shape
-        ho, wo = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
-        w2 = weight.permute(0, 2, 3, 1).reshape(cout, kh * kw * cin).to(torch.bfloat16).contiguous()
-        cols = torch.empty(n * ho * wo, kh * kw * cin, dtype=torch.bfloat16, device=x.device)
-        E.im2col(xh, cols, kh, kw, stride, padding)
-        y = torch.empty(n * ho * wo, cout, dtype=torch.bfloat16, device=x.device)
+        cout, kh, kw, cin = weight.shape
         err = _error_flag(x.device)
-        if bias is not None:
-            E.gemm(cols, w2, y, False, False, 1, bias.float().contiguous(), None, None, 1.0, 0.0, err, 0)
+        b32 = bias.detach().float().contiguous() if bias is not None else None
+        w16 = _bf16_weight(weight)
+        ctx.rowtap = cin % 8 != 0
+        if ctx.rowtap:
+            n, _, h, w = x.shape
+            oh, ow, hp, wp = _rowtap_geometry(h, w, kh, kw, stride, padding)
+            xh = torch.empty(n, hp, wp, 8, dtype=torch.bfloat16, device=x.device)
+            E.pad_image8(x, xh, padding)
+            wr = F.pad(F.pad(w16, (0, 8 - cin)).reshape(cout, kh, kw * 8), (0, 64 - kw * 8)).contiguous()
+            y = torch.empty(n, oh, ow, cout, dtype=torch.bfloat16, device=x.device)
+            E.conv_rowtap_fprop(xh, wr, y, b32, relu, stats, stride, err)
         else:
-            E.gemm(cols, w2, y, False, False, 0, None, None, None, 1.0, 0.0, err, 0)
-        ctx.save_for_backward(xh, w2)
-        ctx.geom = (kh, kw, stride, padding, ho, wo, cin, cout)
+            xh = _nhwc(x)
+            n, h, w, _ = xh.shape
+            oh, ow = (h + 2 * padding - kh) // stride + 1, (w + 2 * padding - kw) // stride + 1
+            y = torch.empty(n, oh, ow, cout, dtype=torch.bfloat16, device=x.device)
+            E.conv_fprop(xh, w16, y, b32, relu, stats, stride, padding, err)
+        ctx.save_for_backward(xh, w16, y if relu else None)
+        ctx.geom = (stride, padding, tuple(weight.shape), tuple(x.shape))
         ctx.has_bias = bias is not None
-        ctx.w_dtype, ctx.x_dtype = weight.dtype, x.dtype
-        return y.view(n, ho, wo, cout).permute(0, 3, 1, 2)
+        ctx.dtypes = (x.dtype, weight.dtype)
+        return y.permute(0, 3, 1, 2)
 
     @staticmethod
     def backward(ctx, dy):
         E = ops.ext(required=True)
-        xh, w2 = ctx.saved_tensors
-        kh, kw, stride, padding, ho, wo, cin, cout = ctx.geom
-        n = xh.shape[0]
+        xh, w16, y = ctx.saved_tensors
+        stride, padding, (cout, kh, kw, cin), x_shape = ctx.geom
         err = _error_flag(dy.device)
-        dy2 = dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous().view(n * ho * wo, cout)
-        cols = torch.empty(n * ho * wo, kh * kw * cin, dtype=torch.bfloat16, device=dy.device)
-        E.im2col(xh, cols, kh, kw, stride, padding)                            # recomputed: cheaper than keeping it
-        dw2 = torch.empty(cout, kh * kw * cin, dtype=torch.float32, device=dy.device)
-        E.gemm(dy2, cols, dw2, True, True, 0, None, None, None, 1.0, 0.0, err, 0)      # dW = dY^T . cols
-        dcols = cols                                                            # reuse the buffer
-        E.gemm(dy2, w2, dcols, False, True, 0, None, None, None, 1.0, 0.0, err, 0)     # dcols = dY . W
-        dx = torch.empty_like(xh)
-        E.col2im(dcols, dx, kh, kw, stride, padding)
-        dw = dw2.view(cout, kh, kw, cin).permute(0, 3, 1, 2).to(ctx.w_dtype)
-        db = dy2.float().sum(0) if ctx.has_bias else None
-        return dx.permute(0, 3, 1, 2).to(ctx.x_dtype), dw, db, None, None
+        dyh = _nhwc(dy)
+        if y is not None:
+            masked = torch.empty_like(dyh)
+            E.relu_bwd(dyh, y, masked)
+            dyh = masked
+        dx = None
+        if ctx.rowtap:
+            dwr = torch.empty(cout, kh, 64, dtype=torch.float32, device=dy.device)
+            E.conv_rowtap_wgrad(dyh, xh, dwr, stride, err)
+            dw = dwr[:, :, :kw * 8].reshape(cout, kh, kw, 8)[..., :cin].contiguous()
+            if ctx.needs_input_grad[0]:
+                w_oihw = w16.float().permute(0, 3, 1, 2)
+                dx = torch.nn.grad.conv2d_input(x_shape, w_oihw, dy.float(), stride, padding).to(ctx.dtypes[0])
+        else:
+            dw = torch.empty(cout, kh, kw, cin, dtype=torch.float32, device=dy.device)
+            E.conv_wgrad(dyh, xh, dw, stride, padding, err)
+            if ctx.needs_input_grad[0]:
+                dxh = torch.empty_like(xh)
+                E.conv_dgrad(dyh, w16, dxh, stride, padding, err)
+                dx = dxh.permute(0, 3, 1, 2).to(ctx.dtypes[0])
+        db = None
+        if ctx.has_bias:
+            db = _colsum(E, dyh.view(-1, cout))
+        return dx, dw.to(ctx.dtypes[1]), db, None, None, None, None
 
 
-def conv2d(x, weight, bias=None, stride=1, padding=0):
-    """Convolution on the hand-written kernels when the channel counts allow it (multiples of 8), else the library."""
-    cout, cin = weight.shape[0], weight.shape[1]
-    if x.is_cuda and cin % 8 == 0 and cout % 8 == 0:
-        return _ConvGemmFn.apply(x, weight, bias, int(stride), int(padding))
-    return F.conv2d(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype), stride, padding)
+def conv2d(x, weight, bias=None, stride=1, padding=0, relu=False, stats=None):
+    """Convolution of a logical ``[N, C, H, W]`` tensor with a ``[Cout, KH, KW, Cin]`` weight (+ bias, + ReLU).
+
+    On a GPU it runs on the implicit-GEMM kernels when the channel counts allow it: ``Cin`` and ``Cout`` multiples of 8,
+    or ``Cin <= 8`` with ``KW <= 8`` (the first layer of an image network, whose input is padded to 8 channels). ``stats``
+    (fp32 ``[2, Cout]``, zeroed by the caller) receives the per-channel sum and sum of squares of the output. Other shapes
+    and CPU tensors use the library convolution."""
+    cout, kh, kw, cin = weight.shape
+    own = x.is_cuda and cout % 8 == 0 and stride in (1, 2) and kh * kw <= 49 and (cin % 8 == 0 or (cin <= 8 and kw <= 8))
+    if own:
+        return _ConvFn.apply(x, weight, bias, int(stride), int(padding), bool(relu), stats)
+    y = F.conv2d(x, weight.permute(0, 3, 1, 2).to(x.dtype), None if bias is None else bias.to(x.dtype), stride, padding)
+    y = F.relu(y) if relu else y
+    if stats is not None:
+        with torch.no_grad():
+            yf = y.float()
+            stats[0] += yf.sum((0, 2, 3))
+            stats[1] += (yf * yf).sum((0, 2, 3))
+    return y
 
 
 class _BatchNormFn(torch.autograd.Function):
-    """Training-mode batch-norm (+ optional ReLU) over channels-last activations on the hand-written kernels."""
+    """Training-mode batch-norm over channels-last activations on the hand-written kernels, with the tail of a residual
+    block fused in: ``y = relu?(bn(x) + residual)``. ``sums`` (fp32 ``[2, C]``: sum and sum of squares per channel, as the
+    convolution's epilogue leaves them) skips the statistics pass."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, relu):
+    def forward(ctx, x, gamma, beta, residual, eps, relu, sums, running):
         E = ops.ext(required=True)
-        xh = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()            # [N, H, W, C]
+        run_mean, run_var, batches, momentum = running if running is not None else (None, None, None, 0.0)
+        xh = _nhwc(x)                                                            # [N, H, W, C]
         c = xh.shape[-1]
         y = torch.empty_like(xh)
         mean = torch.empty(c, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
-        g32, b32 = gamma.float().contiguous(), beta.float().contiguous()
-        E.bn_fwd(xh, g32, b32, y, mean, rstd, eps, relu)
+        g32, b32 = gamma.detach().float().contiguous(), beta.detach().float().contiguous()
+        res = _nhwc(residual) if residual is not None else None
+        E.bn_fwd(xh, g32, b32, res, y, mean, rstd, eps, relu, sums, run_mean, run_var, batches, momentum)
         ctx.save_for_backward(xh, y, mean, rstd, g32)
         ctx.relu = relu
-        ctx.dtypes = (x.dtype, gamma.dtype)
+        ctx.has_res = residual is not None
+        ctx.dtypes = (x.dtype, gamma.dtype, residual.dtype if residual is not None else None)
         ctx.mark_non_differentiable(mean, rstd)
         return y.permute(0, 3, 1, 2), mean, rstd
 
@@ -218,25 +285,38 @@ class _BatchNormFn(torch.autograd.Function):
     def backward(ctx, dy, _dm, _dr):
         E = ops.ext(required=True)
         xh, y, mean, rstd, g32 = ctx.saved_tensors
-        dyh = dy.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+        dyh = _nhwc(dy)
         dx = torch.empty_like(xh)
-        sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, ctx.relu)
-        return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), None, None
+        dres = None
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = torch.empty_like(xh) if ctx.relu else dyh                    # without a ReLU the residual gradient is dy itself
+        sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, dres if ctx.relu else None, ctx.relu)
+        dr = dres.permute(0, 3, 1, 2).to(ctx.dtypes[2]) if dres is not None else None
+        return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), dr, None, None, None, None
 
 
-def batch_norm(x, gamma, beta, running_mean=None, running_var=None, training=True, momentum=0.1, eps=1e-5, relu=False):
-    """Batch-norm (+ ReLU) of an NCHW / channels-last tensor; updates the running statistics like ``F.batch_norm``."""
+def batch_norm(x, gamma, beta, running_mean=None, running_var=None, training=True, momentum=0.1, eps=1e-5, relu=False,
+               residual=None, sums=None, num_batches_tracked=None):
+    """``relu?(batch_norm(x) + residual)`` of an NCHW / channels-last tensor; updates the running statistics like
+    ``F.batch_norm``. ``sums``: per-channel sum / sum of squares of ``x`` when a preceding kernel already produced them."""
     if not (x.is_cuda and training and x.shape[1] % 8 == 0):
         y = F.batch_norm(x, running_mean, running_var, gamma.to(x.dtype) if x.dtype != gamma.dtype and not x.is_cuda else gamma,
                          beta, training, momentum, eps)
+        if residual is not None:
+            y = y + residual
         return F.relu(y) if relu else y
-    y, mean, rstd = _BatchNormFn.apply(x, gamma, beta, eps, relu)
-    if running_mean is not None:
+    running = None
+    if running_mean is not None and running_mean.dtype == torch.float32 and running_var.dtype == torch.float32:
+        running = (running_mean, running_var, num_batches_tracked, float(momentum))     # folded into the statistics kernel
+    y, mean, rstd = _BatchNormFn.apply(x, gamma, beta, residual, eps, relu, sums, running)
+    if running is None and running_mean is not None:
         with torch.no_grad():
             n = x.numel() // x.shape[1]
             var = (1.0 / (rstd * rstd) - eps).clamp_(min=0) * (n / max(n - 1, 1))
             running_mean.mul_(1 - momentum).add_(mean.to(running_mean.dtype), alpha=momentum)
             running_var.mul_(1 - momentum).add_(var.to(running_var.dtype), alpha=momentum)
+        if num_batches_tracked is not None:
+            num_batches_tracked.add_(1)
     return y
 
 

@@ -685,6 +685,8 @@ class _AutogradModel:
                 p.data = p.data.to(device)
         self.flat = FlatParams([(n, p) for n, p in named if p.requires_grad], device, grad_alloc,
                                master_alloc=master_alloc, p16_alloc=p16_alloc)
+        for n, p in zip(self.flat.names, self.flat.params):
+            p._bf16_view = self.flat.w16[n]          # the optimizer kernels keep this compute copy current: no per-call cast
         return self.flat
 
     def check_error(self):

@@ -22,10 +22,17 @@ def _rand(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
-def _check(out, ref, tol):
+def _check(out, ref, tol, fro=None):
+    """Max-norm bound relative to the largest reference value, plus a relative Frobenius bound (default: the same
+    tolerance) so that one wrong tile of a large product cannot hide under a loose element-wise bound."""
+    ref = ref.float()
     diff = (out.float() - ref).abs().max().item()
     bound = tol * max(1.0, ref.abs().max().item())
     assert diff <= bound, f"max diff {diff} > {bound}"
+    denom = ref.norm().item()
+    if denom > 0 and out.numel() >= 64:
+        rel = ((out.float() - ref).norm().item()) / denom
+        assert rel <= (tol if fro is None else fro), f"relative Frobenius error {rel} > {tol if fro is None else fro}"
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (200, 300, 136), (4096, 1024, 1024), (32, 2, 1024),
@@ -350,27 +357,6 @@ def test_power_sgd_kernels_match_the_torch_compressor():
             _check(gpu.error.cpu(), cpu.error, 1e-4)
 
 
-def test_conv1x1_on_the_gemm_matches_the_library_convolution():
-    from autodist_b200.models import cnn
-    from autodist_b200.models.cnn import Conv1x1
-    cnn.USE_TCGEN05_CONV1X1 = True
-    torch.manual_seed(13)
-    for stride in (1, 2):
-        conv = Conv1x1(64, 128, stride).cuda()
-        x = torch.randn(4, 64, 14, 14, device="cuda").to(memory_format=torch.channels_last).requires_grad_(True)
-        y = conv(x.to(torch.bfloat16))
-        dy = torch.randn_like(y.float())
-        y.float().backward(dy)
-        gx, gw = x.grad.clone(), conv.weight.grad.clone()
-        x.grad = conv.weight.grad = None
-        ref = torch.nn.functional.conv2d(x, conv.weight, None, stride)
-        ref.backward(dy)
-        assert y.shape == ref.shape
-        _check(y, ref.detach(), 2e-2)
-        _check(gx, x.grad, 3e-2)
-        _check(gw, conv.weight.grad, 3e-2)
-
-
 @pytest.mark.parametrize("pd", [0.0, 0.1])
 def test_softmax_fused_into_the_attention_gemms(E, err, pd):
     """QK^T with scale + mask + softmax (+ dropout) in the epilogue, and dP -> dS likewise, against the two-kernel path."""
@@ -402,26 +388,86 @@ def test_softmax_fused_into_the_attention_gemms(E, err, pd):
     _check(ds, ds_ref.float(), 3e-2)
 
 
-@pytest.mark.parametrize("k,stride,pad", [(3, 1, 1), (3, 2, 1), (7, 2, 3), (1, 1, 0)])
-def test_convolution_as_im2col_gemm_matches_the_library(k, stride, pad):
+def _rel_fro(out, ref):
+    return ((out.float() - ref).norm() / ref.norm().clamp_min(1e-12)).item()
+
+
+# (N, Cin, H, W, Cout, k, stride, pad): the filter shapes of ResNet-101 (3x3/s1, 3x3/s2, 1x1, 1x1/s2), odd image sizes,
+# channel counts below one 64-channel block, and outputs wider than one N tile
+CONV_CASES = [(3, 16, 13, 15, 24, 3, 1, 1), (4, 64, 14, 14, 64, 3, 1, 1), (2, 128, 28, 28, 128, 3, 2, 1), (3, 64, 9, 11, 256, 1, 1, 0),
+              (2, 256, 14, 14, 512, 1, 2, 0), (2, 72, 7, 7, 320, 3, 1, 1), (5, 32, 17, 9, 48, 3, 2, 1), (2, 64, 8, 8, 64, 3, 1, 0),
+              (8, 512, 7, 7, 512, 3, 1, 1), (2, 40, 12, 12, 40, 5, 1, 2), (2, 24, 11, 13, 32, 3, 2, 0)]
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", CONV_CASES)
+def test_implicit_gemm_convolution_matches_the_library(n, cin, h, w, cout, k, stride, pad):
+    """Forward, input gradient and weight gradient of the tcgen05 implicit-GEMM convolution against ``F.conv2d`` in fp32."""
     from autodist_b200.ops import functional as Fn
     torch.manual_seed(15)
-    x = torch.randn(3, 16, 13, 15, device="cuda").to(memory_format=torch.channels_last).requires_grad_(True)
-    w = (torch.randn(24, 16, k, k, device="cuda") * 0.1).requires_grad_(True)
-    b = torch.randn(24, device="cuda").requires_grad_(True)
-    y = Fn.conv2d(x.to(torch.bfloat16), w, b, stride, pad)
-    dy = torch.randn_like(y.float())
+    x = torch.randn(n, cin, h, w, device="cuda").to(torch.bfloat16).float().to(memory_format=torch.channels_last).requires_grad_(True)
+    wt = (torch.randn(cout, k, k, cin, device="cuda") / math.sqrt(cin * k * k)).to(torch.bfloat16).float().requires_grad_(True)
+    b = torch.randn(cout, device="cuda").requires_grad_(True)
+    y = Fn.conv2d(x.to(torch.bfloat16), wt, b, stride, pad)
+    dy = torch.randn_like(y.float()).to(torch.bfloat16).float()
     y.float().backward(dy)
-    gx, gw, gb = x.grad.clone(), w.grad.clone(), b.grad.clone()
-    x.grad = w.grad = b.grad = None
-    ref = torch.nn.functional.conv2d(x, w, b, stride, pad)
+    gx, gw, gb = x.grad.clone(), wt.grad.clone(), b.grad.clone()
+    x.grad = wt.grad = b.grad = None
+    ref = torch.nn.functional.conv2d(x, wt.permute(0, 3, 1, 2), b, stride, pad)
     ref.backward(dy)
-    assert y.shape == ref.shape
-    _check(y, ref.detach(), 2e-2)
-    _check(gx, x.grad, 3e-2)
-    _check(gw, w.grad, 3e-2)
-    _check(gb, b.grad, 3e-2)
     Fn.check_errors()
+    assert y.shape == ref.shape
+    _check(y, ref.detach(), 1e-2)
+    assert _rel_fro(y, ref.detach()) < 2 ** -8
+    _check(gx, x.grad, 1e-2)
+    assert _rel_fro(gx, x.grad) < 2 ** -7           # dx is rounded to bf16 once
+    _check(gw, wt.grad, 2e-3)
+    assert _rel_fro(gw, wt.grad) < 1e-3             # fp32 accumulation and fp32 output
+    _check(gb, b.grad, 2e-3)
+
+
+@pytest.mark.parametrize("n,h,w,cout,k,stride,pad", [(2, 224, 224, 64, 7, 2, 3), (3, 31, 29, 64, 3, 1, 1), (2, 37, 41, 32, 3, 2, 0)])
+def test_first_layer_convolution_with_three_input_channels(n, h, w, cout, k, stride, pad):
+    """The row-tap path: the image is padded to 8 channels with its halo and each filter row is one 64-element K block."""
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(17)
+    x = torch.randn(n, 3, h, w, device="cuda").to(torch.bfloat16).float().to(memory_format=torch.channels_last)
+    wt = (torch.randn(cout, k, k, 3, device="cuda") / math.sqrt(3 * k * k)).to(torch.bfloat16).float().requires_grad_(True)
+    y = Fn.conv2d(x, wt, None, stride, pad)
+    dy = torch.randn_like(y.float()).to(torch.bfloat16).float()
+    y.float().backward(dy)
+    gw = wt.grad.clone()
+    wt.grad = None
+    ref = torch.nn.functional.conv2d(x, wt.permute(0, 3, 1, 2), None, stride, pad)
+    ref.backward(dy)
+    Fn.check_errors()
+    assert y.shape == ref.shape
+    _check(y, ref.detach(), 1e-2)
+    assert _rel_fro(y, ref.detach()) < 2 ** -8
+    _check(gw, wt.grad, 2e-3)
+    assert _rel_fro(gw, wt.grad) < 1e-3
+
+
+def test_convolution_epilogue_bias_relu_and_batch_norm_sums():
+    from autodist_b200.ops import functional as Fn
+    torch.manual_seed(18)
+    x = torch.randn(6, 64, 14, 14, device="cuda").to(torch.bfloat16).to(memory_format=torch.channels_last).requires_grad_(True)
+    wt = (torch.randn(136, 3, 3, 64, device="cuda") / 24).to(torch.bfloat16).float().requires_grad_(True)
+    b = torch.randn(136, device="cuda")
+    stats = torch.zeros(2, 136, device="cuda")
+    y = Fn.conv2d(x, wt, b, 1, 1, relu=True, stats=stats)
+    dy = torch.randn_like(y.float()).to(torch.bfloat16).float()
+    y.float().backward(dy)
+    gx, gw = x.grad.clone(), wt.grad.clone()
+    x.grad = wt.grad = None
+    ref = torch.relu(torch.nn.functional.conv2d(x.float(), wt.permute(0, 3, 1, 2), b, 1, 1))
+    ref.backward(dy)
+    Fn.check_errors()
+    _check(y, ref.detach(), 1e-2)
+    yf = y.float()
+    _check(stats[0], yf.sum((0, 2, 3)), 1e-4)                # the sums are those of the stored (bf16-rounded) output
+    _check(stats[1], (yf * yf).sum((0, 2, 3)), 1e-4)
+    assert _rel_fro(gx, x.grad.float()) < 2 ** -7
+    assert _rel_fro(gw, wt.grad) < 1e-3
 
 
 @pytest.mark.parametrize("relu", [False, True])
