@@ -355,22 +355,22 @@ void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, const opti
   TORCH_CHECK(y.is_contiguous() && y.numel() == x.numel() && mean.numel() == C && rstd.numel() == C && gamma.numel() == C && beta.numel() == C,
               "output and per-channel tensors must match x");
   if (res.has_value()) TORCH_CHECK(res->is_contiguous() && res->numel() == x.numel() && res->scalar_type() == at::kBFloat16, "residual must match x");
-  Tensor coef = at::empty({2 * C}, x.options().dtype(at::kFloat));              // [scale, shift]
   if (sums_in.has_value()) {
     TORCH_CHECK(sums_in->scalar_type() == at::kFloat && sums_in->numel() == 2 * C && sums_in->is_contiguous(), "sums must be fp32 [2, C]");
     adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(res), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                   nullptr, sums_in->data_ptr<float>(), coef.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, 1, rm, rv, nb, (float)momentum, STREAM);
+                   nullptr, sums_in->data_ptr<float>(), nullptr, rows, C, (float)eps, relu ? 1 : 0, 1, rm, rv, nb, (float)momentum, STREAM);
     return;
   }
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({2 * C}, x.options().dtype(at::kFloat));
   adb200::bn_fwd(CBF(x), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(res), BF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(),
-                 part.data_ptr<float>(), sums.data_ptr<float>(), coef.data_ptr<float>(), rows, C, (float)eps, relu ? 1 : 0, 0, rm, rv, nb, (float)momentum,
+                 part.data_ptr<float>(), sums.data_ptr<float>(), nullptr, rows, C, (float)eps, relu ? 1 : 0, 0, rm, rv, nb, (float)momentum,
                  STREAM);
 }
 // Returns [dbeta, dgamma] stacked as a [2, C] fp32 tensor; writes dx and (optional) dres = dy masked by the ReLU.
+// dgamma_acc / dbeta_acc (optional, fp32 [C]): the batch-norm parameters' gradient buffers; the sums are added into them.
 Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
-              const optional<Tensor>& dres, bool relu) {
+              const optional<Tensor>& dres, bool relu, const optional<Tensor>& dgamma_acc, const optional<Tensor>& dbeta_acc) {
   const int C = x.size(-1), rows = x.numel() / C;
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
               "dy, x, dx must be contiguous bf16 [.., C] of one shape, C % 8 == 0");
@@ -378,7 +378,8 @@ Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& 
   Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({5, C}, x.options().dtype(at::kFloat));              // [dbeta, dgamma, A, B, K]
   adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx), OPT_BF(dres),
-                 part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, relu ? 1 : 0, STREAM);
+                 part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, relu ? 1 : 0, OPT_F(dgamma_acc),
+                 OPT_F(dbeta_acc), STREAM);
   return sums.narrow(0, 0, 2);
 }
 // code: uint8 [N, Ho, Wo, C], the window position of each output's first maximum

@@ -43,7 +43,7 @@ int sm_count() {
 
 // 4-D bf16 map, 128-byte swizzle, zero fill outside. dims / strides in elements, innermost stride 1.
 CUtensorMap map4(const void* base, int64_t d0, int64_t d1, int64_t d2, int64_t d3, int64_t s1, int64_t s2, int64_t s3, int b0, int b1,
-                 int b2, int b3) {
+                 int b2, int b3, bool* ok = nullptr) {
   TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "tensor base must be 16-byte aligned");
   TORCH_CHECK(d0 > 0 && d1 > 0 && d2 > 0 && d3 > 0, "empty tensor");
   TORCH_CHECK(s1 % 8 == 0 && s2 % 8 == 0 && s3 % 8 == 0 && s1 > 0 && s2 > 0 && s3 > 0, "strides must be positive multiples of 8 elements");
@@ -56,7 +56,8 @@ CUtensorMap map4(const void* base, int64_t d0, int64_t d1, int64_t d2, int64_t d
   CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  if (ok != nullptr) *ok = r == CUDA_SUCCESS;
+  else TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
   return m;
 }
 
@@ -169,13 +170,28 @@ void set_grid(adb200::ConvParams& p, int GW, int GH, int GN, Patch pt) {
   p.tiles_w = ceil_div(GW, pt.tw); p.tiles_h = ceil_div(GH, pt.th); p.tiles_n = ceil_div(GN, pt.tn);
 }
 
-void launch(const adb200::ConvMaps& maps, const adb200::ConvParams& p, int bn) {
+// Tuning aid: when set (int64 CUDA tensor of at least 8 x SM-count words, zeroed by the caller), the next launches record
+// clock64 marks per CTA into it.
+long long* g_trace = nullptr;
+void conv_set_trace(const optional<Tensor>& t) {
+  if (t.has_value()) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() && t->numel() >= 8LL * sm_count(), "int64 [SMs, 8] needed");
+    g_trace = reinterpret_cast<long long*>(t->data_ptr<int64_t>());
+  } else {
+    g_trace = nullptr;
+  }
+}
+
+void launch(const adb200::ConvMaps& maps, const adb200::ConvParams& p_, int bn) {
+  adb200::ConvParams p = p_;
+  p.trace = g_trace;
   cudaError_t e = adb200::launch_conv(maps, p, bn, sm_count(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "convolution launch failed: ", cudaGetErrorString(e));
 }
 
+// CTAs per output tile of the weight gradient: as many as fit in one wave, each with at least four K blocks.
 int split_k(int base_tiles, long long patches) {
-  int ks = std::max(1, (sm_count() + base_tiles - 1) / base_tiles);
+  int ks = std::max(1, sm_count() / base_tiles);
   ks = (int)std::min<long long>(ks, std::max<long long>(1, patches / 4));
   return ks;
 }
@@ -279,8 +295,9 @@ void conv_dgrad(const Tensor& dy, const Tensor& w, Tensor dx, int64_t stride, in
     }
 }
 
-// dw (fp32 [Cout, KH, KW, Cin]) = the weight gradient of conv(x, w) given dy; overwritten.
-void conv_wgrad(const Tensor& dy, const Tensor& x, Tensor dw, int64_t stride, int64_t pad, Tensor error_flag) {
+// dw (fp32 [Cout, KH, KW, Cin]) = the weight gradient of conv(x, w) given dy: overwritten, or added to with `accumulate`
+// (the parameter's gradient buffer, cleared once per step by its owner).
+void conv_wgrad(const Tensor& dy, const Tensor& x, Tensor dw, int64_t stride, int64_t pad, Tensor error_flag, bool accumulate) {
   const c10::cuda::CUDAGuard guard(dy.device());
   check_act(dy, "dy"); check_act(x, "x");
   TORCH_CHECK(dw.dim() == 4 && dw.scalar_type() == at::kFloat && dw.is_contiguous(), "dw must be contiguous fp32 [Cout, KH, KW, Cin]");
@@ -310,8 +327,8 @@ void conv_wgrad(const Tensor& dy, const Tensor& x, Tensor dw, int64_t stride, in
   const long long patches = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
   const int base_tiles = ceil_div(g.Cout, 128) * ceil_div(g.Cin, bn) * p.ntaps;
   p.ksplit = split_k(base_tiles, patches);
-  p.accumulate = p.ksplit > 1 ? 1 : 0;
-  if (p.accumulate) dw.zero_();
+  p.accumulate = (p.ksplit > 1 || accumulate) ? 1 : 0;
+  if (p.accumulate && !accumulate) dw.zero_();
   p.out = dw.data_ptr(); p.ldc = (long long)g.KH * g.KW * g.Cin; p.wtap_stride = g.Cin;
   p.error_flag = error_flag.data_ptr<int>();
   launch(maps, p, bn);
@@ -321,13 +338,28 @@ void conv_wgrad(const Tensor& dy, const Tensor& x, Tensor dw, int64_t stride, in
 // xp is the image padded to 8 channels with its spatial halo written out: [N, Hp, Wp, 8] bf16, Hp >= (OH-1)*stride + KH,
 // Wp*8 >= ((OW-1)*stride)*8 + 64. A filter row (KW taps x 8 channels <= 64 elements) of one output pixel is contiguous in
 // memory, so the contraction runs over KH "row taps" of 64 elements each; wr is the weight as [Cout, KH, 64] (zero beyond KW*8).
-void rowtap_maps(adb200::ConvMaps& maps, const Tensor& xp, int64_t stride, int bh, int bn_) {
+// Preferred form: one 4-D map whose second dimension steps by one output column (8 or 16 elements) while the box is 64
+// elements wide, i.e. neighbouring rows of the map overlap in memory; then a whole patch is one box. Should the driver
+// refuse such a map, the caller falls back to one box per patch column (`wsplit`).
+bool rowtap_maps(adb200::ConvMaps& maps, const Tensor& xp, int64_t stride, int OW, Patch pt, bool allow_overlap) {
   const int64_t N = xp.size(0), Hp = xp.size(1), Wp = xp.size(2);
   const char* base = reinterpret_cast<const char*>(xp.data_ptr());
   const int64_t row = Wp * 8;
+  if (allow_overlap) {
+    bool ok = true;
+    for (int ph = 0; ph < (int)stride && ok; ++ph)
+      maps.act[ph] = map4(base + ph * row * 2, 64, OW, (Hp - ph + stride - 1) / stride, N, stride * 8, stride * row, Hp * row, 64, pt.tw, pt.th,
+                          pt.tn, &ok);
+    if (ok) {
+      for (int i = (int)stride; i < 4; ++i) maps.act[i] = maps.act[0];
+      return true;
+    }
+    return false;
+  }
   for (int ph = 0; ph < (int)stride; ++ph)
-    maps.act[ph] = map4(base + ph * row * 2, row, (Hp - ph + stride - 1) / stride, N, 1, stride * row, Hp * row, N * Hp * row, 64, bh, bn_, 1);
+    maps.act[ph] = map4(base + ph * row * 2, row, (Hp - ph + stride - 1) / stride, N, 1, stride * row, Hp * row, N * Hp * row, 64, pt.th, pt.tn, 1);
   for (int i = (int)stride; i < 4; ++i) maps.act[i] = maps.act[0];
+  return true;
 }
 
 int rowtap_taps(adb200::ConvTap* taps, int KH, int stride) {
@@ -361,10 +393,15 @@ void conv_rowtap_fprop(const Tensor& xp, const Tensor& wr, Tensor y, const optio
   adb200::ConvParams p{};
   adb200::ConvMaps maps{};
   p.mode = adb200::CONV_FPROP;
-  const Patch pt = choose_patch(OW, OH, N, 128, false, true);
+  Patch pt = choose_patch(OW, OH, N, 128, false, false);
+  if (rowtap_maps(maps, xp, stride, OW, pt, true)) {
+    p.wsplit = 0;
+  } else {
+    pt = choose_patch(OW, OH, N, 128, false, true);
+    rowtap_maps(maps, xp, stride, OW, pt, false);
+    p.wsplit = 1; p.xstep = (int)stride * 8;
+  }
   set_grid(p, OW, OH, N, pt);
-  p.wsplit = 1; p.xstep = (int)stride * 8;
-  rowtap_maps(maps, xp, stride, pt.th, pt.tn);
   const int bn = pick_bn(Cout);
   maps.w = map4(wr.data_ptr(), 64, KH, Cout, 1, 64, 64 * KH, (int64_t)64 * KH * Cout, 64, 1, bn, 1);
   maps.dy = maps.w;
@@ -395,12 +432,17 @@ void conv_rowtap_wgrad(const Tensor& dy, const Tensor& xp, Tensor dwr, int64_t s
   adb200::ConvParams p{};
   adb200::ConvMaps maps{};
   p.mode = adb200::CONV_WGRAD;
-  const Patch pt = choose_patch(OW, OH, N, 64, true, true);
+  Patch pt = choose_patch(OW, OH, N, 64, true, false);
+  if (rowtap_maps(maps, xp, stride, OW, pt, true)) {
+    p.wsplit = 0;
+  } else {
+    pt = choose_patch(OW, OH, N, 64, true, true);
+    rowtap_maps(maps, xp, stride, OW, pt, false);
+    p.wsplit = 1; p.xstep = (int)stride * 8;
+  }
   set_grid(p, OW, OH, N, pt);
-  p.wsplit = 1; p.xstep = (int)stride * 8;
-  rowtap_maps(maps, xp, stride, pt.th, pt.tn);
   const int64_t C = Cout;
-  maps.dy = map4(dy.data_ptr(), C, OW, OH, N, C, (int64_t)OW * C, (int64_t)OH * OW * C, 64, 1, pt.th, pt.tn);
+  maps.dy = map4(dy.data_ptr(), C, OW, OH, N, C, (int64_t)OW * C, (int64_t)OH * OW * C, 64, p.wsplit ? 1 : pt.tw, pt.th, pt.tn);
   maps.w = maps.dy;
   p.ntaps = rowtap_taps(p.taps, KH, stride);
   p.Nc = 64; p.Mc = Cout;
@@ -416,6 +458,7 @@ void conv_rowtap_wgrad(const Tensor& dy, const Tensor& xp, Tensor dwr, int64_t s
 }  // namespace
 
 void register_conv(pybind11::module& m) {
+  m.def("conv_set_trace", &conv_set_trace);
   m.def("conv_fprop", &conv_fprop);
   m.def("conv_dgrad", &conv_dgrad);
   m.def("conv_wgrad", &conv_wgrad);

@@ -133,6 +133,11 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // trace (when given): 0 start, 1 first load issued, 2 last load issued, 3 first stage full, 4 last MMA committed,
+  // 5 cycles the first epilogue warp spent between "accumulator full" and "accumulator released" (summed over tiles),
+  // 6 cycles it waited for full accumulators, 7 end
+  long long* trace = p.trace != nullptr ? p.trace + (long long)blockIdx.x * 8 : nullptr;
+  if (trace != nullptr && threadIdx.x == 0) trace[0] = clock64();
   const long long total = total_tiles(p, BN, MODE);
   const int kcb = (p.Kc + BK - 1) / BK;
   const int rows = p.tw * p.th * p.tn;
@@ -142,6 +147,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
+      if (trace != nullptr) trace[1] = clock64();
       for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
         const TileCoord tc_ = decode_tile<BN, MODE>(p, t);
         if (MODE != CONV_WGRAD) {
@@ -178,19 +184,19 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
             const int h0 = ((pi / p.tiles_w) % p.tiles_h) * p.th;
             const int n0 = (pi / (p.tiles_w * p.tiles_h)) * p.tn;
             if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(&full[stage], A_BYTES + C::B_BYTES);
+            // output channels beyond Cout need no load: those accumulator rows are never stored
+            const int a_chunks = (tc_.m0 + 64 < p.Mc) ? 2 : 1;
+            mbar_expect_tx(&full[stage], a_chunks * (BK * 128) + C::B_BYTES);
             uint8_t* a_dst = sA + stage * A_BYTES;
             uint8_t* b_dst = sB + stage * C::B_BYTES;
             if (!p.wsplit) {
-#pragma unroll
-              for (int j = 0; j < BM / 64; ++j) tma_load_4d(a_dst + j * (BK * 128), &maps.dy, &full[stage], tc_.m0 + 64 * j, w0, h0, n0);
+              for (int j = 0; j < a_chunks; ++j) tma_load_4d(a_dst + j * (BK * 128), &maps.dy, &full[stage], tc_.m0 + 64 * j, w0, h0, n0);
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
                 tma_load_4d(b_dst + j * (BK * 128), mapX, &full[stage], tc_.c0 + 64 * j, w0 + tap.dw, h0 + tap.dh, n0);
             } else {
               for (int jw = 0; jw < p.tw; ++jw) {
-#pragma unroll
-                for (int j = 0; j < BM / 64; ++j)
+                for (int j = 0; j < a_chunks; ++j)
                   tma_load_4d(a_dst + j * (BK * 128) + jw * col_rows * 128, &maps.dy, &full[stage], tc_.m0 + 64 * j, w0 + jw, h0, n0);
                 tma_load_4d(b_dst + jw * col_rows * 128, mapX, &full[stage], (w0 + jw) * p.xstep, h0 + tap.dh, n0, 0);
               }
@@ -199,6 +205,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
           }
         }
       }
+      if (trace != nullptr) trace[2] = clock64();
       if (!ok) {
         *abort_flag = 1;
         if (p.error_flag) atomicExch(p.error_flag, 11);
@@ -229,6 +236,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (trace != nullptr && t == blockIdx.x && kb == 0) trace[3] = clock64();
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
@@ -245,6 +253,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
         }
         if (!ok) break;
         umma_commit(&tfull[as]);
+        if (trace != nullptr) trace[4] = clock64();
         if (++as == 2) { as = 0; aphase ^= 1; }
       }
       if (!ok) {
@@ -274,7 +283,9 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
         valid = row < p.Mc;
         off = (long long)row * p.ldc + (long long)p.taps[tc_.tap].wtap * p.wtap_stride;
       }
+      const long long tw0 = trace != nullptr ? clock64() : 0;
       if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
+      const long long tw1 = trace != nullptr ? clock64() : 0;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
 #pragma unroll 1
@@ -350,8 +361,10 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
       __syncwarp();
       tc_fence_before();
       mbar_arrive(&tempty[as]);
+      if (trace != nullptr && threadIdx.x == 64) { trace[5] += clock64() - tw1; trace[6] += tw1 - tw0; }
       if (++as == 2) { as = 0; aphase ^= 1; }
     }
+    if (trace != nullptr && threadIdx.x == 64) trace[7] = clock64();
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (p.error_flag) atomicExch(p.error_flag, 13);

@@ -48,6 +48,7 @@ struct ConvParams {
   int relu;                       // forward: clamp at zero after the bias
   float* stats;                   // forward: [2, Nc] fp32, per-channel sum and sum of squares are added here, or null
   int* error_flag;
+  long long* trace;               // optional tuning aid: [grid, 8] clock64 marks per CTA (see conv_kernel), or null
   ConvTap taps[kMaxConvTaps];
 };
 

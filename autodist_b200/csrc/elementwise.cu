@@ -877,49 +877,46 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
   }
 }
 
-// Per-channel mean / rstd and the affine form of the normalisation: y = x * scale + shift.
-// coef = [scale (C), shift (C)]; sums = [sum x (C), sum x^2 (C)].
-// Also folds the batch statistics into the running mean / variance (unbiased) and counts the batch when those are given.
-__global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                   float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ coef, float inv_rows, int C,
-                                   float eps, float* __restrict__ run_mean, float* __restrict__ run_var, long long* __restrict__ batches,
-                                   float momentum, float unbias) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c == 0 && batches != nullptr) *batches += 1;
-  if (c >= C) return;
-  const float mu = sums[c] * inv_rows;
-  const float var = fmaxf(sums[C + c] * inv_rows - mu * mu, 0.f);
-  const float rs = rsqrtf(var + eps);
-  mean[c] = mu;
-  rstd[c] = rs;
-  if (run_mean != nullptr) {
-    run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mu;
-    run_var[c] = (1.0f - momentum) * run_var[c] + momentum * var * unbias;
+// y = relu?(x * scale + shift (+ res)) with scale / shift derived from the per-channel sums (sum x, sum x^2): every block
+// first builds the table for all C channels in shared memory (C rsqrt per block instead of one per element), block 0 also
+// records mean / rstd and folds the batch statistics into the running ones - one launch for the whole normalisation.
+// Dynamic shared memory: 2 * C floats.
+__global__ void bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, bf16* __restrict__ y, long long total8, int C,
+                                int relu, const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                float inv_rows, float eps, float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ run_mean,
+                                float* __restrict__ run_var, long long* __restrict__ batches, float momentum, float unbias) {
+  extern __shared__ float s_coef[];                 // [scale (C), shift (C)]
+  if (blockIdx.x == 0 && threadIdx.x == 0 && batches != nullptr) *batches += 1;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float mu = sums[c] * inv_rows;
+    const float var = fmaxf(sums[C + c] * inv_rows - mu * mu, 0.f);
+    const float rs = rsqrtf(var + eps);
+    const float sc = gamma[c] * rs;
+    s_coef[c] = sc;
+    s_coef[C + c] = beta[c] - mu * sc;
+    if (blockIdx.x == 0) {
+      mean[c] = mu;
+      rstd[c] = rs;
+      if (run_mean != nullptr) {
+        run_mean[c] = (1.0f - momentum) * run_mean[c] + momentum * mu;
+        run_var[c] = (1.0f - momentum) * run_var[c] + momentum * var * unbias;
+      }
+    }
   }
-  const float sc = gamma[c] * rs;
-  coef[c] = sc;
-  coef[C + c] = beta[c] - mu * sc;
-}
-
-// y = relu?(x * scale + shift (+ res))
-__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ coef, const bf16* __restrict__ res, bf16* __restrict__ y,
-                                long long total8, int C, int relu) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total8) return;
-  const int c = (int)(idx % (C / 8)) * 8;
-  float v[8];
-  load8(x + idx * 8, v);
-  const float4 s0 = *reinterpret_cast<const float4*>(coef + c), s1 = *reinterpret_cast<const float4*>(coef + c + 4);
-  const float4 h0 = *reinterpret_cast<const float4*>(coef + C + c), h1 = *reinterpret_cast<const float4*>(coef + C + c + 4);
-  const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w}, sh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-  float rv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (res != nullptr) load8(res + idx * 8, rv);
+  __syncthreads();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += stride) {
+    const int c = (int)(idx % (C / 8)) * 8;
+    float v[8], rv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    load8(x + idx * 8, v);
+    if (res != nullptr) load8(res + idx * 8, rv);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float o = fmaf(v[j], sc[j], sh[j]) + rv[j];
-    v[j] = relu ? fmaxf(o, 0.f) : o;
+    for (int j = 0; j < 8; ++j) {
+      const float o = fmaf(v[j], s_coef[c + j], s_coef[C + c + j]) + rv[j];
+      v[j] = relu ? fmaxf(o, 0.f) : o;
+    }
+    store8(y + idx * 8, v);
   }
-  store8(y + idx * 8, v);
 }
 
 // Backward statistics: part[y][0][c] = sum dy', part[y][1][c] = sum dy' * xhat, dy' = dy masked by the ReLU (y > 0).
@@ -971,12 +968,33 @@ __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __r
 }
 
 // dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M) = A * dy' + B * x + K per channel; coef = [A (C), B (C), K (C)].
-__global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
-                                       const float* __restrict__ rstd, float* __restrict__ coef, float inv_rows, int C) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// Sums the row-chunk partials (part: [parts, 2, C]) first - 32 channels per block, eight warps splitting the chunks;
+// sums = [dbeta (C), dgamma (C)] is written, and added into dbeta_acc / dgamma_acc (the parameters' gradient buffers)
+// when those are given.
+__global__ void bn_bwd_finalize_kernel(const float* __restrict__ part, int parts, float* __restrict__ sums, const float* __restrict__ gamma,
+                                       const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ coef, float inv_rows,
+                                       int C, float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc) {
+  __shared__ float sm0[8][33], sm1[8][33];
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
+  float a0 = 0.f, a1 = 0.f;
+  if (c < C)
+    for (int r = w; r < parts; r += 8) {
+      a0 += part[((long long)r * 2 + 0) * C + c];
+      a1 += part[((long long)r * 2 + 1) * C + c];
+    }
+  sm0[w][threadIdx.x & 31] = a0;
+  sm1[w][threadIdx.x & 31] = a1;
+  __syncthreads();
+  if (w != 0 || c >= C) return;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { s0 += sm0[i][threadIdx.x]; s1 += sm1[i][threadIdx.x]; }
+  sums[c] = s0;
+  sums[C + c] = s1;
+  if (dbeta_acc != nullptr) dbeta_acc[c] += s0;
+  if (dgamma_acc != nullptr) dgamma_acc[c] += s1;
   const float a = gamma[c] * rstd[c];
-  const float k0 = sums[c] * inv_rows, k1 = sums[C + c] * inv_rows;
+  const float k0 = s0 * inv_rows, k1 = s1 * inv_rows;
   const float bx = -a * rstd[c] * k1;
   coef[c] = a;
   coef[C + c] = bx;
@@ -1274,26 +1292,30 @@ int bn_parts(int rows, int C) {
   return parts < 1 ? 1 : parts;
 }
 // part: [bn_parts, 2, C]; sums: [2, C]; coef: [2, C] (forward) or [3, C] (backward)
-// sums_given: `sums` already holds the per-channel sum and sum of squares (the convolution's epilogue produced them).
+// sums_given: `sums` already holds the per-channel sum and sum of squares (the convolution's epilogue produced them); the
+// whole normalisation is then one launch.
 void bn_fwd(const bf16* x, const float* gamma, const float* beta, const bf16* res, bf16* y, float* mean, float* rstd, float* part, float* sums,
             float* coef, int rows, int C, float eps, int relu, int sums_given, float* run_mean, float* run_var, long long* batches,
             float momentum, cudaStream_t st) {
+  const long long total8 = (long long)rows * (C / 8);
+  const float unbias = rows > 1 ? (float)rows / (float)(rows - 1) : 1.0f;
   if (!sums_given) {
     const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
     bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
     colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
   }
-  bn_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, beta, mean, rstd, coef, 1.0f / rows, C, eps, run_mean, run_var, batches,
-                                                         momentum, rows > 1 ? (float)rows / (float)(rows - 1) : 1.0f);
-  const long long total8 = (long long)rows * (C / 8);
-  bn_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(x, coef, res, y, total8, C, relu);
+  // a few elements per thread: the per-block table of 2 * C coefficients is amortised over at least 4 x 2048 elements
+  long long blocks = (total8 + 256 * 4 - 1) / (256 * 4);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  bn_apply_kernel<<<(int)(blocks < 1 ? 1 : blocks), 256, 2 * C * sizeof(float), st>>>(x, res, y, total8, C, relu, sums, gamma, beta, 1.0f / rows,
+                                                                                      eps, mean, rstd, run_mean, run_var, batches, momentum, unbias);
+  (void)coef;
 }
 void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx, bf16* dres,
-            float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st) {
+            float* part, float* sums, float* coef, int rows, int C, int relu, float* dgamma_acc, float* dbeta_acc, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
-  colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
-  bn_bwd_finalize_kernel<<<blocks_for(C, 128), 128, 0, st>>>(sums, gamma, mean, rstd, coef, 1.0f / rows, C);
+  bn_bwd_finalize_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, parts, sums, gamma, mean, rstd, coef, 1.0f / rows, C, dgamma_acc, dbeta_acc);
   const long long total8 = (long long)rows * (C / 8);
   bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
 }

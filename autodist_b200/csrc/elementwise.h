@@ -51,7 +51,7 @@ void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, const bf16_t
             float* sums, float* coef, int rows, int C, float eps, int relu, int sums_given, float* run_mean, float* run_var,
             long long* batches, float momentum, cudaStream_t st);
 void bn_bwd(const bf16_t* dy, const bf16_t* x, const bf16_t* y, const float* mean, const float* rstd, const float* gamma, bf16_t* dx,
-            bf16_t* dres, float* part, float* sums, float* coef, int rows, int C, int relu, cudaStream_t st);
+            bf16_t* dres, float* part, float* sums, float* coef, int rows, int C, int relu, float* dgamma_acc, float* dbeta_acc, cudaStream_t st);
 void maxpool_fwd(const bf16_t* x, bf16_t* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st);
 void maxpool_bwd(const uint8_t* code, const bf16_t* dy, bf16_t* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho,

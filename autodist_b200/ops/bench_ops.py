@@ -47,7 +47,7 @@ def _cnn_rows(E, dev, flush, hbm):
     rows.append({"kernel": "bn_fwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(3 * nbytes / ms / 1e6, 1),
                  "library_ms": round(ms_lib, 4), "frac_of_measured_peak": round(3 * nbytes / ms / 1e6 / hbm, 3)})
     dy, dx = torch.randn_like(xh), torch.empty_like(xh)
-    ms = _time(lambda: E.bn_bwd(dy, xh, y, mean, rstd, gamma, dx, None, True), flush=flush)
+    ms = _time(lambda: E.bn_bwd(dy, xh, y, mean, rstd, gamma, dx, None, True, None, None), flush=flush)
     rows.append({"kernel": "bn_bwd+relu 64x56x56x256", "ms": round(ms, 4), "gbs": round(7 * nbytes / ms / 1e6, 1),
                  "frac_of_measured_peak": round(7 * nbytes / ms / 1e6 / hbm, 3)})
     N, C, Hh, W = 64, 64, 112, 112                                   # the ResNet stem pool
@@ -85,14 +85,84 @@ def _cnn_rows(E, dev, flush, hbm):
     return rows
 
 
+# (label, batch, Cin, H = W, Cout, k, stride, pad): the distinct convolutions of ResNet-101 at 224 x 224, batch 64
+CONV_SHAPES = [("stem 7x7/2 3->64 @224", 64, 3, 224, 64, 7, 2, 3),
+               ("s1 1x1 64->64 @56", 64, 64, 56, 64, 1, 1, 0), ("s1 3x3 64->64 @56", 64, 64, 56, 64, 3, 1, 1),
+               ("s1 1x1 64->256 @56", 64, 64, 56, 256, 1, 1, 0), ("s1 1x1 256->64 @56", 64, 256, 56, 64, 1, 1, 0),
+               ("s2 1x1 256->128 @56", 64, 256, 56, 128, 1, 1, 0), ("s2 3x3/2 128->128 @56", 64, 128, 56, 128, 3, 2, 1),
+               ("s2 1x1/2 256->512 @56", 64, 256, 56, 512, 1, 2, 0), ("s2 3x3 128->128 @28", 64, 128, 28, 128, 3, 1, 1),
+               ("s2 1x1 128->512 @28", 64, 128, 28, 512, 1, 1, 0), ("s2 1x1 512->128 @28", 64, 512, 28, 128, 1, 1, 0),
+               ("s3 3x3/2 256->256 @28", 64, 256, 28, 256, 3, 2, 1), ("s3 3x3 256->256 @14", 64, 256, 14, 256, 3, 1, 1),
+               ("s3 1x1 256->1024 @14", 64, 256, 14, 1024, 1, 1, 0), ("s3 1x1 1024->256 @14", 64, 1024, 14, 256, 1, 1, 0),
+               ("s4 3x3/2 512->512 @14", 64, 512, 14, 512, 3, 2, 1), ("s4 3x3 512->512 @7", 64, 512, 7, 512, 3, 1, 1),
+               ("s4 1x1 512->2048 @7", 64, 512, 7, 2048, 1, 1, 0), ("s4 1x1 2048->512 @7", 64, 2048, 7, 512, 1, 1, 0),
+               ("vgg 3x3 64->64 @224 (batch 32)", 32, 64, 224, 64, 3, 1, 1), ("vgg 3x3 256->256 @56 (batch 32)", 32, 256, 56, 256, 3, 1, 1),
+               ("vgg 3x3 512->512 @28 (batch 32)", 32, 512, 28, 512, 3, 1, 1)]
+
+
+def _conv_rows(E, dev, flush, peaks, iters, only=""):
+    """Forward, input gradient and weight gradient of the implicit-GEMM convolution at the ResNet-101 / VGG-16 layer shapes,
+    beside the library convolution's forward pass (channels-last bf16). The roofline time of a layer is the slower of its
+    FLOPs at the measured GEMM peak and its algorithmic bytes (each operand once) at the measured copy bandwidth."""
+    import torch.nn.functional as F
+    from autodist_b200.ops import functional as Fn
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    peak, hbm = peaks.get("bf16_tflops", 1656.4), peaks.get("hbm_gbs", 6518.6)
+    rows = []
+    for label, n, cin, hw, cout, k, stride, pad in CONV_SHAPES:
+        if only and only not in label:
+            continue
+        oh = (hw + 2 * pad - k) // stride + 1
+        w = (torch.randn(cout, k, k, cin, device=dev) / (cin * k * k) ** 0.5).to(torch.bfloat16)
+        y = torch.empty(n, oh, oh, cout, dtype=torch.bfloat16, device=dev)
+        dy = torch.randn(n, oh, oh, cout, device=dev).to(torch.bfloat16)
+        flops = 2.0 * n * oh * oh * cout * cin * k * k
+        row = {"kernel": f"conv {label}", "gflop": round(flops / 1e9, 1)}
+        if cin % 8:
+            img = torch.randn(n, cin, hw, hw, device=dev)
+            _, _, hp, wp = Fn._rowtap_geometry(hw, hw, k, k, stride, pad)
+            xp = torch.empty(n, hp, wp, 8, dtype=torch.bfloat16, device=dev)
+            E.pad_image8(img, xp, pad)
+            wr = F.pad(F.pad(w, (0, 8 - cin)).reshape(cout, k, k * 8), (0, 64 - k * 8)).contiguous()
+            dwr = torch.empty(cout, k, 64, dtype=torch.float32, device=dev)
+            ops_ = {"fprop": lambda: E.conv_rowtap_fprop(xp, wr, y, None, False, None, stride, err),
+                    "wgrad": lambda: E.conv_rowtap_wgrad(dy, xp, dwr, stride, err)}
+            xl = img.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            act_bytes = xp.numel() * 2
+        else:
+            x = torch.randn(n, hw, hw, cin, device=dev).to(torch.bfloat16)
+            dx = torch.empty_like(x)
+            dw = torch.empty(cout, k, k, cin, dtype=torch.float32, device=dev)
+            ops_ = {"fprop": lambda: E.conv_fprop(x, w, y, None, False, None, stride, pad, err),
+                    "dgrad": lambda: E.conv_dgrad(dy, w, dx, stride, pad, err),
+                    "wgrad": lambda: E.conv_wgrad(dy, x, dw, stride, pad, err, False)}
+            xl = x.permute(0, 3, 1, 2)
+            act_bytes = x.numel() * 2
+        nbytes = act_bytes + y.numel() * 2 + w.numel() * 2
+        roof_ms = max(flops / (peak * 1e9), nbytes / (hbm * 1e6))
+        for name, fn in ops_.items():
+            ms = _time(fn, iters=iters, flush=flush)
+            row[name + "_us"] = round(ms * 1e3, 1)
+            row[name + "_tflops"] = round(flops / ms / 1e9, 1)
+            row[name + "_frac_of_roofline"] = round(roof_ms / ms, 3)
+        wl = w.permute(0, 3, 1, 2)
+        ms = _time(lambda: F.conv2d(xl, wl, None, stride, pad), iters=iters, flush=flush)
+        row["library_fprop_us"] = round(ms * 1e3, 1)
+        row["roofline_us"] = round(roof_ms * 1e3, 1)
+        rows.append(row)
+    assert err.item() == 0, f"a convolution kernel gave up waiting (code {err.item()})"
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default="", help="run only the GEMM shapes whose label contains this text")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--group", default="all", choices=["all", "gemm", "bert", "cnn"],
-                    help="gemm: GEMM shapes; bert: LayerNorm / Adam; cnn: batch-norm, max-pool, row gather, sparse-row update")
+    ap.add_argument("--group", default="all", choices=["all", "gemm", "bert", "cnn", "conv"],
+                    help="gemm: GEMM shapes; bert: LayerNorm / Adam; cnn: batch-norm, max-pool, row gather, sparse-row update; "
+                         "conv: implicit-GEMM convolution at the ResNet-101 / VGG-16 layer shapes")
     args = ap.parse_args()
     from autodist_b200 import ops
     E = ops.ext(required=True)
@@ -114,6 +184,14 @@ def main():
         shapes = shapes[:2]
     if args.only:
         shapes = [s for s in shapes if args.only in s[0]]
+    if args.group == "conv":
+        rows = _conv_rows(E, dev, flush, peaks, args.iters, args.only)
+        for r in rows:
+            print(json.dumps(r))
+        if args.json:
+            with open(args.json, "w") as f:
+                json.dump(rows, f, indent=1)
+        return
     if args.group in ("bert", "cnn"):
         shapes = []
     for name, M, N, K, a_mn, b_mn in shapes:

@@ -33,7 +33,7 @@ class _LinearFn(torch.autograd.Function):
         E = ops.ext(required=True)
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16).contiguous()
-        w16 = weight.to(torch.bfloat16).contiguous()
+        w16 = _bf16_weight(weight)
         y = torch.empty(x2.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)
         err = _error_flag(x.device)
         pre = None
@@ -47,6 +47,8 @@ class _LinearFn(torch.autograd.Function):
         else:
             E.gemm(x2, w16, y, False, False, 0, None, None, None, 1.0, 0.0, err, 0)
         ctx.save_for_backward(x2, w16, pre)
+        ctx.weight = weight
+        _count_use(ctx, weight, 1)
         ctx.has_bias = bias is not None
         ctx.shape = shape
         ctx.w_dtype = weight.dtype
@@ -64,8 +66,13 @@ class _LinearFn(torch.autograd.Function):
             dy2 = du
         dx = torch.empty_like(x2)
         E.gemm(dy2, w16, dx, False, True, 0, None, None, None, 1.0, 0.0, err, 0)          # dX = dY . W
-        dw = torch.empty(w16.shape, dtype=torch.float32, device=dy.device)
-        E.gemm(dy2, x2, dw, True, True, 0, None, None, None, 1.0, 0.0, err, 0)            # dW = dY^T . X
+        acc = _direct_grad(ctx.weight)
+        if acc is not None:
+            E.gemm(dy2, x2, acc, True, True, 0, None, None, None, 1.0, 1.0, err, 0)       # dW += dY^T . X, in the gradient buffer
+            dw = None
+        else:
+            dw = torch.empty(w16.shape, dtype=torch.float32, device=dy.device)
+            E.gemm(dy2, x2, dw, True, True, 0, None, None, None, 1.0, 0.0, err, 0)        # dW = dY^T . X
         db = None
         if ctx.has_bias:
             n = dy2.shape[1]
@@ -75,7 +82,9 @@ class _LinearFn(torch.autograd.Function):
                 E.keyed_colsum(dy2, None, part, db, 1, False)
             else:
                 db = dy2.float().sum(0)
-        return dx.view(ctx.shape).to(dy.dtype), dw.to(ctx.w_dtype), db, None
+        if dw is None:
+            _grad_written(ctx.weight)
+        return dx.view(ctx.shape).to(dy.dtype), None if dw is None else dw.to(ctx.w_dtype), db, None
 
 
 def linear(x, weight, bias=None, activation=None):
@@ -154,6 +163,29 @@ def _bf16_weight(weight):
     return weight.detach().to(torch.bfloat16).contiguous()
 
 
+def _direct_grad(param):
+    """The fp32 gradient buffer of ``param`` when its owner (a flat-buffer engine) asked for gradients to be accumulated
+    in place by the producing kernel instead of travelling through autograd's accumulation; else ``None``."""
+    g = getattr(param, "grad", None)
+    if getattr(param, "_direct_grad", False) and g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.is_cuda:
+        return g
+    return None
+
+
+def _count_use(ctx, param, index):
+    """Forward side of the direct accumulation: remember that one more kernel call will add into ``param``'s gradient."""
+    if ctx.needs_input_grad[index] and getattr(param, "_direct_grad", False):
+        param._pending_uses = getattr(param, "_pending_uses", 0) + 1
+
+
+def _grad_written(param):
+    """Backward side: one pending call has added its part; after the last one tell the owner that the gradient is final."""
+    param._pending_uses = getattr(param, "_pending_uses", 1) - 1
+    hook = getattr(param, "_grad_ready_hook", None)
+    if hook is not None and param._pending_uses <= 0:
+        hook(param)
+
+
 def _colsum(E, dy2):
     n = dy2.shape[1]
     db = torch.empty(n, dtype=torch.float32, device=dy2.device)
@@ -199,6 +231,8 @@ class _ConvFn(torch.autograd.Function):
             y = torch.empty(n, oh, ow, cout, dtype=torch.bfloat16, device=x.device)
             E.conv_fprop(xh, w16, y, b32, relu, stats, stride, padding, err)
         ctx.save_for_backward(xh, w16, y if relu else None)
+        ctx.weight = weight
+        _count_use(ctx, weight, 1)
         ctx.geom = (stride, padding, tuple(weight.shape), tuple(x.shape))
         ctx.has_bias = bias is not None
         ctx.dtypes = (x.dtype, weight.dtype)
@@ -224,8 +258,13 @@ class _ConvFn(torch.autograd.Function):
                 w_oihw = w16.float().permute(0, 3, 1, 2)
                 dx = torch.nn.grad.conv2d_input(x_shape, w_oihw, dy.float(), stride, padding).to(ctx.dtypes[0])
         else:
-            dw = torch.empty(cout, kh, kw, cin, dtype=torch.float32, device=dy.device)
-            E.conv_wgrad(dyh, xh, dw, stride, padding, err)
+            acc = _direct_grad(ctx.weight)
+            if acc is not None:
+                E.conv_wgrad(dyh, xh, acc, stride, padding, err, True)       # split-K atomics land in the parameter's gradient buffer
+                dw = None
+            else:
+                dw = torch.empty(cout, kh, kw, cin, dtype=torch.float32, device=dy.device)
+                E.conv_wgrad(dyh, xh, dw, stride, padding, err, False)
             if ctx.needs_input_grad[0]:
                 dxh = torch.empty_like(xh)
                 E.conv_dgrad(dyh, w16, dxh, stride, padding, err)
@@ -233,7 +272,9 @@ class _ConvFn(torch.autograd.Function):
         db = None
         if ctx.has_bias:
             db = _colsum(E, dyh.view(-1, cout))
-        return dx, dw.to(ctx.dtypes[1]), db, None, None, None, None
+        if dw is None:
+            _grad_written(ctx.weight)
+        return dx, None if dw is None else dw.to(ctx.dtypes[1]), db, None, None, None, None
 
 
 def conv2d(x, weight, bias=None, stride=1, padding=0, relu=False, stats=None):
@@ -275,6 +316,10 @@ class _BatchNormFn(torch.autograd.Function):
         res = _nhwc(residual) if residual is not None else None
         E.bn_fwd(xh, g32, b32, res, y, mean, rstd, eps, relu, sums, run_mean, run_var, batches, momentum)
         ctx.save_for_backward(xh, y, mean, rstd, g32)
+        ctx.params = (gamma, beta)
+        ctx.set_materialize_grads(False)                     # mean / rstd carry no gradient: no zero tensors for them
+        _count_use(ctx, gamma, 1)
+        _count_use(ctx, beta, 2)
         ctx.relu = relu
         ctx.has_res = residual is not None
         ctx.dtypes = (x.dtype, gamma.dtype, residual.dtype if residual is not None else None)
@@ -285,13 +330,23 @@ class _BatchNormFn(torch.autograd.Function):
     def backward(ctx, dy, _dm, _dr):
         E = ops.ext(required=True)
         xh, y, mean, rstd, g32 = ctx.saved_tensors
+        if dy is None:
+            return (None,) * 8
         dyh = _nhwc(dy)
         dx = torch.empty_like(xh)
         dres = None
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = torch.empty_like(xh) if ctx.relu else dyh                    # without a ReLU the residual gradient is dy itself
-        sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, dres if ctx.relu else None, ctx.relu)
+        gamma, beta = ctx.params
+        acc_g, acc_b = _direct_grad(gamma), _direct_grad(beta)
+        direct = acc_g is not None and acc_b is not None
+        sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, dres if ctx.relu else None, ctx.relu, acc_g if direct else None,
+                        acc_b if direct else None)
         dr = dres.permute(0, 3, 1, 2).to(ctx.dtypes[2]) if dres is not None else None
+        if direct:
+            _grad_written(gamma)
+            _grad_written(beta)
+            return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), None, None, dr, None, None, None, None
         return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), dr, None, None, None, None
 
 

@@ -736,16 +736,24 @@ class FlatAutogradEngine(FusedStepEngine):
             members.append(name)
             lo = fl.offsets[name]
             if hi - lo >= limit or name == names[0]:
-                self._flights.append({"lo": lo, "hi": hi, "need": len(members), "have": 0, "sent": False})
+                self._flights.append({"lo": lo, "hi": hi, "need": len(members), "have": 0, "sent": False, "seen": set()})
                 for m in members:
                     self._flight_of[m] = len(self._flights) - 1
                 members, hi = [], lo
         for name, p in zip(fl.names, fl.params):
-            p.register_post_accumulate_grad_hook(self._make_hook(name))
+            hook = self._make_hook(name)
+            p.register_post_accumulate_grad_hook(hook)
+            # kernels that add a gradient straight into the flat buffer (weight-gradient GEMMs, batch-norm parameter sums)
+            # bypass autograd's accumulation and report completion through this attribute instead
+            p._direct_grad = os.environ.get("AUTODIST_DIRECT_GRAD", "1") == "1"
+            p._grad_ready_hook = hook
 
     def _make_hook(self, name):
         def hook(param):
             f = self._flights[self._flight_of[name]]
+            if name in f["seen"]:
+                return          # a directly accumulated gradient may be reported by its kernel's wrapper and by autograd
+            f["seen"].add(name)
             f["have"] += 1
             if f["have"] == f["need"] and not f["sent"]:
                 f["sent"] = True
@@ -762,8 +770,10 @@ class FlatAutogradEngine(FusedStepEngine):
         fl.grad.zero_()
         for f in self._flights:
             f["have"], f["sent"] = 0, False
+            f["seen"].clear()
         for name, p in zip(fl.names, fl.params):
             p.grad = fl.g[name]                      # autograd adds into the flat views in place
+            p._pending_uses = 0
         values = self.forward(all_nodes, feeds, grad=True)
         values[all_nodes.index(train_op.loss_node)].backward()
         for f in self._flights:                      # parameters that received no gradient this step: still synchronised

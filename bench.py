@@ -232,7 +232,7 @@ def main():
         else "synthetic (Zipf(1.1) token ids over the 793471-word vocabulary, random-init weights)" if is_lm else "synthetic (images ~ N(0,1), uniform labels over 1000 classes, random-init weights)",
         "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq if is_bert else (cfg.num_steps if is_lm else None),
                    "max_predictions": max_pred if is_bert else None,
-                   "compute": "hand-written sm_100a kernels" if is_bert else "tcgen05 GEMM + own LSTM-cell / gather kernels, autograd glue" if is_lm else "cuDNN convolutions (library) + own batch-norm / ReLU / max-pool kernels + tcgen05 GEMM for fully connected layers",
+                   "compute": "hand-written sm_100a kernels" if is_bert else "tcgen05 GEMM + own LSTM-cell / gather kernels, autograd glue" if is_lm else "tcgen05 implicit-GEMM convolutions (forward, dgrad, wgrad) + own batch-norm / ReLU / max-pool kernels + tcgen05 GEMM for fully connected layers" if os.environ.get("AUTODIST_CONV", "own") != "library" else "library convolutions + own batch-norm / ReLU / max-pool kernels + tcgen05 GEMM for fully connected layers",
                    "parallelism": f"dp{n_gpus}", "strategy": args.strategy, "optimizer": "Adam, fp32 master + bf16 compute" if is_bert else "Adagrad 0.2, LSTM gradients clipped at norm 10" if is_lm else "SGD momentum 0.9, fp32 master + bf16 autocast",
                    "comm": os.environ.get("AUTODIST_COMM", "fused"),
                    "cuda_graph": os.environ.get("AUTODIST_CUDA_GRAPH", "1") != "0",
