@@ -418,6 +418,18 @@ void pad_image8(const Tensor& x, Tensor xp, int64_t pad) {
   adb200::pad_image8(x.data_ptr(), x.scalar_type() == at::kFloat ? 1 : 0, x.stride(0), x.stride(1), x.stride(2), x.stride(3), x.size(0),
                      x.size(1), x.size(2), x.size(3), BF(xp), xp.size(1), xp.size(2), (int)pad, STREAM);
 }
+// Bias gradient of a convolution over channels-last dy [.., C]: out (fp32 [C]) = column sums of dy, or of dy masked by y > 0
+// when the convolution had a fused ReLU, in which case the masked gradient is also written to dx. accumulate: out += sums.
+void relu_bwd_colsum(const Tensor& dy, const optional<Tensor>& y, const optional<Tensor>& dx, Tensor out, bool accumulate) {
+  const int C = dy.size(-1), rows = dy.numel() / C;
+  TORCH_CHECK(C % 8 == 0 && dy.is_contiguous() && dy.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kFloat && out.numel() == C &&
+              out.is_contiguous(), "dy must be contiguous bf16 [.., C] (C % 8 == 0), out fp32 [C]");
+  TORCH_CHECK(y.has_value() == dx.has_value(), "y and dx come together");
+  if (y.has_value()) TORCH_CHECK(y->is_contiguous() && dx->is_contiguous() && y->numel() == dy.numel() && dx->numel() == dy.numel(), "y, dx must match dy");
+  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * C}, dy.options().dtype(at::kFloat));
+  adb200::relu_bwd_colsum(CBF(dy), y.has_value() ? CBF(*y) : nullptr, dx.has_value() ? BF(*dx) : nullptr, part.data_ptr<float>(),
+                          out.data_ptr<float>(), rows, C, accumulate ? 1 : 0, STREAM);
+}
 void relu_bwd(const Tensor& dy, const Tensor& y, Tensor dx) {
   TORCH_CHECK(dy.is_contiguous() && y.is_contiguous() && dx.is_contiguous() && dy.numel() == y.numel() && dx.numel() == y.numel() && y.numel() % 8 == 0,
               "contiguous bf16 tensors of one size (a multiple of 8)");
@@ -552,6 +564,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("col2im", &col2im);
   m.def("pad_image8", &pad_image8);
   m.def("relu_bwd", &relu_bwd);
+  m.def("relu_bwd_colsum", &relu_bwd_colsum);
   m.def("psgd_p", &psgd_p);
   m.def("psgd_q", &psgd_q);
   m.def("psgd_d", &psgd_d);

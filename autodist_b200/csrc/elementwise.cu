@@ -877,6 +877,51 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
   }
 }
 
+// Bias gradient of a convolution (+ ReLU backward): dx = dy masked by y > 0 (when y is given), part[chunk][c] = sum of dx over
+// the chunk's rows. Channels-last matrix [rows, C]; 64 channels per block column, four 16-byte loads in flight per thread.
+__global__ void relu_bwd_colsum_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, float* __restrict__ part,
+                                       int rows, int C, int rows_per_block) {
+  __shared__ float s1[32][65];
+  const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + vec * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < C)
+    for (int r = r0 + rl; r < r1; r += 128) {
+      float v[4][8], m[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 32 * u;
+        if (rr < r1) {
+          load8(dy + (long long)rr * C + c, v[u]);
+          if (y != nullptr) load8(y + (long long)rr * C + c, m[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { v[u][i] = 0.f; m[u][i] = 1.f; }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 32 * u;
+        if (y != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[u][i] = m[u][i] > 0.f ? v[u][i] : 0.f;
+          if (rr < r1) store8(dx + (long long)rr * C + c, v[u]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] += v[u][i];
+      }
+    }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s1[rl][vec * 8 + i] = a[i];
+  __syncthreads();
+  if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < C) {
+    float t1 = 0.f;
+    for (int i = 0; i < 32; ++i) t1 += s1[i][threadIdx.x];
+    part[(long long)blockIdx.y * C + blockIdx.x * 64 + threadIdx.x] = t1;
+  }
+}
+
 // y = relu?(x * scale + shift (+ res)) with scale / shift derived from the per-channel sums (sum x, sum x^2): every block
 // first builds the table for all C channels in shared memory (C rsqrt per block instead of one per element), block 0 also
 // records mean / rstd and folds the batch statistics into the running ones - one launch for the whole normalisation.
@@ -1318,6 +1363,12 @@ void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, con
   bn_bwd_finalize_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, parts, sums, gamma, mean, rstd, coef, 1.0f / rows, C, dgamma_acc, dbeta_acc);
   const long long total8 = (long long)rows * (C / 8);
   bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
+}
+// dx = relu'(y) * dy (skipped when y is null) and out[c] (+)= column sums of dx. part: [bn_parts(rows, C), C] floats.
+void relu_bwd_colsum(const bf16* dy, const bf16* y, bf16* dx, float* part, float* out, int rows, int C, int accumulate, cudaStream_t st) {
+  const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
+  relu_bwd_colsum_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, y, dx, part, rows, C, rpb);
+  colsum_f32_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, out, parts, C, accumulate);
 }
 void maxpool_fwd(const bf16* x, bf16* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st) {

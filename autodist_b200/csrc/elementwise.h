@@ -60,6 +60,8 @@ void im2col(const bf16_t* x, bf16_t* cols, int N, int H, int W, int C, int KH, i
 void col2im(const bf16_t* dcols, bf16_t* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st);
 void pad_image8(const void* x, int is_fp32, long long sn, long long sc, long long sh, long long sw, int N, int C, int H, int W, bf16_t* xp,
                 int Hp, int Wp, int pad, cudaStream_t st);
+void relu_bwd_colsum(const bf16_t* dy, const bf16_t* y, bf16_t* dx, float* part, float* out, int rows, int C, int accumulate,
+                     cudaStream_t st);
 void relu_bwd(const bf16_t* dy, const bf16_t* y, bf16_t* dx, long long n, cudaStream_t st);
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st);
 void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st);

@@ -282,8 +282,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
         if (p.c_is_fp32) {
           float* dst = reinterpret_cast<float*>(p.C) + coff + col0;
           if (p.beta != 0.0f) {
+            if (ncols == 16 && (p.ldc % 4 == 0)) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) if (j < ncols) dst[j] += v[j];
+              for (int j = 0; j < 16; j += 4) {
+                float4 o = *reinterpret_cast<float4*>(dst + j);
+                o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) if (j < ncols) dst[j] += v[j];
+            }
           } else if (ncols == 16 && (p.ldc % 4 == 0)) {
 #pragma unroll
             for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);

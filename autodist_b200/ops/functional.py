@@ -231,8 +231,10 @@ class _ConvFn(torch.autograd.Function):
             y = torch.empty(n, oh, ow, cout, dtype=torch.bfloat16, device=x.device)
             E.conv_fprop(xh, w16, y, b32, relu, stats, stride, padding, err)
         ctx.save_for_backward(xh, w16, y if relu else None)
-        ctx.weight = weight
+        ctx.weight, ctx.bias = weight, bias
         _count_use(ctx, weight, 1)
+        if bias is not None:
+            _count_use(ctx, bias, 2)
         ctx.geom = (stride, padding, tuple(weight.shape), tuple(x.shape))
         ctx.has_bias = bias is not None
         ctx.dtypes = (x.dtype, weight.dtype)
@@ -245,7 +247,16 @@ class _ConvFn(torch.autograd.Function):
         stride, padding, (cout, kh, kw, cin), x_shape = ctx.geom
         err = _error_flag(dy.device)
         dyh = _nhwc(dy)
-        if y is not None:
+        db = None
+        bias = ctx.bias
+        acc_b = _direct_grad(bias) if bias is not None else None
+        if bias is not None:
+            # bias gradient (and the ReLU mask) in one pass over dy
+            db = acc_b if acc_b is not None else torch.empty(cout, dtype=torch.float32, device=dy.device)
+            masked = torch.empty_like(dyh) if y is not None else None
+            E.relu_bwd_colsum(dyh, y, masked, db, acc_b is not None)
+            dyh = masked if masked is not None else dyh
+        elif y is not None:
             masked = torch.empty_like(dyh)
             E.relu_bwd(dyh, y, masked)
             dyh = masked
@@ -269,11 +280,11 @@ class _ConvFn(torch.autograd.Function):
                 dxh = torch.empty_like(xh)
                 E.conv_dgrad(dyh, w16, dxh, stride, padding, err)
                 dx = dxh.permute(0, 3, 1, 2).to(ctx.dtypes[0])
-        db = None
-        if ctx.has_bias:
-            db = _colsum(E, dyh.view(-1, cout))
         if dw is None:
             _grad_written(ctx.weight)
+        if acc_b is not None:
+            _grad_written(bias)
+            db = None
         return dx, None if dw is None else dw.to(ctx.dtypes[1]), db, None, None, None, None
 
 
