@@ -242,9 +242,13 @@ void ln_bwd(const Tensor& dy, const Tensor& z, const Tensor& mean, const Tensor&
                  OPT_BF(dx), part.data_ptr<float>(), part.data_ptr<float>() + (long long)blocks * H, dgamma.data_ptr<float>(),
                  dbeta.data_ptr<float>(), rows, H, (float)p_drop, (uint64_t)seed, OPT_LL(step), accumulate ? 1 : 0, STREAM);
 }
-void embed_sum(const Tensor& word, const Tensor& pos, const Tensor& type, const Tensor& ids, const optional<Tensor>& tt, Tensor z, int64_t S) {
+// error_flag (optional int32 [1]) is set to 21 when an id lies outside its table; such a row reads row 0.
+void embed_sum(const Tensor& word, const Tensor& pos, const Tensor& type, const Tensor& ids, const optional<Tensor>& tt, Tensor z, int64_t S,
+               const optional<Tensor>& error_flag) {
   const int H = word.size(1), rows = ids.numel();
-  adb200::embed_sum(CBF(word), CBF(pos), CBF(type), ids.data_ptr<int64_t>(), OPT_I64(tt), BF(z), rows, (int)S, H, STREAM);
+  TORCH_CHECK(pos.size(0) >= S, "position table shorter than the sequence");
+  adb200::embed_sum(CBF(word), CBF(pos), CBF(type), ids.data_ptr<int64_t>(), OPT_I64(tt), BF(z), rows, (int)S, H, word.size(0), type.size(0),
+                    error_flag.has_value() ? error_flag->data_ptr<int>() : nullptr, STREAM);
 }
 void scatter_add_rows(Tensor dst, const Tensor& idx, const Tensor& src, double scale) {
   adb200::scatter_add_rows(dst.data_ptr<float>(), idx.data_ptr<int64_t>(), CBF(src), idx.numel(), src.size(-1), (float)scale, STREAM);
@@ -519,6 +523,7 @@ void embedding_gather_peers(const Tensor& flag_ptrs, Tensor epochs, Tensor error
 
 void sym_barrier(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s, int64_t blocks) {
   adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
+  TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "block count must be in [1, ", adb200::kMaxCommBlocks, "]");
   adb200::launch_barrier(c, (int)blocks, STREAM);
 }
 

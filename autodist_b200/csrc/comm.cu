@@ -358,8 +358,13 @@ __global__ void sparse_scatter_add_kernel(SymCtx c, float* const* shard, const i
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (long long r = warp; r < nrows; r += nwarp) {
+    const long long id = ids[r];
+    if ((unsigned long long)id >= (unsigned long long)V) {       // a bad id must not become a write into a peer's memory
+      if (lane == 0) atomicExch(c.error, 301);
+      continue;
+    }
     int owner; long long local;
-    owner_of(ids[r], V, c.world, owner, local);
+    owner_of(id, V, c.world, owner, local);
     float* dst = shard[owner] + local * H;
     for (int col = lane * 4; col < H; col += 128) {
       float4 v;
@@ -382,8 +387,14 @@ __global__ void embedding_gather_peers_kernel(SymCtx c, __nv_bfloat16* const* sh
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (long long r = warp; r < nrows; r += nwarp) {
+    const long long id = ids[r];
+    if ((unsigned long long)id >= (unsigned long long)V) {       // a bad id reads nothing: its row is zero and the error is recorded
+      if (lane == 0) atomicExch(c.error, 302);
+      for (int col = lane * 8; col < H; col += 256) *reinterpret_cast<uint4*>(out + r * H + col) = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
     int owner; long long local;
-    owner_of(ids[r], V, c.world, owner, local);
+    owner_of(id, V, c.world, owner, local);
     const __nv_bfloat16* src = shard[owner] + local * H;
     for (int col = lane * 8; col < H; col += 256)
       *reinterpret_cast<uint4*>(out + r * H + col) = *reinterpret_cast<const uint4*>(src + col);

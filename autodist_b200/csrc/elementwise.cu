@@ -256,10 +256,15 @@ __global__ void colsum2_f32_kernel(const float* __restrict__ part_a, float* __re
 // z[row] = word[ids[row]] + pos[row % S] + type[tt[row]]  (bf16 tables), then the layernorm kernel runs on z.
 __global__ void embed_sum_kernel(const bf16* __restrict__ word, const bf16* __restrict__ pos, const bf16* __restrict__ type,
                                  const int64_t* __restrict__ ids, const int64_t* __restrict__ tt, bf16* __restrict__ z,
-                                 int rows, int S, int H) {
+                                 int rows, int S, int H, long long V, long long types, int* __restrict__ error) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
-  const long long w = ids[warp], t = tt ? tt[warp] : 0;
+  long long w = ids[warp], t = tt ? tt[warp] : 0;
+  if ((unsigned long long)w >= (unsigned long long)V || (unsigned long long)t >= (unsigned long long)types) {
+    // ids outside the tables read row 0 instead of foreign memory; the step is reported as failed
+    if (lane == 0 && error != nullptr) atomicExch(error, 21);
+    w = 0; t = 0;
+  }
   const int s = warp % S;
   for (int vec = lane; vec < H / 8; vec += 32) {
     float a[8], b[8], c[8];
@@ -1224,8 +1229,8 @@ void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd,
   colsum2_f32_kernel<<<dim3(blocks_for(H, 32), 2), 256, 0, st>>>(part_g, dgamma, part_b, dbeta, blocks, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
-               int H, cudaStream_t st) {
-  embed_sum_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(word, pos, type, ids, tt, z, rows, S, H);
+               int H, long long V, long long types, int* error, cudaStream_t st) {
+  embed_sum_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(word, pos, type, ids, tt, z, rows, S, H, V, types, error);
 }
 void scatter_add_rows(float* dst, const int64_t* idx, const bf16* src, int rows, int H, float scale, cudaStream_t st) {
   scatter_add_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H, scale);

@@ -13,7 +13,7 @@ void ln_bwd(const bf16_t* dy, const bf16_t* z, const float* mean, const float* r
             bf16_t* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
             const long long* step, int accumulate, cudaStream_t st);
 void embed_sum(const bf16_t* word, const bf16_t* pos, const bf16_t* type, const int64_t* ids, const int64_t* tt, bf16_t* z, int rows, int S,
-               int H, cudaStream_t st);
+               int H, long long V, long long types, int* error, cudaStream_t st);
 void scatter_add_rows(float* dst, const int64_t* idx, const bf16_t* src, int rows, int H, float scale, cudaStream_t st);
 void strided_rowsum(const bf16_t* x, float* out, int keys, int stride, int count, int H, cudaStream_t st);
 int colsum_parts(int rows);

@@ -268,9 +268,9 @@ class BertPretrainer(nn.Module):
         if self._word_lookup_hook is not None:
             # sharded table: the rows of this batch are fetched from the shards that own them (peer memory)
             rows = self._word_lookup_hook(ids)
-            E.embed_sum(rows, w16["emb.pos"], w16["emb.tok_type"], ws["row_index"], tts, ws["z0"], S)
+            E.embed_sum(rows, w16["emb.pos"], w16["emb.tok_type"], ws["row_index"], tts, ws["z0"], S, ws["err"])
         else:
-            E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S)
+            E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S, ws["err"])
         E.ln_fwd(ws["z0"], None, w32["emb.ln_g"], w32["emb.ln_b"], None, ws["x0"], ws["m0"], ws["r0"], eps, 0.0, 0, None)
         x = ws["x0"]
         for l, A in enumerate(ws["layers"]):
@@ -411,7 +411,8 @@ class BertPretrainer(nn.Module):
         if self._ws is not None:
             code = int(self._ws["err"].item())
             if code:
-                raise RuntimeError(f"a GEMM kernel gave up waiting (code {code})")
+                what = "an input id lies outside its embedding table" if code == 21 else "a GEMM kernel gave up waiting"
+                raise RuntimeError(f"{what} (code {code})")
 
 
 class _FusedBertFn(torch.autograd.Function):

@@ -51,8 +51,11 @@ def ext(required=None):
     if not _TRIED or required:
         _TRIED = True
         path = _build.so_path()
-        if not os.path.exists(path) and required:
-            path = _build.build()
+        stale = os.path.exists(path) and not _build.is_current()
+        if (not os.path.exists(path) or stale) and required:
+            path = _build.build()              # rebuilds when the sources changed since the shared object was made
+        elif stale:
+            raise RuntimeError("the sm_100a extension is older than its sources: run `python -m autodist_b200.ops.build`")
         if os.path.exists(path):
             spec = importlib.util.spec_from_file_location(_build.NAME, path)
             mod = importlib.util.module_from_spec(spec)

@@ -168,9 +168,21 @@ class SymmetricArena:
             return (self.flag_ptrs_b, self.epochs_b, self.error, self.rank, self.world, self.timeout_s)
         return (self.flag_ptrs, self.epochs, self.error, self.rank, self.world, self.timeout_s)
 
+    def reset_error(self):
+        """Clear a recorded time-out and the words of the in-rank block barrier: a barrier that gave up leaves its arrival
+        count behind, which would make the next launch on that channel miscount."""
+        torch.cuda.synchronize()
+        self.error.zero_()
+        n = self.E.MAX_COMM_BLOCKS
+        self.epochs[n:n + 2].zero_()
+        self.epochs_b[n:n + 2].zero_()
+
     def check(self):
         code = int(self.error.item())
         if code:
+            if code in (301, 302):
+                raise RuntimeError(f"rank {self.rank}: a row id outside the sharded table reached the "
+                                   f"{'scatter-add' if code == 301 else 'gather'} kernel (code {code}); the row was skipped")
             raise RuntimeError(f"rank {self.rank}: a communication kernel gave up waiting for a peer (code {code})")
 
 
@@ -647,6 +659,20 @@ class FusedStepEngine(StepEngine):
                 key = f"{full}/{slot}"
                 if buf is not None and key in slots:
                     buf[o:o + n].copy_(slots[key].reshape(-1).to(self.device))
+        # Slots of parameter-server segments live with their owners, slots of a row-sharded table with the owner of each
+        # row block: copy this rank's parts out of the full-size buffers just filled.
+        for st_, ln, ow in getattr(self, "ps_segments", []):
+            if ow == self.rank:
+                o = self._state_offset[st_]
+                for owned, full_buf in ((self.ps_s1, self.slot1), (self.ps_s2, self.slot2)):
+                    if owned is not None and full_buf is not None:
+                        owned[o:o + ln].copy_(full_buf[st_:st_ + ln])
+        for st in getattr(self, "sharded_rows", {}).values():
+            base = self.flat.offsets[st["name"]] + st["off"] * st["H"]
+            n = st["rows"] * st["H"]
+            for owned, full_buf in ((st["s1"], self.slot1), (st["s2"], self.slot2)):
+                if owned is not None and full_buf is not None:
+                    owned.copy_(full_buf[base:base + n])
         self.opt_step.fill_(int(default_step))
 
     def after_restore(self):

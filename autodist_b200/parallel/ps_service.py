@@ -25,15 +25,39 @@ import torch
 
 from autodist_b200.utils import logging
 
-_AUTHKEY = b"autodist-b200-ps"
-
-
 def _base_port():
     return int(os.environ.get("MASTER_PORT", "29500")) + 101
 
 
-def _address(owner):
-    return (os.environ.get("MASTER_ADDR", "127.0.0.1"), _base_port() + owner)
+def _own_host(single_node):
+    """Address this rank's listener binds to: loopback when every rank runs on this machine, else this node's own address
+    (``AUTODIST_NODE_ADDR``, or what the host name resolves to) - never the chief's address on another node."""
+    if single_node:
+        return "127.0.0.1"
+    addr = os.environ.get("AUTODIST_NODE_ADDR")
+    if addr:
+        return addr
+    import socket
+    return socket.gethostbyname(socket.gethostname())
+
+
+def _job_secrets(engine):
+    """(authentication key, host of every rank), agreed over the job's process group.
+
+    The connections carry pickles, so the key must not be guessable: rank 0 draws 32 random bytes per job and the
+    process group (already restricted to the job's ranks) hands them to the others. A single process needs none."""
+    import torch.distributed as dist
+    world = engine.world_size
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+    single_node = local_world >= world
+    if world <= 1 or not dist.is_initialized():
+        return os.urandom(32), {0: "127.0.0.1"}
+    group = getattr(engine.backend, "group", None)
+    box = [os.urandom(32) if engine.rank == 0 else None]
+    dist.broadcast_object_list(box, src=0, group=group)
+    hosts = [None] * world
+    dist.all_gather_object(hosts, _own_host(single_node), group=group)
+    return box[0], dict(enumerate(hosts))
 
 
 class StepClocks:
@@ -70,13 +94,13 @@ class StepClocks:
 class PSServer(threading.Thread):
     """Owner-side service: applies pushed gradients, serves pulls, keeps the clocks (lowest owner only)."""
 
-    def __init__(self, engine, owner, ranks, keeps_clocks):
+    def __init__(self, engine, owner, ranks, keeps_clocks, host="127.0.0.1", authkey=None):
         super().__init__(daemon=True, name=f"ps-server-{owner}")
         self.engine = engine
         self.owner = owner
         self.lock = threading.Lock()
         self.clocks = StepClocks(ranks) if keeps_clocks else None
-        self.listener = Listener(_address(owner), authkey=_AUTHKEY)
+        self.listener = Listener((host, _base_port() + owner), authkey=authkey)
         self._stop = False
         self.pushes_applied = 0
 
@@ -140,11 +164,13 @@ class RelaxedPSClient:
         self.server = None
         self.last_lead = 0
         self.max_lead = 0
+        authkey, hosts = _job_secrets(engine)
         if self.rank in self.owners:
-            self.server = PSServer(engine, self.rank, range(engine.world_size), self.rank == self.owners[0])
+            self.server = PSServer(engine, self.rank, range(engine.world_size), self.rank == self.owners[0],
+                                   host=hosts.get(self.rank, "127.0.0.1"), authkey=authkey)
             self.server.start()
         engine.backend.barrier()  # every listener is up before anybody connects
-        self.conns = {o: Client(_address(o), authkey=_AUTHKEY) for o in self.owners}
+        self.conns = {o: Client((hosts.get(o, "127.0.0.1"), _base_port() + o), authkey=authkey) for o in self.owners}
 
     def _call(self, owner, msg):
         c = self.conns[owner]

@@ -22,6 +22,37 @@ from autodist_b200.const import ENV
 from autodist_b200.graph_item import TrainOp
 
 
+class PinnedStager:
+    """Pinned staging buffers for host values that are not pinned themselves, ``depth`` per placeholder, used in rotation.
+
+    ``upload`` copies the value into the next buffer on the host and starts an asynchronous host-to-device copy from it.
+    Each buffer remembers the event recorded after its last copy; before the host writes into a buffer again it waits for
+    that event, so a step whose copy is still queued behind earlier work (a replayed CUDA graph returns at once) never
+    reads a batch that the host has already overwritten."""
+
+    def __init__(self, device, depth=2):
+        self.device = torch.device(device)
+        self.depth = depth
+        self._slots = {}          # name -> {"bufs": [...], "events": [...], "next": int}
+
+    def upload(self, name, t):
+        slot = self._slots.get(name)
+        if slot is None or slot["bufs"][0].shape != t.shape or slot["bufs"][0].dtype != t.dtype:
+            slot = {"bufs": [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for _ in range(self.depth)],
+                    "events": [None] * self.depth, "next": 0}
+            self._slots[name] = slot
+        i = slot["next"]
+        slot["next"] = (i + 1) % self.depth
+        if slot["events"][i] is not None:
+            slot["events"][i].synchronize()          # the copy that last read this buffer has finished
+        slot["bufs"][i].copy_(t)
+        out = slot["bufs"][i].to(self.device, non_blocking=True)
+        ev = slot["events"][i] or torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        slot["events"][i] = ev
+        return out
+
+
 def _chunk_bounds(n, k, i):
     q, r = divmod(n, k)
     start = i * q + min(i, r)
@@ -36,7 +67,7 @@ class Remapper:
         self._local_group = local_group
         self._num_local = plan.replica.num_local_replicas
         self._local_index = plan.replica.local_replica_index
-        self._staging = {}
+        self._stager = PinnedStager(self._device) if self._device.type == "cuda" else None
         self.fetch_mode = ENV.AUTODIST_FETCH_MODE.val
         if plan.gate_mode != "sync":
             self.fetch_mode = "local"   # relaxed modes must not add a lock-step collective
@@ -60,12 +91,7 @@ class Remapper:
         if t.device.type == "cpu":
             self.h2d_bytes += t.numel() * t.element_size()
             if not t.is_pinned():
-                stage = self._staging.get(name)
-                if stage is None or stage.shape != t.shape or stage.dtype != t.dtype:
-                    stage = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-                    self._staging[name] = stage
-                stage.copy_(t)
-                t = stage
+                return self._stager.upload(name, t)
             return t.to(self._device, non_blocking=True)
         return t.to(self._device)
 

@@ -200,6 +200,38 @@ def main():
     torch.cuda.synchronize()
     arena.check()
     dist.barrier()
+
+    # ---- K20: bounded-staleness gate. Every rank publishes its step into every peer's clock row and may proceed while it
+    # is at most `staleness` steps ahead of the slowest peer; a rank that would have to wait longer than the limit gets
+    # status 200 + (the peer it waited for) and its context stays usable.
+    clocks, cptrs, _ = arena.alloc(8, torch.int32)
+    clocks.zero_()
+    torch.cuda.synchronize(); dist.barrier()
+    E.staleness_gate(*arena.ctx(), cptrs, 1, 0)          # all at step 1: nobody is ahead
+    torch.cuda.synchronize()
+    arena.check()
+    dist.barrier()
+    arena.timeout_s = 0.5
+    if rank == 0:
+        E.staleness_gate(*arena.ctx(), cptrs, 4, 2)      # three steps ahead of peers that stay at step 1: must give up
+        torch.cuda.synchronize()
+        code = int(arena.error.item())
+        assert 200 < code < 200 + world, code
+        arena.error.zero_()
+        print(f"staleness gate gave up with status {code} (peer {code - 200} is behind): ok", flush=True)
+    dist.barrier()
+    if rank != 0:
+        E.staleness_gate(*arena.ctx(), cptrs, 3, 2)      # the others catch up to step 3
+        torch.cuda.synchronize()
+        assert int(arena.error.item()) == 0
+    dist.barrier()
+    if rank == 0:
+        E.staleness_gate(*arena.ctx(), cptrs, 4, 2)      # one step ahead now: the gate opens at once
+        torch.cuda.synchronize()
+        assert int(arena.error.item()) == 0
+        print("staleness gate opens once the peers caught up: ok", flush=True)
+    arena.timeout_s = 20.0
+    dist.barrier()
     arena.check_canaries()                         # no kernel of this rank or a peer wrote outside a symmetric buffer
     y = torch.ones(4, device=dev)
     dist.all_reduce(y)

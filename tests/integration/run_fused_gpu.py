@@ -146,6 +146,66 @@ def check_checkpoint(world, rank):
     return False
 
 
+def check_resume_same_strategy(world, rank, builder_name):
+    """Save after 3 steps, keep training 2 more (the uninterrupted run); then a fresh session under the SAME strategy restores
+    the file and trains 2 steps: parameters and every optimizer slot - including those kept by segment owners and by the
+    owners of a row-sharded table - must equal the uninterrupted run up to the reordering of the scatter-add's atomics (a slot
+    that was not restored restarts from zero and moves the next Adam step by about the learning rate, far above the bound)."""
+    import tempfile
+    import torch.distributed as dist
+    os.environ["AUTODIST_COMM"] = "fused"
+    from autodist_b200 import AutoDist, strategy as S
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.checkpoint.saver import Saver
+    from autodist_b200.models.bert import BertConfig, BertPretrainer, synthetic_batch
+    from autodist_b200.resource_spec import ResourceSpec
+    builders = {"PartitionedPS_gpu": lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu", local_proxy_variable=True),
+                "Parallax_gpu": lambda: S.Parallax(chunk_size=16, reduction_devices="gpu")}
+    cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    batch = synthetic_batch(cfg, 4, 128, 8, seed=10 + rank)
+    tmp = [tempfile.mkdtemp(prefix="adb_resume_") if rank == 0 else None]
+    results = []
+    path = None
+    if True:
+        for phase in ("straight", "resumed"):
+            _reset_default_autodist()
+            ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builders[builder_name]())
+            with ad.scope():
+                torch.manual_seed(0 if phase == "straight" else 7)
+                model = BertPretrainer(cfg)
+                phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in batch.items()}
+                loss = model(**phs)
+                train_op = torch.optim.Adam(model.parameters(), lr=1e-3).minimize(loss)
+                saver = Saver()
+                sess = ad.create_distributed_session()
+                feed = {phs[k]: batch[k] for k in phs}
+                if phase == "straight":
+                    dist.broadcast_object_list(tmp, src=0)
+                    for _ in range(3):
+                        sess.run([loss, train_op], feed)
+                    path = saver.save(sess, os.path.join(tmp[0], "m"), global_step=3)
+                    dist.barrier()
+                else:
+                    saver.restore(sess, path)
+                for _ in range(2):
+                    sess.run([loss, train_op], feed)
+                sess.engine.check_errors()
+                names = [n for n, _ in ad.graph_item.named_parameters()]
+                state = {n: sess.engine.variable_value(n).float().cpu().clone() for n in names}
+                slots = {k: v.float().cpu().clone() for k, v in sess.engine.optimizer_slots().items() if not k.endswith("/step")}
+                results.append((state, slots))
+                sess.close()
+    (s0, o0), (s1, o1) = results
+    worst_p = max((s0[n] - s1[n]).abs().max().item() for n in s0)
+    worst_s = max((o0[k] - o1[k]).abs().max().item() for k in o0)
+    scale = max(o0[k].abs().max().item() for k in o0)
+    ok = worst_p <= 1e-5 and worst_s <= 1e-4 * scale and scale > 0 and set(o0) == set(o1)
+    if rank == 0:
+        print(f"resume {builder_name} -> {builder_name}: max |param diff| {worst_p:.1e}, max |slot diff| {worst_s:.1e} over {len(o0)} slots "
+              f"{'ok' if ok else 'FAIL'}", flush=True)
+    return ok
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     failures = 0
@@ -177,6 +237,8 @@ def main():
     if rank == 0:
         print(f"PartitionedPS_gpu adam: {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
     failures += 0 if check_checkpoint(world, rank) else 1
+    for name in ("PartitionedPS_gpu", "Parallax_gpu"):
+        failures += 0 if check_resume_same_strategy(world, rank, name) else 1
     if rank == 0:
         print("FUSED ENGINE CHECKS PASSED" if failures == 0 else "FUSED ENGINE CHECKS FAILED", flush=True)
     import torch.distributed as dist

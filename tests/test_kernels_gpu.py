@@ -220,7 +220,7 @@ def test_embedding_and_row_ops(E):
     ids = torch.randint(0, V, (B * S,), device="cuda")
     tt = torch.randint(0, 2, (B * S,), device="cuda")
     z = torch.empty(B * S, H, dtype=torch.bfloat16, device="cuda")
-    E.embed_sum(word, pos, typ, ids, tt, z, S)
+    E.embed_sum(word, pos, typ, ids, tt, z, S, err)
     ref = word.float()[ids] + pos.float()[torch.arange(B * S, device="cuda") % S] + typ.float()[tt]
     _check(z, ref, 1e-2)
     dz = _rand(B * S, H)
