@@ -329,6 +329,16 @@ void sparse_rows_update(Tensor p, const optional<Tensor>& s1, const optional<Ten
                              (int)rows.numel(), (int)p.size(1), p.size(0), (int)kind, lr.data_ptr<float>(), (float)b1, (float)b2,
                              (float)eps, OPT_LL(step), (float)grad_scale, STREAM);
 }
+// Owner-side update of the flagged rows of a shard (p, g, s1, s2: fp32 [rows, H]; flags: uint8 [rows]); clears what it used.
+void flagged_rows_update(Tensor p, const optional<Tensor>& s1, const optional<Tensor>& s2, const optional<Tensor>& p16, Tensor g, Tensor flags,
+                         int64_t rows, int64_t H, int64_t kind, const Tensor& lr, double b1, double b2, double eps, const optional<Tensor>& step) {
+  TORCH_CHECK(p.scalar_type() == at::kFloat && g.scalar_type() == at::kFloat && flags.scalar_type() == at::kByte, "fp32 table / gradient, uint8 flags");
+  TORCH_CHECK(p.numel() >= rows * H && g.numel() >= rows * H && flags.numel() >= rows, "buffers smaller than rows x H");
+  TORCH_CHECK(kind == 0 || s1.has_value(), "state 1 needed");
+  TORCH_CHECK(kind != 1 || (s2.has_value() && step.has_value()), "Adam needs both moments and the step");
+  adb200::flagged_rows_update(p.data_ptr<float>(), OPT_F(s1), OPT_F(s2), OPT_BF(p16), g.data_ptr<float>(), flags.data_ptr<uint8_t>(), rows, (int)H,
+                              (int)kind, lr.data_ptr<float>(), (float)b1, (float)b2, (float)eps, OPT_LL(step), STREAM);
+}
 void lstm_cell_fwd(const Tensor& gates, const Tensor& c_prev, Tensor c, Tensor h, double forget_bias) {
   const int B = c_prev.size(0), S = c_prev.size(1);
   TORCH_CHECK(gates.scalar_type() == at::kFloat && gates.size(1) == 4 * S && gates.is_contiguous(), "gates must be fp32 [B, 4S]");
@@ -503,22 +513,25 @@ void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error,
 }
 
 void sparse_scatter_add(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
-                        const Tensor& shard_ptrs, const Tensor& ids, const Tensor& vals, int64_t V, double scale, int64_t blocks) {
+                        const Tensor& shard_ptrs, const optional<Tensor>& touched_ptrs, const Tensor& ids, const Tensor& vals, int64_t V,
+                        double scale, int64_t barriers, int64_t blocks) {
   adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
   const int H = vals.size(-1);
   TORCH_CHECK(H % 4 == 0, "row width must be a multiple of 4");
   TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
-  adb200::launch_sparse_scatter_add(c, reinterpret_cast<float* const*>(shard_ptrs.data_ptr<int64_t>()), ids.data_ptr<int64_t>(), vals.data_ptr(),
-                                    vals.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), H, V, (float)scale, (int)blocks, STREAM);
+  adb200::launch_sparse_scatter_add(c, reinterpret_cast<float* const*>(shard_ptrs.data_ptr<int64_t>()),
+                                    touched_ptrs.has_value() ? reinterpret_cast<uint8_t* const*>(touched_ptrs->data_ptr<int64_t>()) : nullptr,
+                                    ids.data_ptr<int64_t>(), vals.data_ptr(),
+                                    vals.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), H, V, (float)scale, (int)barriers, (int)blocks, STREAM);
 }
 
 void embedding_gather_peers(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
-                            const Tensor& shard_ptrs, const Tensor& ids, Tensor out, int64_t V, bool do_barrier, int64_t blocks) {
+                            const Tensor& shard_ptrs, const Tensor& ids, Tensor out, int64_t V, int64_t barriers, int64_t blocks) {
   adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
   TORCH_CHECK(out.size(-1) % 8 == 0, "row width must be a multiple of 8");
   TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
   adb200::launch_embedding_gather_peers(c, reinterpret_cast<__nv_bfloat16* const*>(shard_ptrs.data_ptr<int64_t>()), ids.data_ptr<int64_t>(),
-                                        BF(out), ids.numel(), out.size(-1), V, do_barrier ? 1 : 0, (int)blocks, STREAM);
+                                        BF(out), ids.numel(), out.size(-1), V, (int)barriers, (int)blocks, STREAM);
 }
 
 void sym_barrier(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s, int64_t blocks) {
@@ -560,6 +573,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_update", &sgd_update);
   m.def("adagrad_update", &adagrad_update);
   m.def("sparse_rows_update", &sparse_rows_update);
+  m.def("flagged_rows_update", &flagged_rows_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("bn_fwd", &bn_fwd);
   m.def("bn_bwd", &bn_bwd);

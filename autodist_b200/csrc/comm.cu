@@ -352,9 +352,14 @@ __device__ __forceinline__ void owner_of(long long id, long long V, int world, i
   local = id - (owner * qn + (owner < rn ? owner : rn));
 }
 
-__global__ void sparse_scatter_add_kernel(SymCtx c, float* const* shard, const int64_t* ids, const __nv_bfloat16* vals32_or_16,
-                                          int vals_are_bf16, long long nrows, int H, long long V, float scale) {
-  if (!sym_barrier(c)) return;    // owners have zeroed their shards
+// barriers: bit 0 = meet the peers before the first access (the owners' shards are ready), bit 1 = after the last one
+// (every rank's rows have landed). A step with several lookups / pushes brackets the whole group instead of each call.
+// touched (optional): per-owner byte flags, one per shard row; the flag of every row that receives a gradient is raised so
+// that the owner's update can skip the rest of its shard.
+__global__ void sparse_scatter_add_kernel(SymCtx c, float* const* shard, uint8_t* const* touched, const int64_t* ids,
+                                          const __nv_bfloat16* vals32_or_16, int vals_are_bf16, long long nrows, int H, long long V,
+                                          float scale, int barriers) {
+  if ((barriers & 1) && !sym_barrier(c)) return;    // owners have zeroed their shards
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (long long r = warp; r < nrows; r += nwarp) {
@@ -366,6 +371,7 @@ __global__ void sparse_scatter_add_kernel(SymCtx c, float* const* shard, const i
     int owner; long long local;
     owner_of(id, V, c.world, owner, local);
     float* dst = shard[owner] + local * H;
+    if (touched != nullptr && lane == 0) touched[owner][local] = 1;
     for (int col = lane * 4; col < H; col += 128) {
       float4 v;
       if (vals_are_bf16) {
@@ -378,12 +384,12 @@ __global__ void sparse_scatter_add_kernel(SymCtx c, float* const* shard, const i
       atomicAdd(reinterpret_cast<float4*>(dst + col), v);   // red.global.add.v4.f32 on the owner's memory
     }
   }
-  sym_barrier(c);
+  if (barriers & 2) sym_barrier(c);
 }
 
 __global__ void embedding_gather_peers_kernel(SymCtx c, __nv_bfloat16* const* shard, const int64_t* ids, __nv_bfloat16* out,
-                                              long long nrows, int H, long long V, int do_barrier) {
-  if (do_barrier && !sym_barrier(c)) return;
+                                              long long nrows, int H, long long V, int barriers) {
+  if ((barriers & 1) && !sym_barrier(c)) return;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   for (long long r = warp; r < nrows; r += nwarp) {
@@ -399,7 +405,7 @@ __global__ void embedding_gather_peers_kernel(SymCtx c, __nv_bfloat16* const* sh
     for (int col = lane * 8; col < H; col += 256)
       *reinterpret_cast<uint4*>(out + r * H + col) = *reinterpret_cast<const uint4*>(src + col);
   }
-  if (do_barrier) sym_barrier(c);
+  if (barriers & 2) sym_barrier(c);
 }
 
 // ------------------------------------------------------------------------------------------------ K20
@@ -446,14 +452,15 @@ void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfl
   reduce_scatter_update_kernel<<<blocks, 512, 0, st>>>(c, grads, p16, p32, master, s1, s2, seg_start, seg_len, seg_state, owned_prefix, nseg, o, scale);
 }
 
-void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, const int64_t* ids, const void* vals, int vals_are_bf16,
-                               long long nrows, int H, long long V, float scale, int blocks, cudaStream_t st) {
-  sparse_scatter_add_kernel<<<blocks, 256, 0, st>>>(c, shard, ids, reinterpret_cast<const __nv_bfloat16*>(vals), vals_are_bf16, nrows, H, V, scale);
+void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* const* touched, const int64_t* ids, const void* vals,
+                               int vals_are_bf16, long long nrows, int H, long long V, float scale, int barriers, int blocks, cudaStream_t st) {
+  sparse_scatter_add_kernel<<<blocks, 256, 0, st>>>(c, shard, touched, ids, reinterpret_cast<const __nv_bfloat16*>(vals), vals_are_bf16, nrows, H, V,
+                                                    scale, barriers);
 }
 
 void launch_embedding_gather_peers(const SymCtx& c, __nv_bfloat16* const* shard, const int64_t* ids, __nv_bfloat16* out, long long nrows,
-                                   int H, long long V, int do_barrier, int blocks, cudaStream_t st) {
-  embedding_gather_peers_kernel<<<blocks, 256, 0, st>>>(c, shard, ids, out, nrows, H, V, do_barrier);
+                                   int H, long long V, int barriers, int blocks, cudaStream_t st) {
+  embedding_gather_peers_kernel<<<blocks, 256, 0, st>>>(c, shard, ids, out, nrows, H, V, barriers);
 }
 
 void launch_barrier(const SymCtx& c, int blocks, cudaStream_t st) { barrier_kernel<<<blocks, 32, 0, st>>>(c); }

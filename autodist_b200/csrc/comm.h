@@ -26,10 +26,10 @@ void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfl
                                   const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
                                   float b2, float eps, float wd, float momentum, float grad_scale, int decoupled, int nesterov,
                                   float scale, int blocks, cudaStream_t st);
-void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, const int64_t* ids, const void* vals, int vals_are_bf16,
-                               long long nrows, int H, long long V, float scale, int blocks, cudaStream_t st);
+void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* const* touched, const int64_t* ids, const void* vals,
+                               int vals_are_bf16, long long nrows, int H, long long V, float scale, int barriers, int blocks, cudaStream_t st);
 void launch_embedding_gather_peers(const SymCtx& c, __nv_bfloat16* const* shard, const int64_t* ids, __nv_bfloat16* out, long long nrows,
-                                   int H, long long V, int do_barrier, int blocks, cudaStream_t st);
+                                   int H, long long V, int barriers, int blocks, cudaStream_t st);
 void launch_barrier(const SymCtx& c, int blocks, cudaStream_t st);
 void launch_staleness_gate(const SymCtx& c, uint32_t* const* clocks, uint32_t my_step, uint32_t staleness, cudaStream_t st);
 

@@ -735,6 +735,49 @@ __global__ void sparse_rows_update_kernel(float* __restrict__ p, float* __restri
   }
 }
 
+// Owner-side update of a row-sharded table: only rows whose flag was raised by the scatter-add of this step are touched.
+// Their gradient row (already the mean over replicas) is applied, written back as bf16, cleared, and the flag is lowered, so
+// that update and clearing cost what the touched rows cost, not what the shard costs. kind as in sparse_rows_update_kernel.
+__global__ void flagged_rows_update_kernel(float* __restrict__ p, float* __restrict__ s1, float* __restrict__ s2, bf16* __restrict__ p16,
+                                           float* __restrict__ g, uint8_t* __restrict__ flags, long long rows, int H, int kind,
+                                           const float* __restrict__ lr_ptr, float b1, float b2, float eps,
+                                           const long long* __restrict__ step_ptr) {
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const float lr = *lr_ptr;
+  float inv_c1 = 1.f, inv_c2 = 1.f;
+  if (kind == 1) {
+    const float t = (float)(*step_ptr);
+    inv_c1 = 1.0f / (1.0f - powf(b1, t));
+    inv_c2 = 1.0f / (1.0f - powf(b2, t));
+  }
+  for (long long r = warp0; r < rows; r += nwarp) {
+    if (flags[r] == 0) continue;
+    for (int c = lane; c < H; c += 32) {
+      const long long i = r * H + c;
+      const float gr = g[i];
+      g[i] = 0.f;
+      float np;
+      if (kind == 0) {
+        np = p[i] - lr * gr;
+      } else if (kind == 1) {
+        const float m = b1 * s1[i] + (1.0f - b1) * gr, v = b2 * s2[i] + (1.0f - b2) * gr * gr;
+        s1[i] = m;
+        s2[i] = v;
+        np = p[i] - lr * (m * inv_c1) / (sqrtf(v * inv_c2) + eps);
+      } else {
+        const float a = s1[i] + gr * gr;
+        s1[i] = a;
+        np = p[i] - lr * gr / (sqrtf(a) + eps);
+      }
+      p[i] = np;
+      if (p16) p16[i] = __float2bfloat16(np);
+    }
+    __syncwarp();
+    if (lane == 0) flags[r] = 0;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ LSTM cell (K17)
 // gates [B, 4S] in the order i, j, f, o (fp32); c = sigmoid(f + fb) * c_prev + sigmoid(i) * tanh(j); h = sigmoid(o) * tanh(c)
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
@@ -1317,6 +1360,13 @@ void sparse_rows_update(float* p, float* s1, float* s2, bf16* p16, const int64_t
                         cudaStream_t st) {
   if (n <= 0) return;
   sparse_rows_update_kernel<<<blocks_for(n, 8), 256, 0, st>>>(p, s1, s2, p16, rows, g, n, H, V, kind, lr, b1, b2, eps, step, grad_scale);
+}
+void flagged_rows_update(float* p, float* s1, float* s2, bf16* p16, float* g, uint8_t* flags, long long rows, int H, int kind,
+                         const float* lr, float b1, float b2, float eps, const long long* step, cudaStream_t st) {
+  if (rows <= 0) return;
+  long long blocks = (rows + 7) / 8;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  flagged_rows_update_kernel<<<(int)blocks, 256, 0, st>>>(p, s1, s2, p16, g, flags, rows, H, kind, lr, b1, b2, eps, step);
 }
 void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16* h, int B, int S, float fb, cudaStream_t st) {
   lstm_cell_fwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, h, B, S, fb);

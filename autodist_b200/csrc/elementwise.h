@@ -39,6 +39,8 @@ void sgd_update(float* p, const float* g, float* mom, bf16_t* p16, long long n, 
 void sparse_rows_update(float* p, float* s1, float* s2, bf16_t* p16, const int64_t* rows, const float* g, int n, int H, long long V,
                         int kind, const float* lr, float b1, float b2, float eps, const long long* step, float grad_scale,
                         cudaStream_t st);
+void flagged_rows_update(float* p, float* s1, float* s2, bf16_t* p16, float* g, uint8_t* flags, long long rows, int H, int kind,
+                         const float* lr, float b1, float b2, float eps, const long long* step, cudaStream_t st);
 void adagrad_update(float* p, const float* g, float* acc, bf16_t* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st);
 void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16_t* h, int B, int S, float fb, cudaStream_t st);

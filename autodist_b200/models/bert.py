@@ -132,6 +132,10 @@ class BertPretrainer(nn.Module):
         """Variables whose gradient is row-sparse (only when the output projection is untied)."""
         return [] if self.config.tie_word_embeddings else [self.emb["word"]]
 
+    def sparse_lookup_parameters(self):
+        """Tables the fused path reads row by row, so that an engine may keep them as one row shard per rank."""
+        return self.sparse_grad_parameters()
+
     # ------------------------------------------------------------------ reference path (plain PyTorch, fp32)
     def reference_loss(self, input_ids, input_mask, segment_ids, mlm_positions, mlm_ids, mlm_weights, nsp_labels,
                        dropout=False):
@@ -265,9 +269,10 @@ class BertPretrainer(nn.Module):
             return t.view(B, S, nh, D).permute(0, 2, 1, 3)
 
         # ------------------------------ forward
-        if self._word_lookup_hook is not None:
+        word_rows = getattr(self.emb["word"], "_sparse_rows", None)
+        if word_rows is not None:
             # sharded table: the rows of this batch are fetched from the shards that own them (peer memory)
-            rows = self._word_lookup_hook(ids)
+            rows = word_rows.lookup(ids)
             E.embed_sum(rows, w16["emb.pos"], w16["emb.tok_type"], ws["row_index"], tts, ws["z0"], S, ws["err"])
         else:
             E.embed_sum(w16["emb.word"], w16["emb.pos"], w16["emb.tok_type"], ids, tts, ws["z0"], S, ws["err"])
@@ -384,8 +389,8 @@ class BertPretrainer(nn.Module):
         dz0 = spare[0]
         E.ln_bwd(d_out, ws["z0"], ws["m0"], ws["r0"], w32["emb.ln_g"], None, dz0, None, ws["part"], g["emb.ln_g"], g["emb.ln_b"],
                  0.0, 0, None, False)
-        if self._word_grad_hook is not None:
-            self._word_grad_hook(ids, dz0)             # sparse path: (row ids, rows) go to the shard owners
+        if word_rows is not None:
+            word_rows.push(ids, dz0)                   # sparse path: (row ids, rows) go to the shard owners
         else:
             if not tied:
                 g["emb.word"].zero_()
@@ -396,8 +401,6 @@ class BertPretrainer(nn.Module):
         ready(0, fl.offsets["layers.0.qkv_w"])
         return ws["loss"]
 
-    _word_grad_hook = None
-    _word_lookup_hook = None
 
     # ------------------------------------------------------------------ module call
     def forward(self, input_ids, input_mask, segment_ids, mlm_positions, mlm_ids, mlm_weights, nsp_labels):

@@ -60,6 +60,10 @@ class LM1B(nn.Module):
     def sparse_grad_parameters(self):
         return [self.emb, self.softmax_w, self.softmax_b]
 
+    def sparse_lookup_parameters(self):
+        """Tables read only through ``sparse_lookup``: an engine may keep them as row shards instead of replicas."""
+        return [self.emb, self.softmax_w]
+
     def dense_parameters(self):
         return [self.W, self.B, self.W_P]
 
@@ -84,10 +88,14 @@ class LM1B(nn.Module):
             out = F.dropout(out, 1.0 - c.keep_prob)
         # sampled softmax: true class + shared log-uniform negatives, logits corrected by -log(expected count)
         targets = y.reshape(-1)
-        if self._gen is None or self._gen.device != x.device:
-            self._gen = torch.Generator(device=x.device)
-            self._gen.manual_seed(1234)
-        neg = log_uniform_sample(c.num_sampled, c.vocab_size, self._gen, x.device)
+        if x.is_cuda:
+            gen = None            # the device's default generator: its state survives capture into a CUDA graph
+        else:
+            if self._gen is None:
+                self._gen = torch.Generator()
+                self._gen.manual_seed(1234)
+            gen = self._gen
+        neg = log_uniform_sample(c.num_sampled, c.vocab_size, gen, x.device)
         true_w = sparse_lookup(self.softmax_w, targets).to(dt)
         true_logit = (out * true_w).sum(1).float() + self.softmax_b[targets] - torch.log(
             c.num_sampled * log_uniform_prob(targets, c.vocab_size))

@@ -166,8 +166,10 @@ def _bf16_weight(weight):
 def _direct_grad(param):
     """The fp32 gradient buffer of ``param`` when its owner (a flat-buffer engine) asked for gradients to be accumulated
     in place by the producing kernel instead of travelling through autograd's accumulation; else ``None``."""
-    g = getattr(param, "grad", None)
-    if getattr(param, "_direct_grad", False) and g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.is_cuda:
+    if not getattr(param, "_direct_grad", False):
+        return None                 # (asked first: reading .grad of a non-leaf tensor makes PyTorch warn)
+    g = param.grad
+    if g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.is_cuda:
         return g
     return None
 
@@ -441,8 +443,39 @@ class _SparseLookupFn(torch.autograd.Function):
             return torch.sparse_coo_tensor(flat[None], vals, ctx.shape, check_invariants=False), None
 
 
+class _ShardedLookupFn(torch.autograd.Function):
+    """Lookup in a table that is kept as one row shard per rank (``parallel.fused_engine.ShardedRows``): rows are gathered
+    from their owners inside the kernel; the backward pass adds the gradient rows straight into the owners' shards, so the
+    table has no gradient tensor at all. ``anchor`` is a dummy that requires grad, so that autograd runs the backward pass."""
+
+    @staticmethod
+    def forward(ctx, anchor, handle, ids):
+        ctx.handle = handle
+        ctx.save_for_backward(ids)
+        return handle.lookup(ids).view(*ids.shape, handle.H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        ctx.handle.push(ids, dy.reshape(-1, ctx.handle.H))
+        return None, None, None
+
+
+_ANCHORS = {}
+
+
 def sparse_lookup(table, ids):
-    """``F.embedding(ids, table, sparse=True)`` returning bf16 on CUDA (fp32 elsewhere)."""
+    """``F.embedding(ids, table, sparse=True)`` returning bf16 on CUDA (fp32 elsewhere).
+
+    A module that reads a table only through this function may list it in ``sparse_lookup_parameters()``; an engine can
+    then keep the table as one row shard per rank and attach the shard handle to the parameter (``_sparse_rows``), in which
+    case the lookup and its gradient run on the peer-memory kernels."""
+    handle = getattr(table, "_sparse_rows", None)
+    if handle is not None and ids.is_cuda:
+        anchor = _ANCHORS.get(ids.device)
+        if anchor is None:
+            anchor = _ANCHORS[ids.device] = torch.zeros((), device=ids.device, requires_grad=True)
+        return _ShardedLookupFn.apply(anchor, handle, ids)
     if table.is_cuda and table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] % 8 == 0:
         return _SparseLookupFn.apply(table, ids)
     return F.embedding(ids, table, sparse=True)

@@ -186,13 +186,179 @@ class SymmetricArena:
             raise RuntimeError(f"rank {self.rank}: a communication kernel gave up waiting for a peer (code {code})")
 
 
+def row_shard_candidates(item, plan, hand_scheduled):
+    """``{variable name: parameter}`` of the row-sparse tables that are kept as one shard per rank instead of replicated.
+
+    A table qualifies when its module reads it through ``ops.functional.sparse_lookup`` (it lists the parameter in
+    ``sparse_lookup_parameters()``), it is fp32 ``[V, H]`` with ``H`` a multiple of 8, and - with more than one rank -
+    the plan splits it along axis 0 into one part per rank, part ``i`` owned by rank ``i`` (what ``Parallax`` and
+    ``PartitionedPS(num_shards=<gpus>)`` with ``reduction_devices="gpu"`` produce). The scatter-add into owner shards
+    uses floating-point atomics, whose order of addition varies from run to run; ``AUTODIST_DETERMINISTIC=1`` (or
+    ``AUTODIST_SPARSE_ROWS=0``) keeps such tables replicated and their gradients on the dense paths."""
+    if os.environ.get("AUTODIST_SPARSE_ROWS", "1") == "0" or os.environ.get("AUTODIST_DETERMINISTIC", "0") == "1":
+        return {}
+    declared = set()
+    for m in item.root.modules():
+        declared |= {id(p) for p in getattr(m, "sparse_lookup_parameters", lambda: [])()}
+    by_var = {}
+    for e in plan.ps_entries.values():
+        by_var.setdefault(e.part.var_name, []).append(e)
+    out = {}
+    world = plan.replica.world_size
+    for var_name, p in item.named_parameters():
+        var = item.variables.get(var_name)
+        if var is None or not var.sparse_grad or id(p) not in declared or not p.requires_grad:
+            continue
+        if world == 1 and hand_scheduled:
+            continue      # a hand-scheduled model keeps its tables in the flat buffers: nothing to gain on one rank
+        if p.dim() != 2 or p.shape[1] % 8 or p.dtype != torch.float32 or p.shape[0] < world:
+            continue
+        if world > 1:
+            entries = sorted(by_var.get(var_name, []), key=lambda e: e.part.offset)
+            q, rem = divmod(p.shape[0], world)
+            if len(entries) != world or not all(e.part.sparse and e.gate == "sync" for e in entries) \
+                    or [e.owner for e in entries] != list(range(world)) \
+                    or [e.part.size for e in entries] != [q + (1 if i < rem else 0) for i in range(world)]:
+                continue
+        out[var_name] = p
+    return out
+
+
+class LocalArena:
+    """Stand-in for ``SymmetricArena`` in a single-process job: plain device buffers with the same ``alloc`` / ``ctx`` face,
+    so that the row-sharded table kernels (one shard, no peers, no barriers) run unchanged on one GPU."""
+
+    def __init__(self, device):
+        from autodist_b200 import ops
+        self.E = ops.ext(required=True)
+        self.device = device
+        self.rank, self.world = 0, 1
+        self.flags = torch.zeros(self.E.MAX_COMM_BLOCKS * 8, dtype=torch.int32, device=device)
+        self.flag_ptrs = torch.tensor([self.flags.data_ptr()], dtype=torch.int64, device=device)
+        self.epochs = torch.zeros(self.E.MAX_COMM_BLOCKS + 8, dtype=torch.int32, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.timeout_s = 1.0
+
+    def alloc(self, numel, dtype):
+        t = torch.zeros(numel, dtype=dtype, device=self.device)
+        return t, torch.tensor([t.data_ptr()], dtype=torch.int64, device=self.device), 0
+
+    def ctx(self, channel=0):
+        return (self.flag_ptrs, self.epochs, self.error, 0, 1, self.timeout_s)
+
+    def check(self):
+        code = int(self.error.item())
+        if code:
+            raise RuntimeError(f"a row id outside the table reached the sharded-table kernels (code {code})")
+
+
+class ShardedRows:
+    """A row-sparse ``[V, H]`` variable split along axis 0 into one shard per rank (rank ``i`` owns block ``i``) and never
+    replicated: lookups gather rows from the owners inside the kernel (``embedding_gather_peers``), gradient rows are added
+    straight into the owners' fp32 shards (``sparse_scatter_add``), and after the last push of a step every owner updates
+    its shard. The reference reaches the same placement with a partitioned ``embedding_lookup`` over variables on the
+    parameter servers (``autodist/kernel/partitioner.py:660-684``, ``examples/lm1b/language_model.py:66``).
+
+    Step protocol (all kernels on the compute stream, flag channel 1): the first lookup of a step meets the peers first (the
+    owners' updates of the previous step are complete); pushes carry no barrier; ``finish`` meets the peers once (every
+    rank's rows have landed), updates and clears. Optimizers that leave untouched rows unchanged (SGD without momentum or
+    weight decay, Adagrad without weight decay) update only the rows whose flag the pushes raised; others sweep the shard."""
+
+    def __init__(self, engine, var_name, param, full_fp32, arena):
+        self.engine, self.var, self.param, self.arena = engine, var_name, param, arena
+        world, rank = arena.world, arena.rank
+        self.V, self.H = int(full_fp32.shape[0]), int(full_fp32.numel() // full_fp32.shape[0])
+        q, rem = divmod(self.V, world)
+        self.rows = q + (1 if rank < rem else 0)
+        self.off = rank * q + min(rank, rem)
+        cap = q + 1
+        dev = engine.device
+        self.shard16, self.s16ptrs, _ = arena.alloc(cap * self.H, torch.bfloat16)
+        self.grad32, self.g32ptrs, _ = arena.alloc(cap * self.H, torch.float32)
+        self.flags8, self.f8ptrs, _ = arena.alloc((cap + 15) // 16 * 16, torch.uint8)
+        self.shard16.zero_(); self.grad32.zero_(); self.flags8.zero_()
+        self.master = full_fp32.reshape(self.V, self.H)[self.off:self.off + self.rows].reshape(-1).to(dev, torch.float32).clone()
+        self.shard16[:self.rows * self.H].copy_(self.master)
+        kind = engine.opt_kind
+        self.s1 = torch.zeros_like(self.master) if engine._needs_slot1() else None
+        self.s2 = torch.zeros_like(self.master) if kind in ("Adam", "AdamW") else None
+        if kind == "Adagrad":
+            self.s1.fill_(float(engine.opt_info.optimizer.param_groups[0].get("initial_accumulator_value", 0.0)))
+        g = engine.opt_info.optimizer.param_groups[0]
+        plain = float(g.get("weight_decay", 0.0)) == 0.0
+        self.flagged = os.environ.get("AUTODIST_SPARSE_FLAGGED", "1") == "1" and plain and (
+            kind == "Adagrad" or (kind == "SGD" and float(g.get("momentum", 0.0)) == 0.0))
+        self.blocks = 32
+
+    # -- forward / backward ------------------------------------------------------------------------------------------
+    def lookup(self, ids):
+        eng = self.engine
+        ids = ids.reshape(-1).contiguous()
+        out = torch.empty(ids.numel(), self.H, dtype=torch.bfloat16, device=eng.device)
+        first = eng._rows_sync_pending and self.arena.world > 1
+        eng._rows_sync_pending = False
+        eng.E.embedding_gather_peers(*self.arena.ctx(1), self.s16ptrs, ids, out, self.V, 1 if first else 0, self.blocks)
+        return out
+
+    def push(self, ids, rows):
+        """Add ``rows`` (bf16 or fp32 ``[n, H]``, this replica's gradient of the looked-up rows) into the owners' shards."""
+        eng = self.engine
+        ids = ids.reshape(-1).contiguous()
+        rows = rows.reshape(ids.numel(), self.H)
+        if rows.dtype not in (torch.bfloat16, torch.float32):
+            rows = rows.float()
+        eng.E.sparse_scatter_add(*self.arena.ctx(1), self.g32ptrs, self.f8ptrs if self.flagged else None, ids, rows.contiguous(), self.V,
+                                 1.0 / self.arena.world, 0, self.blocks)
+        eng._rows_dirty = True
+
+    def update(self):
+        """Owner-side optimizer step on this rank's shard (after the step's barrier), then clear what the pushes wrote."""
+        eng = self.engine
+        g = eng.opt_info.optimizer.param_groups[0]
+        n = self.rows * self.H
+        if self.flagged:
+            kind = {"SGD": 0, "Adagrad": 2}[eng.opt_kind]
+            eng.E.flagged_rows_update(self.master, self.s1, self.s2, self.shard16, self.grad32, self.flags8, self.rows, self.H, kind, eng.lr,
+                                      0.0, 0.0, float(g.get("eps", 1e-10)), None)
+            return
+        eng._apply_optimizer(self.master, self.grad32[:n], self.s1, self.s2, self.shard16[:n])
+        self.grad32.zero_()
+
+    # -- state -------------------------------------------------------------------------------------------------------
+    def gather(self, local_flat):
+        """Full ``[V, H]`` tensor from every owner's rows (checkpoints, variable fetches)."""
+        world = self.arena.world
+        if world == 1:
+            return local_flat[:self.rows * self.H].view(self.V, self.H).clone()
+        cap = self.V // world + 1
+        pad = torch.zeros(cap * self.H, dtype=torch.float32, device=self.engine.device)
+        pad[:local_flat.numel()].copy_(local_flat)
+        parts = [torch.empty_like(pad) for _ in range(world)]
+        dist.all_gather(parts, pad, group=self.engine.backend.group)
+        q, rem = divmod(self.V, world)
+        rows = [q + (1 if i < rem else 0) for i in range(world)]
+        return torch.cat([parts[i][:rows[i] * self.H] for i in range(world)]).view(self.V, self.H)
+
+    def load(self, full_fp32):
+        """Re-slice this rank's rows out of the full table (restore)."""
+        lo, hi = self.off, self.off + self.rows
+        self.master.copy_(full_fp32.reshape(self.V, self.H)[lo:hi].reshape(-1))
+        self.shard16[:self.rows * self.H].copy_(self.master)
+
+    def load_slots(self, slot1=None, slot2=None):
+        lo, hi = self.off, self.off + self.rows
+        for own, full in ((self.s1, slot1), (self.s2, slot2)):
+            if own is not None and full is not None:
+                own.copy_(full.reshape(self.V, self.H)[lo:hi].reshape(-1))
+
+
 class FusedStepEngine(StepEngine):
     @staticmethod
     def supports(graph_item, plan, module):
         if len(graph_item.optimizers) != 1:
             return False
-        if any(op.clip_global_norm for op in graph_item.train_ops):
-            return False      # global-norm clipping sits between reduction and update: the generic engine does it
+        if module is not None and any(op.clip_global_norm for op in graph_item.train_ops):
+            return False      # the hand-scheduled models fuse reduction and update per flight: no place for a global norm
         if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
             return False
         if plan.replica.world_size > 1:
@@ -230,9 +396,13 @@ class FusedStepEngine(StepEngine):
                 t.zero_()
                 self._grad_sym = {"ptrs": ptrs, "mc": mc}
                 return t
+        self._params = {name: p for name, p in graph_item.named_parameters()}
+        self.sharded_rows = {}
+        self._rows_sync_pending, self._rows_dirty = True, False
+        row_sharded = self._row_shard_candidates()
         master_alloc = p16_alloc = None
         self._p32_sym = self._p16_sym = None
-        if self.world_size > 1 and plan.ps_entries:
+        if self.world_size > 1 and any(e.part.var_name not in row_sharded for e in plan.ps_entries.values()):
             # owners write updated parameters straight into every rank's copies: those live in symmetric memory too
             def master_alloc(n):
                 t, ptrs, _ = self.arena.alloc(n, torch.float32)
@@ -245,12 +415,16 @@ class FusedStepEngine(StepEngine):
                 t.zero_()
                 self._p16_sym = ptrs
                 return t
-        self.flat = module.materialize(self.device, grad_alloc, master_alloc, p16_alloc)
-        self._params = {name: p for name, p in graph_item.named_parameters()}
+        if isinstance(module, _AutogradModel):
+            # tables that are never replicated stay out of the flat buffers: no full-size gradient, compute copy or slots
+            self.flat = module.materialize(self.device, grad_alloc, master_alloc, p16_alloc, exclude={id(p) for p in row_sharded.values()})
+        else:
+            self.flat = module.materialize(self.device, grad_alloc, master_alloc, p16_alloc)
         if self.world_size > 1:
             backend.broadcast_(self.flat.master, 0)
         self.flat.refresh_bf16()
         self._setup_optimizer()
+        self._setup_sharded_rows(row_sharded)
         self._setup_flights()
         self.comm_stream = torch.cuda.Stream(device=self.device)
         self._ready_event = torch.cuda.Event()
@@ -274,6 +448,8 @@ class FusedStepEngine(StepEngine):
         n = self.flat.total
         dev = self.device
         self.slot1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
+        if self.opt_kind == "Adagrad":
+            self.slot1.fill_(float(info.optimizer.param_groups[0].get("initial_accumulator_value", 0.0)))
         self.slot2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
         self.lr = torch.zeros(1, dtype=torch.float32, device=dev)
         self._lr_host = None
@@ -291,19 +467,9 @@ class FusedStepEngine(StepEngine):
             self._lr_host = lr
 
     def _update_range(self, lo, hi):
-        g = self.opt_info.optimizer.param_groups[0]
         fl = self.flat
-        p, gr, p16 = fl.master[lo:hi], fl.grad[lo:hi], fl.p16[lo:hi]
-        s1 = self.slot1[lo:hi] if self.slot1 is not None else None
-        if self.opt_kind in ("Adam", "AdamW"):
-            b1, b2 = g["betas"]
-            self.E.adam_update(p, gr, s1, self.slot2[lo:hi], p16, self.lr, b1, b2, g["eps"], g["weight_decay"],
-                               self.opt_kind == "AdamW", self.opt_step, 1.0)
-        elif self.opt_kind == "SGD":
-            self.E.sgd_update(p, gr, s1, p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"],
-                              self.opt_step, 1.0)
-        else:
-            self.E.adagrad_update(p, gr, s1, p16, self.lr, g["eps"], g["weight_decay"], 1.0)
+        self._apply_optimizer(fl.master[lo:hi], fl.grad[lo:hi], self.slot1[lo:hi] if self.slot1 is not None else None,
+                              self.slot2[lo:hi] if self.slot2 is not None else None, fl.p16[lo:hi])
 
     # ------------------------------------------------------------------ flights
     def _setup_flights(self):
@@ -346,11 +512,10 @@ class FusedStepEngine(StepEngine):
         by_var = {}
         for e in self.plan.ps_entries.values():
             by_var.setdefault(e.part.var_name, []).append(e)
-        self.sharded_rows = {}
         for var_name, entries in by_var.items():
+            if var_name in self.sharded_rows:
+                continue                              # kept as one shard per rank, outside the flat buffers' synchronisation
             name = flat_name[var_name]
-            if self._try_row_sharding(var_name, name, entries):
-                continue
             base, end = fl.offsets[name], fl.range_of([name])[1]
             p = fl.params[fl.names.index(name)]
             row = p.numel() // p.shape[0] if p.dim() > 0 and p.shape[0] > 0 else 1
@@ -382,72 +547,43 @@ class FusedStepEngine(StepEngine):
         self.ps_s2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
 
     # ---- row-sparse variables sharded over all ranks: K4 (scatter-add to owners) / K5 (gather from owners) ----------
-    def _try_row_sharding(self, var_name, name, entries):
-        """A sparse variable split along axis 0 into one shard per rank, shard i owned by rank i, is not replicated at
-        all: lookups read rows from the owners and gradients are added into the owners' shards."""
-        hooks = hasattr(self.module, "_word_lookup_hook") and name == "emb.word"
-        if not (hooks and len(entries) == self.world_size and all(e.part.sparse for e in entries)):
-            return False
-        entries.sort(key=lambda e: e.part.offset)
-        # The scatter-add into owner shards uses floating-point atomics, whose order of addition varies from run to
-        # run; AUTODIST_DETERMINISTIC=1 (or AUTODIST_SPARSE_ROWS=0) keeps the table replicated and its gradient on the
-        # dense reduce-scatter path, which adds in a fixed order.
-        if [e.owner for e in entries] != list(range(self.world_size)) or os.environ.get("AUTODIST_SPARSE_ROWS", "1") == "0" \
-                or os.environ.get("AUTODIST_DETERMINISTIC", "0") == "1":
-            return False
-        fl = self.flat
-        p = fl.params[fl.names.index(name)]
-        V, H = p.shape
-        q, rem = divmod(V, self.world_size)
-        if [e.part.size for e in entries] != [q + (1 if i < rem else 0) for i in range(self.world_size)] or H % 8:
-            return False
-        cap = q + 1
-        my_rows, my_off = entries[self.rank].part.size, entries[self.rank].part.offset
-        shard16, s16ptrs, _ = self.arena.alloc(cap * H, torch.bfloat16)
-        grad32, g32ptrs, _ = self.arena.alloc(cap * H, torch.float32)
-        master = fl.w32[name][my_off:my_off + my_rows].reshape(-1).clone()
-        shard16.zero_()
-        shard16[:my_rows * H].copy_(master)
-        st = {"V": V, "H": H, "rows": my_rows, "off": my_off, "shard16": shard16, "s16ptrs": s16ptrs, "grad32": grad32,
-              "g32ptrs": g32ptrs, "master": master, "name": name, "var": var_name,
-              "s1": torch.zeros_like(master) if self._needs_slot1() else None,
-              "s2": torch.zeros_like(master) if self.opt_kind in ("Adam", "AdamW") else None}
-        self.sharded_rows[name] = st
-        self.module._word_lookup_hook = lambda ids: self._lookup_rows(st, ids)
-        self.module._word_grad_hook = lambda ids, rows: self._push_rows(st, ids, rows)
-        return True
+    def _row_shard_candidates(self):
+        return row_shard_candidates(self.item, self.plan, not isinstance(self.module, _AutogradModel))
 
-    def _lookup_rows(self, st, ids):
-        out = torch.empty(ids.numel(), st["H"], dtype=torch.bfloat16, device=self.device)
-        self.E.embedding_gather_peers(*self.arena.ctx(1), st["s16ptrs"], ids, out, st["V"], True, 32)
-        return out
+    def _setup_sharded_rows(self, row_sharded):
+        if not row_sharded:
+            return
+        arena = self.arena if self.world_size > 1 else LocalArena(self.device)
+        self._rows_arena = arena
+        for var_name, p in row_sharded.items():
+            full = p.data
+            if self.world_size > 1:
+                # rank 0's initial values, like every other variable
+                full = full.to(self.device, torch.float32).contiguous()
+                self.backend.broadcast_(full, 0)
+            st = ShardedRows(self, var_name, p, full, arena)
+            del full
+            self.sharded_rows[var_name] = st
+            p._sparse_rows = st                      # ops.functional.sparse_lookup and the fused models route through it
 
-    def _push_rows(self, st, ids, rows):
-        st["grad32"].zero_()
-        self.E.sparse_scatter_add(*self.arena.ctx(1), st["g32ptrs"], ids, rows, st["V"], 1.0 / self.world_size, 32)
-        n = st["rows"] * st["H"]
+    def _finish_rows(self):
+        """After the last push of a step: meet the peers (every rank's rows have landed), then every owner updates its shards."""
+        if not self.sharded_rows:
+            return
+        if self.world_size > 1:
+            self.E.sym_barrier(*self.arena.ctx(1), 1)
+        for st in self.sharded_rows.values():
+            st.update()
+
+    def _apply_optimizer(self, p, gr, s1, s2, p16):
         g = self.opt_info.optimizer.param_groups[0]
-        p, gr, p16 = st["master"], st["grad32"][:n], st["shard16"][:n]
         if self.opt_kind in ("Adam", "AdamW"):
             b1, b2 = g["betas"]
-            self.E.adam_update(p, gr, st["s1"], st["s2"], p16, self.lr, b1, b2, g["eps"], g["weight_decay"],
-                               self.opt_kind == "AdamW", self.opt_step, 1.0)
+            self.E.adam_update(p, gr, s1, s2, p16, self.lr, b1, b2, g["eps"], g["weight_decay"], self.opt_kind == "AdamW", self.opt_step, 1.0)
         elif self.opt_kind == "SGD":
-            self.E.sgd_update(p, gr, st["s1"], p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"],
-                              self.opt_step, 1.0)
+            self.E.sgd_update(p, gr, s1, p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"], self.opt_step, 1.0)
         else:
-            self.E.adagrad_update(p, gr, st["s1"], p16, self.lr, g["eps"], g["weight_decay"], 1.0)
-
-    def _gather_sharded(self, st, local_flat):
-        """Full [V, H] tensor from every owner's rows (checkpoints, variable fetches)."""
-        cap = st["V"] // self.world_size + 1
-        pad = torch.zeros(cap * st["H"], dtype=torch.float32, device=self.device)
-        pad[:local_flat.numel()].copy_(local_flat)
-        parts = [torch.empty_like(pad) for _ in range(self.world_size)]
-        dist.all_gather(parts, pad, group=self.backend.group)
-        q, rem = divmod(st["V"], self.world_size)
-        rows = [q + (1 if i < rem else 0) for i in range(self.world_size)]
-        return torch.cat([parts[i][:rows[i] * st["H"]] for i in range(self.world_size)]).view(st["V"], st["H"])
+            self.E.adagrad_update(p, gr, s1, p16, self.lr, g["eps"], g["weight_decay"], 1.0)
 
     def _ps_table(self, lo, hi):
         """Device tables of this rank's owned segments inside [lo, hi) (cached per flight)."""
@@ -502,6 +638,8 @@ class FusedStepEngine(StepEngine):
                 self.launches_per_step += self._ps_update_range(lo, hi)
             else:
                 covered = [(lo, hi, None, False)]
+            if (lo, hi) in getattr(self, "_deferred_ranges", ()):
+                return                                   # clipped parameters inside: updated once the global norm is known
             for a, b, _, _ in covered:
                 self._update_range(a, b)
             self.launches_per_step += 2 * len(covered)
@@ -535,7 +673,9 @@ class FusedStepEngine(StepEngine):
             all_nodes.append(train_op.loss_node)
         self.E.increment(self.opt_step)
         self.launches_per_step = 0
+        self._rows_sync_pending, self._rows_dirty = True, False
         values = self.forward(all_nodes, feeds, grad=True)
+        self._finish_rows()
         # the optimizer kernels of the last flights run on the communication stream: join it
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
@@ -599,15 +739,17 @@ class FusedStepEngine(StepEngine):
         self.module.check_error()
         if self.arena is not None:
             self.arena.check()
+        elif getattr(self, "_rows_arena", None) is not None:
+            self._rows_arena.check()
 
     def before_read(self):
         return
 
     # ------------------------------------------------------------------ state
     def variable_value(self, name):
-        for st in self.sharded_rows.values() if hasattr(self, "sharded_rows") else ():
-            if st["var"] == name:
-                return self._gather_sharded(st, st["master"])
+        st = self.sharded_rows.get(name)
+        if st is not None:
+            return st.gather(st.master)
         return self._params[name].detach()
 
     def optimizer_slots(self):
@@ -642,11 +784,12 @@ class FusedStepEngine(StepEngine):
                 if buf is not None:
                     out[f"{full}/{slot}"] = buf[o:o + n].view(p.shape).clone()
             out[f"{full}/step"] = torch.as_tensor(float(self.global_step))
-        for st in getattr(self, "sharded_rows", {}).values():
-            full = st["var"][:-2]
-            for slot, buf in zip(names, (st["s1"], st["s2"])):
+        for st in self.sharded_rows.values():
+            full = st.var[:-2]
+            for slot, buf in zip(names, (st.s1, st.s2)):
                 if buf is not None:
-                    out[f"{full}/{slot}"] = self._gather_sharded(st, buf)
+                    out[f"{full}/{slot}"] = st.gather(buf)
+            out[f"{full}/step"] = torch.as_tensor(float(self.global_step))
         return out
 
     def load_optimizer_slots(self, slots, default_step=0):
@@ -667,21 +810,17 @@ class FusedStepEngine(StepEngine):
                 for owned, full_buf in ((self.ps_s1, self.slot1), (self.ps_s2, self.slot2)):
                     if owned is not None and full_buf is not None:
                         owned[o:o + ln].copy_(full_buf[st_:st_ + ln])
-        for st in getattr(self, "sharded_rows", {}).values():
-            base = self.flat.offsets[st["name"]] + st["off"] * st["H"]
-            n = st["rows"] * st["H"]
-            for owned, full_buf in ((st["s1"], self.slot1), (st["s2"], self.slot2)):
-                if owned is not None and full_buf is not None:
-                    owned.copy_(full_buf[base:base + n])
+        for st in self.sharded_rows.values():
+            full = st.var[:-2]
+            loaded = [slots.get(f"{full}/{slot}") for slot in names] + [None]
+            st.load_slots(loaded[0], loaded[1] if len(names) > 1 else None)
         self.opt_step.fill_(int(default_step))
 
     def after_restore(self):
         self.flat.refresh_bf16()
         self.opt_step.fill_(self.global_step)
-        for st in getattr(self, "sharded_rows", {}).values():
-            n = st["rows"] * st["H"]
-            st["master"].copy_(self.flat.w32[st["name"]][st["off"]:st["off"] + st["rows"]].reshape(-1))
-            st["shard16"][:n].copy_(st["master"])
+        for st in self.sharded_rows.values():
+            st.load(st.param.data)                   # the restore wrote the full table into the parameter
         for st_, ln, ow in getattr(self, "ps_segments", []):
             if ow == self.rank:
                 o = self._state_offset[st_]
@@ -699,12 +838,14 @@ class _AutogradModel:
         self.flat = None
         self.grad_ready = None
 
-    def materialize(self, device, grad_alloc=None, master_alloc=None, p16_alloc=None):
+    def materialize(self, device, grad_alloc=None, master_alloc=None, p16_alloc=None, exclude=()):
+        """``exclude``: ids of parameters that stay outside the flat buffers (row-sharded tables: their full value stays
+        where it is, on the host, as the source for shards and checkpoints)."""
         from autodist_b200.ops.flat import FlatParams
         with torch.no_grad():
             for b in self.item.root.buffers():
                 b.data = b.data.to(device)
-        named = [(n[:-2], p) for n, p in self.item.named_parameters()]
+        named = [(n[:-2], p) for n, p in self.item.named_parameters() if id(p) not in exclude]
         frozen = [p for _, p in named if not p.requires_grad]
         with torch.no_grad():
             for p in frozen:
@@ -737,10 +878,25 @@ class FlatAutogradEngine(FusedStepEngine):
         params = [p for _, p in graph_item.named_parameters() if p.requires_grad]
         if not params or any(p.dtype != torch.float32 for p in params):
             return False
-        if any(v.sparse_grad for v in graph_item.variables.values()):
-            return False
         updated = graph_item.updated_variable_names()
         if any(graph_item.name_of_parameter(p) not in updated for p in params):
+            return False
+        # Row-sparse variables: tables that can live as one row shard per rank, or vectors (whose gradient arrives dense).
+        # Any other sparse variable keeps the generic engine's row exchange.
+        sharded = row_shard_candidates(graph_item, plan, False)
+        for name, p in graph_item.named_parameters():
+            var = graph_item.variables.get(name)
+            if var is not None and var.sparse_grad and p.requires_grad and name not in sharded and p.dim() != 1:
+                return False
+        # Global-norm clipping needs the complete reduced gradient before any update: possible for variables whose
+        # gradients are all-reduced (every replica then applies the same clipped update), not for parameter-server parts,
+        # whose kernel reduces and updates in one pass.
+        ps_vars = {e.part.var_name for e in plan.ps_entries.values()}
+        for op in graph_item.train_ops:
+            if op.clip_global_norm and plan.replica.world_size > 1:
+                if any(graph_item.name_of_parameter(p) in ps_vars for p in op.clip_global_norm[1]):
+                    return False
+        if len([op for op in graph_item.train_ops if op.clip_global_norm]) > 1:
             return False
         return FusedStepEngine.supports(graph_item, plan, None)
 
@@ -766,6 +922,7 @@ class FlatAutogradEngine(FusedStepEngine):
                 for m in members:
                     self._flight_of[m] = len(self._flights) - 1
                 members, hi = [], lo
+        self._setup_clip()
         for name, p in zip(fl.names, fl.params):
             hook = self._make_hook(name)
             p.register_post_accumulate_grad_hook(hook)
@@ -773,6 +930,46 @@ class FlatAutogradEngine(FusedStepEngine):
             # bypass autograd's accumulation and report completion through this attribute instead
             p._direct_grad = os.environ.get("AUTODIST_DIRECT_GRAD", "1") == "1"
             p._grad_ready_hook = hook
+
+    def _setup_clip(self):
+        """Global-norm clipping (``minimize(..., clip_global_norm=(max_norm, parameters))``): flights that carry a clipped
+        parameter are reduced as they complete, but their optimizer kernels wait until the norm of all clipped gradients is
+        known (``sumsq`` over the reduced ranges into a device scalar, ``clip_scale`` in place) - the norm never visits the host."""
+        self._clip = None
+        ops_ = [op for op in self.item.train_ops if op.clip_global_norm]
+        if not ops_:
+            return
+        max_norm, params = ops_[0].clip_global_norm
+        fl = self.flat
+        flat_of = {id(p): n for n, p in zip(fl.names, fl.params)}
+        ranges = sorted((fl.offsets[flat_of[id(p)]], fl.offsets[flat_of[id(p)]] + p.numel()) for p in params if id(p) in flat_of)
+        deferred = []
+        for i, f in enumerate(self._flights):
+            if any(lo < f["hi"] and hi > f["lo"] for lo, hi in ranges):
+                deferred.append(i)
+                f["deferred"] = True
+        self._clip = {"max_norm": float(max_norm), "ranges": ranges, "flights": deferred,
+                      "acc": torch.zeros(1, dtype=torch.float32, device=self.device)}
+        self._deferred_ranges = {(self._flights[i]["lo"], self._flights[i]["hi"]) for i in deferred}
+
+    def _finish_clipped(self):
+        c = getattr(self, "_clip", None)
+        if not c:
+            return
+        fl = self.flat
+        compute = torch.cuda.current_stream()
+        self._ready_event.record(compute)
+        self.comm_stream.wait_event(self._ready_event)
+        with torch.cuda.stream(self.comm_stream):          # behind the reductions of every flight
+            c["acc"].zero_()
+            for lo, hi in c["ranges"]:
+                self.E.sumsq(fl.grad[lo:hi], c["acc"], 1.0)
+            for lo, hi in c["ranges"]:
+                self.E.clip_scale(fl.grad[lo:hi], c["acc"], c["max_norm"])
+            for i in c["flights"]:
+                f = self._flights[i]
+                for a, b, _, _ in (self._policy_for(f["lo"], f["hi"]) if self.world_size > 1 else [(f["lo"], f["hi"], None, False)]):
+                    self._update_range(a, b)
 
     def _make_hook(self, name):
         def hook(param):
@@ -792,6 +989,7 @@ class FlatAutogradEngine(FusedStepEngine):
             all_nodes.append(train_op.loss_node)
         self.E.increment(self.opt_step)
         self.launches_per_step = 0
+        self._rows_sync_pending, self._rows_dirty = True, False
         fl = self.flat
         fl.grad.zero_()
         for f in self._flights:
@@ -806,6 +1004,8 @@ class FlatAutogradEngine(FusedStepEngine):
             if not f["sent"]:
                 f["sent"] = True
                 self._on_grad_ready(f["lo"], f["hi"])
+        self._finish_rows()
+        self._finish_clipped()
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
         return values

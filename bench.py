@@ -167,7 +167,7 @@ def run_ours(model_name, args, n_gpus, world, rank):
 
     kind = _kind(model_name)
     batch = args.batch or _default_batch(model_name)
-    strategy = args.strategy or ("parallax" if kind == "bert" and n_gpus > 1 else "allreduce")
+    strategy = args.strategy or ("parallax" if kind in ("bert", "lm") and n_gpus > 1 else "allreduce")
     builders = {
         "allreduce": lambda: S.AllReduce(chunk_size=256 if kind == "bert" else 512),
         "allreduce_ef": lambda: S.AllReduce(chunk_size=256 if kind == "bert" else 512, compressor="HorovodCompressorEF"),
@@ -362,8 +362,8 @@ def main():
                                                               "resnet50", "densenet121", "inceptionv3", "lm1b", "lm1b-tiny"])
     ap.add_argument("--strategy", default=None, choices=["allreduce", "allreduce_ef", "powersgd", "parallax", "ps", "partitioned_ps",
                                                          "uneven_partitioned_ps"],
-                    help="default: parallax for BERT on more than one GPU (dense gradients all-reduced, word embeddings through the "
-                         "sparse parameter-server path), allreduce otherwise")
+                    help="default: parallax for BERT and LM1B on more than one GPU (dense gradients all-reduced, embedding tables "
+                         "through the sparse parameter-server path), allreduce otherwise")
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU (default: 32 sequences, 64 images, 32 for vgg16)")
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--comm", default=None, help="fused (own kernels) or nccl (baseline)")

@@ -142,7 +142,7 @@ def main():
     ids = torch.randint(0, V, (777 + 13 * rank,), device=dev)
     out = torch.empty(ids.numel(), H, dtype=torch.bfloat16, device=dev)
     torch.cuda.synchronize(); dist.barrier()
-    E.embedding_gather_peers(*ctx(), s16ptrs, ids, out, V, True, 16)
+    E.embedding_gather_peers(*ctx(), s16ptrs, ids, out, V, 3, 16)
     torch.cuda.synchronize()
     arena.check()
     assert torch.equal(out, table[ids]), "peer gather mismatch"
@@ -154,7 +154,7 @@ def main():
     dense /= world
     shard32.zero_()
     torch.cuda.synchronize(); dist.barrier()
-    E.sparse_scatter_add(*ctx(), s32ptrs, ids, vals, V, 1.0 / world, 16)
+    E.sparse_scatter_add(*ctx(), s32ptrs, None, ids, vals, V, 1.0 / world, 3, 16)
     torch.cuda.synchronize()
     arena.check()
     check("sparse_scatter_add owner shard", shard32[:my_rows * H].view(my_rows, H), dense[my_off:my_off + my_rows], 1e-4)

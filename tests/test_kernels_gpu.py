@@ -213,7 +213,7 @@ def test_xent(E):
     assert logits[:, V:].abs().max().item() == 0
 
 
-def test_embedding_and_row_ops(E):
+def test_embedding_and_row_ops(E, err):
     torch.manual_seed(8)
     V, H, B, S = 500, 256, 4, 32
     word, pos, typ = _rand(V, H), _rand(64, H), _rand(2, H)
@@ -221,6 +221,7 @@ def test_embedding_and_row_ops(E):
     tt = torch.randint(0, 2, (B * S,), device="cuda")
     z = torch.empty(B * S, H, dtype=torch.bfloat16, device="cuda")
     E.embed_sum(word, pos, typ, ids, tt, z, S, err)
+    assert err.item() == 0
     ref = word.float()[ids] + pos.float()[torch.arange(B * S, device="cuda") % S] + typ.float()[tt]
     _check(z, ref, 1e-2)
     dz = _rand(B * S, H)
