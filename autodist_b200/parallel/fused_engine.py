@@ -544,6 +544,8 @@ class FusedStepEngine(StepEngine):
             o = self._state_offset[st]
             self.ps_master[o:o + ln].copy_(fl.master[st:st + ln])
         self.ps_s1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
+        if self.opt_kind == "Adagrad":
+            self.ps_s1.fill_(float(self.opt_info.optimizer.param_groups[0].get("initial_accumulator_value", 0.0)))
         self.ps_s2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
 
     # ---- row-sparse variables sharded over all ranks: K4 (scatter-add to owners) / K5 (gather from owners) ----------

@@ -91,6 +91,41 @@ def run_cnn(strategy_name, comm, world, rank):
     return state, losses, engine
 
 
+def run_lm1b(comm, world, rank):
+    """LM1B-tiny under Parallax with GPU owners: the embedding and softmax tables as row shards (gather from owners, scatter-add
+    into owners, flagged-row Adagrad), the LSTM gradients all-reduced and clipped by their global norm."""
+    os.environ["AUTODIST_COMM"] = comm
+    os.environ["AUTODIST_AUTOGRAD_GRAPH"] = "0"          # eager launches: both engines then draw the same random negatives
+    from autodist_b200 import AutoDist, strategy as S
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.models.lm1b import LM1B, LM1BConfig, zipf_tokens
+    from autodist_b200.resource_spec import ResourceSpec
+    _reset_default_autodist()
+    cfg = LM1BConfig.tiny()
+    cfg.keep_prob = 1.0
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=S.Parallax(chunk_size=16, reduction_devices="gpu"))
+    data = zipf_tokens(8 * world, cfg.num_steps, cfg.vocab_size, seed=3)
+    with ad.scope():
+        torch.manual_seed(0)
+        torch.cuda.manual_seed(0)
+        model = LM1B(cfg)
+        phs = {k: ad.placeholder((None,) + tuple(v.shape[1:]), v.dtype, name=k) for k, v in data.items()}
+        loss = model(**phs)
+        opt = torch.optim.Adagrad(model.parameters(), lr=0.2, initial_accumulator_value=1.0)
+        train_op = opt.minimize(loss, clip_global_norm=(0.5, model.dense_parameters()))      # a bound small enough to bite
+        sess = ad.create_distributed_session()
+        losses = [float(sess.run([loss, train_op], {phs[k]: data[k] for k in phs})[0]) for _ in range(4)]
+        if hasattr(sess.engine, "check_errors"):
+            sess.engine.check_errors()
+        torch.cuda.synchronize()
+        state = {n: sess.engine.variable_value(n).float().cpu().clone() for n, _ in ad.graph_item.named_parameters()}
+        engine = type(sess.engine).__name__
+        rows = len(getattr(sess.engine, "sharded_rows", {}))
+        sess.close()
+    os.environ.pop("AUTODIST_AUTOGRAD_GRAPH", None)
+    return state, losses, engine, rows
+
+
 def check_checkpoint(world, rank):
     """Save under PartitionedPS on the fused engine (owner segments + row-sharded embedding), restore under AllReduce:
     the file holds full tensors under the original names and training continues from the same state."""
@@ -230,6 +265,14 @@ def main():
         if rank == 0:
             print(f"{name}: engines {ref_engine} vs {engine}, max |param diff| {diff:.2e} (tol {tol}), bf16 copy diff {d16:.2e}, "
                   f"loss {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
+    ref, ref_losses, ref_engine, _ = run_lm1b("nccl", world, rank)
+    got, losses, engine, rows = run_lm1b("fused", world, rank)
+    diff = max((got[n] - ref[n]).abs().max().item() for n in got)
+    ok = diff <= 2e-3 and engine == "FlatAutogradEngine" and ref_engine == "StepEngine" and rows == 2 and all(l == l for l in losses)
+    failures += 0 if ok else 1
+    if rank == 0:
+        print(f"lm1b Parallax_gpu: engines {ref_engine} vs {engine} ({rows} row-sharded tables), max |param diff| {diff:.2e}, "
+              f"loss {losses[0]:.3f} -> {losses[-1]:.3f} (reference {ref_losses[-1]:.3f}) {'ok' if ok else 'FAIL'}", flush=True)
     # Adam through the fused path: finite and decreasing
     _, _, losses, engine = run("PartitionedPS_gpu", "fused", world, rank, opt_name="adam")
     ok = losses[-1] < losses[0] and all(l == l for l in losses)
