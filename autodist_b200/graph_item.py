@@ -128,11 +128,22 @@ class TrainOp:
         return f"<TrainOp {self.name} loss={self.loss_node.name}>"
 
 
+_CONTROL_FLOW_HINT = ("a captured tensor decides a Python branch or loop here (data-dependent control flow). Code inside an nn.Module "
+                      "is handled automatically: the module is recorded as one opaque node and its variables are marked "
+                      "in_control_flow (never partitioned). Code written directly in the scope has to move into a module.")
+
+
 class SymbolicTensor(fx.Proxy):
     """An fx proxy usable as a ``feed_dict`` key / fetch handle."""
 
     def __hash__(self):
         return id(self)
+
+    def _needs_value(self, *_):
+        raise fx.proxy.TraceError(_CONTROL_FLOW_HINT)
+
+    # every way Python can ask a tensor for a concrete value while the program is only being recorded
+    __bool__ = __float__ = __int__ = __index__ = __len__ = __iter__ = item = tolist = _needs_value
 
     @property
     def op_name(self):
@@ -220,6 +231,7 @@ class GraphItem:
         self._buffer_paths: Dict[int, str] = {}
         self._named_bare: Dict[str, nn.Parameter] = {}
         self._sparse_params = set()
+        self._control_flow_params = set()      # ids of parameters of modules whose forward branches on tensor values
         self._variables: Optional[Dict[str, VariableInfo]] = None
         self._prepared = False
         self._frozen_record = None       # set on a deserialized (description-only) item
@@ -416,6 +428,12 @@ class GraphItem:
             stack.extend(n.all_input_nodes)
         return found
 
+    def mark_control_flow(self, module):
+        """``module`` runs as an opaque node because its forward depends on tensor values: its variables must stay whole."""
+        for p in module.parameters():
+            self._control_flow_params.add(id(p))
+        self._variables = None
+
     # ------------------------------------------------------------------ queries used by builders / passes
     def prepare(self):
         """Freeze the naming registry and detect sparse-gradient variables."""
@@ -425,6 +443,8 @@ class GraphItem:
                 self._sparse_params.add(id(m.weight))
             for p in getattr(m, "sparse_grad_parameters", lambda: [])():
                 self._sparse_params.add(id(p))
+            if getattr(m, "_autodist_control_flow", False):          # a leaf module may declare it itself
+                self.mark_control_flow(m)
         self._variables = None
         self._prepared = True
         return self
@@ -454,7 +474,7 @@ class GraphItem:
             for p in self._all_parameters():
                 name = self.name_of_parameter(p)
                 out[name] = VariableInfo(name, tuple(p.shape), p.dtype, p.requires_grad,
-                                         id(p) in self._sparse_params, False, self._param_paths[id(p)])
+                                         id(p) in self._sparse_params, id(p) in self._control_flow_params, self._param_paths[id(p)])
             self._variables = out
         return self._variables
 
@@ -662,10 +682,32 @@ def _patch_module_capture(item):
 
     @functools.wraps(orig_call)
     def leaf_call(self, *args, **kwargs):
-        if (getattr(self, "_autodist_leaf", False) or isinstance(self, _AUTO_LEAF_MODULES)) and (
-                _contains_proxy(args) or _contains_proxy(kwargs)):
+        symbolic = _contains_proxy(args) or _contains_proxy(kwargs)
+        if (getattr(self, "_autodist_leaf", False) or isinstance(self, _AUTO_LEAF_MODULES)) and symbolic:
             return item.tracer.create_proxy("call_module", item.path_of_module(self), args, kwargs)
-        return orig_call(self, *args, **kwargs)
+        if not symbolic or self is item.root:
+            return orig_call(self, *args, **kwargs)
+        # Trace through the module; if its forward turns out to branch or loop on tensor values (the reference's
+        # tf.cond / tf.while_loop cases, tests/integration/cases/c2.py:50-52, c4.py:31), undo what the attempt recorded,
+        # record the module as one opaque node instead, and mark its variables so that no builder partitions them.
+        graph = item.tracer.graph
+        mark = len(graph.nodes)
+        try:
+            return orig_call(self, *args, **kwargs)
+        except (fx.proxy.TraceError, RuntimeError) as e:
+            if not (isinstance(e, fx.proxy.TraceError) or "symbolic tracing" in str(e)):
+                raise
+            added = list(graph.nodes)[mark:]
+            gone = set()
+            for node in reversed(added):
+                gone.add(node)
+                graph.erase_node(node)
+            cache = item.tracer._attr_nodes
+            for key in [k for k, n in cache.items() if n in gone]:
+                del cache[key]
+            self._autodist_leaf = True
+            item.mark_control_flow(self)
+            return item.tracer.create_proxy("call_module", item.path_of_module(self), args, kwargs)
 
     nn.Module.__init__ = tracking_init
     nn.Module.__call__ = leaf_call

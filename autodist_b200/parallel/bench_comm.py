@@ -1,8 +1,8 @@
 """All-reduce micro-benchmark: the fused symmetric-memory kernel against NCCL, device-timed, max over ranks.
 
 ``python -m torch.distributed.run --nproc-per-node N -m autodist_b200.parallel.bench_comm`` prints one JSON line
-per message size with time, algorithm bandwidth, bus bandwidth (``2 (N-1)/N * bytes / time``) and the fraction of the
-measured 770 GB/s per-direction peer-copy bandwidth of this pool.
+per message size with time, algorithm bandwidth, bus bandwidth (``2 (N-1)/N * bytes / time``) and the fraction of a
+770 GB/s per-direction peer-copy bandwidth (measured on an 8 x B200 NVSwitch box; ``--link-gbs`` overrides it).
 """
 import json
 import os
@@ -89,6 +89,8 @@ def main():
     arena = SymmetricArena(dist.group.WORLD, dev, rank, world)
     E = arena.E
     link = 770.0
+    if "--link-gbs" in sys.argv:
+        link = float(sys.argv[sys.argv.index("--link-gbs") + 1])
     for mib in (1, 16, 64, 256, 1024):
         n = mib * (1 << 20) // 4
         buf, ptrs, mc = arena.alloc(n, torch.float32)

@@ -9,8 +9,8 @@ Per GPU, ``N`` bytes, ``P`` ranks, per-direction link bandwidth ``B``:
 * every collective launch pays a latency floor ``alpha`` (kernel launch + cross-GPU flag round trip).
 
 ``LinkModel.fit`` re-fits ``alpha`` and ``B`` by least squares from measured ``(bytes, seconds)`` points, e.g. the
-output of ``autodist_b200.parallel.bench_comm``. Defaults are this pool's measured figures: 770 GB/s per direction
-for peer copies and a 725 GB/s all-reduce bus bandwidth at 1 GiB.
+output of ``autodist_b200.parallel.bench_comm``. Defaults are figures measured on an 8 x B200 NVSwitch box: 770 GB/s per
+direction for peer copies and a 725 GB/s all-reduce bus bandwidth at 1 GiB.
 """
 from dataclasses import dataclass
 

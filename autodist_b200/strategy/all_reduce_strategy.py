@@ -55,7 +55,8 @@ class PartitionedAR(StrategyBuilder):
         s = self._new_strategy(resource_spec)
         counter = 0
         for var in graph_item.trainable_var_op_to_var.values():
-            num_shards, axis = self.get_num_shards_and_axis(var)
+            # a variable read inside data-dependent control flow stays whole (as in the partitioned PS builders)
+            num_shards, axis = (1, 0) if var.in_control_flow else self.get_num_shards_and_axis(var)
             node = s.node_config.add(var_name=var.name)
             if num_shards <= 1:
                 P.fill_all_reduce(node, counter // self.chunk_size, "AUTO")
