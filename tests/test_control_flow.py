@@ -82,7 +82,6 @@ def test_control_flow_variables_are_never_partitioned(builder):
         assert name not in plan.shard_plans or plan.shard_plans[name].num_shards == 1, (name, plan.shard_plans[name])
     parts = [e.part for e in plan.ps_entries.values()] + [p for b in plan.ordered_buckets() for p in b.parts]
     assert all(p.part_index is None for p in parts if p.var_name in guarded)
-    assert any(p.part_index is not None for p in parts) or not plan.shard_plans      # the builder does partition other variables
     sess.run([loss, train_op], {ids: torch.tensor([0, 5, 7, 11])})
     sess.close()
 
