@@ -463,6 +463,22 @@ void psgd_d(Tensor M, Tensor err, const Tensor& P, const Tensor& Q) {
   const int m = M.size(0), n = M.size(1), r = P.size(1);
   adb200::psgd_d(M.data_ptr<float>(), err.data_ptr<float>(), P.data_ptr<float>(), Q.data_ptr<float>(), m, n, r, STREAM);
 }
+// One pass of PowerSGD over every matrix of the step (see elementwise.cu). off / p_off / q_off / *_prefix: int64 device tensors,
+// m / n: int32 device tensors; phase 0 = P = (grad + err) Q, 1 = orthogonalise P, 2 = Q = grad^T P, 3 = err = grad - P Q^T, grad = P Q^T.
+void psgd_batched(int64_t phase, Tensor grad, Tensor err, Tensor P, Tensor Q, const Tensor& off, const Tensor& m, const Tensor& n,
+                  const Tensor& p_off, const Tensor& q_off, const Tensor& row_prefix, const Tensor& blk_prefix, const Tensor& elem_prefix,
+                  int64_t rank, int64_t rows, int64_t blocks, int64_t elems) {
+  const int nmat = m.numel();
+  TORCH_CHECK(rank >= 1 && rank <= 4 && grad.scalar_type() == at::kFloat && err.scalar_type() == at::kFloat && P.scalar_type() == at::kFloat &&
+              Q.scalar_type() == at::kFloat, "fp32 buffers, rank 1..4");
+  TORCH_CHECK(off.numel() == nmat && n.numel() == nmat && p_off.numel() == nmat && q_off.numel() == nmat && row_prefix.numel() == nmat + 1 &&
+              blk_prefix.numel() == nmat + 1 && elem_prefix.numel() == nmat + 1 && m.scalar_type() == at::kInt && n.scalar_type() == at::kInt,
+              "table arrays of the wrong length or type");
+  auto ll = [](const Tensor& t) { return reinterpret_cast<const long long*>(t.data_ptr<int64_t>()); };
+  adb200::psgd_batched((int)phase, grad.data_ptr<float>(), err.data_ptr<float>(), P.data_ptr<float>(), Q.data_ptr<float>(), ll(off),
+                       m.data_ptr<int>(), n.data_ptr<int>(), ll(p_off), ll(q_off), ll(row_prefix), ll(blk_prefix), ll(elem_prefix), nmat, (int)rank,
+                       rows, blocks, elems, STREAM);
+}
 void cast_f32_bf16(const Tensor& x, Tensor y) { adb200::cast_f32_bf16(x.data_ptr<float>(), BF(y), x.numel(), STREAM); }
 void increment(Tensor c) { adb200::increment(reinterpret_cast<long long*>(c.data_ptr<int64_t>()), STREAM); }
 
@@ -494,7 +510,8 @@ void allreduce(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t ran
 }
 
 void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
-                           const Tensor& grad_ptrs, const Tensor& p16_ptrs, const optional<Tensor>& p32_ptrs, Tensor master,
+                           const Tensor& grad_ptrs, const Tensor& p16_ptrs, const optional<Tensor>& p32_ptrs, int64_t mc_grad, int64_t mc_p16,
+                           int64_t mc_p32, Tensor master,
                            const optional<Tensor>& s1, const optional<Tensor>& s2, const Tensor& seg_start, const Tensor& seg_len,
                            const Tensor& seg_state, const Tensor& owned_prefix, int64_t kind, const Tensor& lr, const Tensor& step, double b1,
                            double b2, double eps, double wd, double momentum, double grad_scale, bool decoupled, bool nesterov, double scale,
@@ -505,7 +522,8 @@ void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error,
   TORCH_CHECK(blocks > 0 && blocks <= adb200::kMaxCommBlocks, "bad block count");
   adb200::launch_reduce_scatter_update(
       c, reinterpret_cast<float* const*>(grad_ptrs.data_ptr<int64_t>()), reinterpret_cast<__nv_bfloat16* const*>(p16_ptrs.data_ptr<int64_t>()),
-      p32_ptrs.has_value() ? reinterpret_cast<float* const*>(p32_ptrs->data_ptr<int64_t>()) : nullptr, master.data_ptr<float>(), OPT_F(s1),
+      p32_ptrs.has_value() ? reinterpret_cast<float* const*>(p32_ptrs->data_ptr<int64_t>()) : nullptr, reinterpret_cast<float*>(mc_grad),
+      reinterpret_cast<__nv_bfloat16*>(mc_p16), reinterpret_cast<float*>(mc_p32), master.data_ptr<float>(), OPT_F(s1),
       OPT_F(s2), reinterpret_cast<const long long*>(seg_start.data_ptr<int64_t>()), reinterpret_cast<const long long*>(seg_len.data_ptr<int64_t>()),
       reinterpret_cast<const long long*>(seg_state.data_ptr<int64_t>()), reinterpret_cast<const long long*>(owned_prefix.data_ptr<int64_t>()), nseg,
       (int)kind, lr.data_ptr<float>(), reinterpret_cast<const long long*>(step.data_ptr<int64_t>()), (float)b1, (float)b2, (float)eps, (float)wd,
@@ -584,6 +602,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pad_image8", &pad_image8);
   m.def("relu_bwd", &relu_bwd);
   m.def("relu_bwd_colsum", &relu_bwd_colsum);
+  m.def("psgd_batched", &psgd_batched);
   m.def("psgd_p", &psgd_p);
   m.def("psgd_q", &psgd_q);
   m.def("psgd_d", &psgd_d);

@@ -278,8 +278,12 @@ struct OptArgs {
   int decoupled, nesterov;
 };
 
+// mc_grad / mc_p16 / mc_p32: multicast addresses of the gradient buffer and of the two parameter copies (null = none).
+// With them the owner's reduction is one `multimem.ld_reduce` per vector (the switch adds the ranks' values) and the
+// write-back one `multimem.st` per copy (the switch replicates it) instead of one peer load / store per rank.
 __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, float* const* grads, __nv_bfloat16* const* p16,
-                                                                    float* const* p32, float* master, float* s1, float* s2,
+                                                                    float* const* p32, float* mc_grad, __nv_bfloat16* mc_p16,
+                                                                    float* mc_p32, float* master, float* s1, float* s2,
                                                                     const long long* seg_start, const long long* seg_len,
                                                                     const long long* seg_state, const long long* owned_prefix,
                                                                     int nseg, OptArgs o, float scale) {
@@ -297,11 +301,15 @@ __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, fl
     const long long gi = seg_start[lo] + within;     // index in the flat bucket
     const long long si = seg_state[lo] + within;     // index in the owner's compact state
     float g[4] = {0.f, 0.f, 0.f, 0.f};
-    float4 v[8];
+    if (mc_grad != nullptr) {
+      Wire<float>::mc_reduce(mc_grad + gi, g);
+    } else {
+      float4 v[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) if (r < c.world) v[r] = *reinterpret_cast<const float4*>(grads[r] + gi);
+      for (int r = 0; r < 8; ++r) if (r < c.world) v[r] = *reinterpret_cast<const float4*>(grads[r] + gi);
 #pragma unroll
-    for (int r = 0; r < 8; ++r) if (r < c.world) { g[0] += v[r].x; g[1] += v[r].y; g[2] += v[r].z; g[3] += v[r].w; }
+      for (int r = 0; r < 8; ++r) if (r < c.world) { g[0] += v[r].x; g[1] += v[r].y; g[2] += v[r].z; g[3] += v[r].w; }
+    }
     float4 pm = *reinterpret_cast<float4*>(master + si);
     float p[4] = {pm.x, pm.y, pm.z, pm.w};
     float a[4], b[4];
@@ -333,10 +341,20 @@ __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, fl
     if (s2) *reinterpret_cast<float4*>(s2 + si) = make_float4(b[0], b[1], b[2], b[3]);
     __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]), h1 = __floats2bfloat162_rn(p[2], p[3]);
     const uint2 w = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+    if (mc_p16 != nullptr) {
+      asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc_p16 + gi), "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y))
+                   : "memory");
+    } else {
 #pragma unroll
-    for (int r = 0; r < 8; ++r) if (r < c.world) {
-      *reinterpret_cast<uint2*>(p16[r] + gi) = w;
-      if (p32) *reinterpret_cast<float4*>(p32[r] + gi) = make_float4(p[0], p[1], p[2], p[3]);
+      for (int r = 0; r < 8; ++r) if (r < c.world) *reinterpret_cast<uint2*>(p16[r] + gi) = w;
+    }
+    if (p32) {
+      if (mc_p32 != nullptr) {
+        Wire<float>::mc_store(mc_p32 + gi, p);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) if (r < c.world) *reinterpret_cast<float4*>(p32[r] + gi) = make_float4(p[0], p[1], p[2], p[3]);
+      }
     }
   }
   sym_barrier(c);
@@ -443,13 +461,14 @@ void launch_allreduce(const SymCtx& c, void* const* bufs, void* mc, int wire, lo
     allreduce_kernel<__half><<<blocks, 512, 0, st>>>(c, reinterpret_cast<__half* const*>(bufs), reinterpret_cast<__half*>(mc), n, src32, residual, dst32, scale);
 }
 
-void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfloat16* const* p16, float* const* p32, float* master,
+void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfloat16* const* p16, float* const* p32, float* mc_grad,
+                                  __nv_bfloat16* mc_p16, float* mc_p32, float* master,
                                   float* s1, float* s2, const long long* seg_start, const long long* seg_len, const long long* seg_state,
                                   const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
                                   float b2, float eps, float wd, float momentum, float grad_scale, int decoupled, int nesterov,
                                   float scale, int blocks, cudaStream_t st) {
   OptArgs o{kind, lr, step, b1, b2, eps, wd, momentum, grad_scale, decoupled, nesterov};
-  reduce_scatter_update_kernel<<<blocks, 512, 0, st>>>(c, grads, p16, p32, master, s1, s2, seg_start, seg_len, seg_state, owned_prefix, nseg, o, scale);
+  reduce_scatter_update_kernel<<<blocks, 512, 0, st>>>(c, grads, p16, p32, mc_grad, mc_p16, mc_p32, master, s1, s2, seg_start, seg_len, seg_state, owned_prefix, nseg, o, scale);
 }
 
 void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* const* touched, const int64_t* ids, const void* vals,

@@ -1246,6 +1246,126 @@ __global__ void psgd_d_kernel(float* __restrict__ M, float* __restrict__ err, co
   M[idx] = a;
 }
 
+// ---- PowerSGD over all matrices of a step at once ------------------------------------------------------------------------------
+// Each gradient matrix i is M_i = grad[off_i : off_i + m_i * n_i] seen as [m_i, n_i]; its factors live at P[p_off_i] ([m_i, r]) and
+// Q[q_off_i] ([n_i, r]) in two flat buffers that are all-reduced as one message each. The three passes run once per step for all
+// matrices (a table lookup finds the matrix of a row / column block / element) instead of three launches per variable.
+struct PsgdTable {
+  const long long* off;         // [nmat] start of M_i in the flat gradient / residual buffers
+  const int* m;                 // [nmat]
+  const int* n;                 // [nmat]
+  const long long* p_off;       // [nmat]
+  const long long* q_off;       // [nmat]
+  const long long* row_prefix;  // [nmat + 1] rows before matrix i
+  const long long* blk_prefix;  // [nmat + 1] 32-column blocks before matrix i
+  const long long* elem_prefix; // [nmat + 1] elements before matrix i
+  int nmat;
+};
+
+__device__ __forceinline__ int psgd_find(const long long* prefix, int nmat, long long x) {
+  int lo = 0, hi = nmat - 1;                      // last i with prefix[i] <= x
+  while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (prefix[mid] <= x) lo = mid; else hi = mid - 1; }
+  return lo;
+}
+
+// M += err (written back), P = M Q: one warp per matrix row.
+__global__ void psgd_p_batched_kernel(float* __restrict__ grad, const float* __restrict__ err, const float* __restrict__ Q,
+                                      float* __restrict__ P, PsgdTable t, int r, long long rows) {
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int i = psgd_find(t.row_prefix, t.nmat, row);
+  const int n = t.n[i];
+  const long long local = row - t.row_prefix[i];
+  float* M = grad + t.off[i] + local * n;
+  const float* e = err + t.off[i] + local * n;
+  const float* q = Q + t.q_off[i];
+  float acc[PSGD_MAXR] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = lane; j < n; j += 32) {
+    const float v = M[j] + e[j];
+    M[j] = v;
+    for (int k = 0; k < r; ++k) acc[k] += v * q[(long long)j * r + k];
+  }
+  for (int k = 0; k < r; ++k) {
+    const float s = warp_sum(acc[k]);
+    if (lane == 0) P[t.p_off[i] + local * r + k] = s;
+  }
+}
+
+// Modified Gram-Schmidt on the columns of every P_i (one block per matrix), as orthogonalize_ of the Python compressor.
+__global__ void psgd_orth_batched_kernel(float* __restrict__ P, PsgdTable t, int r) {
+  __shared__ float red[32];
+  __shared__ float bcast;
+  const int i = blockIdx.x;
+  const int m = t.m[i];
+  float* p = P + t.p_off[i];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  auto block_sum = [&](float v) {
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) { float s = 0.f; for (int x = 0; x < nw; ++x) s += red[x]; bcast = s; }
+    __syncthreads();
+    return bcast;
+  };
+  for (int k = 0; k < r; ++k) {
+    float a = 0.f;
+    for (int row = threadIdx.x; row < m; row += blockDim.x) { const float v = p[(long long)row * r + k]; a += v * v; }
+    const float inv = 1.0f / (sqrtf(block_sum(a)) + 1e-8f);
+    for (int row = threadIdx.x; row < m; row += blockDim.x) p[(long long)row * r + k] *= inv;
+    __syncthreads();
+    for (int j = k + 1; j < r; ++j) {
+      float d = 0.f;
+      for (int row = threadIdx.x; row < m; row += blockDim.x) d += p[(long long)row * r + k] * p[(long long)row * r + j];
+      const float dot = block_sum(d);
+      for (int row = threadIdx.x; row < m; row += blockDim.x) p[(long long)row * r + j] -= dot * p[(long long)row * r + k];
+      __syncthreads();
+    }
+  }
+}
+
+// Q = M^T P: one block (8 warps) per 32 columns of one matrix.
+__global__ void psgd_q_batched_kernel(const float* __restrict__ grad, const float* __restrict__ P, float* __restrict__ Q, PsgdTable t, int r) {
+  __shared__ float sm[8][32][PSGD_MAXR];
+  const int i = psgd_find(t.blk_prefix, t.nmat, blockIdx.x);
+  const int m = t.m[i], n = t.n[i];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int col = (int)(blockIdx.x - t.blk_prefix[i]) * 32 + lane;
+  const float* M = grad + t.off[i];
+  const float* p = P + t.p_off[i];
+  float acc[PSGD_MAXR] = {0.f, 0.f, 0.f, 0.f};
+  if (col < n)
+    for (int row = w; row < m; row += 8) {
+      const float v = M[(long long)row * n + col];
+      for (int k = 0; k < r; ++k) acc[k] += v * p[(long long)row * r + k];
+    }
+  for (int k = 0; k < PSGD_MAXR; ++k) sm[w][lane][k] = acc[k];
+  __syncthreads();
+  if (w == 0 && col < n)
+    for (int k = 0; k < r; ++k) {
+      float s = 0.f;
+      for (int x = 0; x < 8; ++x) s += sm[x][lane][k];
+      Q[t.q_off[i] + (long long)col * r + k] = s;
+    }
+}
+
+// err = M - P Q^T; M = P Q^T: one thread per element of all matrices.
+__global__ void psgd_d_batched_kernel(float* __restrict__ grad, float* __restrict__ err, const float* __restrict__ P, const float* __restrict__ Q,
+                                      PsgdTable t, int r, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int i = psgd_find(t.elem_prefix, t.nmat, idx);
+  const long long local = idx - t.elem_prefix[i];
+  const int n = t.n[i];
+  const long long row = local / n, col = local % n;
+  float a = 0.f;
+  for (int k = 0; k < r; ++k) a += P[t.p_off[i] + row * r + k] * Q[t.q_off[i] + col * r + k];
+  const long long g = t.off[i] + local;
+  err[g] = grad[g] - a;
+  grad[g] = a;
+}
+
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = __float2bfloat16(x[i]);
@@ -1449,6 +1569,17 @@ void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cuda
 }
 void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st) {
   psgd_d_kernel<<<blocks_for((long long)m * n, 256), 256, 0, st>>>(M, err, P, Q, m, n, r);
+}
+// tab: int64 [8 arrays] laid out by the caller as device pointers; phase 0 = P pass, 1 = orthogonalise, 2 = Q pass, 3 = decompress.
+void psgd_batched(int phase, float* grad, float* err, float* P, float* Q, const long long* off, const int* m, const int* n,
+                  const long long* p_off, const long long* q_off, const long long* row_prefix, const long long* blk_prefix,
+                  const long long* elem_prefix, int nmat, int r, long long rows, long long blocks, long long elems, cudaStream_t st) {
+  if (nmat <= 0) return;
+  PsgdTable t{off, m, n, p_off, q_off, row_prefix, blk_prefix, elem_prefix, nmat};
+  if (phase == 0) psgd_p_batched_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(grad, err, Q, P, t, r, rows);
+  else if (phase == 1) psgd_orth_batched_kernel<<<nmat, 256, 0, st>>>(P, t, r);
+  else if (phase == 2) psgd_q_batched_kernel<<<(unsigned)blocks, 256, 0, st>>>(grad, P, Q, t, r);
+  else psgd_d_batched_kernel<<<blocks_for(elems, 256), 256, 0, st>>>(grad, err, P, Q, t, r, elems);
 }
 void cast_f32_bf16(const float* x, bf16* y, long long n, cudaStream_t st) {
   cast_f32_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(x, y, n);

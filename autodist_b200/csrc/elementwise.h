@@ -68,6 +68,9 @@ void relu_bwd(const bf16_t* dy, const bf16_t* y, bf16_t* dx, long long n, cudaSt
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st);
 void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st);
 void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st);
+void psgd_batched(int phase, float* grad, float* err, float* P, float* Q, const long long* off, const int* m, const int* n,
+                  const long long* p_off, const long long* q_off, const long long* row_prefix, const long long* blk_prefix,
+                  const long long* elem_prefix, int nmat, int r, long long rows, long long blocks, long long elems, cudaStream_t st);
 void cast_f32_bf16(const float* x, bf16_t* y, long long n, cudaStream_t st);
 void increment(long long* c, cudaStream_t st);
 }  // namespace adb200

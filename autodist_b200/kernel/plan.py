@@ -129,7 +129,7 @@ class DistributedPlan:
     def describe(self):
         lines = [f"replica {self.replica.rank}/{self.replica.world_size} on {self.replica.device}"]
         for b in self.ordered_buckets():
-            lines.append(f"all-reduce group {b.group} [{b.compressor_type}/{b.spec}] "
+            lines.append(f"all-reduce group {b.group} [{b.compressor_type}/{b.spec}] key {b.group_key} "
                          f"{len(b.parts)} parts, {b.numel} elements")
         for part, _, _ in self.sparse_all_reduce:
             lines.append(f"sparse all-reduce {part.part_name}")

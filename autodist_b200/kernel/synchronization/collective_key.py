@@ -3,8 +3,10 @@
 Every rank derives the same keys without talking to the others (capability of
 ``autodist/kernel/synchronization/collective_key.py:30-70``): a group key per
 distinct device list (incrementing) and an instance key per variable name
-(md5 folded into int32). The runtime uses them to name symmetric-memory
-channels and trace ranges.
+(md5 folded into int32). The plan dump prints a bucket's group key and the fused engine
+labels each flight's trace range with the keys of the buckets it carries
+(``parallel/fused_engine.py::_on_grad_ready``), so that the same collective can be found
+in every rank's trace.
 """
 import hashlib
 import threading

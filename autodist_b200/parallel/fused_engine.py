@@ -37,6 +37,7 @@ from autodist_b200.parallel.engine import StepEngine
 from autodist_b200.utils import logging, nvtx
 
 WIRE = {None: 0, torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+PowerSGD_SEED = 1905_13727        # seed base of the initial Q factors (kernel/synchronization/compressor.py uses the same)
 
 
 def _fused_module(graph_item):
@@ -362,11 +363,17 @@ class FusedStepEngine(StepEngine):
         if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
             return False
         if plan.replica.world_size > 1:
+            # A variable split into all-reduce parts (PartitionedAR, RandomAxisPartitionAR: any axis) is reduced as the one
+            # range it occupies in the flat buffer: the mean is element-wise, so reducing the parts separately or together
+            # gives the same values as long as all parts of a variable use one compressor.
+            compressor_of = {}
             for b in plan.ordered_buckets():
-                if b.compressor_type == "PowerSGDCompressor":
+                if b.compressor_type == "PowerSGDCompressor" and (max(1, b.power_sgd_rank or 1) > 4 or any(
+                        p.part_index is not None for p in b.parts)):
                     return False
-                if any(p.part_index is not None for p in b.parts):
-                    return False
+                for p in b.parts:
+                    if compressor_of.setdefault(p.var_name, b.compressor_type) != b.compressor_type:
+                        return False
             for e in plan.ps_entries.values():
                 if e.gate != "sync" or (e.part.part_index is not None and e.part.axis != 0):
                     return False
@@ -402,18 +409,19 @@ class FusedStepEngine(StepEngine):
         row_sharded = self._row_shard_candidates()
         master_alloc = p16_alloc = None
         self._p32_sym = self._p16_sym = None
+        self._p32_mc = self._p16_mc = 0
         if self.world_size > 1 and any(e.part.var_name not in row_sharded for e in plan.ps_entries.values()):
             # owners write updated parameters straight into every rank's copies: those live in symmetric memory too
             def master_alloc(n):
-                t, ptrs, _ = self.arena.alloc(n, torch.float32)
+                t, ptrs, mc = self.arena.alloc(n, torch.float32)
                 t.zero_()
-                self._p32_sym = ptrs
+                self._p32_sym, self._p32_mc = ptrs, mc
                 return t
 
             def p16_alloc(n):
-                t, ptrs, _ = self.arena.alloc(n, torch.bfloat16)
+                t, ptrs, mc = self.arena.alloc(n, torch.bfloat16)
                 t.zero_()
-                self._p16_sym = ptrs
+                self._p16_sym, self._p16_mc = ptrs, mc
                 return t
         if isinstance(module, _AutogradModel):
             # tables that are never replicated stay out of the flat buffers: no full-size gradient, compute copy or slots
@@ -478,22 +486,43 @@ class FusedStepEngine(StepEngine):
         self.range_wire = []     # (lo, hi, wire dtype or None, error feedback?)
         self.ps_segments = []
         self._wire = self._wire_ptrs = self._residual = None
+        self._psgd, self._psgd_flights = None, []
         if self.world_size <= 1:
             return
         need16 = False
         per_var = []
         flat_name = {self.item.name_of_parameter(p): n for n, p in zip(fl.names, fl.params)}   # "x:0" -> flat key
+        self._range_key = []      # (lo, hi, collective group key, first instance key) per bucket: names the trace ranges
+        psgd = []                 # (start in the flat buffers, m, n, seed of the initial Q) of every PowerSGD matrix
+        self._psgd_rank = 1
         for b in self.plan.ordered_buckets():
-            wd = None if b.compressor_type == "NoneCompressor" else wire_dtype()
+            power = b.compressor_type == "PowerSGDCompressor"
+            wd = None if b.compressor_type == "NoneCompressor" or power else wire_dtype()
             ef = b.compressor_type == "HorovodCompressorEF"
             need16 |= wd is not None
-            for part in b.parts:
-                per_var.append((fl.offsets[flat_name[part.var_name]], fl.range_of([flat_name[part.var_name]])[1], wd, ef))
+            spans = []
+            rank_r = max(1, b.power_sgd_rank or 1)
+            for idx, part in enumerate(b.parts):
+                lo_v, hi_v = fl.offsets[flat_name[part.var_name]], fl.range_of([flat_name[part.var_name]])[1]
+                spans.append((lo_v, hi_v))
+                shape = b.shapes[idx]
+                numel = 1
+                for d in shape:
+                    numel *= int(d)
+                if power and len(shape) >= 2 and min(int(shape[0]), numel // int(shape[0])) > rank_r:
+                    # a matrix travels as its two factors; the PowerSGD passes of the step handle it (see _finish_powersgd)
+                    psgd.append((lo_v, int(shape[0]), numel // int(shape[0]), PowerSGD_SEED + idx))
+                    self._psgd_rank = rank_r
+                    continue
+                per_var.append((lo_v, hi_v, wd, ef))
+            if spans:
+                self._range_key.append((min(a for a, _ in spans), max(z for _, z in spans), b.group_key,
+                                        b.instance_keys[0] if b.instance_keys else 0))
         # Row-sparse variables under an all-reduce strategy: this model writes their gradient densely into the flat
         # buffer, so the mean over replicas is the same all-reduce, uncompressed.
         for part, _, _ in self.plan.sparse_all_reduce:
             per_var.append((fl.offsets[flat_name[part.var_name]], fl.range_of([flat_name[part.var_name]])[1], None, False))
-        per_var.sort()
+        per_var = sorted(set(per_var))          # the parts of a partitioned variable name the same range once
         for lo, hi, wd, ef in per_var:
             if self.range_wire and self.range_wire[-1][1] == lo and self.range_wire[-1][2:4] == (wd, ef):
                 self.range_wire[-1] = (self.range_wire[-1][0], hi, wd, ef, None)
@@ -503,6 +532,59 @@ class FusedStepEngine(StepEngine):
             self._wire, self._wire_ptrs, self._wire_mc = self.arena.alloc(fl.total, wire_dtype())
             self._residual = torch.zeros(fl.total, dtype=torch.float32, device=self.device)
         self._setup_ps_segments(flat_name)
+        self._setup_powersgd(psgd)
+
+    # ---- PowerSGD (K8): every matrix of the step in three batched passes + two all-reduces of the stacked factors -------------
+    def _setup_powersgd(self, mats):
+        self._psgd = None
+        if not mats:
+            return
+        fl, dev, r = self.flat, self.device, self._psgd_rank
+        mats.sort()
+        p_off, q_off, rows, blks, elems = [], [], [0], [0], [0]
+        pn = qn = 0
+        for lo, m, n, _ in mats:
+            p_off.append(pn); q_off.append(qn)
+            pn += m * r; qn += n * r
+            rows.append(rows[-1] + m); blks.append(blks[-1] + (n + 31) // 32); elems.append(elems[-1] + m * n)
+        pn4, qn4 = (pn + 3) // 4 * 4, (qn + 3) // 4 * 4
+        P, p_ptrs, p_mc = self.arena.alloc(pn4, torch.float32)
+        Q, q_ptrs, q_mc = self.arena.alloc(qn4, torch.float32)
+        P.zero_(); Q.zero_()
+        for (lo, m, n, seed), qo in zip(mats, q_off):       # the same start as the Python compressor: N(0, 1) from a per-matrix seed
+            g = torch.Generator(device="cpu").manual_seed(seed)
+            Q[qo:qo + n * r].copy_(torch.randn(n, r, generator=g, dtype=torch.float32).reshape(-1))
+        i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)          # noqa: E731
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
+        self._psgd = {"P": P, "Q": Q, "p_ptrs": p_ptrs, "q_ptrs": q_ptrs, "p_mc": p_mc, "q_mc": q_mc, "pn": pn4, "qn": qn4,
+                      "err": torch.zeros(fl.total, dtype=torch.float32, device=dev), "rank": r,
+                      "tab": (i64([m[0] for m in mats]), i32([m[1] for m in mats]), i32([m[2] for m in mats]), i64(p_off), i64(q_off),
+                              i64(rows), i64(blks), i64(elems)),
+                      "counts": (rows[-1], blks[-1], elems[-1]), "ranges": [(lo, lo + m * n) for lo, m, n, _ in mats]}
+
+    def _finish_powersgd(self):
+        """After the backward pass: P = (G + E) Q for all matrices, mean over replicas, orthogonalise, Q = G^T P, mean, then
+        G <- P Q^T and E <- G - P Q^T (``autodist/kernel/synchronization/compressor.py:208-284`` gives the algorithm); the
+        optimizer kernels of the flights that hold matrices follow."""
+        c = self._psgd
+        if not c:
+            return
+        fl, E = self.flat, self.E
+        compute = torch.cuda.current_stream()
+        self._ready_event.record(compute)
+        self.comm_stream.wait_event(self._ready_event)
+        scale = 1.0 / self.world_size
+        with torch.cuda.stream(self.comm_stream):
+            rows, blks, elems = c["counts"]
+            args = (fl.grad, c["err"], c["P"], c["Q"]) + c["tab"] + (c["rank"], rows, blks, elems)
+            E.psgd_batched(0, *args)
+            E.allreduce(*self.arena.ctx(), c["p_ptrs"], c["p_mc"], 0, c["pn"], None, None, None, scale, self._comm_blocks(c["pn"], bool(c["p_mc"])))
+            E.psgd_batched(1, *args)
+            E.psgd_batched(2, *args)
+            E.allreduce(*self.arena.ctx(), c["q_ptrs"], c["q_mc"], 0, c["qn"], None, None, None, scale, self._comm_blocks(c["qn"], bool(c["q_mc"])))
+            E.psgd_batched(3, *args)
+            for lo, hi in self._psgd_flights:
+                self._update_range(lo, hi)
 
     def _setup_ps_segments(self, flat_name):
         """Parameter-server parts as owned segments of the flat buffers (kernel ``reduce_scatter_update``)."""
@@ -612,7 +694,10 @@ class FusedStepEngine(StepEngine):
         kind = {"SGD": 0, "Adam": 1, "AdamW": 1, "Adagrad": 2}[self.opt_kind]
         b1, b2 = g.get("betas", (0.0, 0.0))
         blocks = max(8, min(self.E.MAX_COMM_BLOCKS, total // (4 * 512 * self.world_size) + 1))
-        self.E.reduce_scatter_update(*self.arena.ctx(), self._grad_sym["ptrs"], self._p16_sym, self._p32_sym, self.ps_master,
+        use_mc = os.environ.get("AUTODIST_PS_MULTIMEM", "1") == "1"      # through the switch when the fabric offers multicast
+        self.E.reduce_scatter_update(*self.arena.ctx(), self._grad_sym["ptrs"], self._p16_sym, self._p32_sym,
+                                     self._grad_sym["mc"] if use_mc else 0, self._p16_mc if use_mc else 0, self._p32_mc if use_mc else 0,
+                                     self.ps_master,
                                      self.ps_s1, self.ps_s2, starts, lens, state, prefix, kind, self.lr, self.opt_step,
                                      b1, b2, g.get("eps", 1e-8), g.get("weight_decay", 0.0), g.get("momentum", 0.0), 1.0,
                                      self.opt_kind == "AdamW", bool(g.get("nesterov", False)), 1.0 / self.world_size, blocks)
@@ -632,7 +717,8 @@ class FusedStepEngine(StepEngine):
         compute = torch.cuda.current_stream()
         self._ready_event.record(compute)
         self.comm_stream.wait_event(self._ready_event)
-        with nvtx.annotate(f"flight [{lo}, {hi})"), torch.cuda.stream(self.comm_stream):
+        keys = [f"g{gk}/i{ik}" for a, z, gk, ik in getattr(self, "_range_key", ()) if a < hi and z > lo]
+        with nvtx.annotate(f"flight [{lo}, {hi}) {' '.join(keys[:4])}"), torch.cuda.stream(self.comm_stream):
             if self.world_size > 1:
                 for a, b, wd, ef in self._policy_for(lo, hi):
                     self._all_reduce_range(a, b, wd, ef)
@@ -642,6 +728,9 @@ class FusedStepEngine(StepEngine):
                 covered = [(lo, hi, None, False)]
             if (lo, hi) in getattr(self, "_deferred_ranges", ()):
                 return                                   # clipped parameters inside: updated once the global norm is known
+            if self._psgd and any(a < hi and z > lo for a, z in self._psgd["ranges"]):
+                self._psgd_flights.append((lo, hi))      # holds matrices that travel as factors: updated after decompression
+                return
             for a, b, _, _ in covered:
                 self._update_range(a, b)
             self.launches_per_step += 2 * len(covered)
@@ -676,8 +765,10 @@ class FusedStepEngine(StepEngine):
         self.E.increment(self.opt_step)
         self.launches_per_step = 0
         self._rows_sync_pending, self._rows_dirty = True, False
+        self._psgd_flights = []
         values = self.forward(all_nodes, feeds, grad=True)
         self._finish_rows()
+        self._finish_powersgd()
         # the optimizer kernels of the last flights run on the communication stream: join it
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
@@ -992,6 +1083,7 @@ class FlatAutogradEngine(FusedStepEngine):
         self.E.increment(self.opt_step)
         self.launches_per_step = 0
         self._rows_sync_pending, self._rows_dirty = True, False
+        self._psgd_flights = []
         fl = self.flat
         fl.grad.zero_()
         for f in self._flights:
@@ -1008,6 +1100,7 @@ class FlatAutogradEngine(FusedStepEngine):
                 self._on_grad_ready(f["lo"], f["hi"])
         self._finish_rows()
         self._finish_clipped()
+        self._finish_powersgd()
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
         return values

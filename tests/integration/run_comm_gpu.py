@@ -83,48 +83,53 @@ def main():
             dist.barrier()
 
     # ---- K2: reduce-scatter + Adam on the owner + parameter write to every peer
+    # (peer loads / stores first, then the same through the multicast addresses where the fabric has them)
     total = 8192
-    grads, gptrs, _ = arena.alloc(total, torch.float32)
-    p16, p16ptrs, _ = arena.alloc(total, torch.bfloat16)
-    p32, p32ptrs, _ = arena.alloc(total, torch.float32)
-    torch.manual_seed(7)
-    init = torch.randn(total, device=dev)
-    # three segments with round-robin owners: [0,2048) -> 0, [2048, 5000+120) -> 1 % world, rest -> 2 % world
-    bounds = [0, 2048, 5120, total]
-    owners = [0, 1 % world, 2 % world]
-    mine = [(bounds[i], bounds[i + 1]) for i in range(3) if owners[i] == rank]
-    n_owned = sum(b - a for a, b in mine)
-    master = torch.zeros(max(n_owned, 4), device=dev)
-    m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
-    seg_start, seg_len, seg_state, prefix, off = [], [], [], [0], 0
-    for a, b in mine:
-        seg_start.append(a); seg_len.append(b - a); seg_state.append(off)
-        master[off:off + b - a] = init[a:b]
-        off += b - a
-        prefix.append(off)
-    if not mine:
-        seg_start, seg_len, seg_state, prefix = [0], [0], [0], [0, 0]
-    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)   # noqa: E731
-    ref_p = init.clone().requires_grad_(True)
-    opt = torch.optim.Adam([ref_p], lr=1e-2)
-    lr = torch.tensor([1e-2], device=dev)
-    step = torch.zeros(1, dtype=torch.int64, device=dev)
-    for it in range(3):
-        torch.manual_seed(1000 * it + rank)
-        g = torch.randn(total, device=dev)
-        grads.copy_(g)
-        mean = g.clone(); dist.all_reduce(mean); mean /= world
-        ref_p.grad = mean
-        opt.step()
-        E.increment(step)
-        torch.cuda.synchronize(); dist.barrier()
-        E.reduce_scatter_update(*ctx(), gptrs, p16ptrs, p32ptrs, master, m1, m2, i64(seg_start), i64(seg_len), i64(seg_state),
-                                i64(prefix), 1, lr, step, 0.9, 0.999, 1e-8, 0.0, 0.0, 1.0, False, False, 1.0 / world, 8)
-        torch.cuda.synchronize()
-        arena.check()
-        dist.barrier()
-    check("reduce_scatter_update fp32 params on every rank", p32, ref_p.detach(), 1e-5)
-    check("reduce_scatter_update bf16 params on every rank", p16, ref_p.detach(), 2e-2)
+    grads, gptrs, g_mc = arena.alloc(total, torch.float32)
+    p16, p16ptrs, p16_mc = arena.alloc(total, torch.bfloat16)
+    p32, p32ptrs, p32_mc = arena.alloc(total, torch.float32)
+    for label, mcs in (("p2p", (0, 0, 0)), ("nvls", (g_mc, p16_mc, p32_mc))):
+        if label == "nvls" and (not all(mcs) or not use_mc):
+            continue
+        p16.zero_(); p32.zero_()
+        torch.manual_seed(7)
+        init = torch.randn(total, device=dev)
+        # three segments with round-robin owners: [0,2048) -> 0, [2048, 5000+120) -> 1 % world, rest -> 2 % world
+        bounds = [0, 2048, 5120, total]
+        owners = [0, 1 % world, 2 % world]
+        mine = [(bounds[i], bounds[i + 1]) for i in range(3) if owners[i] == rank]
+        n_owned = sum(b - a for a, b in mine)
+        master = torch.zeros(max(n_owned, 4), device=dev)
+        m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
+        seg_start, seg_len, seg_state, prefix, off = [], [], [], [0], 0
+        for a, b in mine:
+            seg_start.append(a); seg_len.append(b - a); seg_state.append(off)
+            master[off:off + b - a] = init[a:b]
+            off += b - a
+            prefix.append(off)
+        if not mine:
+            seg_start, seg_len, seg_state, prefix = [0], [0], [0], [0, 0]
+        i64 = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)   # noqa: E731
+        ref_p = init.clone().requires_grad_(True)
+        opt = torch.optim.Adam([ref_p], lr=1e-2)
+        lr = torch.tensor([1e-2], device=dev)
+        step = torch.zeros(1, dtype=torch.int64, device=dev)
+        for it in range(3):
+            torch.manual_seed(1000 * it + rank)
+            g = torch.randn(total, device=dev)
+            grads.copy_(g)
+            mean = g.clone(); dist.all_reduce(mean); mean /= world
+            ref_p.grad = mean
+            opt.step()
+            E.increment(step)
+            torch.cuda.synchronize(); dist.barrier()
+            E.reduce_scatter_update(*ctx(), gptrs, p16ptrs, p32ptrs, mcs[0], mcs[1], mcs[2], master, m1, m2, i64(seg_start), i64(seg_len), i64(seg_state),
+                                    i64(prefix), 1, lr, step, 0.9, 0.999, 1e-8, 0.0, 0.0, 1.0, False, False, 1.0 / world, 8)
+            torch.cuda.synchronize()
+            arena.check()
+            dist.barrier()
+        check(f"reduce_scatter_update {label} fp32 params on every rank", p32, ref_p.detach(), 1e-5)
+        check(f"reduce_scatter_update {label} bf16 params on every rank", p16, ref_p.detach(), 2e-2)
 
     # ---- K4 / K5: sparse rows to / from the owner shards (uneven split of V rows)
     V, H = 1003, 64

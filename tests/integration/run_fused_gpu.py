@@ -20,9 +20,13 @@ def run(strategy_name, comm, world, rank, opt_name="sgd"):
     builders = {
         "AllReduce": lambda: S.AllReduce(chunk_size=16),
         "AllReduce_EF": lambda: S.AllReduce(chunk_size=16, compressor="HorovodCompressorEF"),
+        "AllReduce_PowerSGD": lambda: S.AllReduce(chunk_size=16, compressor="PowerSGDCompressor"),
         "PSLoadBalancing_gpu": lambda: S.PSLoadBalancing(reduction_devices="gpu", local_proxy_variable=True),
         "PartitionedPS_gpu": lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu", local_proxy_variable=True),
         "Parallax_gpu": lambda: S.Parallax(chunk_size=16, reduction_devices="gpu"),
+        "PartitionedAR": lambda: S.PartitionedAR(chunk_size=16),
+        "RandomAxisPartitionAR": lambda: S.RandomAxisPartitionAR(chunk_size=16, seed=3),
+        "UnevenPartitionedPS_gpu": lambda: S.UnevenPartitionedPS(reduction_devices="gpu", local_proxy_variable=True),
     }
     cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builders[strategy_name]())
@@ -67,6 +71,7 @@ def run_cnn(strategy_name, comm, world, rank):
     builders = {
         "AllReduce": lambda: S.AllReduce(chunk_size=8),
         "AllReduce_EF": lambda: S.AllReduce(chunk_size=8, compressor="HorovodCompressorEF"),
+        "AllReduce_PowerSGD": lambda: S.AllReduce(chunk_size=8, compressor="PowerSGDCompressor"),
         "PartitionedPS_gpu": lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu", local_proxy_variable=True),
     }
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builders[strategy_name]())
@@ -244,7 +249,7 @@ def check_resume_same_strategy(world, rank, builder_name):
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     failures = 0
-    for name in ("AllReduce", "AllReduce_EF", "PartitionedPS_gpu"):
+    for name in ("AllReduce", "AllReduce_EF", "AllReduce_PowerSGD", "PartitionedPS_gpu"):
         ref, ref_losses, ref_engine = run_cnn(name, "nccl", world, rank)
         got, losses, engine = run_cnn(name, "fused", world, rank)
         diff = (got - ref).abs().max().item()
@@ -254,7 +259,8 @@ def main():
         if rank == 0:
             print(f"cnn {name}: engines {ref_engine} vs {engine}, max |param diff| {diff:.2e} (tol {tol}), "
                   f"loss {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
-    for name in ("AllReduce", "AllReduce_EF", "PSLoadBalancing_gpu", "PartitionedPS_gpu", "Parallax_gpu"):
+    for name in ("AllReduce", "AllReduce_EF", "AllReduce_PowerSGD", "PSLoadBalancing_gpu", "PartitionedPS_gpu", "UnevenPartitionedPS_gpu",
+                 "Parallax_gpu", "PartitionedAR", "RandomAxisPartitionAR"):
         ref, _, ref_losses, ref_engine = run(name, "nccl", world, rank)
         got, p16, losses, engine = run(name, "fused", world, rank)
         tol = 2e-3 if name == "AllReduce_EF" else 1e-4      # fp16 wire vs fp32 wire; summation order differs from NCCL's
