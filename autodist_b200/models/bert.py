@@ -239,6 +239,8 @@ class BertPretrainer(nn.Module):
         """Loss (device scalar) of one batch; with ``backward`` the flat gradient buffer is filled as well."""
         c, fl = self.config, self.flat
         B, S = input_ids.shape
+        if B == 0:
+            raise ValueError("this replica received an empty batch: feed at least one sequence per replica of the node")
         P = mlm_positions.shape[1]
         ws = self._workspace(B, S, P)
         E = ws["E"]

@@ -30,7 +30,7 @@ def run(strategy_name, comm, world, rank, opt_name="sgd"):
     }
     cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
     ad = AutoDist(resource_spec=ResourceSpec.local(num_gpus=world), strategy_builder=builders[strategy_name]())
-    batch = synthetic_batch(cfg, 4, 128, 8, seed=10 + rank)
+    batch = synthetic_batch(cfg, 2 * world, 128, 8, seed=10 + rank)      # the node batch: two sequences per replica
     with ad.scope():
         torch.manual_seed(0)
         model = BertPretrainer(cfg)
@@ -143,7 +143,7 @@ def check_checkpoint(world, rank):
     from autodist_b200.models.bert import BertConfig, BertPretrainer, synthetic_batch
     from autodist_b200.resource_spec import ResourceSpec
     cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
-    batch = synthetic_batch(cfg, 4, 128, 8, seed=10 + rank)
+    batch = synthetic_batch(cfg, 2 * world, 128, 8, seed=10 + rank)      # the node batch: two sequences per replica
     tmp = [tempfile.mkdtemp(prefix="adb_ckpt_") if rank == 0 else None]
     path = None
     states = []
@@ -202,7 +202,7 @@ def check_resume_same_strategy(world, rank, builder_name):
     builders = {"PartitionedPS_gpu": lambda: S.PartitionedPS(num_shards=world, reduction_devices="gpu", local_proxy_variable=True),
                 "Parallax_gpu": lambda: S.Parallax(chunk_size=16, reduction_devices="gpu")}
     cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
-    batch = synthetic_batch(cfg, 4, 128, 8, seed=10 + rank)
+    batch = synthetic_batch(cfg, 2 * world, 128, 8, seed=10 + rank)      # the node batch: two sequences per replica
     tmp = [tempfile.mkdtemp(prefix="adb_resume_") if rank == 0 else None]
     results = []
     path = None
