@@ -71,147 +71,185 @@ __device__ __forceinline__ void store8(bf16* p, const float* v) {
 // what the backward pass needs), y = LN(z) * gamma + beta.
 constexpr int MAXV = 4;   // 8-element vectors per lane -> H <= 1024
 
+// Sum of `v` over the block (at most 4 warps); every thread gets the result. `red` holds one float per warp.
+__device__ __forceinline__ float ln_block_sum(float v, float* red, int lane, int wib, int nw) {
+  v = warp_sum(v);
+  if (nw == 1) return v;
+  __syncthreads();                       // the previous use of `red` has been read
+  if (lane == 0) red[wib] = v;
+  __syncthreads();
+  float s = red[0];
+  for (int w = 1; w < nw; ++w) s += red[w];
+  return s;
+}
+
+// One block per row, one thread per 8 columns (H / 8 threads, rounded up to whole warps): every access is one 16-byte
+// vector per thread, registers stay few and a whole wave of rows is in flight per SM.
 __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const float* __restrict__ gamma,
                               const float* __restrict__ beta, bf16* __restrict__ z, bf16* __restrict__ y,
                               float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, float eps,
                               float p_drop, uint64_t seed, const long long* step) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= rows) return;
-  const int nvec = H / 8;
-  const uint32_t thresh = (uint32_t)(p_drop * 65536.0f);
-  const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
-  const uint64_t sd = step_seed(seed, step);
-  float v[MAXV][8];
-  float s = 0.f;
+  __shared__ float red[4];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int row = blockIdx.x;
+  const int col = threadIdx.x * 8;
+  const bool active = col < H;
+  const long long off = (long long)row * H + col;
+  float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (active) {
+    load8(x + off, v);
+    if (p_drop > 0.f) {
+      float ks[8];
+      keep_scale8(step_seed(seed, step), (uint64_t)off, (uint32_t)(p_drop * 65536.0f), 1.0f / (1.0f - p_drop), ks);
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-      const long long off = (long long)warp * H + vec * 8;
-      load8(x + off, v[i]);
-      if (p_drop > 0.f) {
-        float ks[8];
-        keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
+      for (int j = 0; j < 8; ++j) v[j] *= ks[j];
+    }
+    if (res) {
+      float r[8];
+      load8(res + off, r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] *= ks[j];
-      }
-      if (res) {
-        float r[8];
-        load8(res + off, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s += v[i][j];
+      for (int j = 0; j < 8; ++j) v[j] += r[j];
     }
   }
-  const float mu = warp_sum(s) / H;
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s += v[j];
+  const float mu = ln_block_sum(s, red, lane, wib, nw) / H;
   float q = 0.f;
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i)
-    if (lane + 32 * i < nvec) {
+    for (int j = 0; j < 8; ++j) { const float d = v[j] - mu; q += d * d; }
+  }
+  const float rs = rsqrtf(ln_block_sum(q, red, lane, wib, nw) / H + eps);
+  if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+  if (active) {
+    if (z) store8(z + off, v);
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + col), g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(beta + col), b1 = *reinterpret_cast<const float4*>(beta + col + 4);
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float o[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; q += d * d; }
-    }
-  const float rs = rsqrtf(warp_sum(q) / H + eps);
-  if (lane == 0) { mean[warp] = mu; rstd[warp] = rs; }
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-      const long long off = (long long)warp * H + vec * 8;
-      if (z) store8(z + off, v[i]);
-      float o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mu) * rs * gamma[vec * 8 + j] + beta[vec * 8 + j];
-      store8(y + off, o);
-    }
+    for (int j = 0; j < 8; ++j) o[j] = (v[j] - mu) * rs * gg[j] + bb[j];
+    store8(y + off, o);
   }
 }
 
 // dz = rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat)); dx = dz * dropout mask (only written when p_drop > 0).
 // `dz_add` (optional) is added to dz before it is stored: the gradient arriving over the residual connection.
+// One thread per 8 columns, a block walks rows blockIdx.x, blockIdx.x + gridDim.x, ... with the next row's loads issued
+// before the current row's reductions; its per-column sums (dgamma, dbeta and, when asked, the sum of what it writes to
+// dx - the bias gradient of the linear layer in front of the residual) stay in registers and are written once per block
+// as partials part[k][block][H], k = 0 (dgamma), 1 (dbeta), 2 (sum of the output).
 __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ z, const float* __restrict__ mean,
                               const float* __restrict__ rstd, const float* __restrict__ gamma, const bf16* __restrict__ dz_add,
-                              bf16* __restrict__ dz, bf16* __restrict__ dx, float* __restrict__ part_g, float* __restrict__ part_b,
-                              int rows, int H, float p_drop, uint64_t seed, const long long* step) {
-  extern __shared__ float sm[];   // [warps][H] x 2
-  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-  const int nvec = H / 8;
+                              bf16* __restrict__ dz, bf16* __restrict__ dx, float* __restrict__ part, int rows, int H, float p_drop,
+                              uint64_t seed, const long long* step, int want_out_sum) {
+  __shared__ float red[2][4];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int col = threadIdx.x * 8;
+  const bool active = col < H;
   const uint32_t thresh = (uint32_t)(p_drop * 65536.0f);
   const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
   const uint64_t sd = step_seed(seed, step);
-  float ag[MAXV][8], ab[MAXV][8];
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { ag[i][j] = 0.f; ab[i][j] = 0.f; }
-  for (int row = blockIdx.x * wpb + wib; row < rows; row += gridDim.x * wpb) {
+  float gam[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (active) {
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + col), g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
+    gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w; gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
+  }
+  float ag[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float d[8] = {0, 0, 0, 0, 0, 0, 0, 0}, zz[8] = {0, 0, 0, 0, 0, 0, 0, 0}, add[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int row = blockIdx.x;
+  if (row < rows && active) {
+    const long long off = (long long)row * H + col;
+    load8(dy + off, d);
+    load8(z + off, zz);
+    if (dz_add) load8(dz_add + off, add);
+  }
+  for (; row < rows; row += gridDim.x) {
     const float mu = mean[row], rs = rstd[row];
-    float g[MAXV][8], xh[MAXV][8];
+    const long long off = (long long)row * H + col;
+    // the next row's vectors are requested now and consumed in the next iteration
+    float dn[8] = {0, 0, 0, 0, 0, 0, 0, 0}, zn[8] = {0, 0, 0, 0, 0, 0, 0, 0}, an[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int next = row + gridDim.x;
+    if (next < rows && active) {
+      const long long noff = (long long)next * H + col;
+      load8(dy + noff, dn);
+      load8(z + noff, zn);
+      if (dz_add) load8(dz_add + noff, an);
+    }
+    float xh[8], g[8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int vec = lane + 32 * i;
-      if (vec < nvec) {
-        const long long off = (long long)row * H + vec * 8;
-        float d[8], zz[8];
-        load8(dy + off, d);
-        load8(z + off, zz);
+    for (int j = 0; j < 8; ++j) {
+      xh[j] = (zz[j] - mu) * rs;
+      ag[j] += d[j] * xh[j];
+      ab[j] += d[j];
+      g[j] = d[j] * gam[j];
+      s1 += g[j];
+      s2 += g[j] * xh[j];
+    }
+    if (!active) { s1 = 0.f; s2 = 0.f; }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (nw > 1) {
+      __syncthreads();
+      if (lane == 0) { red[0][wib] = s1; red[1][wib] = s2; }
+      __syncthreads();
+      s1 = red[0][0]; s2 = red[1][0];
+      for (int w = 1; w < nw; ++w) { s1 += red[0][w]; s2 += red[1][w]; }
+    }
+    s1 /= H; s2 /= H;
+    if (active) {
+      float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (zz[j] - mu) * rs;
-          ag[i][j] += d[j] * xh[i][j];
-          ab[i][j] += d[j];
-          g[i][j] = d[j] * gamma[vec * 8 + j];
-          s1 += g[i][j];
-          s2 += g[i][j] * xh[i][j];
-        }
+      for (int j = 0; j < 8; ++j) o[j] = rs * (g[j] - s1 - xh[j] * s2) + add[j];
+      store8(dz + off, o);
+      if (p_drop > 0.f && dx) {
+        float ks[8];
+        keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] *= ks[j];
+        store8(dx + off, o);
+      }
+      if (want_out_sum) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ax[j] += __bfloat162float(__float2bfloat16(o[j]));     // what the next kernel reads
       }
     }
-    s1 = warp_sum(s1) / H;
-    s2 = warp_sum(s2) / H;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int vec = lane + 32 * i;
-      if (vec < nvec) {
-        const long long off = (long long)row * H + vec * 8;
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - s1 - xh[i][j] * s2);
-        if (dz_add) {
-          float a[8];
-          load8(dz_add + off, a);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += a[j];
-        }
-        store8(dz + off, o);
-        if (p_drop > 0.f && dx) {
-          float ks[8];
-          keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] *= ks[j];
-          store8(dx + off, o);
-        }
-      }
+    for (int j = 0; j < 8; ++j) { d[j] = dn[j]; zz[j] = zn[j]; add[j] = an[j]; }
+  }
+  if (active) {
+    const long long stride = (long long)gridDim.x * H;
+    float* p0 = part + (long long)blockIdx.x * H + col;
+    *reinterpret_cast<float4*>(p0) = make_float4(ag[0], ag[1], ag[2], ag[3]);
+    *reinterpret_cast<float4*>(p0 + 4) = make_float4(ag[4], ag[5], ag[6], ag[7]);
+    *reinterpret_cast<float4*>(p0 + stride) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+    *reinterpret_cast<float4*>(p0 + stride + 4) = make_float4(ab[4], ab[5], ab[6], ab[7]);
+    if (want_out_sum) {
+      *reinterpret_cast<float4*>(p0 + 2 * stride) = make_float4(ax[0], ax[1], ax[2], ax[3]);
+      *reinterpret_cast<float4*>(p0 + 2 * stride + 4) = make_float4(ax[4], ax[5], ax[6], ax[7]);
     }
   }
-  float* sg = sm;
-  float* sb = sm + wpb * H;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int vec = lane + 32 * i;
-    if (vec < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { sg[wib * H + vec * 8 + j] = ag[i][j]; sb[wib * H + vec * 8 + j] = ab[i][j]; }
-    }
-  }
+}
+
+// Up to three column sums over partials laid out [k][parts][H] in one launch: blockIdx.y = k, out = outs[k].
+__global__ void colsum3_f32_kernel(const float* __restrict__ part, float* __restrict__ out0, float* __restrict__ out1,
+                                   float* __restrict__ out2, int parts, int H, int accumulate) {
+  __shared__ float sm[8][33];
+  const float* src = part + (long long)blockIdx.y * parts * H;
+  float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
+  float a = 0.f;
+  if (c < H)
+    for (int r = w; r < parts; r += 8) a += src[(long long)r * H + c];
+  sm[w][threadIdx.x & 31] = a;
   __syncthreads();
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float a = 0.f, b = 0.f;
-    for (int w = 0; w < wpb; ++w) { a += sg[w * H + c]; b += sb[w * H + c]; }
-    part_g[(long long)blockIdx.x * H + c] = a;
-    part_b[(long long)blockIdx.x * H + c] = b;
+  if (w == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
   }
 }
 
@@ -1380,16 +1418,22 @@ inline int blocks_for(long long n, int per) { return (int)((n + per - 1) / per);
 // ---------------------------------------------------------------------------------------------- launchers
 void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* beta, bf16* z, bf16* y, float* mean, float* rstd,
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st) {
-  ln_fwd_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
+  if (rows <= 0) return;
+  const int threads = ((H / 8 + 31) / 32) * 32;
+  ln_fwd_kernel<<<rows, threads, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
 }
-int ln_bwd_blocks(int rows) { return rows < 1184 * 4 ? (rows + 3) / 4 : 1184; }
+// Blocks of the backward kernel: four per SM when there are rows enough, so that a block keeps several rows (its
+// per-column partial sums are written once per block).
+int ln_bwd_blocks(int rows) { return rows < 592 ? (rows < 1 ? 1 : rows) : 592; }
+// part: 3 * ln_bwd_blocks(rows) * H floats. dsum (optional): column sums of the tensor the kernel hands to the layer in
+// front of the residual connection (dx when the dropout copy is written, else dz).
 void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd, const float* gamma, const bf16* dz_add, bf16* dz,
-            bf16* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
+            bf16* dx, float* part, float* dgamma, float* dbeta, float* dsum, int rows, int H, float p_drop, uint64_t seed,
             const long long* step, int accumulate, cudaStream_t st) {
   const int blocks = ln_bwd_blocks(rows);
-  ln_bwd_kernel<<<blocks, 128, 2 * 4 * H * sizeof(float), st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part_g, part_b, rows, H,
-                                                                p_drop, seed, step);
-  colsum2_f32_kernel<<<dim3(blocks_for(H, 32), 2), 256, 0, st>>>(part_g, dgamma, part_b, dbeta, blocks, H, accumulate);
+  const int threads = ((H / 8 + 31) / 32) * 32;
+  ln_bwd_kernel<<<blocks, threads, 0, st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part, rows, H, p_drop, seed, step, dsum != nullptr);
+  colsum3_f32_kernel<<<dim3(blocks_for(H, 32), dsum != nullptr ? 3 : 2), 256, 0, st>>>(part, dgamma, dbeta, dsum, blocks, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
                int H, long long V, long long types, int* error, cudaStream_t st) {

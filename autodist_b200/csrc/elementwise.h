@@ -10,7 +10,7 @@ void ln_fwd(const bf16_t* x, const bf16_t* res, const float* gamma, const float*
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st);
 int ln_bwd_blocks(int rows);
 void ln_bwd(const bf16_t* dy, const bf16_t* z, const float* mean, const float* rstd, const float* gamma, const bf16_t* dz_add, bf16_t* dz,
-            bf16_t* dx, float* part_g, float* part_b, float* dgamma, float* dbeta, int rows, int H, float p_drop, uint64_t seed,
+            bf16_t* dx, float* part, float* dgamma, float* dbeta, float* dsum, int rows, int H, float p_drop, uint64_t seed,
             const long long* step, int accumulate, cudaStream_t st);
 void embed_sum(const bf16_t* word, const bf16_t* pos, const bf16_t* type, const int64_t* ids, const int64_t* tt, bf16_t* z, int rows, int S,
                int H, long long V, long long types, int* error, cudaStream_t st);

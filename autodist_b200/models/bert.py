@@ -27,6 +27,7 @@ parameter-server path, which the reference's tied head makes dense
 (``networks/masked_lm.py:56,76-78``).
 """
 import math
+import os
 import json
 from dataclasses import asdict, dataclass, fields
 
@@ -127,6 +128,8 @@ class BertPretrainer(nn.Module):
         # S == 128: softmax inside the QK^T / dP GEMM epilogues. Measured slower than the stand-alone softmax kernels
         # (20.9 vs 20.1 ms per BERT-large step: a 64-deep contraction cannot hide a 128-exponential epilogue), so off.
         self.fused_attention_softmax = False
+        # Bias gradients (column sums) on a side stream next to the weight-gradient GEMMs instead of between them.
+        self.side_stream_bias_grads = os.environ.get("AUTODIST_BERT_SIDE_STREAM", "1") == "1"
 
     def sparse_grad_parameters(self):
         """Variables whose gradient is row-sparse (only when the output projection is untied)."""
@@ -208,7 +211,7 @@ class BertPretrainer(nn.Module):
                 "qkv": bf(T, 3 * H), "p": bf(B, nh, S, S), "pd": bf(B, nh, S, S) if drop_a else None,
                 "ctx": bf(T, H), "z1": bf(T, H), "m1": f32(T), "r1": f32(T), "x1": bf(T, H),
                 "u": bf(T, Fd), "g": bf(T, Fd), "z2": bf(T, H), "m2": f32(T), "r2": f32(T), "out": bf(T, H)})
-        n_part = max(2 * E.ln_bwd_blocks(T) * H, E.colsum_parts(T) * max(4 * H, Fd, 3 * H, 2 * H),
+        n_part = max(3 * E.ln_bwd_blocks(T) * H, E.colsum_parts(T) * max(4 * H, Fd, 3 * H, 2 * H),
                      E.colsum_parts(B * P) * Vp)
         ws = {
             "key": key, "E": E, "layers": layers, "Vp": Vp,
@@ -217,6 +220,10 @@ class BertPretrainer(nn.Module):
             # backward scratch
             "d_a": bf(T, H), "d_b": bf(T, H), "d_c": bf(T, H), "d_big": bf(T, Fd), "d_qkv": bf(T, 3 * H),
             "d_p": bf(B, nh, S, S), "part": f32(n_part),
+            # bias gradients are column sums that nothing in the layer waits for: they run on a side stream next to the
+            # GEMMs, each with its own partial-sum scratch (joined before the layer's gradients are reported ready)
+            "side_part": [f32(E.colsum_parts(T) * max(Fd, 3 * H)) for _ in range(4)],
+            "side_stream": torch.cuda.Stream(device=dev), "side_fork": torch.cuda.Event(), "side_join": torch.cuda.Event(),
             # heads
             "pooled": bf(B, H), "nsp_logits": bf(B, 8), "d_pooled": bf(B, H), "d_pre": bf(B, H),
             "flat_pos": torch.empty(B * P, dtype=torch.int64, device=dev),
@@ -315,6 +322,23 @@ class BertPretrainer(nn.Module):
 
         # ------------------------------ backward (logits / nsp_logits now hold d loss / d logits)
         ready = self.grad_ready or (lambda lo, hi: None)
+        side, use_side = ws["side_stream"], self.side_stream_bias_grads
+
+        def bias_grad(src, dst, slot):
+            """dst = column sums of src. On the side stream when enabled: the caller joins before dst or src is needed again."""
+            if not use_side:
+                E.keyed_colsum(src, None, ws["part"], dst, 1, False)
+                return
+            ws["side_fork"].record(torch.cuda.current_stream())
+            side.wait_event(ws["side_fork"])
+            with torch.cuda.stream(side):
+                E.keyed_colsum(src, None, ws["side_part"][slot], dst, 1, False)
+
+        def join_side():
+            if use_side:
+                ws["side_join"].record(side)
+                torch.cuda.current_stream().wait_event(ws["side_join"])
+
         dl = ws["logits"]
         E.keyed_colsum(dl, None, ws["part"], ws["d_bias"], 1, False)
         g["mlm.bias"].copy_(ws["d_bias"][:V])
@@ -325,7 +349,7 @@ class BertPretrainer(nn.Module):
         gm(dlv, ws["hl"], g[dec], a_mn=True, b_mn=True)                               # dE = dlogits^T . hl
         gm(dlv, w16[dec], ws["d_hl"], b_mn=True)                                        # dhl = dlogits . E
         E.ln_bwd(ws["d_hl"], ws["hm"], ws["mm"], ws["mr"], w32["mlm.ln_g"], None, ws["d_hm"], None, ws["part"],
-                 g["mlm.ln_g"], g["mlm.ln_b"], 0.0, 0, None, False)
+                 g["mlm.ln_g"], g["mlm.ln_b"], 0.0, 0, None, False, None)
         E.gelu_bwd(ws["d_hm"], ws["hm_u"], ws["d_hu"])
         E.keyed_colsum(ws["d_hu"], None, ws["part"], g["mlm.dense_b"], 1, False)
         gm(ws["d_hu"], ws["xm"], g["mlm.dense_w"], a_mn=True, b_mn=True)
@@ -352,19 +376,18 @@ class BertPretrainer(nn.Module):
             n = f"layers.{l}."
             x_in = ws["layers"][l - 1]["out"] if l > 0 else ws["x0"]
             dz2, dfo = spare[0], (spare[1] if ph > 0 else spare[0])
+            # the layernorm backward also sums what it hands to the linear layer in front of the residual: that layer's bias gradient
             E.ln_bwd(d_out, A["z2"], A["m2"], A["r2"], w32[n + "ln2_g"], None, dz2, dfo if ph > 0 else None, ws["part"],
-                     g[n + "ln2_g"], g[n + "ln2_b"], ph, seed(l, 3), step, False)
-            E.keyed_colsum(dfo, None, ws["part"], g[n + "b2"], 1, False)
+                     g[n + "ln2_g"], g[n + "ln2_b"], ph, seed(l, 3), step, False, g[n + "b2"])
             gm(dfo, A["g"], g[n + "w2"], a_mn=True, b_mn=True)                          # dW2 = dfo^T . g
             gm(dfo, w16[n + "w2"], ws["d_big"], b_mn=True, epi=EPI_MUL_GELU_GRAD, aux=A["u"])   # dU
-            E.keyed_colsum(ws["d_big"], None, ws["part"], g[n + "b1"], 1, False)
+            bias_grad(ws["d_big"], g[n + "b1"], 1)
             gm(ws["d_big"], A["x1"], g[n + "w1"], a_mn=True, b_mn=True)                 # dW1 = dU^T . x1
             dx1 = d_out                                                                 # d_out is dead: reuse
             gm(ws["d_big"], w16[n + "w1"], dx1, b_mn=True, epi=EPI_ADD, aux=dz2)        # dx1 = dU . W1 + dz2
             dz1, dao = spare[0], (spare[1] if ph > 0 else spare[0])
             E.ln_bwd(dx1, A["z1"], A["m1"], A["r1"], w32[n + "ln1_g"], None, dz1, dao if ph > 0 else None, ws["part"],
-                     g[n + "ln1_g"], g[n + "ln1_b"], ph, seed(l, 2), step, False)
-            E.keyed_colsum(dao, None, ws["part"], g[n + "out_b"], 1, False)
+                     g[n + "ln1_g"], g[n + "ln1_b"], ph, seed(l, 2), step, False, g[n + "out_b"])
             gm(dao, A["ctx"], g[n + "out_w"], a_mn=True, b_mn=True)                     # dWo
             dctx = dx1                                                                  # reuse again
             gm(dao, w16[n + "out_w"], dctx, b_mn=True)                                  # dctx = dao . Wo
@@ -379,18 +402,19 @@ class BertPretrainer(nn.Module):
                 E.softmax_bwd(ws["d_p"], A["p"], scale, pa, seed(l, 1), step)           # dS (in place)
             gm(ws["d_p"], k, dq, b_mn=True, bn=64)                                      # dQ = dS . K
             gm(ws["d_p"], q, dk, a_mn=True, b_mn=True, bn=64)                           # dK = dS^T . Q
-            E.keyed_colsum(ws["d_qkv"], None, ws["part"], g[n + "qkv_b"], 1, False)
+            bias_grad(ws["d_qkv"], g[n + "qkv_b"], 3)
             gm(ws["d_qkv"], x_in, g[n + "qkv_w"], a_mn=True, b_mn=True)                 # dWqkv
             d_prev = dctx
             gm(ws["d_qkv"], w16[n + "qkv_w"], d_prev, b_mn=True, epi=EPI_ADD, aux=dz1)  # dx = dqkv . Wqkv + dz1
             d_out = d_prev           # always ws["d_a"]: the two spare buffers hold this layer's dz / dropped copies
             lo = fl.offsets[n + "qkv_w"]
             hi = fl.offsets[f"layers.{l + 1}.qkv_w"] if l + 1 < c.num_hidden_layers else fl.offsets["pooler.w"]
+            join_side()              # the four bias gradients of this layer are complete; their sources may be reused
             ready(lo, hi)
         # embeddings
         dz0 = spare[0]
         E.ln_bwd(d_out, ws["z0"], ws["m0"], ws["r0"], w32["emb.ln_g"], None, dz0, None, ws["part"], g["emb.ln_g"], g["emb.ln_b"],
-                 0.0, 0, None, False)
+                 0.0, 0, None, False, None)
         if word_rows is not None:
             word_rows.push(ids, dz0)                   # sparse path: (row ids, rows) go to the shard owners
         else:

@@ -57,8 +57,11 @@ def test_dropout_path_runs_and_is_reproducible():
     g1 = model.flat.grad.clone()
     model._ws["step"].zero_()
     l2 = model.fused_forward_backward(**batch).item()
-    assert l1 == l2 and torch.equal(g1, model.flat.grad)          # same step counter -> same masks
+    # same step counter -> same dropout masks; the loss and the embedding gradients are accumulated with floating-point atomics,
+    # whose order may differ between two runs, so equality holds up to fp32 rounding (a different mask moves the loss by ~1e-2)
+    assert abs(l1 - l2) < 1e-5 * abs(l1)
+    assert (g1 - model.flat.grad).abs().max().item() <= 1e-5 * g1.abs().max().item()
     l3 = model.fused_forward_backward(**batch).item()
-    assert l3 != l1                                                # next step -> new masks
+    assert abs(l3 - l1) > 1e-4 * abs(l1)                           # next step -> new masks
     assert torch.isfinite(model.flat.grad).all()
     model.check_error()

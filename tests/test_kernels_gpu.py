@@ -149,13 +149,16 @@ def test_layernorm(E, rows, H, p):
     dy = _rand(rows, H)
     yr.backward(dy.float())
     dz, dx = torch.empty_like(x), torch.empty_like(x)
-    part = torch.empty(2 * E.ln_bwd_blocks(rows) * H, device="cuda")
+    part = torch.empty(3 * E.ln_bwd_blocks(rows) * H, device="cuda")
     dg, db = torch.empty(H, device="cuda"), torch.empty(H, device="cuda")
-    E.ln_bwd(dy, z, mean, rstd, gamma, None, dz, dx, part, dg, db, p, 1234, None, False)
+    dsum = torch.empty(H, device="cuda")
+    E.ln_bwd(dy, z, mean, rstd, gamma, None, dz, dx, part, dg, db, p, 1234, None, False, dsum)
     torch.cuda.synchronize()
     _check(dz, zr.grad, 2e-2)
     _check(dg, g.grad, 2e-2)
     _check(db, b.grad, 2e-2)
+    # the extra output: column sums of what the kernel hands on (dx with dropout, dz without) = the bias gradient in front
+    _check(dsum, (dx if p > 0 else dz).float().sum(0), 1e-3)
     if p > 0:
         # dx is dz with the forward's dropout decisions: every element is either dropped or scaled by 1/(1-p)
         d, full = dx.float(), dz.float() / (1 - p)
