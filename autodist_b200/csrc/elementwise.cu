@@ -83,54 +83,71 @@ __device__ __forceinline__ float ln_block_sum(float v, float* red, int lane, int
   return s;
 }
 
-// One block per row, one thread per 8 columns (H / 8 threads, rounded up to whole warps): every access is one 16-byte
-// vector per thread, registers stay few and a whole wave of rows is in flight per SM.
+// One thread per 8 columns (H / 8 threads, rounded up to whole warps): every access is one 16-byte vector per thread and
+// registers stay few. A block walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and requests the next row's vectors before
+// it reduces the current one.
 __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const float* __restrict__ gamma,
                               const float* __restrict__ beta, bf16* __restrict__ z, bf16* __restrict__ y,
                               float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, float eps,
                               float p_drop, uint64_t seed, const long long* step) {
   __shared__ float red[4];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int row = blockIdx.x;
   const int col = threadIdx.x * 8;
   const bool active = col < H;
-  const long long off = (long long)row * H + col;
-  float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const uint32_t thresh = (uint32_t)(p_drop * 65536.0f);
+  const float inv_keep = p_drop > 0.f ? 1.0f / (1.0f - p_drop) : 1.0f;
+  const uint64_t sd = step_seed(seed, step);
+  float gg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, bb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (active) {
-    load8(x + off, v);
-    if (p_drop > 0.f) {
-      float ks[8];
-      keep_scale8(step_seed(seed, step), (uint64_t)off, (uint32_t)(p_drop * 65536.0f), 1.0f / (1.0f - p_drop), ks);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] *= ks[j];
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + col), g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(beta + col), b1 = *reinterpret_cast<const float4*>(beta + col + 4);
+    gg[0] = g0.x; gg[1] = g0.y; gg[2] = g0.z; gg[3] = g0.w; gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
+    bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+  }
+  float v[8] = {0, 0, 0, 0, 0, 0, 0, 0}, r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int row = blockIdx.x;
+  if (row < rows && active) {
+    load8(x + (long long)row * H + col, v);
+    if (res) load8(res + (long long)row * H + col, r);
+  }
+  for (; row < rows; row += gridDim.x) {
+    const long long off = (long long)row * H + col;
+    float vn[8] = {0, 0, 0, 0, 0, 0, 0, 0}, rn[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int next = row + gridDim.x;
+    if (next < rows && active) {
+      load8(x + (long long)next * H + col, vn);
+      if (res) load8(res + (long long)next * H + col, rn);
     }
-    if (res) {
-      float r[8];
-      load8(res + off, r);
+    if (active) {
+      if (p_drop > 0.f) {
+        float ks[8];
+        keep_scale8(sd, (uint64_t)off, thresh, inv_keep, ks);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= ks[j];
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] += r[j];
     }
-  }
-  float s = 0.f;
+    float s = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) s += v[j];
-  const float mu = ln_block_sum(s, red, lane, wib, nw) / H;
-  float q = 0.f;
-  if (active) {
+    for (int j = 0; j < 8; ++j) s += v[j];
+    const float mu = ln_block_sum(s, red, lane, wib, nw) / H;
+    float q = 0.f;
+    if (active) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { const float d = v[j] - mu; q += d * d; }
-  }
-  const float rs = rsqrtf(ln_block_sum(q, red, lane, wib, nw) / H + eps);
-  if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
-  if (active) {
-    if (z) store8(z + off, v);
-    const float4 g0 = *reinterpret_cast<const float4*>(gamma + col), g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
-    const float4 b0 = *reinterpret_cast<const float4*>(beta + col), b1 = *reinterpret_cast<const float4*>(beta + col + 4);
-    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    float o[8];
+      for (int j = 0; j < 8; ++j) { const float dd = v[j] - mu; q += dd * dd; }
+    }
+    const float rs = rsqrtf(ln_block_sum(q, red, lane, wib, nw) / H + eps);
+    if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+    if (active) {
+      if (z) store8(z + off, v);
+      float o[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = (v[j] - mu) * rs * gg[j] + bb[j];
-    store8(y + off, o);
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mu) * rs * gg[j] + bb[j];
+      store8(y + off, o);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] = vn[j]; r[j] = rn[j]; }
   }
 }
 
@@ -159,23 +176,30 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
   float ag[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   float d[8] = {0, 0, 0, 0, 0, 0, 0, 0}, zz[8] = {0, 0, 0, 0, 0, 0, 0, 0}, add[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   int row = blockIdx.x;
-  if (row < rows && active) {
-    const long long off = (long long)row * H + col;
-    load8(dy + off, d);
-    load8(z + off, zz);
-    if (dz_add) load8(dz_add + off, add);
+  float mu = 0.f, rs = 0.f;
+  if (row < rows) {
+    mu = mean[row]; rs = rstd[row];
+    if (active) {
+      const long long off = (long long)row * H + col;
+      load8(dy + off, d);
+      load8(z + off, zz);
+      if (dz_add) load8(dz_add + off, add);
+    }
   }
   for (; row < rows; row += gridDim.x) {
-    const float mu = mean[row], rs = rstd[row];
     const long long off = (long long)row * H + col;
     // the next row's vectors are requested now and consumed in the next iteration
     float dn[8] = {0, 0, 0, 0, 0, 0, 0, 0}, zn[8] = {0, 0, 0, 0, 0, 0, 0, 0}, an[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     const int next = row + gridDim.x;
-    if (next < rows && active) {
-      const long long noff = (long long)next * H + col;
-      load8(dy + noff, dn);
-      load8(z + noff, zn);
-      if (dz_add) load8(dz_add + noff, an);
+    float mun = 0.f, rsn = 0.f;
+    if (next < rows) {
+      mun = mean[next]; rsn = rstd[next];
+      if (active) {
+        const long long noff = (long long)next * H + col;
+        load8(dy + noff, dn);
+        load8(z + noff, zn);
+        if (dz_add) load8(dz_add + noff, an);
+      }
     }
     float xh[8], g[8];
     float s1 = 0.f, s2 = 0.f;
@@ -218,6 +242,7 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) { d[j] = dn[j]; zz[j] = zn[j]; add[j] = an[j]; }
+    mu = mun; rs = rsn;
   }
   if (active) {
     const long long stride = (long long)gridDim.x * H;
@@ -1420,7 +1445,7 @@ void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* bet
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st) {
   if (rows <= 0) return;
   const int threads = ((H / 8 + 31) / 32) * 32;
-  ln_fwd_kernel<<<rows, threads, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
+  ln_fwd_kernel<<<rows < 1184 ? rows : 1184, threads, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
 }
 // Blocks of the backward kernel: four per SM when there are rows enough, so that a block keeps several rows (its
 // per-column partial sums are written once per block).
