@@ -217,6 +217,43 @@ void gemm_gathered_b(const Tensor& a_, const std::vector<int64_t>& shard_ptrs, i
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
 }
 
+// dX = dY . W where W [N_out, K_in] is split by rows into `world` equal shards in the owners' memories (the input gradient of
+// gemm_gathered_b's layer): W is the MN-major B operand and every 64-row K block is fetched from the owner of those rows.
+void gemm_gathered_bt(const Tensor& a_, const std::vector<int64_t>& shard_ptrs, int64_t rows_per_shard, int64_t cols, Tensor c_, Tensor error_flag) {
+  const c10::cuda::CUDAGuard guard(a_.device());
+  Tensor a = as4d(a_), c = as4d(c_);
+  const int world = (int)shard_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8, "1 to 8 shards");
+  const int M = a.size(2), K = a.size(3);
+  TORCH_CHECK(K == rows_per_shard * world, "dY width must equal the number of weight rows");
+  TORCH_CHECK(a.size(0) == 1 && a.size(1) == 1, "the gathered-weight GEMM is not batched");
+  TORCH_CHECK(c.size(2) == M && c.size(3) == cols && c.stride(3) == 1, "output shape mismatch");
+  TORCH_CHECK(rows_per_shard % 64 == 0 && cols % 8 == 0, "rows per shard must be a multiple of 64 and the width a multiple of 8");
+  const int64_t bn = cols >= 256 ? 256 : (cols > 64 ? 128 : 64);
+  CUtensorMap tmA = make_map(a, 128);
+  adb200::TmapArray tmB;
+  for (int s = 0; s < 8; ++s) {
+    const int src = s < world ? s : 0;
+    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows_per_shard, 1, 1};
+    cuuint64_t strides[3] = {(cuuint64_t)cols * 2, (cuuint64_t)cols * 2 * rows_per_shard, (cuuint64_t)cols * 2 * rows_per_shard};
+    cuuint32_t box[4] = {64, 64, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode_fn()(&tmB.m[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, reinterpret_cast<void*>(shard_ptrs[src]), dims, strides, box,
+                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed for shard ", s, " with code ", (int)r);
+  }
+  adb200::GemmParams p{};
+  p.M = M; p.N = (int)cols; p.K = K; p.batch_lo = 1; p.batch_hi = 1;
+  p.C = c.data_ptr(); p.ldc = c.stride(2); p.strideC_lo = 0; p.strideC_hi = 0;
+  p.c_is_fp32 = c.scalar_type() == at::kFloat;
+  p.epilogue = adb200::EPI_NONE; p.alpha = 1.0f; p.beta = 0.0f;
+  p.error_flag = error_flag.data_ptr<int>();
+  p.b_shard_rows = (int)rows_per_shard;
+  cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, false, true, num_sms(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
+}
+
 #define BF(t) reinterpret_cast<__nv_bfloat16*>((t).data_ptr())
 #define CBF(t) reinterpret_cast<const __nv_bfloat16*>((t).data_ptr())
 #define OPT_BF(t) ((t).has_value() ? reinterpret_cast<__nv_bfloat16*>((t)->data_ptr()) : nullptr)
@@ -516,7 +553,7 @@ void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error,
                            const Tensor& grad_ptrs, const Tensor& p16_ptrs, const optional<Tensor>& p32_ptrs, int64_t mc_grad, int64_t mc_p16,
                            int64_t mc_p32, Tensor master,
                            const optional<Tensor>& s1, const optional<Tensor>& s2, const Tensor& seg_start, const Tensor& seg_len,
-                           const Tensor& seg_state, const Tensor& owned_prefix, int64_t kind, const Tensor& lr, const Tensor& step, double b1,
+                           const Tensor& seg_state, const optional<Tensor>& seg_flags, const Tensor& owned_prefix, int64_t kind, const Tensor& lr, const Tensor& step, double b1,
                            double b2, double eps, double wd, double momentum, double grad_scale, bool decoupled, bool nesterov, double scale,
                            int64_t blocks) {
   adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
@@ -528,7 +565,9 @@ void reduce_scatter_update(const Tensor& flag_ptrs, Tensor epochs, Tensor error,
       p32_ptrs.has_value() ? reinterpret_cast<float* const*>(p32_ptrs->data_ptr<int64_t>()) : nullptr, reinterpret_cast<float*>(mc_grad),
       reinterpret_cast<__nv_bfloat16*>(mc_p16), reinterpret_cast<float*>(mc_p32), master.data_ptr<float>(), OPT_F(s1),
       OPT_F(s2), reinterpret_cast<const long long*>(seg_start.data_ptr<int64_t>()), reinterpret_cast<const long long*>(seg_len.data_ptr<int64_t>()),
-      reinterpret_cast<const long long*>(seg_state.data_ptr<int64_t>()), reinterpret_cast<const long long*>(owned_prefix.data_ptr<int64_t>()), nseg,
+      reinterpret_cast<const long long*>(seg_state.data_ptr<int64_t>()),
+      seg_flags.has_value() ? reinterpret_cast<const long long*>(seg_flags->data_ptr<int64_t>()) : nullptr,
+      reinterpret_cast<const long long*>(owned_prefix.data_ptr<int64_t>()), nseg,
       (int)kind, lr.data_ptr<float>(), reinterpret_cast<const long long*>(step.data_ptr<int64_t>()), (float)b1, (float)b2, (float)eps, (float)wd,
       (float)momentum, (float)grad_scale, decoupled ? 1 : 0, nesterov ? 1 : 0, (float)scale, (int)blocks, STREAM);
 }
@@ -573,6 +612,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_softmax", &gemm_softmax);
   m.def("gemm_gathered_b", &gemm_gathered_b);
+  m.def("gemm_gathered_bt", &gemm_gathered_bt);
   m.def("ln_fwd", &ln_fwd);
   m.def("ln_bwd", &ln_bwd);
   m.def("ln_bwd_blocks", &adb200::ln_bwd_blocks);

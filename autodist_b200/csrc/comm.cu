@@ -285,8 +285,8 @@ __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, fl
                                                                     float* const* p32, float* mc_grad, __nv_bfloat16* mc_p16,
                                                                     float* mc_p32, float* master, float* s1, float* s2,
                                                                     const long long* seg_start, const long long* seg_len,
-                                                                    const long long* seg_state, const long long* owned_prefix,
-                                                                    int nseg, OptArgs o, float scale) {
+                                                                    const long long* seg_state, const long long* seg_flags,
+                                                                    const long long* owned_prefix, int nseg, OptArgs o, float scale) {
   if (!sym_barrier(c)) return;
   const long long total4 = owned_prefix[nseg] / 4;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
@@ -300,6 +300,9 @@ __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, fl
     const long long within = e - owned_prefix[lo];
     const long long gi = seg_start[lo] + within;     // index in the flat bucket
     const long long si = seg_state[lo] + within;     // index in the owner's compact state
+    // bit 0 of the segment's flags: the consumers fetch this segment from its owner inside their GEMMs (gemm_gathered_b),
+    // so the updated values are written to the owner's own copies only
+    const bool local_only = seg_flags != nullptr && (seg_flags[lo] & 1);
     float g[4] = {0.f, 0.f, 0.f, 0.f};
     if (mc_grad != nullptr) {
       Wire<float>::mc_reduce(mc_grad + gi, g);
@@ -341,6 +344,11 @@ __global__ void __launch_bounds__(512) reduce_scatter_update_kernel(SymCtx c, fl
     if (s2) *reinterpret_cast<float4*>(s2 + si) = make_float4(b[0], b[1], b[2], b[3]);
     __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]), h1 = __floats2bfloat162_rn(p[2], p[3]);
     const uint2 w = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+    if (local_only) {
+      *reinterpret_cast<uint2*>(p16[c.rank] + gi) = w;
+      if (p32) *reinterpret_cast<float4*>(p32[c.rank] + gi) = make_float4(p[0], p[1], p[2], p[3]);
+      continue;
+    }
     if (mc_p16 != nullptr) {
       asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc_p16 + gi), "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y))
                    : "memory");
@@ -464,11 +472,12 @@ void launch_allreduce(const SymCtx& c, void* const* bufs, void* mc, int wire, lo
 void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfloat16* const* p16, float* const* p32, float* mc_grad,
                                   __nv_bfloat16* mc_p16, float* mc_p32, float* master,
                                   float* s1, float* s2, const long long* seg_start, const long long* seg_len, const long long* seg_state,
-                                  const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
+                                  const long long* seg_flags, const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
                                   float b2, float eps, float wd, float momentum, float grad_scale, int decoupled, int nesterov,
                                   float scale, int blocks, cudaStream_t st) {
   OptArgs o{kind, lr, step, b1, b2, eps, wd, momentum, grad_scale, decoupled, nesterov};
-  reduce_scatter_update_kernel<<<blocks, 512, 0, st>>>(c, grads, p16, p32, mc_grad, mc_p16, mc_p32, master, s1, s2, seg_start, seg_len, seg_state, owned_prefix, nseg, o, scale);
+  reduce_scatter_update_kernel<<<blocks, 512, 0, st>>>(c, grads, p16, p32, mc_grad, mc_p16, mc_p32, master, s1, s2, seg_start, seg_len, seg_state, seg_flags,
+                                                       owned_prefix, nseg, o, scale);
 }
 
 void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* const* touched, const int64_t* ids, const void* vals,

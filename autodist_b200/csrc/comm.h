@@ -24,7 +24,7 @@ void launch_allreduce(const SymCtx& c, void* const* bufs, void* mc, int wire, lo
 void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfloat16* const* p16, float* const* p32, float* mc_grad,
                                   __nv_bfloat16* mc_p16, float* mc_p32, float* master,
                                   float* s1, float* s2, const long long* seg_start, const long long* seg_len, const long long* seg_state,
-                                  const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
+                                  const long long* seg_flags, const long long* owned_prefix, int nseg, int kind, const float* lr, const long long* step, float b1,
                                   float b2, float eps, float wd, float momentum, float grad_scale, int decoupled, int nesterov,
                                   float scale, int blocks, cudaStream_t st);
 void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* const* touched, const int64_t* ids, const void* vals,

@@ -97,15 +97,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
           } else {
             tma_load_4d(a_dst, &tmA, &full[stage], k0, m0, b_lo, b_hi);
           }
-          // Row-sharded B: the tile's rows live in one owner's memory; its map addresses that peer directly.
-          const int shard = p.b_shard_rows > 0 ? n0 / p.b_shard_rows : 0;
-          const int nb = n0 - shard * p.b_shard_rows;
-          const CUtensorMap* tmB = &tmBs.m[shard];
+          // Row-sharded B: the rows of the stored matrix live in their owners' memories; each shard's map addresses that peer
+          // directly. K-major B stores [N, K] (a tile's N rows come from one owner), MN-major B stores [K, N] (a K block's
+          // 64 rows come from one owner).
           if (B_MN) {
+            const int shard = p.b_shard_rows > 0 ? k0 / p.b_shard_rows : 0;
+            const int kl = k0 - shard * p.b_shard_rows;
+            const CUtensorMap* tmB = &tmBs.m[shard];
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_4d(b_dst + j * (BK * 128), tmB, &full[stage], nb + 64 * j, k0, b_lo, b_hi);
+            for (int j = 0; j < BN / 64; ++j) tma_load_4d(b_dst + j * (BK * 128), tmB, &full[stage], n0 + 64 * j, kl, b_lo, b_hi);
           } else {
-            tma_load_4d(b_dst, tmB, &full[stage], k0, nb, b_lo, b_hi);
+            const int shard = p.b_shard_rows > 0 ? n0 / p.b_shard_rows : 0;
+            const int nb = n0 - shard * p.b_shard_rows;
+            tma_load_4d(b_dst, &tmBs.m[shard], &full[stage], k0, nb, b_lo, b_hi);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }

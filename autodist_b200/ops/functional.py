@@ -38,7 +38,12 @@ class _LinearFn(torch.autograd.Function):
         err = _error_flag(x.device)
         pre = None
         b32 = bias.float().contiguous() if bias is not None else None
-        if activation == "gelu":
+        gathered = getattr(weight, "_gathered", None) if activation is None else None
+        ctx.gathered = gathered
+        if gathered is not None:
+            # the weight's row shards stay with their owners: B tiles are fetched over NVLink inside the GEMM
+            E.gemm_gathered_b(x2, gathered["ptrs"], gathered["rows"], y, 1 if b32 is not None else 0, b32, err, 0)
+        elif activation == "gelu":
             pre = torch.empty_like(y)
             E.gemm(x2, w16, pre, False, False, 2, b32 if b32 is not None else torch.zeros(weight.shape[0], device=x.device),
                    y, None, 1.0, 0.0, err, 0)
@@ -65,7 +70,10 @@ class _LinearFn(torch.autograd.Function):
             E.gelu_bwd(dy2, pre, du)
             dy2 = du
         dx = torch.empty_like(x2)
-        E.gemm(dy2, w16, dx, False, True, 0, None, None, None, 1.0, 0.0, err, 0)          # dX = dY . W
+        if ctx.gathered is not None:
+            E.gemm_gathered_bt(dy2, ctx.gathered["ptrs"], ctx.gathered["rows"], w16.shape[1], dx, err)   # dX = dY . W, W from its owners
+        else:
+            E.gemm(dy2, w16, dx, False, True, 0, None, None, None, 1.0, 0.0, err, 0)      # dX = dY . W
         acc = _direct_grad(ctx.weight)
         if acc is not None:
             E.gemm(dy2, x2, acc, True, True, 0, None, None, None, 1.0, 1.0, err, 0)       # dW += dY^T . X, in the gradient buffer

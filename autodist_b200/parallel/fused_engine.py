@@ -678,16 +678,18 @@ class FusedStepEngine(StepEngine):
             starts = [st for st, _ in mine] or [0]
             lens = [ln for _, ln in mine] or [0]
             state = [self._state_offset[st] for st, _ in mine] or [0]
+            local = getattr(self, "_local_segments", set())
+            flags = [1 if st in local else 0 for st, _ in mine] or [0]
             prefix = [0]
             for ln in lens:
                 prefix.append(prefix[-1] + ln)
             t = lambda v: torch.tensor(v, dtype=torch.int64, device=self.device)   # noqa: E731
             total = sum(ln for _, ln, _ in inside)
-            self._ps_tables[key] = (bool(inside), t(starts), t(lens), t(state), t(prefix), total)
+            self._ps_tables[key] = (bool(inside), t(starts), t(lens), t(state), t(prefix), total, t(flags) if any(flags) else None)
         return self._ps_tables[key]
 
     def _ps_update_range(self, lo, hi):
-        any_inside, starts, lens, state, prefix, total = self._ps_table(lo, hi)
+        any_inside, starts, lens, state, prefix, total, flags = self._ps_table(lo, hi)
         if not any_inside:
             return 0
         g = self.opt_info.optimizer.param_groups[0]
@@ -698,7 +700,7 @@ class FusedStepEngine(StepEngine):
         self.E.reduce_scatter_update(*self.arena.ctx(), self._grad_sym["ptrs"], self._p16_sym, self._p32_sym,
                                      self._grad_sym["mc"] if use_mc else 0, self._p16_mc if use_mc else 0, self._p32_mc if use_mc else 0,
                                      self.ps_master,
-                                     self.ps_s1, self.ps_s2, starts, lens, state, prefix, kind, self.lr, self.opt_step,
+                                     self.ps_s1, self.ps_s2, starts, lens, state, flags, prefix, kind, self.lr, self.opt_step,
                                      b1, b2, g.get("eps", 1e-8), g.get("weight_decay", 0.0), g.get("momentum", 0.0), 1.0,
                                      self.opt_kind == "AdamW", bool(g.get("nesterov", False)), 1.0 / self.world_size, blocks)
         return 1
@@ -1016,6 +1018,7 @@ class FlatAutogradEngine(FusedStepEngine):
                     self._flight_of[m] = len(self._flights) - 1
                 members, hi = [], lo
         self._setup_clip()
+        self._setup_gathered_weights()
         for name, p in zip(fl.names, fl.params):
             hook = self._make_hook(name)
             p.register_post_accumulate_grad_hook(hook)
@@ -1023,6 +1026,71 @@ class FlatAutogradEngine(FusedStepEngine):
             # bypass autograd's accumulation and report completion through this attribute instead
             p._direct_grad = os.environ.get("AUTODIST_DIRECT_GRAD", "1") == "1"
             p._grad_ready_hook = hook
+
+    def _setup_gathered_weights(self):
+        """All-gather fused into the consumer (K3): a large fully connected weight that the plan splits along axis 0 into one
+        shard per rank (rank ``i`` owns block ``i``) is not written back to the other replicas after its owner's update.
+        Its consumers - ``ops.functional.linear`` forward and input gradient - fetch the shards from their owners tile by
+        tile inside the GEMM (``gemm_gathered_b`` / ``gemm_gathered_bt``, plain TMA loads over NVLink), so the weight crosses
+        the links as bf16 tiles that are used at once instead of as fp32 + bf16 copies that are stored first. The reference
+        reads such a variable from its parameter server, or from a mirror refreshed after every update
+        (``autodist/kernel/synchronization/ps_synchronizer.py:175-176``, ``autodist/kernel/common/proxy_variable.py:96-114``)."""
+        self.gathered_vars = {}
+        self._local_segments = set()
+        if self.world_size <= 1 or not self.ps_segments or os.environ.get("AUTODIST_GATHER_WEIGHTS", "1") != "1":
+            return
+        from autodist_b200.ops.functional import Linear
+        min_bytes = float(os.environ.get("AUTODIST_GATHER_MIN_MB", "64")) * (1 << 20)
+        fl, world = self.flat, self.world_size
+        flat_of = {id(p): n for n, p in zip(fl.names, fl.params)}
+        by_var = {}
+        for e in self.plan.ps_entries.values():
+            by_var.setdefault(e.part.var_name, []).append(e)
+        seg_owner = {st: (ln, ow) for st, ln, ow in self.ps_segments}
+        bases = [int(x) for x in self._p16_sym.tolist()]
+        for m in self.item.root.modules():
+            if not isinstance(m, Linear) or id(m.weight) not in flat_of:
+                continue
+            p = m.weight
+            n_out, k_in = p.shape
+            var_name = self.item.name_of_parameter(p)
+            entries = sorted(by_var.get(var_name, []), key=lambda e: e.part.offset)
+            rows = n_out // world
+            if p.numel() * 2 < min_bytes or len(entries) != world or n_out % world or rows % 64 or k_in % 8:
+                continue
+            owners = [e.owner for e in entries]
+            if sorted(owners) != list(range(world)) or any(e.part.axis != 0 or e.part.size != rows for e in entries):
+                continue              # (every rank owns exactly one block, in any order)
+            base = fl.offsets[flat_of[id(p)]]
+            starts = [base + i * rows * k_in for i in range(world)]
+            if any(seg_owner.get(st) != (rows * k_in, owners[i]) for i, st in enumerate(starts)):
+                continue
+            self._local_segments.update(starts)
+            p._gathered = {"ptrs": [bases[owners[i]] + 2 * starts[i] for i in range(world)], "rows": rows}
+            self.gathered_vars[var_name] = (flat_of[id(p)], rows, k_in, owners)
+        if self.gathered_vars:
+            logging.info("weights gathered inside their GEMMs instead of written back: %s", ", ".join(self.gathered_vars))
+
+    def _refresh_gathered(self):
+        """Bring every replica's copies of the gathered weights up to date (variable fetches, checkpoints): each owner
+        contributes its rows."""
+        fl = self.flat
+        for name, rows, k_in, owners in self.gathered_vars.values():
+            base = fl.offsets[name]
+            n = rows * k_in
+            blk = owners.index(self.rank)                      # the block this rank owns and keeps current
+            mine = fl.master[base + blk * n: base + (blk + 1) * n].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(self.world_size)]
+            dist.all_gather(parts, mine, group=self.backend.group)
+            for i in range(self.world_size):
+                t = parts[owners[i]]
+                fl.master[base + i * n: base + (i + 1) * n].copy_(t)
+                fl.p16[base + i * n: base + (i + 1) * n].copy_(t)
+
+    def variable_value(self, name):
+        if getattr(self, "gathered_vars", None) and name in self.gathered_vars:
+            self._refresh_gathered()
+        return super().variable_value(name)
 
     def _setup_clip(self):
         """Global-norm clipping (``minimize(..., clip_global_norm=(max_norm, parameters))``): flights that carry a clipped

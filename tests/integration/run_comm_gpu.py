@@ -124,7 +124,7 @@ def main():
             E.increment(step)
             torch.cuda.synchronize(); dist.barrier()
             E.reduce_scatter_update(*ctx(), gptrs, p16ptrs, p32ptrs, mcs[0], mcs[1], mcs[2], master, m1, m2, i64(seg_start), i64(seg_len), i64(seg_state),
-                                    i64(prefix), 1, lr, step, 0.9, 0.999, 1e-8, 0.0, 0.0, 1.0, False, False, 1.0 / world, 8)
+                                    None, i64(prefix), 1, lr, step, 0.9, 0.999, 1e-8, 0.0, 0.0, 1.0, False, False, 1.0 / world, 8)
             torch.cuda.synchronize()
             arena.check()
             dist.barrier()

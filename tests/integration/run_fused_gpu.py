@@ -92,6 +92,7 @@ def run_cnn(strategy_name, comm, world, rank):
         torch.cuda.synchronize()
         state = torch.cat([sess.engine.variable_value(n).reshape(-1).float() for n, _ in ad.graph_item.named_parameters()])
         engine = type(sess.engine).__name__
+        run_cnn.gathered = sorted(getattr(sess.engine, "gathered_vars", {}))
         sess.close()
     return state, losses, engine
 
@@ -259,6 +260,17 @@ def main():
         if rank == 0:
             print(f"cnn {name}: engines {ref_engine} vs {engine}, max |param diff| {diff:.2e} (tol {tol}), "
                   f"loss {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
+    # K3: the large fully connected weight stays sharded; its GEMMs fetch the shards from their owners
+    os.environ["AUTODIST_GATHER_MIN_MB"] = "1"
+    ref, _, ref_engine = run_cnn("PartitionedPS_gpu", "nccl", world, rank)
+    got, losses, engine = run_cnn("PartitionedPS_gpu", "fused", world, rank)
+    os.environ.pop("AUTODIST_GATHER_MIN_MB")
+    diff = (got - ref).abs().max().item()
+    ok = diff <= 2e-3 and engine == "FlatAutogradEngine" and len(run_cnn.gathered) >= 1 and all(l == l for l in losses)
+    failures += 0 if ok else 1
+    if rank == 0:
+        print(f"cnn PartitionedPS_gpu, weights gathered inside the GEMMs ({', '.join(run_cnn.gathered)}): max |param diff| {diff:.2e} "
+              f"(tol 0.002), loss {losses[0]:.4f} -> {losses[-1]:.4f} {'ok' if ok else 'FAIL'}", flush=True)
     for name in ("AllReduce", "AllReduce_EF", "AllReduce_PowerSGD", "PSLoadBalancing_gpu", "PartitionedPS_gpu", "UnevenPartitionedPS_gpu",
                  "Parallax_gpu", "PartitionedAR", "RandomAxisPartitionAR"):
         ref, _, ref_losses, ref_engine = run(name, "nccl", world, rank)
