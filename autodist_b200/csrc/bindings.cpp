@@ -600,10 +600,33 @@ void sym_barrier(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t r
   adb200::launch_barrier(c, (int)blocks, STREAM);
 }
 
+// step (optional int64 device scalar) overrides my_step; staleness < 0 publishes the step without waiting; max_lead (optional int32
+// device scalar) keeps the largest lead this rank had when it passed the gate.
 void staleness_gate(const Tensor& flag_ptrs, Tensor epochs, Tensor error, int64_t rank, int64_t world, double timeout_s,
-                    const Tensor& clock_ptrs, int64_t my_step, int64_t staleness) {
+                    const Tensor& clock_ptrs, int64_t my_step, int64_t staleness, const optional<Tensor>& step, const optional<Tensor>& max_lead) {
   adb200::SymCtx c = make_ctx(flag_ptrs, epochs, error, rank, world, timeout_s);
-  adb200::launch_staleness_gate(c, reinterpret_cast<uint32_t* const*>(clock_ptrs.data_ptr<int64_t>()), (uint32_t)my_step, (uint32_t)staleness, STREAM);
+  adb200::launch_staleness_gate(c, reinterpret_cast<uint32_t* const*>(clock_ptrs.data_ptr<int64_t>()), (uint32_t)my_step, OPT_LL(step),
+                                (int)staleness, max_lead.has_value() ? max_lead->data_ptr<int>() : nullptr, STREAM);
+}
+
+// Relaxed parameter server with GPU owners (plain SGD): p32_owner[segment] -= lr * grad_scale * grad[segment], as vector reductions on
+// the owners' fp32 copies. Segment tables: int64 device tensors; prefix has nseg + 1 entries; every start / length a multiple of 4.
+void relaxed_push_sgd(const Tensor& p32_ptrs, const Tensor& grad, const Tensor& seg_start, const Tensor& seg_len, const Tensor& seg_owner,
+                      const Tensor& prefix, const Tensor& lr, double grad_scale, int64_t blocks) {
+  const int nseg = seg_start.numel();
+  TORCH_CHECK(prefix.numel() == nseg + 1 && seg_owner.numel() == nseg && grad.scalar_type() == at::kFloat, "bad segment tables");
+  auto ll = [](const Tensor& t) { return reinterpret_cast<const long long*>(t.data_ptr<int64_t>()); };
+  adb200::launch_relaxed_push_sgd(reinterpret_cast<float* const*>(p32_ptrs.data_ptr<int64_t>()), grad.data_ptr<float>(), ll(seg_start), ll(seg_len),
+                                  ll(seg_owner), ll(prefix), nseg, lr.data_ptr<float>(), (float)grad_scale, (int)blocks, STREAM);
+}
+// Refresh this rank's fp32 and bf16 copies of every segment from the segment's owner.
+void relaxed_pull(const Tensor& p32_ptrs, Tensor master, Tensor p16, const Tensor& seg_start, const Tensor& seg_len, const Tensor& seg_owner,
+                  const Tensor& prefix, int64_t rank, int64_t blocks) {
+  const int nseg = seg_start.numel();
+  TORCH_CHECK(prefix.numel() == nseg + 1 && seg_owner.numel() == nseg, "bad segment tables");
+  auto ll = [](const Tensor& t) { return reinterpret_cast<const long long*>(t.data_ptr<int64_t>()); };
+  adb200::launch_relaxed_pull(reinterpret_cast<float* const*>(p32_ptrs.data_ptr<int64_t>()), master.data_ptr<float>(), BF(p16), ll(seg_start),
+                              ll(seg_len), ll(seg_owner), ll(prefix), nseg, (int)rank, (int)blocks, STREAM);
 }
 
 }  // namespace
@@ -660,6 +683,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_gather_peers", &embedding_gather_peers);
   m.def("sym_barrier", &sym_barrier);
   m.def("staleness_gate", &staleness_gate);
+  m.def("relaxed_push_sgd", &relaxed_push_sgd);
+  m.def("relaxed_pull", &relaxed_pull);
   m.attr("MAX_COMM_BLOCKS") = adb200::kMaxCommBlocks;
   register_conv(m);
 }

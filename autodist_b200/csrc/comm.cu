@@ -438,16 +438,62 @@ __global__ void embedding_gather_peers_kernel(SymCtx c, __nv_bfloat16* const* sh
 // Staleness gate: publishes this rank's step to every peer and waits until step - min(peer steps) <= staleness.
 __global__ void barrier_kernel(SymCtx c) { sym_barrier(c); }
 
-__global__ void staleness_gate_kernel(SymCtx c, uint32_t* const* clocks, uint32_t my_step, uint32_t staleness) {
+// step_ptr (optional): the step is read from device memory (a counter the step's kernels increment), so that the launch can
+// be replayed from a CUDA graph. staleness < 0: publish the step only (no wait). max_lead (optional): the largest lead over
+// the slowest peer this rank ever had when it passed the gate.
+__global__ void staleness_gate_kernel(SymCtx c, uint32_t* const* clocks, uint32_t my_step, const long long* step_ptr, int staleness,
+                                      int* max_lead) {
+  if (step_ptr != nullptr) my_step = (uint32_t)(*step_ptr);
   if (threadIdx.x < c.world) {
     __threadfence_system();
     st_release_sys(clocks[threadIdx.x] + c.rank, my_step);
+    if (staleness < 0) return;
     const uint32_t* theirs = clocks[c.rank] + threadIdx.x;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t it = 0;
-    while ((int32_t)(my_step - ld_acquire_sys(theirs)) > (int32_t)staleness) {
+    int32_t lead;
+    while ((lead = (int32_t)(my_step - ld_acquire_sys(theirs))) > (int32_t)staleness) {
       if (((++it) & 63u) == 0 && globaltimer_ns() - t0 > c.timeout_ns) { atomicExch(c.error, 200 + threadIdx.x); break; }
     }
+    if (max_lead != nullptr && lead > 0) atomicMax(max_lead, (int)lead);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ relaxed parameter server
+// Bounded-staleness / asynchronous modes with GPU owners and plain SGD: a worker applies its own gradient to the owner's fp32
+// copy as soon as it has it - p_owner -= lr * g as a vector reduction over NVLink, which commutes with every other worker's, so
+// no lock and no barrier is needed - and later refreshes its local copies from the owners. seg_owner[s] names the rank whose
+// copy of segment s is the authoritative one.
+__global__ void relaxed_push_sgd_kernel(float* const* p32, const float* __restrict__ grad, const long long* seg_start,
+                                        const long long* seg_len, const long long* seg_owner, const long long* prefix, int nseg,
+                                        const float* lr_ptr, float grad_scale) {
+  const long long total4 = prefix[nseg] / 4;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+  const float step = -(*lr_ptr) * grad_scale;
+  for (long long q = tid; q < total4; q += nthr) {
+    const long long e = q * 4;
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (prefix[mid] <= e) lo = mid; else hi = mid - 1; }
+    const long long gi = seg_start[lo] + (e - prefix[lo]);
+    const float4 g = *reinterpret_cast<const float4*>(grad + gi);
+    atomicAdd(reinterpret_cast<float4*>(p32[seg_owner[lo]] + gi), make_float4(step * g.x, step * g.y, step * g.z, step * g.w));
+  }
+}
+
+__global__ void relaxed_pull_kernel(float* const* p32, float* __restrict__ master, __nv_bfloat16* __restrict__ p16, const long long* seg_start,
+                                    const long long* seg_len, const long long* seg_owner, const long long* prefix, int nseg, int rank) {
+  const long long total4 = prefix[nseg] / 4;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+  for (long long q = tid; q < total4; q += nthr) {
+    const long long e = q * 4;
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (prefix[mid] <= e) lo = mid; else hi = mid - 1; }
+    const long long gi = seg_start[lo] + (e - prefix[lo]);
+    const int owner = (int)seg_owner[lo];
+    const float4 v = *reinterpret_cast<const float4*>(p32[owner] + gi);
+    if (owner != rank) *reinterpret_cast<float4*>(master + gi) = v;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p16 + gi) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
   }
 }
 
@@ -493,8 +539,20 @@ void launch_embedding_gather_peers(const SymCtx& c, __nv_bfloat16* const* shard,
 
 void launch_barrier(const SymCtx& c, int blocks, cudaStream_t st) { barrier_kernel<<<blocks, 32, 0, st>>>(c); }
 
-void launch_staleness_gate(const SymCtx& c, uint32_t* const* clocks, uint32_t my_step, uint32_t staleness, cudaStream_t st) {
-  staleness_gate_kernel<<<1, 32, 0, st>>>(c, clocks, my_step, staleness);
+void launch_staleness_gate(const SymCtx& c, uint32_t* const* clocks, uint32_t my_step, const long long* step_ptr, int staleness, int* max_lead,
+                           cudaStream_t st) {
+  staleness_gate_kernel<<<1, 32, 0, st>>>(c, clocks, my_step, step_ptr, staleness, max_lead);
+}
+
+void launch_relaxed_push_sgd(float* const* p32, const float* grad, const long long* seg_start, const long long* seg_len,
+                             const long long* seg_owner, const long long* prefix, int nseg, const float* lr, float grad_scale, int blocks,
+                             cudaStream_t st) {
+  relaxed_push_sgd_kernel<<<blocks, 512, 0, st>>>(p32, grad, seg_start, seg_len, seg_owner, prefix, nseg, lr, grad_scale);
+}
+
+void launch_relaxed_pull(float* const* p32, float* master, __nv_bfloat16* p16, const long long* seg_start, const long long* seg_len,
+                         const long long* seg_owner, const long long* prefix, int nseg, int rank, int blocks, cudaStream_t st) {
+  relaxed_pull_kernel<<<blocks, 512, 0, st>>>(p32, master, p16, seg_start, seg_len, seg_owner, prefix, nseg, rank);
 }
 
 }  // namespace adb200

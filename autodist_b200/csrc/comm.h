@@ -32,6 +32,12 @@ void launch_sparse_scatter_add(const SymCtx& c, float* const* shard, uint8_t* co
 void launch_embedding_gather_peers(const SymCtx& c, __nv_bfloat16* const* shard, const int64_t* ids, __nv_bfloat16* out, long long nrows,
                                    int H, long long V, int barriers, int blocks, cudaStream_t st);
 void launch_barrier(const SymCtx& c, int blocks, cudaStream_t st);
-void launch_staleness_gate(const SymCtx& c, uint32_t* const* clocks, uint32_t my_step, uint32_t staleness, cudaStream_t st);
+void launch_staleness_gate(const SymCtx& c, uint32_t* const* clocks, uint32_t my_step, const long long* step_ptr, int staleness, int* max_lead,
+                           cudaStream_t st);
+void launch_relaxed_push_sgd(float* const* p32, const float* grad, const long long* seg_start, const long long* seg_len,
+                             const long long* seg_owner, const long long* prefix, int nseg, const float* lr, float grad_scale, int blocks,
+                             cudaStream_t st);
+void launch_relaxed_pull(float* const* p32, float* master, __nv_bfloat16* p16, const long long* seg_start, const long long* seg_len,
+                         const long long* seg_owner, const long long* prefix, int nseg, int rank, int blocks, cudaStream_t st);
 
 }  // namespace adb200

@@ -375,7 +375,17 @@ class FusedStepEngine(StepEngine):
                     if compressor_of.setdefault(p.var_name, b.compressor_type) != b.compressor_type:
                         return False
             for e in plan.ps_entries.values():
-                if e.gate != "sync" or (e.part.part_index is not None and e.part.axis != 0):
+                if e.part.part_index is not None and e.part.axis != 0:
+                    return False
+            if plan.gate_mode != "sync":
+                # Bounded staleness / asynchronous updates with GPU owners: every worker applies its own gradient to the
+                # owner's copy as a reduction over NVLink, which is only order-independent for plain SGD; there is no
+                # lock-step collective in such a step, so all-reduce buckets cannot be mixed in. Anything else keeps
+                # the host-side service of the generic engine.
+                g = graph_item.optimizers[0].optimizer.param_groups[0]
+                plain_sgd = type(graph_item.optimizers[0].optimizer).__name__ == "SGD" and not g.get("momentum", 0) \
+                    and not g.get("weight_decay", 0)
+                if not plain_sgd or plan.ar_buckets or plan.sparse_all_reduce or any(e.gate == "sync" for e in plan.ps_entries.values()):
                     return False
         return True
 
@@ -533,6 +543,68 @@ class FusedStepEngine(StepEngine):
             self._residual = torch.zeros(fl.total, dtype=torch.float32, device=self.device)
         self._setup_ps_segments(flat_name)
         self._setup_powersgd(psgd)
+        self._setup_relaxed()
+
+    # ---- relaxed parameter server on GPUs (bounded staleness / asynchronous): push, gate, pull -------------------------------
+    def _setup_relaxed(self):
+        """``sync=False`` or ``staleness > 0`` with GPU owners (reference: token queues of capacity ``staleness`` and unaggregated
+        updates, ``autodist/kernel/synchronization/ps_synchronizer.py:261-262,388-458``). Each flight pushes this worker's
+        gradient into the owners' fp32 copies (``relaxed_push_sgd``: vector reductions over NVLink); at the end of the step
+        the worker publishes its step and - under bounded staleness - waits until it is at most ``staleness`` steps ahead of
+        the slowest peer (``staleness_gate``, a bounded wait that reports ``200 + peer``), then refreshes its copies from the
+        owners (``relaxed_pull``). Nothing in such a step is a collective, so a slow worker delays nobody beyond the bound."""
+        self._relaxed = None
+        if self.world_size <= 1 or self.plan.gate_mode == "sync" or not self.ps_segments:
+            return
+        dev = self.device
+        t = lambda v: torch.tensor(v, dtype=torch.int64, device=dev)        # noqa: E731
+        clocks, cptrs, _ = self.arena.alloc(8, torch.int32)
+        clocks.zero_()
+        self._relaxed = {"staleness": int(self.plan.staleness) if self.plan.gate_mode == "stale" else -1, "clocks": clocks, "cptrs": cptrs,
+                         "max_lead": torch.zeros(1, dtype=torch.int32, device=dev), "tables": {}, "t": t}
+        self.arena.timeout_s = float(os.environ.get("AUTODIST_GATE_TIMEOUT", str(self.arena.timeout_s)))
+        torch.cuda.synchronize()
+        dist.barrier(group=self.backend.group)
+
+    def _relaxed_table(self, lo, hi):
+        tabs = self._relaxed["tables"]
+        if (lo, hi) not in tabs:
+            inside = [(st, ln, ow) for st, ln, ow in self.ps_segments if st >= lo and st + ln <= hi]
+            prefix = [0]
+            for _, ln, _ in inside:
+                prefix.append(prefix[-1] + ln)
+            t = self._relaxed["t"]
+            tabs[(lo, hi)] = (t([x[0] for x in inside] or [0]), t([x[1] for x in inside] or [0]), t([x[2] for x in inside] or [0]), t(prefix),
+                              prefix[-1]) if inside else None
+        return tabs[(lo, hi)]
+
+    def _relaxed_push(self, lo, hi):
+        tab = self._relaxed_table(lo, hi)
+        if tab is None:
+            return
+        starts, lens, owners, prefix, total = tab
+        blocks = max(8, min(self.E.MAX_COMM_BLOCKS, total // (4 * 512 * 4) + 1))
+        self.E.relaxed_push_sgd(self._p32_sym, self.flat.grad, starts, lens, owners, prefix, self.lr, 1.0, blocks)
+
+    def _finish_relaxed(self):
+        r = self._relaxed
+        if not r:
+            return
+        compute = torch.cuda.current_stream()
+        self._ready_event.record(compute)
+        self.comm_stream.wait_event(self._ready_event)
+        with torch.cuda.stream(self.comm_stream):
+            self.E.staleness_gate(*self.arena.ctx(), r["cptrs"], 0, r["staleness"], self.opt_step, r["max_lead"])
+            tab = self._relaxed_table(0, self.flat.total)
+            if tab is not None:
+                starts, lens, owners, prefix, total = tab
+                blocks = max(8, min(self.E.MAX_COMM_BLOCKS, total // (4 * 512 * 4) + 1))
+                self.E.relaxed_pull(self._p32_sym, self.flat.master, self.flat.p16, starts, lens, owners, prefix, self.rank, blocks)
+
+    @property
+    def max_lead(self):
+        """Largest number of steps this rank was ahead of the slowest peer when it passed the staleness gate."""
+        return int(self._relaxed["max_lead"].item()) if self._relaxed else 0
 
     # ---- PowerSGD (K8): every matrix of the step in three batched passes + two all-reduces of the stacked factors -------------
     def _setup_powersgd(self, mats):
@@ -721,6 +793,10 @@ class FusedStepEngine(StepEngine):
         self.comm_stream.wait_event(self._ready_event)
         keys = [f"g{gk}/i{ik}" for a, z, gk, ik in getattr(self, "_range_key", ()) if a < hi and z > lo]
         with nvtx.annotate(f"flight [{lo}, {hi}) {' '.join(keys[:4])}"), torch.cuda.stream(self.comm_stream):
+            if getattr(self, "_relaxed", None):
+                self._relaxed_push(lo, hi)               # this worker's gradient goes to the owners now; no collective, no local update
+                self.launches_per_step += 1
+                return
             if self.world_size > 1:
                 for a, b, wd, ef in self._policy_for(lo, hi):
                     self._all_reduce_range(a, b, wd, ef)
@@ -771,6 +847,7 @@ class FusedStepEngine(StepEngine):
         values = self.forward(all_nodes, feeds, grad=True)
         self._finish_rows()
         self._finish_powersgd()
+        self._finish_relaxed()
         # the optimizer kernels of the last flights run on the communication stream: join it
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
@@ -922,7 +999,13 @@ class FusedStepEngine(StepEngine):
                 self.ps_master[o:o + ln].copy_(self.flat.master[st_:st_ + ln])
 
     def close(self):
-        return
+        r = getattr(self, "_relaxed", None)
+        if r:
+            # leaving: publish a step no peer can be ahead of, so that nobody waits for a worker that has finished
+            torch.cuda.synchronize()
+            self.E.staleness_gate(*self.arena.ctx(), r["cptrs"], 1 << 30, -1, None, None)
+            torch.cuda.synchronize()
+            self._relaxed = None
 
 
 class _AutogradModel:
@@ -1169,6 +1252,7 @@ class FlatAutogradEngine(FusedStepEngine):
         self._finish_rows()
         self._finish_clipped()
         self._finish_powersgd()
+        self._finish_relaxed()
         self._done_event.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done_event)
         return values

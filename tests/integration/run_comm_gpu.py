@@ -212,13 +212,13 @@ def main():
     clocks, cptrs, _ = arena.alloc(8, torch.int32)
     clocks.zero_()
     torch.cuda.synchronize(); dist.barrier()
-    E.staleness_gate(*arena.ctx(), cptrs, 1, 0)          # all at step 1: nobody is ahead
+    E.staleness_gate(*arena.ctx(), cptrs, 1, 0, None, None)          # all at step 1: nobody is ahead
     torch.cuda.synchronize()
     arena.check()
     dist.barrier()
     arena.timeout_s = 0.5
     if rank == 0:
-        E.staleness_gate(*arena.ctx(), cptrs, 4, 2)      # three steps ahead of peers that stay at step 1: must give up
+        E.staleness_gate(*arena.ctx(), cptrs, 4, 2, None, None)      # three steps ahead of peers that stay at step 1: must give up
         torch.cuda.synchronize()
         code = int(arena.error.item())
         assert 200 < code < 200 + world, code
@@ -226,12 +226,12 @@ def main():
         print(f"staleness gate gave up with status {code} (peer {code - 200} is behind): ok", flush=True)
     dist.barrier()
     if rank != 0:
-        E.staleness_gate(*arena.ctx(), cptrs, 3, 2)      # the others catch up to step 3
+        E.staleness_gate(*arena.ctx(), cptrs, 3, 2, None, None)      # the others catch up to step 3
         torch.cuda.synchronize()
         assert int(arena.error.item()) == 0
     dist.barrier()
     if rank == 0:
-        E.staleness_gate(*arena.ctx(), cptrs, 4, 2)      # one step ahead now: the gate opens at once
+        E.staleness_gate(*arena.ctx(), cptrs, 4, 2, None, None)      # one step ahead now: the gate opens at once
         torch.cuda.synchronize()
         assert int(arena.error.item()) == 0
         print("staleness gate opens once the peers caught up: ok", flush=True)
