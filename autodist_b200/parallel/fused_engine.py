@@ -497,6 +497,7 @@ class FusedStepEngine(StepEngine):
         self.ps_segments = []
         self._wire = self._wire_ptrs = self._residual = None
         self._psgd, self._psgd_flights = None, []
+        self._relaxed = None
         if self.world_size <= 1:
             return
         need16 = False
