@@ -269,15 +269,15 @@ void ln_fwd(const Tensor& x, const optional<Tensor>& res, const Tensor& gamma, c
   adb200::ln_fwd(CBF(x), OPT_BF(res), gamma.data_ptr<float>(), beta.data_ptr<float>(), OPT_BF(z), BF(y), mean.data_ptr<float>(),
                  rstd.data_ptr<float>(), rows, H, (float)eps, (float)p_drop, (uint64_t)seed, OPT_LL(step), STREAM);
 }
-// dsum (optional, fp32 [H]): column sums of the tensor handed to the layer in front of the residual connection (dx when the dropout
+// part: fp32 scratch of ln_bwd_part_floats(H) elements that must be ZERO on entry (allocate it with zeros once); it is zero again on
+// return. dsum (optional, fp32 [H]): column sums of the tensor handed to the layer in front of the residual connection (dx when the dropout
 // copy is written, else dz) - the bias gradient of that layer, produced without another pass over the tensor.
 void ln_bwd(const Tensor& dy, const Tensor& z, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, const optional<Tensor>& dz_add,
             Tensor dz, const optional<Tensor>& dx, Tensor part, Tensor dgamma, Tensor dbeta, double p_drop, int64_t seed,
             const optional<Tensor>& step, bool accumulate, const optional<Tensor>& dsum) {
   const int H = dy.size(-1), rows = dy.numel() / H;
-  const int blocks = adb200::ln_bwd_blocks(rows);
   TORCH_CHECK(H % 8 == 0 && H <= 1024, "layernorm width must be a multiple of 8 and at most 1024");
-  TORCH_CHECK(part.numel() >= 3LL * blocks * H, "partial buffer too small (3 x ln_bwd_blocks(rows) x H floats)");
+  TORCH_CHECK(part.numel() >= adb200::ln_bwd_part_floats(H), "partial buffer too small (ln_bwd_part_floats(H) floats, zero-filled)");
   if (dsum.has_value()) TORCH_CHECK(dsum->scalar_type() == at::kFloat && dsum->numel() >= H, "dsum must be fp32 [H]");
   adb200::ln_bwd(CBF(dy), CBF(z), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), OPT_BF(dz_add), BF(dz),
                  OPT_BF(dx), part.data_ptr<float>(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), OPT_F(dsum), rows, H, (float)p_drop,
@@ -639,6 +639,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ln_fwd", &ln_fwd);
   m.def("ln_bwd", &ln_bwd);
   m.def("ln_bwd_blocks", &adb200::ln_bwd_blocks);
+  m.def("ln_bwd_part_floats", &adb200::ln_bwd_part_floats);
   m.def("colsum_parts", &adb200::colsum_parts);
   m.def("embed_sum", &embed_sum);
   m.def("scatter_add_rows", &scatter_add_rows);

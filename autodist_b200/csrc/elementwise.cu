@@ -156,7 +156,10 @@ __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict
 // One thread per 8 columns, a block walks rows blockIdx.x, blockIdx.x + gridDim.x, ... with the next row's loads issued
 // before the current row's reductions; its per-column sums (dgamma, dbeta and, when asked, the sum of what it writes to
 // dx - the bias gradient of the linear layer in front of the residual) stay in registers and are written once per block
-// as partials part[k][block][H], k = 0 (dgamma), 1 (dbeta), 2 (sum of the output).
+// into part[k][slot][H], k = 0 (dgamma), 1 (dbeta), 2 (sum of the output), slot = block % kLnSlots. `part` must be zero on
+// entry; the reduction kernel that follows clears what it reads, so the buffer is zero again afterwards.
+constexpr int kLnSlots = 16;
+
 __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ z, const float* __restrict__ mean,
                               const float* __restrict__ rstd, const float* __restrict__ gamma, const bf16* __restrict__ dz_add,
                               bf16* __restrict__ dz, bf16* __restrict__ dx, float* __restrict__ part, int rows, int H, float p_drop,
@@ -245,29 +248,32 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
     mu = mun; rs = rsn;
   }
   if (active) {
-    const long long stride = (long long)gridDim.x * H;
-    float* p0 = part + (long long)blockIdx.x * H + col;
-    *reinterpret_cast<float4*>(p0) = make_float4(ag[0], ag[1], ag[2], ag[3]);
-    *reinterpret_cast<float4*>(p0 + 4) = make_float4(ag[4], ag[5], ag[6], ag[7]);
-    *reinterpret_cast<float4*>(p0 + stride) = make_float4(ab[0], ab[1], ab[2], ab[3]);
-    *reinterpret_cast<float4*>(p0 + stride + 4) = make_float4(ab[4], ab[5], ab[6], ab[7]);
+    // The blocks add their sums into kLnSlots shared rows (vector reductions, a few dozen blocks per address) instead of
+    // writing one row each: the follow-up kernel then reads 16 rows per output instead of hundreds.
+    const long long stride = (long long)kLnSlots * H;
+    float* p0 = part + (long long)(blockIdx.x % kLnSlots) * H + col;
+    atomicAdd(reinterpret_cast<float4*>(p0), make_float4(ag[0], ag[1], ag[2], ag[3]));
+    atomicAdd(reinterpret_cast<float4*>(p0 + 4), make_float4(ag[4], ag[5], ag[6], ag[7]));
+    atomicAdd(reinterpret_cast<float4*>(p0 + stride), make_float4(ab[0], ab[1], ab[2], ab[3]));
+    atomicAdd(reinterpret_cast<float4*>(p0 + stride + 4), make_float4(ab[4], ab[5], ab[6], ab[7]));
     if (want_out_sum) {
-      *reinterpret_cast<float4*>(p0 + 2 * stride) = make_float4(ax[0], ax[1], ax[2], ax[3]);
-      *reinterpret_cast<float4*>(p0 + 2 * stride + 4) = make_float4(ax[4], ax[5], ax[6], ax[7]);
+      atomicAdd(reinterpret_cast<float4*>(p0 + 2 * stride), make_float4(ax[0], ax[1], ax[2], ax[3]));
+      atomicAdd(reinterpret_cast<float4*>(p0 + 2 * stride + 4), make_float4(ax[4], ax[5], ax[6], ax[7]));
     }
   }
 }
 
-// Up to three column sums over partials laid out [k][parts][H] in one launch: blockIdx.y = k, out = outs[k].
-__global__ void colsum3_f32_kernel(const float* __restrict__ part, float* __restrict__ out0, float* __restrict__ out1,
+// Up to three column sums over partials laid out [k][parts][H] in one launch: blockIdx.y = k, out = outs[k]. The partials are
+// cleared as they are read (the producer adds into them again next time).
+__global__ void colsum3_f32_kernel(float* __restrict__ part, float* __restrict__ out0, float* __restrict__ out1,
                                    float* __restrict__ out2, int parts, int H, int accumulate) {
   __shared__ float sm[8][33];
-  const float* src = part + (long long)blockIdx.y * parts * H;
+  float* src = part + (long long)blockIdx.y * parts * H;
   float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
   const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
   float a = 0.f;
   if (c < H)
-    for (int r = w; r < parts; r += 8) a += src[(long long)r * H + c];
+    for (int r = w; r < parts; r += 8) { a += src[(long long)r * H + c]; src[(long long)r * H + c] = 0.f; }
   sm[w][threadIdx.x & 31] = a;
   __syncthreads();
   if (w == 0 && c < H) {
@@ -1450,7 +1456,8 @@ void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* bet
 // Blocks of the backward kernel: four per SM when there are rows enough, so that a block keeps several rows (its
 // per-column partial sums are written once per block).
 int ln_bwd_blocks(int rows) { return rows < 592 ? (rows < 1 ? 1 : rows) : 592; }
-// part: 3 * ln_bwd_blocks(rows) * H floats. dsum (optional): column sums of the tensor the kernel hands to the layer in
+int ln_bwd_part_floats(int H) { return 3 * kLnSlots * H; }
+// part: 3 * 16 * H floats, zero on entry and zero again on return. dsum (optional): column sums of the tensor the kernel hands to the layer in
 // front of the residual connection (dx when the dropout copy is written, else dz).
 void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd, const float* gamma, const bf16* dz_add, bf16* dz,
             bf16* dx, float* part, float* dgamma, float* dbeta, float* dsum, int rows, int H, float p_drop, uint64_t seed,
@@ -1458,7 +1465,7 @@ void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd,
   const int blocks = ln_bwd_blocks(rows);
   const int threads = ((H / 8 + 31) / 32) * 32;
   ln_bwd_kernel<<<blocks, threads, 0, st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part, rows, H, p_drop, seed, step, dsum != nullptr);
-  colsum3_f32_kernel<<<dim3(blocks_for(H, 32), dsum != nullptr ? 3 : 2), 256, 0, st>>>(part, dgamma, dbeta, dsum, blocks, H, accumulate);
+  colsum3_f32_kernel<<<dim3(blocks_for(H, 32), dsum != nullptr ? 3 : 2), 256, 0, st>>>(part, dgamma, dbeta, dsum, kLnSlots, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
                int H, long long V, long long types, int* error, cudaStream_t st) {

@@ -9,6 +9,7 @@ typedef __nv_bfloat16 bf16_t;
 void ln_fwd(const bf16_t* x, const bf16_t* res, const float* gamma, const float* beta, bf16_t* z, bf16_t* y, float* mean, float* rstd,
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st);
 int ln_bwd_blocks(int rows);
+int ln_bwd_part_floats(int H);
 void ln_bwd(const bf16_t* dy, const bf16_t* z, const float* mean, const float* rstd, const float* gamma, const bf16_t* dz_add, bf16_t* dz,
             bf16_t* dx, float* part, float* dgamma, float* dbeta, float* dsum, int rows, int H, float p_drop, uint64_t seed,
             const long long* step, int accumulate, cudaStream_t st);

@@ -211,7 +211,7 @@ class BertPretrainer(nn.Module):
                 "qkv": bf(T, 3 * H), "p": bf(B, nh, S, S), "pd": bf(B, nh, S, S) if drop_a else None,
                 "ctx": bf(T, H), "z1": bf(T, H), "m1": f32(T), "r1": f32(T), "x1": bf(T, H),
                 "u": bf(T, Fd), "g": bf(T, Fd), "z2": bf(T, H), "m2": f32(T), "r2": f32(T), "out": bf(T, H)})
-        n_part = max(3 * E.ln_bwd_blocks(T) * H, E.colsum_parts(T) * max(4 * H, Fd, 3 * H, 2 * H),
+        n_part = max( E.colsum_parts(T) * max(4 * H, Fd, 3 * H, 2 * H),
                      E.colsum_parts(B * P) * Vp)
         ws = {
             "key": key, "E": E, "layers": layers, "Vp": Vp,
@@ -220,6 +220,7 @@ class BertPretrainer(nn.Module):
             # backward scratch
             "d_a": bf(T, H), "d_b": bf(T, H), "d_c": bf(T, H), "d_big": bf(T, Fd), "d_qkv": bf(T, 3 * H),
             "d_p": bf(B, nh, S, S), "part": f32(n_part),
+            "ln_part": torch.zeros(E.ln_bwd_part_floats(H), dtype=torch.float32, device=dev),     # zero between calls by contract
             # bias gradients are column sums that nothing in the layer waits for: they run on a side stream next to the
             # GEMMs, each with its own partial-sum scratch (joined before the layer's gradients are reported ready)
             "side_part": [f32(E.colsum_parts(T) * max(Fd, 3 * H)) for _ in range(4)],
@@ -348,7 +349,7 @@ class BertPretrainer(nn.Module):
             g["emb.word"].zero_()
         gm(dlv, ws["hl"], g[dec], a_mn=True, b_mn=True)                               # dE = dlogits^T . hl
         gm(dlv, w16[dec], ws["d_hl"], b_mn=True)                                        # dhl = dlogits . E
-        E.ln_bwd(ws["d_hl"], ws["hm"], ws["mm"], ws["mr"], w32["mlm.ln_g"], None, ws["d_hm"], None, ws["part"],
+        E.ln_bwd(ws["d_hl"], ws["hm"], ws["mm"], ws["mr"], w32["mlm.ln_g"], None, ws["d_hm"], None, ws["ln_part"],
                  g["mlm.ln_g"], g["mlm.ln_b"], 0.0, 0, None, False, None)
         E.gelu_bwd(ws["d_hm"], ws["hm_u"], ws["d_hu"])
         E.keyed_colsum(ws["d_hu"], None, ws["part"], g["mlm.dense_b"], 1, False)
@@ -377,7 +378,7 @@ class BertPretrainer(nn.Module):
             x_in = ws["layers"][l - 1]["out"] if l > 0 else ws["x0"]
             dz2, dfo = spare[0], (spare[1] if ph > 0 else spare[0])
             # the layernorm backward also sums what it hands to the linear layer in front of the residual: that layer's bias gradient
-            E.ln_bwd(d_out, A["z2"], A["m2"], A["r2"], w32[n + "ln2_g"], None, dz2, dfo if ph > 0 else None, ws["part"],
+            E.ln_bwd(d_out, A["z2"], A["m2"], A["r2"], w32[n + "ln2_g"], None, dz2, dfo if ph > 0 else None, ws["ln_part"],
                      g[n + "ln2_g"], g[n + "ln2_b"], ph, seed(l, 3), step, False, g[n + "b2"])
             gm(dfo, A["g"], g[n + "w2"], a_mn=True, b_mn=True)                          # dW2 = dfo^T . g
             gm(dfo, w16[n + "w2"], ws["d_big"], b_mn=True, epi=EPI_MUL_GELU_GRAD, aux=A["u"])   # dU
@@ -386,7 +387,7 @@ class BertPretrainer(nn.Module):
             dx1 = d_out                                                                 # d_out is dead: reuse
             gm(ws["d_big"], w16[n + "w1"], dx1, b_mn=True, epi=EPI_ADD, aux=dz2)        # dx1 = dU . W1 + dz2
             dz1, dao = spare[0], (spare[1] if ph > 0 else spare[0])
-            E.ln_bwd(dx1, A["z1"], A["m1"], A["r1"], w32[n + "ln1_g"], None, dz1, dao if ph > 0 else None, ws["part"],
+            E.ln_bwd(dx1, A["z1"], A["m1"], A["r1"], w32[n + "ln1_g"], None, dz1, dao if ph > 0 else None, ws["ln_part"],
                      g[n + "ln1_g"], g[n + "ln1_b"], ph, seed(l, 2), step, False, g[n + "out_b"])
             gm(dao, A["ctx"], g[n + "out_w"], a_mn=True, b_mn=True)                     # dWo
             dctx = dx1                                                                  # reuse again
@@ -413,7 +414,7 @@ class BertPretrainer(nn.Module):
             ready(lo, hi)
         # embeddings
         dz0 = spare[0]
-        E.ln_bwd(d_out, ws["z0"], ws["m0"], ws["r0"], w32["emb.ln_g"], None, dz0, None, ws["part"], g["emb.ln_g"], g["emb.ln_b"],
+        E.ln_bwd(d_out, ws["z0"], ws["m0"], ws["r0"], w32["emb.ln_g"], None, dz0, None, ws["ln_part"], g["emb.ln_g"], g["emb.ln_b"],
                  0.0, 0, None, False, None)
         if word_rows is not None:
             word_rows.push(ids, dz0)                   # sparse path: (row ids, rows) go to the shard owners

@@ -19,7 +19,7 @@ launch_count = 0      # kernels launched through the extension by this process (
 
 class _Counting:
     """Thin proxy over the extension module that counts kernel-launching calls."""
-    _NO_LAUNCH = {"ln_bwd_blocks", "colsum_parts", "MAX_COMM_BLOCKS"}
+    _NO_LAUNCH = {"ln_bwd_blocks", "ln_bwd_part_floats", "colsum_parts", "MAX_COMM_BLOCKS"}
     _MULTI = {"ln_bwd": 2, "keyed_colsum": 2, "bn_fwd": 3, "bn_bwd": 3}
 
     def __init__(self, mod):

@@ -231,7 +231,7 @@ def main():
     ms = _time(lambda: E.ln_fwd(x, res, g, bta, z, y, mean, rstd, 1e-12, 0.1, 1, None), flush=flush)
     rows.append({"kernel": "ln_fwd 32768x1024 (+res+dropout)", "ms": round(ms, 4), "gbs": round(4 * x.numel() * 2 / ms / 1e6, 1),
                  "frac_of_measured_peak": round(4 * x.numel() * 2 / ms / 1e6 / peaks.get("hbm_gbs", 6518.6), 3)})
-    part = torch.empty(3 * E.ln_bwd_blocks(T * 8) * H, device=dev)
+    part = torch.zeros(E.ln_bwd_part_floats(H), device=dev)
     dg, db = torch.empty(H, device=dev), torch.empty(H, device=dev)
     ms = _time(lambda: E.ln_bwd(y, z, mean, rstd, g, None, x, res, part, dg, db, 0.1, 1, None, False, None), flush=flush)
     rows.append({"kernel": "ln_bwd 32768x1024 (+dropout)", "ms": round(ms, 4), "gbs": round(4 * x.numel() * 2 / ms / 1e6, 1),
