@@ -6,6 +6,7 @@
 #include <torch/extension.h>
 
 #include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "comm.h"
@@ -429,7 +430,12 @@ Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& 
   TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
               "dy, x, dx must be contiguous bf16 [.., C] of one shape, C % 8 == 0");
   if (dres.has_value()) TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel() && dres->scalar_type() == at::kBFloat16, "dres must match x");
-  Tensor part = at::empty({(int64_t)adb200::bn_parts(rows, C) * 2 * C}, x.options().dtype(at::kFloat));
+  // partial sums: a per-device scratch that the kernels keep zero between calls (they add into it and clear what they read);
+  // batch-norm backward calls of one device are issued on one stream
+  static std::unordered_map<int, Tensor> scratch;
+  Tensor& part = scratch[x.get_device()];
+  if (!part.defined() || part.numel() < adb200::bn_bwd_part_floats(C))
+    part = at::zeros({(int64_t)adb200::bn_bwd_part_floats(std::max(C, 4096))}, x.options().dtype(at::kFloat));
   Tensor sums = at::empty({5, C}, x.options().dtype(at::kFloat));              // [dbeta, dgamma, A, B, K]
   adb200::bn_bwd(CBF(dy), CBF(x), CBF(y), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), BF(dx), OPT_BF(dres),
                  part.data_ptr<float>(), sums.data_ptr<float>(), sums.data_ptr<float>() + 2 * C, rows, C, relu ? 1 : 0, OPT_F(dgamma_acc),

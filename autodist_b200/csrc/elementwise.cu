@@ -1081,7 +1081,10 @@ __global__ void bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restri
   }
 }
 
-// Backward statistics: part[y][0][c] = sum dy', part[y][1][c] = sum dy' * xhat, dy' = dy masked by the ReLU (y > 0).
+// Backward statistics: part[y % kBnSlots][0][c] += sum dy', part[..][1][c] += sum dy' * xhat, dy' = dy masked by the ReLU
+// (y > 0). `part` ([kBnSlots, 2, C]) must be zero on entry; bn_bwd_finalize_kernel hands it back cleared.
+constexpr int kBnSlots = 16;
+
 __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
                                     const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ part,
                                     int rows, int C, int rows_per_block, int relu) {
@@ -1124,8 +1127,9 @@ __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __r
   if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < C) {
     float t1 = 0.f, t2 = 0.f;
     for (int i = 0; i < 32; ++i) { t1 += s1[i][threadIdx.x]; t2 += s2[i][threadIdx.x]; }
-    part[((long long)blockIdx.y * 2 + 0) * C + blockIdx.x * 64 + threadIdx.x] = t1;
-    part[((long long)blockIdx.y * 2 + 1) * C + blockIdx.x * 64 + threadIdx.x] = t2;
+    // row chunks share kBnSlots rows of partials (reductions); the finalize kernel reads those and clears them
+    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 0) * C + blockIdx.x * 64 + threadIdx.x], t1);
+    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 1) * C + blockIdx.x * 64 + threadIdx.x], t2);
   }
 }
 
@@ -1133,7 +1137,7 @@ __global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __r
 // Sums the row-chunk partials (part: [parts, 2, C]) first - 32 channels per block, eight warps splitting the chunks;
 // sums = [dbeta (C), dgamma (C)] is written, and added into dbeta_acc / dgamma_acc (the parameters' gradient buffers)
 // when those are given.
-__global__ void bn_bwd_finalize_kernel(const float* __restrict__ part, int parts, float* __restrict__ sums, const float* __restrict__ gamma,
+__global__ void bn_bwd_finalize_kernel(float* __restrict__ part, int parts, float* __restrict__ sums, const float* __restrict__ gamma,
                                        const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ coef, float inv_rows,
                                        int C, float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc) {
   __shared__ float sm0[8][33], sm1[8][33];
@@ -1143,6 +1147,8 @@ __global__ void bn_bwd_finalize_kernel(const float* __restrict__ part, int parts
     for (int r = w; r < parts; r += 8) {
       a0 += part[((long long)r * 2 + 0) * C + c];
       a1 += part[((long long)r * 2 + 1) * C + c];
+      part[((long long)r * 2 + 0) * C + c] = 0.f;
+      part[((long long)r * 2 + 1) * C + c] = 0.f;
     }
   sm0[w][threadIdx.x & 31] = a0;
   sm1[w][threadIdx.x & 31] = a1;
@@ -1580,6 +1586,7 @@ void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStr
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
 }
 // Row chunks per channel block: enough blocks to fill the SMs (~8 per SM) while each chunk keeps >= 128 rows.
+int bn_bwd_part_floats(int C) { return kBnSlots * 2 * C; }
 int bn_parts(int rows, int C) {
   const int cb = (C + 63) / 64;
   int parts = (1184 + cb - 1) / cb;
@@ -1611,7 +1618,7 @@ void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, con
             float* part, float* sums, float* coef, int rows, int C, int relu, float* dgamma_acc, float* dbeta_acc, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
   bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
-  bn_bwd_finalize_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, parts, sums, gamma, mean, rstd, coef, 1.0f / rows, C, dgamma_acc, dbeta_acc);
+  bn_bwd_finalize_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, parts < kBnSlots ? parts : kBnSlots, sums, gamma, mean, rstd, coef, 1.0f / rows, C, dgamma_acc, dbeta_acc);
   const long long total8 = (long long)rows * (C / 8);
   bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
 }

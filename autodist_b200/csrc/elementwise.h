@@ -50,6 +50,7 @@ void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, cons
 void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st);
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st);
 int bn_parts(int rows, int C);
+int bn_bwd_part_floats(int C);
 void bn_fwd(const bf16_t* x, const float* gamma, const float* beta, const bf16_t* res, bf16_t* y, float* mean, float* rstd, float* part,
             float* sums, float* coef, int rows, int C, float eps, int relu, int sums_given, float* run_mean, float* run_var,
             long long* batches, float momentum, cudaStream_t st);
