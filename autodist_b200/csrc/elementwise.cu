@@ -1232,8 +1232,12 @@ __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
   *reinterpret_cast<uint2*>(code + idx * 8) = make_uint2(lo, hi4);
 }
 
+// KT / ST: window and stride as compile-time constants for the common poolings (3x3 stride 2, 2x2 stride 2), so that the
+// divisions and the tap loop cost nothing; 0 = take them from the arguments.
+template <int KT, int ST>
 __global__ void maxpool_bwd_kernel(const uint8_t* __restrict__ code, const bf16* __restrict__ dy, bf16* __restrict__ dx, int N, int H,
-                                   int W, int C, int k, int stride, int pad, int Ho, int Wo) {
+                                   int W, int C, int k_arg, int stride_arg, int pad, int Ho, int Wo) {
+  const int k = KT > 0 ? KT : k_arg, stride = ST > 0 ? ST : stride_arg;
   const int c8 = C / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)N * H * W * c8) return;
@@ -1241,11 +1245,13 @@ __global__ void maxpool_bwd_kernel(const uint8_t* __restrict__ code, const bf16*
   long long r = idx / c8;
   const int wi = (int)(r % W), hi = (int)((r / W) % H), n = (int)(r / ((long long)W * H));
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
   for (int kh = 0; kh < k; ++kh) {
     const int hn = hi + pad - kh;
     if (hn < 0 || hn % stride) continue;
     const int ho = hn / stride;
     if (ho >= Ho) continue;
+#pragma unroll
     for (int kw = 0; kw < k; ++kw) {
       const int wn = wi + pad - kw;
       if (wn < 0 || wn % stride) continue;
@@ -1634,7 +1640,10 @@ void maxpool_fwd(const bf16* x, bf16* y, uint8_t* code, int N, int H, int W, int
 }
 void maxpool_bwd(const uint8_t* code, const bf16* dy, bf16* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st) {
-  maxpool_bwd_kernel<<<blocks_for((long long)N * H * W * (C / 8), 256), 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  const int blocks = blocks_for((long long)N * H * W * (C / 8), 256);
+  if (k == 3 && stride == 2) maxpool_bwd_kernel<3, 2><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  else if (k == 2 && stride == 2) maxpool_bwd_kernel<2, 2><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  else maxpool_bwd_kernel<0, 0><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
 }
 void im2col(const bf16* x, bf16* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
   const long long total = (long long)N * Ho * Wo * KH * KW * (C / 8);
