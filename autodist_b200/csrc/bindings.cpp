@@ -427,7 +427,7 @@ void bn_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, const opti
 Tensor bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd, const Tensor& gamma, Tensor dx,
               const optional<Tensor>& dres, bool relu, const optional<Tensor>& dgamma_acc, const optional<Tensor>& dbeta_acc) {
   const int C = x.size(-1), rows = x.numel() / C;
-  TORCH_CHECK(C % 8 == 0 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
+  TORCH_CHECK(C % 8 == 0 && C <= 16384 && x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dy.numel() == x.numel() && dx.numel() == x.numel(),
               "dy, x, dx must be contiguous bf16 [.., C] of one shape, C % 8 == 0");
   if (dres.has_value()) TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel() && dres->scalar_type() == at::kBFloat16, "dres must match x");
   // partial sums: a per-device scratch that the kernels keep zero between calls (they add into it and clear what they read);

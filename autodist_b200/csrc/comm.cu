@@ -83,7 +83,8 @@ __device__ bool sym_barrier(const SymCtx& c) {
 // Grid-wide barrier among the blocks of this launch on this GPU (arrival count + generation word in device memory).
 // The cross-GPU barrier above pairs block b with the peers' block b only; where a phase reads data that *any* block
 // of a rank produced (the packed wire buffer, the reduced result), the blocks of that rank meet here first.
-// All blocks of a communication launch are resident at once (at most kMaxCommBlocks of 512 threads); the wait is bounded.
+// The launcher cuts the grid to the number of blocks the GPU holds at once (occupancy calculator), so all of them are
+// resident; the wait is bounded.
 __device__ bool grid_barrier(const SymCtx& c) {
   __shared__ int s_ok;
   __syncthreads();
@@ -505,14 +506,32 @@ int comm_grid(long long n_vec, int max_blocks) {
   return (int)(b > max_blocks ? max_blocks : b);
 }
 
+// The grid barrier inside allreduce_kernel needs every block of the launch on an SM at the same time. The launch is an
+// ordinary one, so the grid is cut to what the occupancy calculator says one GPU holds at once (SMs x blocks per SM for
+// this kernel's registers and 512 threads); every rank runs the same kernel on the same part and gets the same number.
+// Blocks of other streams' kernels only delay the arrival of a block: they never wait on this launch, and the wait is
+// bounded by the context's timeout.
+template <typename T>
+static int resident_blocks(int blocks) {
+  static int limit = 0;
+  if (limit == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel<T>, 512, 0);
+    limit = sms * per_sm > 0 ? sms * per_sm : 1;
+  }
+  return blocks < limit ? blocks : limit;
+}
+
 void launch_allreduce(const SymCtx& c, void* const* bufs, void* mc, int wire, long long n, const float* src32, float* residual,
                       float* dst32, float scale, int blocks, cudaStream_t st) {
   if (wire == WIRE_F32)
-    allreduce_kernel<float><<<blocks, 512, 0, st>>>(c, reinterpret_cast<float* const*>(bufs), reinterpret_cast<float*>(mc), n, src32, residual, dst32, scale);
+    allreduce_kernel<float><<<resident_blocks<float>(blocks), 512, 0, st>>>(c, reinterpret_cast<float* const*>(bufs), reinterpret_cast<float*>(mc), n, src32, residual, dst32, scale);
   else if (wire == WIRE_BF16)
-    allreduce_kernel<__nv_bfloat16><<<blocks, 512, 0, st>>>(c, reinterpret_cast<__nv_bfloat16* const*>(bufs), reinterpret_cast<__nv_bfloat16*>(mc), n, src32, residual, dst32, scale);
+    allreduce_kernel<__nv_bfloat16><<<resident_blocks<__nv_bfloat16>(blocks), 512, 0, st>>>(c, reinterpret_cast<__nv_bfloat16* const*>(bufs), reinterpret_cast<__nv_bfloat16*>(mc), n, src32, residual, dst32, scale);
   else
-    allreduce_kernel<__half><<<blocks, 512, 0, st>>>(c, reinterpret_cast<__half* const*>(bufs), reinterpret_cast<__half*>(mc), n, src32, residual, dst32, scale);
+    allreduce_kernel<__half><<<resident_blocks<__half>(blocks), 512, 0, st>>>(c, reinterpret_cast<__half* const*>(bufs), reinterpret_cast<__half*>(mc), n, src32, residual, dst32, scale);
 }
 
 void launch_reduce_scatter_update(const SymCtx& c, float* const* grads, __nv_bfloat16* const* p16, float* const* p32, float* mc_grad,

@@ -234,9 +234,14 @@ void conv_fprop(const Tensor& x, const Tensor& w, Tensor y, const optional<Tenso
 }
 
 // dx = the input gradient of conv(x, w) given dy. Every element of dx is written.
-void conv_dgrad(const Tensor& dy, const Tensor& w, Tensor dx, int64_t stride, int64_t pad, Tensor error_flag) {
+void conv_dgrad(const Tensor& dy, const Tensor& w, Tensor dx, int64_t stride, int64_t pad, Tensor error_flag,
+                const c10::optional<Tensor>& addend) {
   const c10::cuda::CUDAGuard guard(dy.device());
   check_act(dy, "dy"); check_act(dx, "dx");
+  if (addend.has_value()) {
+    check_act(*addend, "addend");
+    TORCH_CHECK(addend->sizes() == dx.sizes() && addend->data_ptr() != dx.data_ptr(), "addend must have dx's shape and its own storage");
+  }
   const Geometry g = geometry(dx, w, dy, stride, pad);
   const int bn = pick_bn(g.Cin);
   adb200::ConvMaps maps{};
@@ -264,7 +269,9 @@ void conv_dgrad(const Tensor& dy, const Tensor& w, Tensor dx, int64_t stride, in
   bool uncovered = false;
   for (int ph = 0; ph < classes; ++ph)
     for (int pw = 0; pw < classes; ++pw) uncovered |= class_taps(ph, pw, nullptr) == 0;
-  if (uncovered) dx.zero_();
+  if (uncovered) {
+    if (addend.has_value()) dx.copy_(*addend); else dx.zero_();
+  }
   for (int ph = 0; ph < classes; ++ph)
     for (int pw = 0; pw < classes; ++pw) {
       adb200::ConvParams p{};
@@ -289,6 +296,7 @@ void conv_dgrad(const Tensor& dy, const Tensor& w, Tensor dx, int64_t stride, in
       for (int i = 1; i < 4; ++i) maps.act[i] = maps.act[0];
       p.Nc = g.Cin; p.Kc = g.Cout; p.Mc = 0; p.ksplit = 1;
       p.out = dx.data_ptr(); p.ldc = g.Cin;
+      p.addend = addend.has_value() ? reinterpret_cast<const __nv_bfloat16*>(addend->data_ptr()) : nullptr;
       p.os = classes; p.oh0 = ph; p.ow0 = pw;
       p.error_flag = error_flag.data_ptr<int>();
       launch(maps, p, bn);
@@ -460,7 +468,9 @@ void conv_rowtap_wgrad(const Tensor& dy, const Tensor& xp, Tensor dwr, int64_t s
 void register_conv(pybind11::module& m) {
   m.def("conv_set_trace", &conv_set_trace);
   m.def("conv_fprop", &conv_fprop);
-  m.def("conv_dgrad", &conv_dgrad);
+  namespace py = pybind11;
+  m.def("conv_dgrad", &conv_dgrad, py::arg("dy"), py::arg("w"), py::arg("dx"), py::arg("stride"), py::arg("pad"), py::arg("error_flag"),
+        py::arg("addend") = py::none());
   m.def("conv_wgrad", &conv_wgrad);
   m.def("conv_rowtap_fprop", &conv_rowtap_fprop);
   m.def("conv_rowtap_wgrad", &conv_rowtap_wgrad);

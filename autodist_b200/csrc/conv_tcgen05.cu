@@ -284,6 +284,46 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
         off = (long long)row * p.ldc + (long long)p.taps[tc_.tap].wtap * p.wtap_stride;
       }
       const long long tw0 = trace != nullptr ? clock64() : 0;
+      if (MODE == CONV_DGRAD) {
+        if (p.addend != nullptr) {
+          // The gradient another consumer of the same tensor produced (a residual fork) is added to this tile. Its whole
+          // row segment is requested before the wait for the accumulator, so the loads overlap the tile's MMAs, and
+          // the chunk loop below is unrolled so that the prefetched vectors stay in registers.
+          uint4 pre[BN / 8];
+          const __nv_bfloat16* src = p.addend + off + tc_.c0;
+#pragma unroll
+          for (int h = 0; h < BN / 8; ++h) {
+            pre[h] = make_uint4(0, 0, 0, 0);
+            if (valid && tc_.c0 + h * 8 < p.Nc) pre[h] = *reinterpret_cast<const uint4*>(src + h * 8);
+          }
+          if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+#pragma unroll
+          for (int c = 0; c < BN / 16; ++c) {
+            const int col0 = tc_.c0 + c * 16;
+            if (col0 < p.Nc) {                     // uniform over the CTA
+              float v[16], a[16];
+              __syncwarp();
+              tmem_ld16(t_row + c * 16, v);
+              unpack8_bf16(pre[2 * c], a);
+              unpack8_bf16(pre[2 * c + 1], a + 8);
+#pragma unroll
+              for (int jj = 0; jj < 16; ++jj) v[jj] += a[jj];
+              if (valid) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off + col0;
+                store8_bf16(dst, v);                                  // Nc is a multiple of 8: a chunk holds 8 or 16 columns
+                if (col0 + 8 < p.Nc) store8_bf16(dst + 8, v + 8);
+              }
+            }
+          }
+          __syncwarp();
+          tc_fence_before();
+          mbar_arrive(&tempty[as]);
+          if (++as == 2) { as = 0; aphase ^= 1; }
+          continue;
+        }
+      }
       if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
       const long long tw1 = trace != nullptr ? clock64() : 0;
       tc_fence_after();

@@ -47,6 +47,7 @@ struct ConvParams {
   const float* bias;              // forward: per output channel, or null
   int relu;                       // forward: clamp at zero after the bias
   float* stats;                   // forward: [2, Nc] fp32, per-channel sum and sum of squares are added here, or null
+  const __nv_bfloat16* addend;    // pixel modes: tensor of the output's shape added to the result before it is stored, or null
   int* error_flag;
   long long* trace;               // optional tuning aid: [grid, 8] clock64 marks per CTA (see conv_kernel), or null
   ConvTap taps[kMaxConvTaps];

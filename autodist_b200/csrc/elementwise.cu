@@ -58,6 +58,11 @@ __device__ __forceinline__ void load8(const bf16* p, float* v) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
+__device__ __forceinline__ void unpack8(const uint4& u, float* v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
 __device__ __forceinline__ void store8(bf16* p, const float* v) {
   uint4 u;
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
@@ -1043,11 +1048,19 @@ __global__ void relu_bwd_colsum_kernel(const bf16* __restrict__ dy, const bf16* 
 // first builds the table for all C channels in shared memory (C rsqrt per block instead of one per element), block 0 also
 // records mean / rstd and folds the batch statistics into the running ones - one launch for the whole normalisation.
 // Dynamic shared memory: 2 * C floats.
-__global__ void bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, bf16* __restrict__ y, long long total8, int C,
+__global__ void __launch_bounds__(256, 6) bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, bf16* __restrict__ y, long long total8, int C,
                                 int relu, const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
                                 float inv_rows, float eps, float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ run_mean,
                                 float* __restrict__ run_var, long long* __restrict__ batches, float momentum, float unbias) {
   extern __shared__ float s_coef[];                 // [scale (C), shift (C)]
+  // the first elements are requested before the table is built, so that the table's latency hides under them
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  uint4 xq = make_uint4(0, 0, 0, 0), rq = make_uint4(0, 0, 0, 0);
+  if (idx < total8) {
+    xq = *reinterpret_cast<const uint4*>(x + idx * 8);
+    if (res != nullptr) rq = *reinterpret_cast<const uint4*>(res + idx * 8);
+  }
   if (blockIdx.x == 0 && threadIdx.x == 0 && batches != nullptr) *batches += 1;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     const float mu = sums[c] * inv_rows;
@@ -1066,107 +1079,120 @@ __global__ void bn_apply_kernel(const bf16* __restrict__ x, const bf16* __restri
     }
   }
   __syncthreads();
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += stride) {
+  while (idx < total8) {
+    const long long next = idx + stride;
+    uint4 xn = make_uint4(0, 0, 0, 0), rn = make_uint4(0, 0, 0, 0);
+    if (next < total8) {
+      xn = *reinterpret_cast<const uint4*>(x + next * 8);
+      if (res != nullptr) rn = *reinterpret_cast<const uint4*>(res + next * 8);
+    }
     const int c = (int)(idx % (C / 8)) * 8;
-    float v[8], rv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    load8(x + idx * 8, v);
-    if (res != nullptr) load8(res + idx * 8, rv);
+    float v[8], rv[8];
+    unpack8(xq, v);
+    unpack8(rq, rv);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float o = fmaf(v[j], s_coef[c + j], s_coef[C + c + j]) + rv[j];
       v[j] = relu ? fmaxf(o, 0.f) : o;
     }
     store8(y + idx * 8, v);
+    idx = next; xq = xn; rq = rn;
   }
 }
 
-// Backward statistics: part[y % kBnSlots][0][c] += sum dy', part[..][1][c] += sum dy' * xhat, dy' = dy masked by the ReLU
-// (y > 0). `part` ([kBnSlots, 2, C]) must be zero on entry; bn_bwd_finalize_kernel hands it back cleared.
+// Backward statistics and coefficients in one launch. Each block adds its sums over a chunk of rows into one of kBnSlots
+// shared rows of partials: part[y % kBnSlots][0][c] += sum dy', part[..][1][c] += sum dy' * xhat, dy' = dy masked by the
+// ReLU (y > 0). The last block of a 64-channel group to finish (a ticket counter per group) adds the slots up, clears them
+// and its counter, and writes what the second pass needs:
+//   dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M) = A * dy' + B * x + K per channel; coef = [A (C), B (C), K (C)]
+// together with sums = [dbeta (C), dgamma (C)], which are also added into dbeta_acc / dgamma_acc (the parameters'
+// gradient buffers) when those are given. `counters` ([C / 64]) and `part` ([kBnSlots, 2, C]) must be zero on entry and
+// are zero again on exit.
 constexpr int kBnSlots = 16;
+constexpr int kBnCounterFloats = 256;          // ticket counters in front of the slots: one per 64 channels, C <= 16384
 
-__global__ void bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
-                                    const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ part,
-                                    int rows, int C, int rows_per_block, int relu) {
+__global__ void __launch_bounds__(256, 4) bn_bwd_stats_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
+                                    const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                    unsigned int* __restrict__ counters, float* __restrict__ part, float* __restrict__ sums,
+                                    float* __restrict__ coef, float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc,
+                                    int rows, int C, int rows_per_block, int relu, float inv_rows) {
   __shared__ float s1[32][65], s2[32][65];
+  __shared__ int s_last;
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const int c = blockIdx.x * 64 + vec * 8;
   const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  // a = sum dy', b = sum dy' * x; sum dy' * xhat = rstd * (b - mean * a) is formed once per block from the totals
   float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (c < C) {
-    float mu[8], rs[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { mu[i] = mean[c + i]; rs[i] = rstd[c + i]; }
     for (int r = r0 + rl; r < r1; r += 64) {
-      float d[2][8], xv[2][8], yv[2][8];
+      uint4 dq[2], xq[2], yq[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int rr = r + 32 * u;
+        dq[u] = xq[u] = make_uint4(0, 0, 0, 0);
+        yq[u] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);      // bf16 ones: keeps the gradient
         if (rr < r1) {
-          load8(dy + (long long)rr * C + c, d[u]);
-          load8(x + (long long)rr * C + c, xv[u]);
-          if (relu) load8(y + (long long)rr * C + c, yv[u]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { d[u][i] = 0.f; xv[u][i] = 0.f; yv[u][i] = 1.f; }
+          dq[u] = *reinterpret_cast<const uint4*>(dy + (long long)rr * C + c);
+          xq[u] = *reinterpret_cast<const uint4*>(x + (long long)rr * C + c);
+          if (relu) yq[u] = *reinterpret_cast<const uint4*>(y + (long long)rr * C + c);
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+      for (int u = 0; u < 2; ++u) {
+        float d[8], xv[8], yv[8];
+        unpack8(dq[u], d);
+        unpack8(xq[u], xv);
+        unpack8(yq[u], yv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float g = (relu && yv[u][i] <= 0.f) ? 0.f : d[u][i];
+          const float g = yv[i] <= 0.f ? 0.f : d[i];
           a[i] += g;
-          b[i] += g * (xv[u][i] - mu[i]) * rs[i];
+          b[i] = fmaf(g, xv[i], b[i]);
         }
+      }
     }
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) { s1[rl][vec * 8 + i] = a[i]; s2[rl][vec * 8 + i] = b[i]; }
   __syncthreads();
-  if (threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < C) {
+  const int cc = blockIdx.x * 64 + threadIdx.x;              // the channel thread < 64 owns from here on
+  if (threadIdx.x < 64 && cc < C) {
     float t1 = 0.f, t2 = 0.f;
     for (int i = 0; i < 32; ++i) { t1 += s1[i][threadIdx.x]; t2 += s2[i][threadIdx.x]; }
-    // row chunks share kBnSlots rows of partials (reductions); the finalize kernel reads those and clears them
-    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 0) * C + blockIdx.x * 64 + threadIdx.x], t1);
-    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 1) * C + blockIdx.x * 64 + threadIdx.x], t2);
+    t2 = rstd[cc] * (t2 - mean[cc] * t1);
+    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 0) * C + cc], t1);
+    atomicAdd(&part[((long long)(blockIdx.y % kBnSlots) * 2 + 1) * C + cc], t2);
+    __threadfence();                                         // the sums are visible before the ticket is taken
   }
-}
-
-// dx = gamma * rstd * (dy' - dbeta / M - xhat * dgamma / M) = A * dy' + B * x + K per channel; coef = [A (C), B (C), K (C)].
-// Sums the row-chunk partials (part: [parts, 2, C]) first - 32 channels per block, eight warps splitting the chunks;
-// sums = [dbeta (C), dgamma (C)] is written, and added into dbeta_acc / dgamma_acc (the parameters' gradient buffers)
-// when those are given.
-__global__ void bn_bwd_finalize_kernel(float* __restrict__ part, int parts, float* __restrict__ sums, const float* __restrict__ gamma,
-                                       const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ coef, float inv_rows,
-                                       int C, float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc) {
-  __shared__ float sm0[8][33], sm1[8][33];
-  const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
-  float a0 = 0.f, a1 = 0.f;
-  if (c < C)
-    for (int r = w; r < parts; r += 8) {
-      a0 += part[((long long)r * 2 + 0) * C + c];
-      a1 += part[((long long)r * 2 + 1) * C + c];
-      part[((long long)r * 2 + 0) * C + c] = 0.f;
-      part[((long long)r * 2 + 1) * C + c] = 0.f;
-    }
-  sm0[w][threadIdx.x & 31] = a0;
-  sm1[w][threadIdx.x & 31] = a1;
   __syncthreads();
-  if (w != 0 || c >= C) return;
-  float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { s0 += sm0[i][threadIdx.x]; s1 += sm1[i][threadIdx.x]; }
-  sums[c] = s0;
-  sums[C + c] = s1;
-  if (dbeta_acc != nullptr) dbeta_acc[c] += s0;
-  if (dgamma_acc != nullptr) dgamma_acc[c] += s1;
-  const float a = gamma[c] * rstd[c];
-  const float k0 = s0 * inv_rows, k1 = s1 * inv_rows;
-  const float bx = -a * rstd[c] * k1;
-  coef[c] = a;
-  coef[C + c] = bx;
-  coef[2 * C + c] = -bx * mean[c] - a * k0;
+  if (threadIdx.x == 0) s_last = atomicAdd(&counters[blockIdx.x], 1u) == gridDim.y - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 64 && cc < C) {
+    const int slots = gridDim.y < kBnSlots ? gridDim.y : kBnSlots;
+    float s0 = 0.f, sx = 0.f;
+    for (int r = 0; r < slots; ++r) {
+      float* p0 = &part[((long long)r * 2 + 0) * C + cc];
+      float* p1 = &part[((long long)r * 2 + 1) * C + cc];
+      s0 += __ldcg(p0);                                      // written by atomics in L2: read there, not through L1
+      sx += __ldcg(p1);
+      *p0 = 0.f;
+      *p1 = 0.f;
+    }
+    sums[cc] = s0;
+    sums[C + cc] = sx;
+    if (dbeta_acc != nullptr) dbeta_acc[cc] += s0;
+    if (dgamma_acc != nullptr) dgamma_acc[cc] += sx;
+    const float rsd = rstd[cc];
+    const float ga = gamma[cc] * rsd;
+    const float k0 = s0 * inv_rows, k1 = sx * inv_rows;
+    const float bx = -ga * rsd * k1;
+    coef[cc] = ga;
+    coef[C + cc] = bx;
+    coef[2 * C + cc] = -bx * mean[cc] - ga * k0;
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] = 0u;
 }
 
 __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
@@ -1592,10 +1618,10 @@ void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStr
   clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
 }
 // Row chunks per channel block: enough blocks to fill the SMs (~8 per SM) while each chunk keeps >= 128 rows.
-int bn_bwd_part_floats(int C) { return kBnSlots * 2 * C; }
+int bn_bwd_part_floats(int C) { return kBnCounterFloats + kBnSlots * 2 * C; }
 int bn_parts(int rows, int C) {
   const int cb = (C + 63) / 64;
-  int parts = (1184 + cb - 1) / cb;
+  int parts = (592 + cb - 1) / cb;
   if (parts > rows / 128) parts = rows / 128;
   if (parts > 512) parts = 512;
   return parts < 1 ? 1 : parts;
@@ -1615,7 +1641,7 @@ void bn_fwd(const bf16* x, const float* gamma, const float* beta, const bf16* re
   }
   // a few elements per thread: the per-block table of 2 * C coefficients is amortised over at least 4 x 2048 elements
   long long blocks = (total8 + 256 * 4 - 1) / (256 * 4);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > 148 * 6) blocks = 148 * 6;          // one resident wave (6 blocks of 256 threads per SM)
   bn_apply_kernel<<<(int)(blocks < 1 ? 1 : blocks), 256, 2 * C * sizeof(float), st>>>(x, res, y, total8, C, relu, sums, gamma, beta, 1.0f / rows,
                                                                                       eps, mean, rstd, run_mean, run_var, batches, momentum, unbias);
   (void)coef;
@@ -1623,8 +1649,9 @@ void bn_fwd(const bf16* x, const float* gamma, const float* beta, const bf16* re
 void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx, bf16* dres,
             float* part, float* sums, float* coef, int rows, int C, int relu, float* dgamma_acc, float* dbeta_acc, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
-  bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, part, rows, C, rpb, relu);
-  bn_bwd_finalize_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, parts < kBnSlots ? parts : kBnSlots, sums, gamma, mean, rstd, coef, 1.0f / rows, C, dgamma_acc, dbeta_acc);
+  bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, gamma, reinterpret_cast<unsigned int*>(part),
+                                                                      part + kBnCounterFloats, sums, coef, dgamma_acc, dbeta_acc, rows, C, rpb,
+                                                                      relu, 1.0f / rows);
   const long long total8 = (long long)rows * (C / 8);
   bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
 }

@@ -134,6 +134,11 @@ __device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) 
   }
   *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
 }
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float* v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+}
 __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* src, float* v) {
   const uint4 u = *reinterpret_cast<const uint4*>(src);
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);

@@ -16,7 +16,7 @@ import torch
 from torch import nn
 import torch.nn.functional as F
 
-from autodist_b200.ops.functional import Linear, batch_norm, conv2d, max_pool2d
+from autodist_b200.ops.functional import Linear, batch_norm, conv2d, fork, max_pool2d
 
 CONV_MODE = os.environ.get("AUTODIST_CONV", "own")                      # own | library
 
@@ -36,9 +36,9 @@ class Conv2d(nn.Module):
             if bias:
                 self.bias.uniform_(-bound, bound)
 
-    def forward(self, x, stats=None):
+    def forward(self, x, stats=None, fork=None):
         if x.is_cuda and CONV_MODE != "library":
-            return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.relu, stats)
+            return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.relu, stats, fork)
         y = F.conv2d(x, self.weight.permute(0, 3, 1, 2).to(x.dtype), None if self.bias is None else self.bias.to(x.dtype), self.stride,
                      self.padding)
         return F.relu(y) if self.relu else y
@@ -61,10 +61,10 @@ class BatchNormAct(nn.BatchNorm2d):
         super().__init__(channels)
         self.relu = relu
 
-    def forward(self, x, residual=None, sums=None):
+    def forward(self, x, residual=None, sums=None, fork=None):
         if _own_norm_pool(x) and self.training and self.momentum is not None:
             return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, True, self.momentum, self.eps, self.relu,
-                              residual, sums, self.num_batches_tracked)
+                              residual, sums, self.num_batches_tracked, fork)
         y = super().forward(x)
         if residual is not None:
             y = y + residual
@@ -105,17 +105,19 @@ class ConvBN(nn.Module):
         self.conv = _conv(cin, cout, k, stride, padding)
         self.bn = BatchNormAct(cout, relu=relu)
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, in_fork=None, res_fork=None):
+        """``in_fork`` / ``res_fork``: the ``GradFork`` of ``x`` / of ``residual`` when that tensor has a second consumer."""
         cout = self.conv.out_channels
         fused = x.is_cuda and x.dim() == 4 and CONV_MODE != "library" and NORM_POOL_MODE != "library" and FUSE_BN_STATS and self.training \
             and self.bn.momentum is not None and cout % 8 == 0 and cout <= 2048 and (x.dtype == torch.bfloat16 or torch.is_autocast_enabled())
         if fused:
             sums = _ARENA.take(cout, x.device)
-            return self.bn(self.conv(x, sums), residual, sums)
-        return self.bn(self.conv(x), residual)
+            return self.bn(self.conv(x, sums, in_fork), residual, sums, res_fork)
+        return self.bn(self.conv(x, None, in_fork), residual, None, res_fork)
 
 
 FUSE_BN_STATS = os.environ.get("AUTODIST_FUSE_BN_STATS", "1") == "1"
+FORK_FUSION = os.environ.get("AUTODIST_FORK_FUSION", "1") == "1"
 
 
 class MaxPool(nn.MaxPool2d):
@@ -152,8 +154,13 @@ class Bottleneck(nn.Module):
             self.down = _conv_bn(cin, cout, 1, stride, relu=False)
 
     def forward(self, x):
-        idn = x if self.down is None else self.down(x)
-        return self.c(self.b(self.a(x)), residual=idn)
+        # the block's input feeds the first convolution and the skip path: whichever gradient comes second is added inside
+        # the kernel that produces it (the skip convolution is evaluated after the main path so that its backward runs first)
+        xa, xr, box = fork(x) if FORK_FUSION else (x, x, None)
+        if self.down is None:
+            return self.c(self.b(self.a(xa, in_fork=box)), residual=xr, res_fork=box)
+        h = self.b(self.a(xa, in_fork=box))
+        return self.c(h, residual=self.down(xr, in_fork=box))
 
 
 class ResNet(nn.Module):

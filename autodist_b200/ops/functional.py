@@ -213,14 +213,59 @@ def _rowtap_geometry(h, w, kh, kw, stride, padding):
     return oh, ow, hp, wp + (wp & 1)
 
 
+class GradFork:
+    """Meeting point of the two consumers of a forked tensor (the input of a residual block feeds the block's first
+    convolution and its skip connection). Whichever consumer's backward runs first leaves its gradient here and returns
+    none; the second adds it inside its own kernel (the input-gradient convolution's epilogue) and returns the sum, so
+    the fork costs no elementwise pass of its own."""
+    __slots__ = ("grad",)
+
+    def __init__(self):
+        self.grad = None
+
+    def take(self):
+        g, self.grad = self.grad, None
+        return g
+
+
+class _ForkFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, box):
+        ctx.box = box
+        ctx.set_materialize_grads(False)
+        return x.view_as(x), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, ga, gb):
+        # a gradient left behind (its partner never ran, or could not fuse the add) still counts
+        parts = [g for g in (ga, gb, ctx.box.take()) if g is not None]
+        if not parts:
+            return None, None
+        out = parts[0]
+        for g in parts[1:]:
+            out = out + g
+        return out, None
+
+
+def fork(x):
+    """Two aliases of ``x`` for its two consumers plus the ``GradFork`` both pass to their kernels (``conv2d(fork=...)``,
+    ``batch_norm(fork=...)``); ``(x, x, None)`` where no gradient flows."""
+    if not (x.is_cuda and x.requires_grad and torch.is_grad_enabled()):
+        return x, x, None
+    box = GradFork()
+    a, b = _ForkFn.apply(x, box)
+    return a, b, box
+
+
 class _ConvFn(torch.autograd.Function):
     """2-D convolution as an implicit GEMM on tcgen05 (``csrc/conv_tcgen05.cu``): forward, input gradient and weight
     gradient read the channels-last bf16 activations in place through TMA boxes, one per filter tap; bias, ReLU and the
     per-channel sums a following batch-norm needs are fused into the forward epilogue. ``weight`` is ``[Cout, KH, KW, Cin]``."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, stride, padding, relu, stats):
+    def forward(ctx, x, weight, bias, stride, padding, relu, stats, fork=None):
         E = ops.ext(required=True)
+        ctx.fork = fork
         cout, kh, kw, cin = weight.shape
         err = _error_flag(x.device)
         b32 = bias.detach().float().contiguous() if bias is not None else None
@@ -288,17 +333,20 @@ class _ConvFn(torch.autograd.Function):
                 E.conv_wgrad(dyh, xh, dw, stride, padding, err, False)
             if ctx.needs_input_grad[0]:
                 dxh = torch.empty_like(xh)
-                E.conv_dgrad(dyh, w16, dxh, stride, padding, err)
+                other = ctx.fork.take() if ctx.fork is not None else None
+                E.conv_dgrad(dyh, w16, dxh, stride, padding, err, None if other is None else _nhwc(other))
                 dx = dxh.permute(0, 3, 1, 2).to(ctx.dtypes[0])
+                if ctx.fork is not None and other is None:
+                    ctx.fork.grad, dx = dx, None            # first of the two consumers: the other one adds this in its kernel
         if dw is None:
             _grad_written(ctx.weight)
         if acc_b is not None:
             _grad_written(bias)
             db = None
-        return dx, None if dw is None else dw.to(ctx.dtypes[1]), db, None, None, None, None
+        return dx, None if dw is None else dw.to(ctx.dtypes[1]), db, None, None, None, None, None
 
 
-def conv2d(x, weight, bias=None, stride=1, padding=0, relu=False, stats=None):
+def conv2d(x, weight, bias=None, stride=1, padding=0, relu=False, stats=None, fork=None):
     """Convolution of a logical ``[N, C, H, W]`` tensor with a ``[Cout, KH, KW, Cin]`` weight (+ bias, + ReLU).
 
     On a GPU it runs on the implicit-GEMM kernels when the channel counts allow it: ``Cin`` and ``Cout`` multiples of 8,
@@ -308,7 +356,7 @@ def conv2d(x, weight, bias=None, stride=1, padding=0, relu=False, stats=None):
     cout, kh, kw, cin = weight.shape
     own = x.is_cuda and cout % 8 == 0 and stride in (1, 2) and kh * kw <= 49 and (cin % 8 == 0 or (cin <= 8 and kw <= 8))
     if own:
-        return _ConvFn.apply(x, weight, bias, int(stride), int(padding), bool(relu), stats)
+        return _ConvFn.apply(x, weight, bias, int(stride), int(padding), bool(relu), stats, fork)
     y = F.conv2d(x, weight.permute(0, 3, 1, 2).to(x.dtype), None if bias is None else bias.to(x.dtype), stride, padding)
     y = F.relu(y) if relu else y
     if stats is not None:
@@ -325,8 +373,9 @@ class _BatchNormFn(torch.autograd.Function):
     convolution's epilogue leaves them) skips the statistics pass."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, eps, relu, sums, running):
+    def forward(ctx, x, gamma, beta, residual, eps, relu, sums, running, fork=None):
         E = ops.ext(required=True)
+        ctx.fork = fork
         run_mean, run_var, batches, momentum = running if running is not None else (None, None, None, 0.0)
         xh = _nhwc(x)                                                            # [N, H, W, C]
         c = xh.shape[-1]
@@ -352,7 +401,7 @@ class _BatchNormFn(torch.autograd.Function):
         E = ops.ext(required=True)
         xh, y, mean, rstd, g32 = ctx.saved_tensors
         if dy is None:
-            return (None,) * 8
+            return (None,) * 9
         dyh = _nhwc(dy)
         dx = torch.empty_like(xh)
         dres = None
@@ -364,15 +413,21 @@ class _BatchNormFn(torch.autograd.Function):
         sums = E.bn_bwd(dyh, xh, y, mean, rstd, g32, dx, dres if ctx.relu else None, ctx.relu, acc_g if direct else None,
                         acc_b if direct else None)
         dr = dres.permute(0, 3, 1, 2).to(ctx.dtypes[2]) if dres is not None else None
+        if ctx.fork is not None and dr is not None:
+            other = ctx.fork.take()
+            if other is None:
+                ctx.fork.grad, dr = dr, None            # the residual's other consumer adds this in its input-gradient kernel
+            else:
+                dr = dr + other
         if direct:
             _grad_written(gamma)
             _grad_written(beta)
-            return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), None, None, dr, None, None, None, None
-        return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), dr, None, None, None, None
+            return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), None, None, dr, None, None, None, None, None
+        return dx.permute(0, 3, 1, 2).to(ctx.dtypes[0]), sums[1].to(ctx.dtypes[1]), sums[0].to(ctx.dtypes[1]), dr, None, None, None, None, None
 
 
 def batch_norm(x, gamma, beta, running_mean=None, running_var=None, training=True, momentum=0.1, eps=1e-5, relu=False,
-               residual=None, sums=None, num_batches_tracked=None):
+               residual=None, sums=None, num_batches_tracked=None, fork=None):
     """``relu?(batch_norm(x) + residual)`` of an NCHW / channels-last tensor; updates the running statistics like
     ``F.batch_norm``. ``sums``: per-channel sum / sum of squares of ``x`` when a preceding kernel already produced them."""
     if not (x.is_cuda and training and x.shape[1] % 8 == 0):
@@ -384,7 +439,7 @@ def batch_norm(x, gamma, beta, running_mean=None, running_var=None, training=Tru
     running = None
     if running_mean is not None and running_mean.dtype == torch.float32 and running_var.dtype == torch.float32:
         running = (running_mean, running_var, num_batches_tracked, float(momentum))     # folded into the statistics kernel
-    y, mean, rstd = _BatchNormFn.apply(x, gamma, beta, residual, eps, relu, sums, running)
+    y, mean, rstd = _BatchNormFn.apply(x, gamma, beta, residual, eps, relu, sums, running, fork)
     if running is None and running_mean is not None:
         with torch.no_grad():
             n = x.numel() // x.shape[1]

@@ -453,6 +453,10 @@ class FusedStepEngine(StepEngine):
         self._warm_steps = 0
         self.launches_per_step = 0
         self.graph_kernels = 0
+        # AUTODIST_FLIGHT_TIMING=1: CUDA events around every flight of a step (read them with `flight_report`).
+        # Timed events cannot be recorded into a CUDA graph, so the step runs as eager launches while this is on.
+        self._flight_log = [] if os.environ.get("AUTODIST_FLIGHT_TIMING", "0") == "1" else None
+        self._step_start = None
         module.grad_ready = self._on_grad_ready
         if self.world_size > 1:
             torch.cuda.synchronize()
@@ -793,6 +797,18 @@ class FusedStepEngine(StepEngine):
         self._ready_event.record(compute)
         self.comm_stream.wait_event(self._ready_event)
         keys = [f"g{gk}/i{ik}" for a, z, gk, ik in getattr(self, "_range_key", ()) if a < hi and z > lo]
+        if self._flight_log is not None:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(self.comm_stream)
+            try:
+                self._launch_flight(lo, hi, keys)
+            finally:
+                t1.record(self.comm_stream)
+                self._flight_log.append((lo, hi, t0, t1))
+            return
+        self._launch_flight(lo, hi, keys)
+
+    def _launch_flight(self, lo, hi, keys):
         with nvtx.annotate(f"flight [{lo}, {hi}) {' '.join(keys[:4])}"), torch.cuda.stream(self.comm_stream):
             if getattr(self, "_relaxed", None):
                 self._relaxed_push(lo, hi)               # this worker's gradient goes to the owners now; no collective, no local update
@@ -845,6 +861,10 @@ class FusedStepEngine(StepEngine):
         self.launches_per_step = 0
         self._rows_sync_pending, self._rows_dirty = True, False
         self._psgd_flights = []
+        if self._flight_log is not None:
+            self._flight_log.clear()
+            self._step_start = torch.cuda.Event(enable_timing=True)
+            self._step_start.record()
         values = self.forward(all_nodes, feeds, grad=True)
         self._finish_rows()
         self._finish_powersgd()
@@ -854,9 +874,18 @@ class FusedStepEngine(StepEngine):
         torch.cuda.current_stream().wait_event(self._done_event)
         return values
 
+    def flight_report(self):
+        """Flights of the last step, in launch order: ``(lo, hi, start_ms, ms)`` with the start measured from the first
+        kernel of the step and ``ms`` the time the flight's kernels (collective + optimizer) held the communication
+        stream. Needs ``AUTODIST_FLIGHT_TIMING=1``; synchronises the device."""
+        if not self._flight_log or self._step_start is None:
+            return []
+        torch.cuda.synchronize(self.device)
+        return [(lo, hi, self._step_start.elapsed_time(t0), t0.elapsed_time(t1)) for lo, hi, t0, t1 in self._flight_log]
+
     def train_step(self, train_op, nodes, feeds):
         self._sync_lr()
-        if not self._use_graph:
+        if not self._use_graph or self._flight_log is not None:
             values = self._run_model(train_op, nodes, feeds)
         else:
             values = self._graphed_step(train_op, nodes, feeds)
@@ -1236,6 +1265,10 @@ class FlatAutogradEngine(FusedStepEngine):
         self.launches_per_step = 0
         self._rows_sync_pending, self._rows_dirty = True, False
         self._psgd_flights = []
+        if self._flight_log is not None:
+            self._flight_log.clear()
+            self._step_start = torch.cuda.Event(enable_timing=True)
+            self._step_start.record()
         fl = self.flat
         fl.grad.zero_()
         for f in self._flights:

@@ -225,6 +225,8 @@ def run_ours(model_name, args, n_gpus, world, rank):
         if hasattr(sess.engine, "check_errors"):
             sess.engine.check_errors()
         engine_name = type(sess.engine).__name__
+        if getattr(args, "flights", None) and hasattr(sess.engine, "flight_report"):
+            _write_flights(args.flights, sess.engine, model_name, strategy, n_gpus, ms / args.steps, rank, world, dev)
         graph_launches = getattr(sess.engine, "graph_kernels", 0)
         eager = (counted["after"] or 0) - (counted["before"] or 0)
         launches = eager if eager > 0 else graph_launches * args.steps
@@ -267,6 +269,36 @@ def run_ours(model_name, args, n_gpus, world, rank):
         "gpu_launches": int(launches),
         "impl": "ours",
     }
+
+
+def _write_flights(path, engine, model_name, strategy, n_gpus, ms_step, rank, world, dev):
+    """Table of the last step's flights: range, bytes, start since the step's first kernel, duration (max over ranks)."""
+    import torch
+    rows = engine.flight_report()
+    t = torch.tensor([[r[2], r[3]] for r in rows] or [[0.0, 0.0]], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return
+    t = t.cpu().tolist()
+    lines = [f"# Gradient flights of one {model_name} step, {n_gpus} GPU(s), strategy {strategy}", "",
+             f"Eager launches (timed events cannot be captured), {ms_step:.2f} ms per step in this mode. `start` is measured from the",
+             "first kernel of the step; `ms` is how long the flight's kernels (collective + optimizer update) held the",
+             "communication stream, max over ranks; `GB/s` is the bus bandwidth 2(N-1)/N x bytes / ms of an all-reduce of that",
+             "size (the optimizer update is inside the same interval, so this is a lower bound).", "",
+             "| flight | elements | MB (fp32) | start ms | ms | bus GB/s |", "|---|---|---|---|---|---|"]
+    total = 0.0
+    for i, (r, (start, ms)) in enumerate(zip(rows, t)):
+        n = r[1] - r[0]
+        bus = 2 * (n_gpus - 1) / n_gpus * n * 4 / (ms * 1e-3) / 1e9 if ms > 0 and n_gpus > 1 else 0.0
+        total += ms
+        lines.append(f"| {i} | {n} | {n * 4 / 2**20:.1f} | {start:.2f} | {ms:.3f} | {bus:.0f} |")
+    last_end = max((s + m for s, m in t), default=0.0)
+    lines += ["", f"Communication stream busy {total:.2f} ms of the {ms_step:.2f} ms step; the last flight ends {last_end:.2f} ms after the step's first kernel."]
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
 
 
 def _timed_with_count(step_dev, step_host, args, world, dev, rank, ops, counted):
@@ -369,6 +401,9 @@ def main():
     ap.add_argument("--comm", default=None, help="fused (own kernels) or nccl (baseline)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--only", action="store_true", help="measure --model alone: no ResNet-101 block, no library block")
+    ap.add_argument("--flights", default=None, metavar="PATH",
+                    help="also time every gradient flight of the last step with CUDA events (the step then runs as eager launches, "
+                         "not as a CUDA graph) and write the table to PATH; implies --only")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -376,6 +411,9 @@ def main():
         os.environ["AUTODIST_COMM"] = args.comm
     if args.no_graph:
         os.environ["AUTODIST_CUDA_GRAPH"] = "0"
+    if args.flights:
+        os.environ["AUTODIST_FLIGHT_TIMING"] = "1"
+        args.only = True
     os.environ.setdefault("AUTODIST_MIN_LOG_LEVEL", "WARNING")
     os.environ.setdefault("AUTODIST_FETCH_MODE", "local")
     args.warmup = max(args.warmup, 3)

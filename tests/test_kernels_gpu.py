@@ -501,6 +501,46 @@ def test_batch_norm_kernels_match_the_library(relu):
     _check(rv, rv2, 1e-2)
 
 
+@pytest.mark.parametrize("cin,width,stride", [(64, 16, 1), (32, 16, 2), (32, 16, 1)])
+def test_residual_fork_gradient_is_added_inside_the_input_gradient_kernel(cin, width, stride, monkeypatch):
+    """A bottleneck block with the fork fusion (the skip path's gradient added in the first convolution's dgrad epilogue)
+    against the same block with autograd's own accumulation, and against the fp32 library computation."""
+    from autodist_b200.models import cnn
+    torch.manual_seed(23)
+    block = cnn.Bottleneck(cin, width, stride).cuda().train()
+    x0 = torch.randn(4, cin, 14, 14, device="cuda").to(torch.bfloat16).to(memory_format=torch.channels_last)
+    grads = {}
+    for mode in (True, False):
+        monkeypatch.setattr(cnn, "FORK_FUSION", mode)
+        x = x0.clone().requires_grad_(True)
+        xin = x * 1.0                                         # a non-leaf input, as inside a network
+        y = block(xin)
+        torch.manual_seed(5)
+        dy = torch.randn_like(y)
+        block.zero_grad()
+        y.backward(dy)
+        grads[mode] = (y.detach().float(), x.grad.float().clone(), block.a.conv.weight.grad.float().clone())
+    for a, b in zip(grads[True], grads[False]):
+        _check(a, b, 2e-2)
+    # library reference in fp32 on the same (bf16-rounded) input
+    monkeypatch.setattr(cnn, "CONV_MODE", "library")
+    monkeypatch.setattr(cnn, "NORM_POOL_MODE", "library")
+    monkeypatch.setattr(cnn, "FORK_FUSION", False)
+    ref = cnn.Bottleneck(cin, width, stride).cuda().train()
+    ref.load_state_dict(block.state_dict())
+    for m in ref.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            m.reset_running_stats()
+    x = x0.float().requires_grad_(True)
+    yr = ref(x)
+    yr.backward(dy.float())
+    _check(grads[True][0], yr.detach(), 5e-2)
+    # an activation that bf16 rounding moves across zero flips its ReLU mask, which changes single elements of dx by the
+    # size of a gradient: the input gradient is compared in the Frobenius norm only
+    rel = ((grads[True][1] - x.grad).norm() / x.grad.norm()).item()
+    assert rel < 0.1, rel
+
+
 @pytest.mark.parametrize("k,stride,pad", [(3, 2, 1), (2, 2, 0)])
 def test_max_pool_kernels_match_the_library(k, stride, pad):
     from autodist_b200.ops import functional as Fn
