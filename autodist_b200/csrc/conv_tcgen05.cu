@@ -19,6 +19,7 @@
 //
 // The reference's convolutions are tf.keras layers running in cuDNN (examples/benchmark/imagenet.py:232-249).
 #include "conv_tcgen05.h"
+#include "pdl.cuh"
 #include "tcgen05_common.cuh"
 
 namespace adb200 {
@@ -132,6 +133,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_sync();       // everything above touched only this CTA's shared and tensor memory; global memory is read from here on
 
   // trace (when given): 0 start, 1 first load issued, 2 last load issued, 3 first stage full, 4 last MMA committed,
   // 5 cycles the first epilogue warp spent between "accumulator full" and "accumulator released" (summed over tiles),
@@ -443,7 +445,7 @@ cudaError_t launch_one(const ConvMaps& maps, const ConvParams& p, int num_sms, c
   else tiles = (long long)((p.Mc + BM - 1) / BM) * c_tiles * p.ntaps * p.ksplit;
   if (tiles <= 0) return cudaSuccess;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  kern<<<grid, kThreads, C::SMEM, stream>>>(maps, p);
+  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, maps, p);
   return cudaGetLastError();
 }
 

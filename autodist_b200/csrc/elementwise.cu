@@ -13,6 +13,7 @@
 #include <stdint.h>
 
 #include "elementwise.h"
+#include "pdl.cuh"
 
 namespace adb200 {
 namespace {
@@ -95,6 +96,7 @@ __global__ void ln_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict
                               const float* __restrict__ beta, bf16* __restrict__ z, bf16* __restrict__ y,
                               float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, float eps,
                               float p_drop, uint64_t seed, const long long* step) {
+  pdl_sync();
   __shared__ float red[4];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int col = threadIdx.x * 8;
@@ -169,6 +171,7 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
                               const float* __restrict__ rstd, const float* __restrict__ gamma, const bf16* __restrict__ dz_add,
                               bf16* __restrict__ dz, bf16* __restrict__ dx, float* __restrict__ part, int rows, int H, float p_drop,
                               uint64_t seed, const long long* step, int want_out_sum) {
+  pdl_sync();
   __shared__ float red[2][4];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int col = threadIdx.x * 8;
@@ -272,6 +275,7 @@ __global__ void ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restric
 // cleared as they are read (the producer adds into them again next time).
 __global__ void colsum3_f32_kernel(float* __restrict__ part, float* __restrict__ out0, float* __restrict__ out1,
                                    float* __restrict__ out2, int parts, int H, int accumulate) {
+  pdl_sync();
   __shared__ float sm[8][33];
   float* src = part + (long long)blockIdx.y * parts * H;
   float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
@@ -291,6 +295,7 @@ __global__ void colsum3_f32_kernel(float* __restrict__ part, float* __restrict__
 
 // out[c] (+)= sum over `parts` rows of part[r][c]. A block covers 32 columns; its 8 warps split the partial rows.
 __global__ void colsum_f32_kernel(const float* __restrict__ part, float* __restrict__ out, int parts, int H, int accumulate) {
+  pdl_sync();
   __shared__ float sm[8][33];
   const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;
   float a = 0.f;
@@ -309,6 +314,7 @@ __global__ void colsum_f32_kernel(const float* __restrict__ part, float* __restr
 // Two reductions in one launch (layernorm's dgamma and dbeta): blockIdx.y picks the pair.
 __global__ void colsum2_f32_kernel(const float* __restrict__ part_a, float* __restrict__ out_a, const float* __restrict__ part_b,
                                    float* __restrict__ out_b, int parts, int H, int accumulate) {
+  pdl_sync();
   __shared__ float sm[8][33];
   const float* part = blockIdx.y ? part_b : part_a;
   float* out = blockIdx.y ? out_b : out_a;
@@ -331,6 +337,7 @@ __global__ void colsum2_f32_kernel(const float* __restrict__ part_a, float* __re
 __global__ void embed_sum_kernel(const bf16* __restrict__ word, const bf16* __restrict__ pos, const bf16* __restrict__ type,
                                  const int64_t* __restrict__ ids, const int64_t* __restrict__ tt, bf16* __restrict__ z,
                                  int rows, int S, int H, long long V, long long types, int* __restrict__ error) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   long long w = ids[warp], t = tt ? tt[warp] : 0;
@@ -354,6 +361,7 @@ __global__ void embed_sum_kernel(const bf16* __restrict__ word, const bf16* __re
 // dst[idx[r]] += src[r] (fp32 destination, bf16 source rows): dense embedding gradient by vector atomics.
 __global__ void scatter_add_rows_kernel(float* __restrict__ dst, const int64_t* __restrict__ idx, const bf16* __restrict__ src,
                                         int rows, int H, float scale) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const long long r = idx[warp];
@@ -368,6 +376,7 @@ __global__ void scatter_add_rows_kernel(float* __restrict__ dst, const int64_t* 
 
 // out[k][c] = sum over rows r = k + j*stride (j < count) of x[r][c]: position-embedding gradient (k = position).
 __global__ void strided_rowsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, int keys, int stride, int count, int H) {
+  pdl_sync();
   const int k = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= H || k >= keys) return;
@@ -387,6 +396,7 @@ __global__ void strided_rowsum_kernel(const bf16* __restrict__ x, float* __restr
 // with 32 row lanes per vector; the lanes' sums meet in shared memory.
 __global__ void keyed_colsum_kernel(const bf16* __restrict__ x, const int64_t* __restrict__ key, float* __restrict__ part,
                                     int rows, int H, int keys, int rows_per_block) {
+  pdl_sync();
   __shared__ float sm[32][65];
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const int c = blockIdx.x * 64 + vec * 8;
@@ -416,6 +426,7 @@ __global__ void keyed_colsum_kernel(const bf16* __restrict__ x, const int64_t* _
 
 // out[r] = src[idx[r]] (bf16 rows)
 __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* __restrict__ idx, bf16* __restrict__ out, int rows, int H) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const long long r = idx[warp];
@@ -425,6 +436,7 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int64_t* 
 
 // Row gather from an fp32 table with the bf16 cast fused (sampled-softmax / embedding lookups of master weights).
 __global__ void gather_rows_f32_kernel(const float* __restrict__ src, const int64_t* __restrict__ idx, bf16* __restrict__ out, int rows, int H) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const long long r = idx[warp];
@@ -438,6 +450,7 @@ __global__ void gather_rows_f32_kernel(const float* __restrict__ src, const int6
 
 // dst[idx[r]] += src[r] for bf16 rows whose indices are unique (MLM positions of one sequence never repeat)
 __global__ void scatter_add_rows_bf16_kernel(bf16* __restrict__ dst, const int64_t* __restrict__ idx, const bf16* __restrict__ src, int rows, int H) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= rows) return;
   const long long r = idx[warp];
@@ -470,6 +483,7 @@ template <int TPR, int VPT>
 __global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __restrict__ mask, bf16* __restrict__ p,
                                    bf16* __restrict__ p_drop, long long rows, int S, int rows_per_batch, float scale,
                                    float pd, uint64_t seed, const long long* step) {
+  pdl_sync();
   const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long row = gt / TPR;
   const int t = (int)(gt % TPR);
@@ -522,6 +536,7 @@ __global__ void softmax_fwd_kernel(const bf16* __restrict__ x, const float* __re
 template <int TPR, int VPT>
 __global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict__ p, long long rows, int S, float scale,
                                    float pd, uint64_t seed, const long long* step) {
+  pdl_sync();
   const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long row = gt / TPR;
   const int t = (int)(gt % TPR);
@@ -561,6 +576,7 @@ __global__ void softmax_bwd_kernel(bf16* __restrict__ dp, const bf16* __restrict
 // overwritten by d loss / d logits = w / denom * (softmax - onehot) (zero in the padding columns). denom is read
 // from device memory (sum of weights, computed by weight_sum_kernel) so that the whole step stays on the device.
 __global__ void weight_sum_kernel(const float* __restrict__ w, int n, float* __restrict__ out, float eps) {
+  pdl_sync();
   float a = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) a += w[i];
   a = warp_sum(a);
@@ -576,6 +592,7 @@ __global__ void weight_sum_kernel(const float* __restrict__ w, int n, float* __r
 
 __global__ void xent_kernel(bf16* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ weights,
                             const float* __restrict__ denom, float* __restrict__ loss_sum, int V, int ld, float loss_scale) {
+  pdl_sync();
   const int row = blockIdx.x;
   bf16* x = logits + (long long)row * ld;
   __shared__ float red[32];
@@ -614,6 +631,7 @@ __global__ void xent_kernel(bf16* __restrict__ logits, const int64_t* __restrict
 template <typename T>
 __global__ void pad_image8_kernel(const T* __restrict__ x, long long sn, long long sc, long long sh, long long sw, int C, int H, int W,
                                   bf16* __restrict__ xp, int Hp, int Wp, int pad, long long total) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int wp = (int)(i % Wp), hp = (int)((i / Wp) % Hp);
@@ -637,6 +655,7 @@ __global__ void pad_image8_kernel(const T* __restrict__ x, long long sn, long lo
 }
 
 __global__ void relu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ y, uint4* __restrict__ dx, long long n8) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   uint4 d = dy[i];
@@ -655,11 +674,13 @@ __global__ void relu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __res
 }
 
 __global__ void tanh_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, long long n) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) { float t = __bfloat162float(y[i]); dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * (1.0f - t * t)); }
 }
 
 __global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ u, bf16* __restrict__ dx, long long n) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float x = __bfloat162float(u[i]);
@@ -670,6 +691,7 @@ __global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restr
 }
 
 __global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n8) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   float x[8], y[8];
@@ -686,6 +708,7 @@ __global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restri
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                             bf16* __restrict__ p16, long long n, const float* __restrict__ lr_ptr, float b1, float b2, float eps,
                             float wd, int decoupled, const long long* __restrict__ step_ptr, float grad_scale) {
+  pdl_sync();
   const float lr = *lr_ptr;
   const float t = (float)(*step_ptr);
   const float c1 = 1.0f - powf(b1, t), c2 = 1.0f - powf(b2, t);
@@ -745,6 +768,7 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
 __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ mom, bf16* __restrict__ p16,
                            long long n, const float* __restrict__ lr_ptr, float momentum, float dampening, float wd, int nesterov,
                            const long long* __restrict__ step_ptr, float grad_scale) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float lr = *lr_ptr;
@@ -761,6 +785,7 @@ __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ g, f
 
 __global__ void adagrad_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ acc, bf16* __restrict__ p16,
                                long long n, const float* __restrict__ lr_ptr, float eps, float wd, float grad_scale) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float gr = g[i] * grad_scale + wd * p[i];
@@ -777,6 +802,7 @@ __global__ void sparse_rows_update_kernel(float* __restrict__ p, float* __restri
                                           bf16* __restrict__ p16, const int64_t* __restrict__ rows, const float* __restrict__ g,
                                           int n, int H, long long V, int kind, const float* __restrict__ lr_ptr, float b1, float b2,
                                           float eps, const long long* __restrict__ step_ptr, float grad_scale) {
+  pdl_sync();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n) return;
   const long long r = rows[warp];
@@ -816,6 +842,7 @@ __global__ void flagged_rows_update_kernel(float* __restrict__ p, float* __restr
                                            float* __restrict__ g, uint8_t* __restrict__ flags, long long rows, int H, int kind,
                                            const float* __restrict__ lr_ptr, float b1, float b2, float eps,
                                            const long long* __restrict__ step_ptr) {
+  pdl_sync();
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarp = ((long long)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   const float lr = *lr_ptr;
@@ -858,6 +885,7 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __ex
 
 __global__ void lstm_cell_fwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_prev, float* __restrict__ c,
                                      bf16* __restrict__ h, int B, int S, float forget_bias) {
+  pdl_sync();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)B * S) return;
   const int b = (int)(idx / S), s = (int)(idx % S);
@@ -871,6 +899,7 @@ __global__ void lstm_cell_fwd_kernel(const float* __restrict__ gates, const floa
 __global__ void lstm_cell_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_prev, const float* __restrict__ c,
                                      const float* __restrict__ dh, const float* __restrict__ dc_next, float* __restrict__ dgates,
                                      float* __restrict__ dc_prev, int B, int S, float forget_bias) {
+  pdl_sync();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)B * S) return;
   const int b = (int)(idx / S), s = (int)(idx % S);
@@ -890,6 +919,7 @@ __global__ void lstm_cell_bwd_kernel(const float* __restrict__ gates, const floa
 // ------------------------------------------------------------------------------------------------ global-norm clip (K19)
 // acc += weight * sum(x^2); later x *= min(1, max_norm / (sqrt(acc) + 1e-6)). The norm never visits the host.
 __global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ acc, float weight) {
+  pdl_sync();
   float a = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) a += x[i] * x[i];
   a = warp_sum(a);
@@ -903,6 +933,7 @@ __global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __
   }
 }
 __global__ void clip_scale_kernel(float* __restrict__ x, long long n, const float* __restrict__ acc, float max_norm) {
+  pdl_sync();
   const float norm = sqrtf(*acc);
   if (norm <= max_norm) return;
   const float sc = max_norm / (norm + 1e-6f);
@@ -915,6 +946,7 @@ __global__ void clip_scale_kernel(float* __restrict__ x, long long n, const floa
 // col2im is its adjoint in gather form: every input pixel sums the taps that read it, so no atomics are needed.
 __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, int N, int H, int W, int C, int KH, int KW,
                               int stride, int pad, int Ho, int Wo) {
+  pdl_sync();
   const int c8 = C / 8;
   const long long total = (long long)N * Ho * Wo * KH * KW * c8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -933,6 +965,7 @@ __global__ void im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col
 
 __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__ dx, int N, int H, int W, int C, int KH, int KW,
                               int stride, int pad, int Ho, int Wo) {
+  pdl_sync();
   const int c8 = C / 8;
   const long long total = (long long)N * H * W * c8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -965,6 +998,7 @@ __global__ void col2im_kernel(const bf16* __restrict__ dcols, bf16* __restrict__
 // Statistics: part[y][0][c] = sum x, part[y][1][c] = sum x^2 over row chunk y (then colsum_f32 over the chunks).
 // Each thread keeps four independent 16-byte loads in flight.
 __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ part, int rows, int C, int rows_per_block) {
+  pdl_sync();
   __shared__ float s1[32][65], s2[32][65];
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const int c = blockIdx.x * 64 + vec * 8;
@@ -1003,6 +1037,7 @@ __global__ void bn_stats_kernel(const bf16* __restrict__ x, float* __restrict__ 
 // the chunk's rows. Channels-last matrix [rows, C]; 64 channels per block column, four 16-byte loads in flight per thread.
 __global__ void relu_bwd_colsum_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, float* __restrict__ part,
                                        int rows, int C, int rows_per_block) {
+  pdl_sync();
   __shared__ float s1[32][65];
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const int c = blockIdx.x * 64 + vec * 8;
@@ -1052,6 +1087,7 @@ __global__ void __launch_bounds__(256, 6) bn_apply_kernel(const bf16* __restrict
                                 int relu, const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
                                 float inv_rows, float eps, float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ run_mean,
                                 float* __restrict__ run_var, long long* __restrict__ batches, float momentum, float unbias) {
+  pdl_sync();
   extern __shared__ float s_coef[];                 // [scale (C), shift (C)]
   // the first elements are requested before the table is built, so that the table's latency hides under them
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -1116,6 +1152,7 @@ __global__ void __launch_bounds__(256, 4) bn_bwd_stats_kernel(const bf16* __rest
                                     unsigned int* __restrict__ counters, float* __restrict__ part, float* __restrict__ sums,
                                     float* __restrict__ coef, float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc,
                                     int rows, int C, int rows_per_block, int relu, float inv_rows) {
+  pdl_sync();
   __shared__ float s1[32][65], s2[32][65];
   __shared__ int s_last;
   const int vec = threadIdx.x & 7, rl = threadIdx.x >> 3;
@@ -1198,6 +1235,7 @@ __global__ void __launch_bounds__(256, 4) bn_bwd_stats_kernel(const bf16* __rest
 __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ y,
                                     const float* __restrict__ coef, bf16* __restrict__ dx, bf16* __restrict__ dres, long long total8, int C,
                                     int relu) {
+  pdl_sync();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const int c = (int)(idx % (C / 8)) * 8;
@@ -1231,6 +1269,7 @@ __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ dy, const bf16* __r
 // with that code, so ties (common after a ReLU) go to exactly one input as in the library.
 __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ code, int N, int H, int W,
                                    int C, int k, int stride, int pad, int Ho, int Wo) {
+  pdl_sync();
   const int c8 = C / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)N * Ho * Wo * c8) return;
@@ -1263,6 +1302,7 @@ __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
 template <int KT, int ST>
 __global__ void maxpool_bwd_kernel(const uint8_t* __restrict__ code, const bf16* __restrict__ dy, bf16* __restrict__ dx, int N, int H,
                                    int W, int C, int k_arg, int stride_arg, int pad, int Ho, int Wo) {
+  pdl_sync();
   const int k = KT > 0 ? KT : k_arg, stride = ST > 0 ? ST : stride_arg;
   const int c8 = C / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1307,6 +1347,7 @@ constexpr int PSGD_MAXR = 4;
 
 __global__ void psgd_p_kernel(float* __restrict__ M, const float* __restrict__ err, const float* __restrict__ Q, float* __restrict__ P,
                               int m, int n, int r) {
+  pdl_sync();
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (row >= m) return;
   float acc[PSGD_MAXR] = {0.f, 0.f, 0.f, 0.f};
@@ -1323,6 +1364,7 @@ __global__ void psgd_p_kernel(float* __restrict__ M, const float* __restrict__ e
 }
 
 __global__ void psgd_q_kernel(const float* __restrict__ M, const float* __restrict__ P, float* __restrict__ Qn, int m, int n, int r) {
+  pdl_sync();
   __shared__ float sm[8][32][PSGD_MAXR];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + lane;
@@ -1344,6 +1386,7 @@ __global__ void psgd_q_kernel(const float* __restrict__ M, const float* __restri
 
 __global__ void psgd_d_kernel(float* __restrict__ M, float* __restrict__ err, const float* __restrict__ P, const float* __restrict__ Q,
                               int m, int n, int r) {
+  pdl_sync();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)m * n) return;
   const int i = (int)(idx / n), j = (int)(idx % n);
@@ -1378,6 +1421,7 @@ __device__ __forceinline__ int psgd_find(const long long* prefix, int nmat, long
 // M += err (written back), P = M Q: one warp per matrix row.
 __global__ void psgd_p_batched_kernel(float* __restrict__ grad, const float* __restrict__ err, const float* __restrict__ Q,
                                       float* __restrict__ P, PsgdTable t, int r, long long rows) {
+  pdl_sync();
   const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -1401,6 +1445,7 @@ __global__ void psgd_p_batched_kernel(float* __restrict__ grad, const float* __r
 
 // Modified Gram-Schmidt on the columns of every P_i (one block per matrix), as orthogonalize_ of the Python compressor.
 __global__ void psgd_orth_batched_kernel(float* __restrict__ P, PsgdTable t, int r) {
+  pdl_sync();
   __shared__ float red[32];
   __shared__ float bcast;
   const int i = blockIdx.x;
@@ -1434,6 +1479,7 @@ __global__ void psgd_orth_batched_kernel(float* __restrict__ P, PsgdTable t, int
 
 // Q = M^T P: one block (8 warps) per 32 columns of one matrix.
 __global__ void psgd_q_batched_kernel(const float* __restrict__ grad, const float* __restrict__ P, float* __restrict__ Q, PsgdTable t, int r) {
+  pdl_sync();
   __shared__ float sm[8][32][PSGD_MAXR];
   const int i = psgd_find(t.blk_prefix, t.nmat, blockIdx.x);
   const int m = t.m[i], n = t.n[i];
@@ -1460,6 +1506,7 @@ __global__ void psgd_q_batched_kernel(const float* __restrict__ grad, const floa
 // err = M - P Q^T; M = P Q^T: one thread per element of all matrices.
 __global__ void psgd_d_batched_kernel(float* __restrict__ grad, float* __restrict__ err, const float* __restrict__ P, const float* __restrict__ Q,
                                       PsgdTable t, int r, long long total) {
+  pdl_sync();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int i = psgd_find(t.elem_prefix, t.nmat, idx);
@@ -1474,11 +1521,13 @@ __global__ void psgd_d_batched_kernel(float* __restrict__ grad, float* __restric
 }
 
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = __float2bfloat16(x[i]);
 }
 
-__global__ void increment_kernel(long long* c) { *c += 1; }
+__global__ void increment_kernel(long long* c) {
+  pdl_sync(); *c += 1; }
 
 inline int blocks_for(long long n, int per) { return (int)((n + per - 1) / per); }
 
@@ -1489,7 +1538,7 @@ void ln_fwd(const bf16* x, const bf16* res, const float* gamma, const float* bet
             int rows, int H, float eps, float p_drop, uint64_t seed, const long long* step, cudaStream_t st) {
   if (rows <= 0) return;
   const int threads = ((H / 8 + 31) / 32) * 32;
-  ln_fwd_kernel<<<rows < 1184 ? rows : 1184, threads, 0, st>>>(x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
+  launch_pdl(ln_fwd_kernel, dim3(rows < 1184 ? rows : 1184), dim3(threads), 0, st, x, res, gamma, beta, z, y, mean, rstd, rows, H, eps, p_drop, seed, step);
 }
 // Blocks of the backward kernel: four per SM when there are rows enough, so that a block keeps several rows (its
 // per-column partial sums are written once per block).
@@ -1502,45 +1551,45 @@ void ln_bwd(const bf16* dy, const bf16* z, const float* mean, const float* rstd,
             const long long* step, int accumulate, cudaStream_t st) {
   const int blocks = ln_bwd_blocks(rows);
   const int threads = ((H / 8 + 31) / 32) * 32;
-  ln_bwd_kernel<<<blocks, threads, 0, st>>>(dy, z, mean, rstd, gamma, dz_add, dz, dx, part, rows, H, p_drop, seed, step, dsum != nullptr);
-  colsum3_f32_kernel<<<dim3(blocks_for(H, 32), dsum != nullptr ? 3 : 2), 256, 0, st>>>(part, dgamma, dbeta, dsum, kLnSlots, H, accumulate);
+  launch_pdl(ln_bwd_kernel, dim3(blocks), dim3(threads), 0, st, dy, z, mean, rstd, gamma, dz_add, dz, dx, part, rows, H, p_drop, seed, step, dsum != nullptr);
+  launch_pdl(colsum3_f32_kernel, dim3(dim3(blocks_for(H, 32), dsum != nullptr ? 3 : 2)), dim3(256), 0, st, part, dgamma, dbeta, dsum, kLnSlots, H, accumulate);
 }
 void embed_sum(const bf16* word, const bf16* pos, const bf16* type, const int64_t* ids, const int64_t* tt, bf16* z, int rows, int S,
                int H, long long V, long long types, int* error, cudaStream_t st) {
-  embed_sum_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(word, pos, type, ids, tt, z, rows, S, H, V, types, error);
+  launch_pdl(embed_sum_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, word, pos, type, ids, tt, z, rows, S, H, V, types, error);
 }
 void scatter_add_rows(float* dst, const int64_t* idx, const bf16* src, int rows, int H, float scale, cudaStream_t st) {
-  scatter_add_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H, scale);
+  launch_pdl(scatter_add_rows_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, dst, idx, src, rows, H, scale);
 }
 void strided_rowsum(const bf16* x, float* out, int keys, int stride, int count, int H, cudaStream_t st) {
   dim3 grid(blocks_for(H / 8, 128), keys);
-  strided_rowsum_kernel<<<grid, 128, 0, st>>>(x, out, keys, stride, count, H);
+  launch_pdl(strided_rowsum_kernel, dim3(grid), dim3(128), 0, st, x, out, keys, stride, count, H);
 }
 int colsum_parts(int rows) { return rows >= 2048 ? 16 : (rows >= 256 ? 4 : 1); }
 void keyed_colsum(const bf16* x, const int64_t* key, float* part, float* out, int rows, int H, int keys, int accumulate, cudaStream_t st) {
   const int parts = colsum_parts(rows);
   const int rpb = (rows + parts - 1) / parts;
   dim3 grid(blocks_for(H, 64), parts);
-  keyed_colsum_kernel<<<grid, 256, 0, st>>>(x, key, part, rows, H, keys, rpb);
-  colsum_f32_kernel<<<blocks_for(keys * H, 32), 256, 0, st>>>(part, out, parts, keys * H, accumulate);
+  launch_pdl(keyed_colsum_kernel, dim3(grid), dim3(256), 0, st, x, key, part, rows, H, keys, rpb);
+  launch_pdl(colsum_f32_kernel, dim3(blocks_for(keys * H, 32)), dim3(256), 0, st, part, out, parts, keys * H, accumulate);
 }
 void gather_rows(const bf16* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
-  gather_rows_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
+  launch_pdl(gather_rows_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, src, idx, out, rows, H);
 }
 void gather_rows_f32(const float* src, const int64_t* idx, bf16* out, int rows, int H, cudaStream_t st) {
-  gather_rows_f32_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(src, idx, out, rows, H);
+  launch_pdl(gather_rows_f32_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, src, idx, out, rows, H);
 }
 void scatter_add_rows_bf16(bf16* dst, const int64_t* idx, const bf16* src, int rows, int H, cudaStream_t st) {
-  scatter_add_rows_bf16_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(dst, idx, src, rows, H);
+  launch_pdl(scatter_add_rows_bf16_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, dst, idx, src, rows, H);
 }
 #define ADB_SOFTMAX_DISPATCH(KERNEL, ...)                                                              \
   do {                                                                                                 \
     const int threads = S / 8;                                                                         \
-    if (threads == 8) KERNEL<8, 1><<<blocks_for(rows * 8, 256), 256, 0, st>>>(__VA_ARGS__);            \
-    else if (threads == 16) KERNEL<16, 1><<<blocks_for(rows * 16, 256), 256, 0, st>>>(__VA_ARGS__);    \
-    else if (threads == 32) KERNEL<32, 1><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);    \
-    else if (threads == 64) KERNEL<32, 2><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);    \
-    else if (threads == 128) KERNEL<32, 4><<<blocks_for(rows * 32, 256), 256, 0, st>>>(__VA_ARGS__);   \
+    if (threads == 8) launch_pdl(KERNEL<8, 1>, dim3(blocks_for(rows * 8, 256)), dim3(256), 0, st, __VA_ARGS__);            \
+    else if (threads == 16) launch_pdl(KERNEL<16, 1>, dim3(blocks_for(rows * 16, 256)), dim3(256), 0, st, __VA_ARGS__);    \
+    else if (threads == 32) launch_pdl(KERNEL<32, 1>, dim3(blocks_for(rows * 32, 256)), dim3(256), 0, st, __VA_ARGS__);    \
+    else if (threads == 64) launch_pdl(KERNEL<32, 2>, dim3(blocks_for(rows * 32, 256)), dim3(256), 0, st, __VA_ARGS__);    \
+    else if (threads == 128) launch_pdl(KERNEL<32, 4>, dim3(blocks_for(rows * 32, 256)), dim3(256), 0, st, __VA_ARGS__);   \
   } while (0)
 bool softmax_supported(int S) { return S == 64 || S == 128 || S == 256 || S == 512 || S == 1024; }
 void softmax_fwd(const bf16* x, const float* mask, bf16* p, bf16* p_drop, long long rows, int S, int rows_per_batch, float scale,
@@ -1551,71 +1600,71 @@ void softmax_bwd(bf16* dp, const bf16* p, long long rows, int S, float scale, fl
                  cudaStream_t st) {
   ADB_SOFTMAX_DISPATCH(softmax_bwd_kernel, dp, p, rows, S, scale, pd, seed, step);
 }
-void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st) { weight_sum_kernel<<<1, 256, 0, st>>>(w, n, out, eps); }
+void weight_sum(const float* w, int n, float* out, float eps, cudaStream_t st) { launch_pdl(weight_sum_kernel, dim3(1), dim3(256), 0, st, w, n, out, eps); }
 void xent(bf16* logits, const int64_t* labels, const float* weights, const float* denom, float* loss_sum, int rows, int V, int ld,
           float loss_scale, cudaStream_t st) {
-  xent_kernel<<<rows, V >= 4096 ? 1024 : 128, 0, st>>>(logits, labels, weights, denom, loss_sum, V, ld, loss_scale);
+  launch_pdl(xent_kernel, dim3(rows), dim3(V >= 4096 ? 1024 : 128), 0, st, logits, labels, weights, denom, loss_sum, V, ld, loss_scale);
 }
 void gelu_bwd(const bf16* dy, const bf16* u, bf16* dx, long long n, cudaStream_t st) {
-  gelu_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, u, dx, n);
+  launch_pdl(gelu_bwd_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, st, dy, u, dx, n);
 }
 void pad_image8(const void* x, int is_fp32, long long sn, long long sc, long long sh, long long sw, int N, int C, int H, int W, bf16* xp,
                 int Hp, int Wp, int pad, cudaStream_t st) {
   const long long total = (long long)N * Hp * Wp;
-  if (is_fp32) pad_image8_kernel<float><<<blocks_for(total, 256), 256, 0, st>>>(reinterpret_cast<const float*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
-  else pad_image8_kernel<bf16><<<blocks_for(total, 256), 256, 0, st>>>(reinterpret_cast<const bf16*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
+  if (is_fp32) launch_pdl(pad_image8_kernel<float>, dim3(blocks_for(total, 256)), dim3(256), 0, st, reinterpret_cast<const float*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
+  else launch_pdl(pad_image8_kernel<bf16>, dim3(blocks_for(total, 256)), dim3(256), 0, st, reinterpret_cast<const bf16*>(x), sn, sc, sh, sw, C, H, W, xp, Hp, Wp, pad, total);
 }
 void relu_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
-  relu_bwd_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(dy), reinterpret_cast<const uint4*>(y),
+  launch_pdl(relu_bwd_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, reinterpret_cast<const uint4*>(dy), reinterpret_cast<const uint4*>(y),
                                                           reinterpret_cast<uint4*>(dx), n / 8);
 }
 void tanh_bwd(const bf16* dy, const bf16* y, bf16* dx, long long n, cudaStream_t st) {
-  tanh_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(dy, y, dx, n);
+  launch_pdl(tanh_bwd_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, st, dy, y, dx, n);
 }
 void add_bf16(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t st) {
-  add_bf16_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(a, b, out, n / 8);
+  launch_pdl(add_bf16_kernel, dim3(blocks_for(n / 8, 256)), dim3(256), 0, st, a, b, out, n / 8);
 }
 void adam_update(float* p, const float* g, float* m, float* v, bf16* p16, long long n, const float* lr, float b1, float b2,
                  float eps, float wd, int decoupled, const long long* step, float grad_scale, cudaStream_t st) {
   const long long groups = (n / 4 + 1) / 2 + 1;
   const int blocks = (int)((groups + 255) / 256 < 148 * 16 ? (groups + 255) / 256 : 148 * 16);
-  adam_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(p, g, m, v, p16, n, lr, b1, b2, eps, wd, decoupled, step, grad_scale);
+  launch_pdl(adam_kernel, dim3(blocks < 1 ? 1 : blocks), dim3(256), 0, st, p, g, m, v, p16, n, lr, b1, b2, eps, wd, decoupled, step, grad_scale);
 }
 void sgd_update(float* p, const float* g, float* mom, bf16* p16, long long n, const float* lr, float momentum, float dampening,
                 float wd, int nesterov, const long long* step, float grad_scale, cudaStream_t st) {
-  sgd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, mom, p16, n, lr, momentum, dampening, wd, nesterov, step, grad_scale);
+  launch_pdl(sgd_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, st, p, g, mom, p16, n, lr, momentum, dampening, wd, nesterov, step, grad_scale);
 }
 void adagrad_update(float* p, const float* g, float* acc, bf16* p16, long long n, const float* lr, float eps, float wd,
                     float grad_scale, cudaStream_t st) {
-  adagrad_kernel<<<blocks_for(n, 256), 256, 0, st>>>(p, g, acc, p16, n, lr, eps, wd, grad_scale);
+  launch_pdl(adagrad_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, st, p, g, acc, p16, n, lr, eps, wd, grad_scale);
 }
 void sparse_rows_update(float* p, float* s1, float* s2, bf16* p16, const int64_t* rows, const float* g, int n, int H, long long V,
                         int kind, const float* lr, float b1, float b2, float eps, const long long* step, float grad_scale,
                         cudaStream_t st) {
   if (n <= 0) return;
-  sparse_rows_update_kernel<<<blocks_for(n, 8), 256, 0, st>>>(p, s1, s2, p16, rows, g, n, H, V, kind, lr, b1, b2, eps, step, grad_scale);
+  launch_pdl(sparse_rows_update_kernel, dim3(blocks_for(n, 8)), dim3(256), 0, st, p, s1, s2, p16, rows, g, n, H, V, kind, lr, b1, b2, eps, step, grad_scale);
 }
 void flagged_rows_update(float* p, float* s1, float* s2, bf16* p16, float* g, uint8_t* flags, long long rows, int H, int kind,
                          const float* lr, float b1, float b2, float eps, const long long* step, cudaStream_t st) {
   if (rows <= 0) return;
   long long blocks = (rows + 7) / 8;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  flagged_rows_update_kernel<<<(int)blocks, 256, 0, st>>>(p, s1, s2, p16, g, flags, rows, H, kind, lr, b1, b2, eps, step);
+  launch_pdl(flagged_rows_update_kernel, dim3((int)blocks), dim3(256), 0, st, p, s1, s2, p16, g, flags, rows, H, kind, lr, b1, b2, eps, step);
 }
 void lstm_cell_fwd(const float* gates, const float* c_prev, float* c, bf16* h, int B, int S, float fb, cudaStream_t st) {
-  lstm_cell_fwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, h, B, S, fb);
+  launch_pdl(lstm_cell_fwd_kernel, dim3(blocks_for((long long)B * S, 256)), dim3(256), 0, st, gates, c_prev, c, h, B, S, fb);
 }
 void lstm_cell_bwd(const float* gates, const float* c_prev, const float* c, const float* dh, const float* dc_next, float* dgates,
                    float* dc_prev, int B, int S, float fb, cudaStream_t st) {
-  lstm_cell_bwd_kernel<<<blocks_for((long long)B * S, 256), 256, 0, st>>>(gates, c_prev, c, dh, dc_next, dgates, dc_prev, B, S, fb);
+  launch_pdl(lstm_cell_bwd_kernel, dim3(blocks_for((long long)B * S, 256)), dim3(256), 0, st, gates, c_prev, c, dh, dc_next, dgates, dc_prev, B, S, fb);
 }
 void sumsq(const float* x, long long n, float* acc, float weight, cudaStream_t st) {
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
-  sumsq_kernel<<<blocks, 256, 0, st>>>(x, n, acc, weight);
+  launch_pdl(sumsq_kernel, dim3(blocks), dim3(256), 0, st, x, n, acc, weight);
 }
 void clip_scale(float* x, long long n, const float* acc, float max_norm, cudaStream_t st) {
   const int blocks = (int)(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
-  clip_scale_kernel<<<blocks, 256, 0, st>>>(x, n, acc, max_norm);
+  launch_pdl(clip_scale_kernel, dim3(blocks), dim3(256), 0, st, x, n, acc, max_norm);
 }
 // Row chunks per channel block: enough blocks to fill the SMs (~8 per SM) while each chunk keeps >= 128 rows.
 int bn_bwd_part_floats(int C) { return kBnCounterFloats + kBnSlots * 2 * C; }
@@ -1636,58 +1685,58 @@ void bn_fwd(const bf16* x, const float* gamma, const float* beta, const bf16* re
   const float unbias = rows > 1 ? (float)rows / (float)(rows - 1) : 1.0f;
   if (!sums_given) {
     const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
-    bn_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(x, part, rows, C, rpb);
-    colsum_f32_kernel<<<blocks_for(2 * C, 32), 256, 0, st>>>(part, sums, parts, 2 * C, 0);
+    launch_pdl(bn_stats_kernel, dim3(dim3(blocks_for(C, 64), parts)), dim3(256), 0, st, x, part, rows, C, rpb);
+    launch_pdl(colsum_f32_kernel, dim3(blocks_for(2 * C, 32)), dim3(256), 0, st, part, sums, parts, 2 * C, 0);
   }
   // a few elements per thread: the per-block table of 2 * C coefficients is amortised over at least 4 x 2048 elements
   long long blocks = (total8 + 256 * 4 - 1) / (256 * 4);
   if (blocks > 148 * 6) blocks = 148 * 6;          // one resident wave (6 blocks of 256 threads per SM)
-  bn_apply_kernel<<<(int)(blocks < 1 ? 1 : blocks), 256, 2 * C * sizeof(float), st>>>(x, res, y, total8, C, relu, sums, gamma, beta, 1.0f / rows,
+  launch_pdl(bn_apply_kernel, dim3((int)(blocks < 1 ? 1 : blocks)), dim3(256), 2 * C * sizeof(float), st, x, res, y, total8, C, relu, sums, gamma, beta, 1.0f / rows,
                                                                                       eps, mean, rstd, run_mean, run_var, batches, momentum, unbias);
   (void)coef;
 }
 void bn_bwd(const bf16* dy, const bf16* x, const bf16* y, const float* mean, const float* rstd, const float* gamma, bf16* dx, bf16* dres,
             float* part, float* sums, float* coef, int rows, int C, int relu, float* dgamma_acc, float* dbeta_acc, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
-  bn_bwd_stats_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, x, y, mean, rstd, gamma, reinterpret_cast<unsigned int*>(part),
+  launch_pdl(bn_bwd_stats_kernel, dim3(dim3(blocks_for(C, 64), parts)), dim3(256), 0, st, dy, x, y, mean, rstd, gamma, reinterpret_cast<unsigned int*>(part),
                                                                       part + kBnCounterFloats, sums, coef, dgamma_acc, dbeta_acc, rows, C, rpb,
                                                                       relu, 1.0f / rows);
   const long long total8 = (long long)rows * (C / 8);
-  bn_bwd_apply_kernel<<<blocks_for(total8, 256), 256, 0, st>>>(dy, x, y, coef, dx, dres, total8, C, relu);
+  launch_pdl(bn_bwd_apply_kernel, dim3(blocks_for(total8, 256)), dim3(256), 0, st, dy, x, y, coef, dx, dres, total8, C, relu);
 }
 // dx = relu'(y) * dy (skipped when y is null) and out[c] (+)= column sums of dx. part: [bn_parts(rows, C), C] floats.
 void relu_bwd_colsum(const bf16* dy, const bf16* y, bf16* dx, float* part, float* out, int rows, int C, int accumulate, cudaStream_t st) {
   const int parts = bn_parts(rows, C), rpb = (rows + parts - 1) / parts;
-  relu_bwd_colsum_kernel<<<dim3(blocks_for(C, 64), parts), 256, 0, st>>>(dy, y, dx, part, rows, C, rpb);
-  colsum_f32_kernel<<<blocks_for(C, 32), 256, 0, st>>>(part, out, parts, C, accumulate);
+  launch_pdl(relu_bwd_colsum_kernel, dim3(dim3(blocks_for(C, 64), parts)), dim3(256), 0, st, dy, y, dx, part, rows, C, rpb);
+  launch_pdl(colsum_f32_kernel, dim3(blocks_for(C, 32)), dim3(256), 0, st, part, out, parts, C, accumulate);
 }
 void maxpool_fwd(const bf16* x, bf16* y, uint8_t* code, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st) {
-  maxpool_fwd_kernel<<<blocks_for((long long)N * Ho * Wo * (C / 8), 256), 256, 0, st>>>(x, y, code, N, H, W, C, k, stride, pad, Ho, Wo);
+  launch_pdl(maxpool_fwd_kernel, dim3(blocks_for((long long)N * Ho * Wo * (C / 8), 256)), dim3(256), 0, st, x, y, code, N, H, W, C, k, stride, pad, Ho, Wo);
 }
 void maxpool_bwd(const uint8_t* code, const bf16* dy, bf16* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
                  cudaStream_t st) {
   const int blocks = blocks_for((long long)N * H * W * (C / 8), 256);
-  if (k == 3 && stride == 2) maxpool_bwd_kernel<3, 2><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
-  else if (k == 2 && stride == 2) maxpool_bwd_kernel<2, 2><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
-  else maxpool_bwd_kernel<0, 0><<<blocks, 256, 0, st>>>(code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  if (k == 3 && stride == 2) launch_pdl(maxpool_bwd_kernel<3, 2>, dim3(blocks), dim3(256), 0, st, code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  else if (k == 2 && stride == 2) launch_pdl(maxpool_bwd_kernel<2, 2>, dim3(blocks), dim3(256), 0, st, code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
+  else launch_pdl(maxpool_bwd_kernel<0, 0>, dim3(blocks), dim3(256), 0, st, code, dy, dx, N, H, W, C, k, stride, pad, Ho, Wo);
 }
 void im2col(const bf16* x, bf16* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
   const long long total = (long long)N * Ho * Wo * KH * KW * (C / 8);
-  im2col_kernel<<<blocks_for(total, 256), 256, 0, st>>>(x, cols, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
+  launch_pdl(im2col_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, st, x, cols, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
 }
 void col2im(const bf16* dcols, bf16* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Ho, int Wo, cudaStream_t st) {
   const long long total = (long long)N * H * W * (C / 8);
-  col2im_kernel<<<blocks_for(total, 256), 256, 0, st>>>(dcols, dx, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
+  launch_pdl(col2im_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, st, dcols, dx, N, H, W, C, KH, KW, stride, pad, Ho, Wo);
 }
 void psgd_p(float* M, const float* err, const float* Q, float* P, int m, int n, int r, cudaStream_t st) {
-  psgd_p_kernel<<<blocks_for(m, 4), 128, 0, st>>>(M, err, Q, P, m, n, r);
+  launch_pdl(psgd_p_kernel, dim3(blocks_for(m, 4)), dim3(128), 0, st, M, err, Q, P, m, n, r);
 }
 void psgd_q(const float* M, const float* P, float* Qn, int m, int n, int r, cudaStream_t st) {
-  psgd_q_kernel<<<blocks_for(n, 32), 256, 0, st>>>(M, P, Qn, m, n, r);
+  launch_pdl(psgd_q_kernel, dim3(blocks_for(n, 32)), dim3(256), 0, st, M, P, Qn, m, n, r);
 }
 void psgd_d(float* M, float* err, const float* P, const float* Q, int m, int n, int r, cudaStream_t st) {
-  psgd_d_kernel<<<blocks_for((long long)m * n, 256), 256, 0, st>>>(M, err, P, Q, m, n, r);
+  launch_pdl(psgd_d_kernel, dim3(blocks_for((long long)m * n, 256)), dim3(256), 0, st, M, err, P, Q, m, n, r);
 }
 // tab: int64 [8 arrays] laid out by the caller as device pointers; phase 0 = P pass, 1 = orthogonalise, 2 = Q pass, 3 = decompress.
 void psgd_batched(int phase, float* grad, float* err, float* P, float* Q, const long long* off, const int* m, const int* n,
@@ -1695,14 +1744,14 @@ void psgd_batched(int phase, float* grad, float* err, float* P, float* Q, const 
                   const long long* elem_prefix, int nmat, int r, long long rows, long long blocks, long long elems, cudaStream_t st) {
   if (nmat <= 0) return;
   PsgdTable t{off, m, n, p_off, q_off, row_prefix, blk_prefix, elem_prefix, nmat};
-  if (phase == 0) psgd_p_batched_kernel<<<blocks_for(rows, 4), 128, 0, st>>>(grad, err, Q, P, t, r, rows);
-  else if (phase == 1) psgd_orth_batched_kernel<<<nmat, 256, 0, st>>>(P, t, r);
-  else if (phase == 2) psgd_q_batched_kernel<<<(unsigned)blocks, 256, 0, st>>>(grad, P, Q, t, r);
-  else psgd_d_batched_kernel<<<blocks_for(elems, 256), 256, 0, st>>>(grad, err, P, Q, t, r, elems);
+  if (phase == 0) launch_pdl(psgd_p_batched_kernel, dim3(blocks_for(rows, 4)), dim3(128), 0, st, grad, err, Q, P, t, r, rows);
+  else if (phase == 1) launch_pdl(psgd_orth_batched_kernel, dim3(nmat), dim3(256), 0, st, P, t, r);
+  else if (phase == 2) launch_pdl(psgd_q_batched_kernel, dim3((unsigned)blocks), dim3(256), 0, st, grad, P, Q, t, r);
+  else launch_pdl(psgd_d_batched_kernel, dim3(blocks_for(elems, 256)), dim3(256), 0, st, grad, err, P, Q, t, r, elems);
 }
 void cast_f32_bf16(const float* x, bf16* y, long long n, cudaStream_t st) {
-  cast_f32_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(x, y, n);
+  launch_pdl(cast_f32_bf16_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, st, x, y, n);
 }
-void increment(long long* c, cudaStream_t st) { increment_kernel<<<1, 1, 0, st>>>(c); }
+void increment(long long* c, cudaStream_t st) { launch_pdl(increment_kernel, dim3(1), dim3(1), 0, st, c); }
 
 }  // namespace adb200

@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "gemm_tcgen05.h"
+#include "pdl.cuh"
 #include "tcgen05_common.cuh"
 
 namespace adb200 {
@@ -69,6 +70,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_sync();       // everything above touched only this CTA's shared and tensor memory; global memory is read from here on
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -369,7 +371,7 @@ cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmP
   }
   const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch_lo * p.batch_hi;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  kern<<<grid, kThreads, C::SMEM, stream>>>(tmA, tmB, p);
+  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, tmA, tmB, p);
   return cudaGetLastError();
 }
 
