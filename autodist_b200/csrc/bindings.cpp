@@ -1,4 +1,5 @@
 // Python bindings of the sm_100a kernels: tensor-map construction, argument checks, launches on the current stream.
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
@@ -92,11 +93,22 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
   TORCH_CHECK(a.size(0) == b.size(0) && a.size(1) == b.size(1), "batch dimensions of A and B differ");
   TORCH_CHECK(c.size(0) == a.size(0) && c.size(1) == a.size(1) && c.size(2) == M && c.size(3) == N, "output shape mismatch");
   TORCH_CHECK(c.stride(3) == 1, "output inner stride must be 1");
-  if (bn <= 0) bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
-  TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "bn must be 64, 128 or 256");
+  // bn: tile width 64 / 128 / 256 of the one-CTA kernel, or 512 = the 256 x 256 tile of the two-CTA kernel; 0 picks one
+  // (two CTAs when both extents fill a pair's tile and AUTODIST_GEMM_PAIR is not 0)
+  const bool softmax_epi = epilogue == adb200::EPI_SOFTMAX || epilogue == adb200::EPI_SOFTMAX_GRAD;
+  if (bn <= 0) {
+    static const bool pair_default = [] { const char* e = std::getenv("AUTODIST_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+    bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+    // pairs pay off once their 256 x 256 tiles fill the SM pairs, or when a long contraction makes the shared-memory
+    // fill per FLOP (what the pair halves for B) the limit
+    const int64_t pair_tiles = (int64_t)((M + 255) / 256) * ((N + 255) / 256) * a.size(0) * a.size(1);
+    if (pair_default && bn == 256 && M >= 256 && !softmax_epi && (pair_tiles >= num_sms() / 2 || K >= 2048)) bn = 512;
+  }
+  TORCH_CHECK(bn == 64 || bn == 128 || bn == 256 || bn == 512, "bn must be 64, 128, 256 or 512 (two-CTA tile)");
+  const bool pair = bn == 512;
   CUtensorMap tmA = make_map(a, a_mn ? 64 : 128);
   adb200::TmapArray tmB;
-  tmB.m[0] = make_map(b, b_mn ? 64 : (int)bn);
+  tmB.m[0] = make_map(b, b_mn ? 64 : (pair ? 128 : (int)bn));
   for (int i = 1; i < 8; ++i) tmB.m[i] = tmB.m[0];
   adb200::GemmParams p{};
   p.b_shard_rows = 0;
@@ -151,7 +163,8 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
     }
   }
   p.error_flag = error_flag.data_ptr<int>();
-  cudaError_t e = adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
+  cudaError_t e = pair ? adb200::launch_gemm_pair(tmA, tmB.m[0], p, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream())
+                       : adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
 }
 

@@ -44,4 +44,9 @@ struct TmapArray {
 cudaError_t launch_gemm(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int bn, bool a_mn,
                         bool b_mn, int num_sms, cudaStream_t stream);
 
+// The same product on pairs of SMs (tcgen05.mma.cta_group::2, 256 x 256 tiles; gemm_tcgen05_2cta.cu). Maps as above
+// with boxes of 128 rows for a K-major operand. No fused softmax, no row-sharded B.
+cudaError_t launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, bool a_mn, bool b_mn, int num_sms,
+                             cudaStream_t stream);
+
 }  // namespace adb200

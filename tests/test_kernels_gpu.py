@@ -63,6 +63,48 @@ def test_gemm_tile_widths_fp32_out(E, err, bn):
     _check(c2, 2 * c, 2e-3)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K,batch", [(256, 256, 64, 1), (512, 768, 1024, 1), (304, 520, 200, 1), (1000, 264, 72, 1), (4096, 1024, 2048, 1),
+                                         (384, 512, 128, 3)])
+def test_gemm_on_sm_pairs(E, err, a_mn, b_mn, M, N, K, batch):
+    """The two-CTA kernel (tcgen05.mma.cta_group::2, 256 x 256 tiles, bn = 512): every operand layout, ragged extents
+    (rows and columns past the last full tile are zero-filled by TMA and masked in the epilogue), batches, fp32
+    accumulation into the output and the bias + GELU epilogue."""
+    torch.manual_seed(6)
+    a = _rand(batch, K, M) if a_mn else _rand(batch, M, K)
+    b = _rand(batch, K, N) if b_mn else _rand(batch, N, K)
+    A = a.float().transpose(1, 2) if a_mn else a.float()
+    B = b.float() if b_mn else b.float().transpose(1, 2)
+    ref = A @ B
+    c = torch.empty(batch, M, N, dtype=torch.bfloat16, device="cuda")
+    E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, 512)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(c, ref, 1e-2)
+    c32 = torch.ones(batch, M, N, dtype=torch.float32, device="cuda")
+    E.gemm(a, b, c32, a_mn, b_mn, 0, None, None, None, 0.5, 1.0, err, 512)
+    bias = torch.randn(N, device="cuda")
+    pre, act = torch.empty_like(c), torch.empty_like(c)
+    E.gemm(a, b, pre, a_mn, b_mn, 2, bias, act, None, 0.1, 0.0, err, 512)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    _check(c32, 1.0 + 0.5 * ref, 2e-3)
+    _check(pre, 0.1 * ref + bias, 1e-2)
+    _check(act, torch.nn.functional.gelu(pre.float(), approximate="tanh"), 1e-2)
+
+
+def test_gemm_picks_the_pair_kernel_for_large_products_and_matches_the_one_cta_kernel(E, err):
+    torch.manual_seed(7)
+    M, N, K = 2560, 2304, 512
+    a, b = _rand(M, K), _rand(N, K)
+    c0, c1 = (torch.empty(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    E.gemm(a, b, c0, False, False, 0, None, None, None, 1.0, 0.0, err, 0)        # chooser: 90 pair tiles >= 74 pairs
+    E.gemm(a, b, c1, False, False, 0, None, None, None, 1.0, 0.0, err, 256)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    assert torch.equal(c0, c1)          # same products in the same K order: the accumulators agree bit for bit
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 320, 192), (1024, 4096, 4096)])
 def test_gemm_mn_major(E, err, a_mn, b_mn, M, N, K):
