@@ -80,6 +80,43 @@ CUtensorMap make_map(const Tensor& v, int box_outer) {
   return m;
 }
 
+// 4-D map over an output view [b_hi, b_lo, rows, cols] (bf16 or fp32, inner stride 1) for the TMA-store epilogue: boxes of
+// 128 bytes of columns x 32 rows, 128-byte swizzle. Returns false when the view cannot be described (a base or a stride
+// that is not a multiple of 16 bytes): the caller then keeps the direct stores.
+bool make_store_map(const Tensor& v, CUtensorMap* out) {
+  const bool f32 = v.scalar_type() == at::kFloat;
+  const int64_t esz = f32 ? 4 : 2;
+  if (v.stride(3) != 1 || reinterpret_cast<uintptr_t>(v.data_ptr()) % 16 != 0) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)v.size(3), (cuuint64_t)v.size(2), (cuuint64_t)v.size(1), (cuuint64_t)v.size(0)};
+  cuuint64_t strides[3];
+  int64_t prev = v.size(3);
+  for (int i = 0; i < 3; ++i) {
+    const int d = 2 - i;
+    const int64_t s = v.size(d) > 1 ? v.stride(d) : prev;
+    if (s <= 0 || (s * esz) % 16 != 0) return false;
+    strides[i] = (cuuint64_t)(s * esz);
+    prev = s * v.size(d);
+  }
+  cuuint32_t box[4] = {(cuuint32_t)(128 / esz), 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, v.data_ptr(), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Tuning aid: when set (int64 CUDA tensor of at least 8 x SM-count words, zeroed by the caller), launches of the two-CTA
+// GEMM record nanosecond marks per CTA into it (see gemm_tcgen05_2cta.cu).
+long long* g_gemm_trace = nullptr;
+void gemm_set_trace(const optional<Tensor>& t) {
+  if (t.has_value()) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() && t->numel() >= 8LL * num_sms(), "int64 [SMs, 8] needed");
+    g_gemm_trace = reinterpret_cast<long long*>(t->data_ptr<int64_t>());
+  } else {
+    g_gemm_trace = nullptr;
+  }
+}
+
 // D = alpha * A.B^T (+ epilogue). a: [.., M, K] (K-major) or [.., K, M] (a_mn); b: [.., N, K] or [.., K, N] (b_mn);
 // c: [.., M, N] bf16 or fp32 view with unit inner stride.
 void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_mn, int64_t epilogue, const optional<Tensor>& bias,
@@ -112,6 +149,7 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
   for (int i = 1; i < 8; ++i) tmB.m[i] = tmB.m[0];
   adb200::GemmParams p{};
   p.b_shard_rows = 0;
+  p.trace = g_gemm_trace;
   p.M = M; p.N = N; p.K = K;
   p.batch_lo = a.size(1); p.batch_hi = a.size(0);
   p.C = c.data_ptr();
@@ -163,8 +201,20 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
     }
   }
   p.error_flag = error_flag.data_ptr<int>();
-  cudaError_t e = pair ? adb200::launch_gemm_pair(tmA, tmB.m[0], p, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream())
-                       : adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream());
+  // Output through shared memory and TMA (whole lines instead of 16-byte pieces of 32 rows per store instruction) for
+  // products large enough to care; AUTODIST_GEMM_TMA_STORE=0 keeps direct stores everywhere.
+  static const bool tma_store_default = [] { const char* e = std::getenv("AUTODIST_GEMM_TMA_STORE"); return e == nullptr || e[0] != '0'; }();
+  CUtensorMap tmC, tmC2;
+  p.tma_store = 0;
+  if (tma_store_default && !softmax_epi && bn >= 256 && (!p.c_is_fp32 || p.beta == 0.0f || p.beta == 1.0f) && make_store_map(c, &tmC)) {
+    p.tma_store = 1;
+    tmC2 = tmC;
+    if (epilogue == adb200::EPI_BIAS_GELU && !make_store_map(as4d(*c2), &tmC2)) p.tma_store = 0;
+  }
+  cudaError_t e = pair ? adb200::launch_gemm_pair(tmA, tmB.m[0], p, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream(),
+                                                  p.tma_store ? &tmC : nullptr, p.tma_store ? &tmC2 : nullptr)
+                       : adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream(),
+                                             p.tma_store ? &tmC : nullptr, p.tma_store ? &tmC2 : nullptr);
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
 }
 
@@ -651,6 +701,7 @@ void relaxed_pull(const Tensor& p32_ptrs, Tensor master, Tensor p16, const Tenso
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm_set_trace", &gemm_set_trace);
   m.def("gemm", &gemm);
   m.def("gemm_softmax", &gemm_softmax);
   m.def("gemm_gathered_b", &gemm_gathered_b);

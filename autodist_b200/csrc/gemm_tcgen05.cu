@@ -34,18 +34,21 @@ template <int BN> struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN;              // double-buffered fp32 accumulator
-  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int STAGING = (BN == 256) ? 4 * 2 * 4096 : 0;   // TMA-store staging (widest tile only): two 4 KB buffers per epilogue warp
+  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + STAGING + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmapArray tmBs, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmapArray tmBs, const __grid_constant__ CUtensorMap tmC,
+            const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + C::STAGES * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * (A_BYTES + C::B_BYTES));
+  uint8_t* staging = smem + C::STAGES * (A_BYTES + C::B_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
   uint64_t* tfull = bars + 2 * C::STAGES;
@@ -168,6 +171,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
     const int q = warp & 3;
     int as = 0; uint32_t aphase = 0; bool ok = true;
     const bool vec_ok = (p.ldc % 8 == 0);
+    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)q * 8192u, 0};
     for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
       const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
       const int tn = rem / tiles_m, tm = rem % tiles_m;
@@ -245,12 +249,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
           }
         }
       }
-      if (!handled) gemm_epilogue_row<BN>(p, t_row, row, n0, coff, vec_ok);
+      if (!handled) {
+        if (BN == 256 && p.tma_store) gemm_epilogue_row_tma<BN>(p, est, t_row, row, tm * BM + q * 32, n0, b_lo, b_hi, coff, vec_ok, lane);
+        else gemm_epilogue_row<BN>(p, t_row, row, n0, coff, vec_ok);
+      }
       __syncwarp();
       tc_fence_before();
       mbar_arrive(&tempty[as]);
       if (++as == 2) { as = 0; aphase ^= 1; }
     }
+    if (BN == 256 && p.tma_store && lane == 0) bulk_wait_all();       // this warp's output copies have landed
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (p.error_flag) atomicExch(p.error_flag, 3);
@@ -266,7 +274,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
 }
 
 template <int BN, bool A_MN, bool B_MN>
-cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int num_sms, cudaStream_t stream) {
+cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int num_sms, cudaStream_t stream,
+                       const CUtensorMap& tmC, const CUtensorMap& tmC2) {
   using C = Cfg<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -277,20 +286,24 @@ cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmP
   }
   const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch_lo * p.batch_hi;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, tmA, tmB, p);
+  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, tmA, tmB, tmC, tmC2, p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t launch_gemm(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int bn, bool a_mn, bool b_mn,
-                        int num_sms, cudaStream_t stream) {
+                        int num_sms, cudaStream_t stream, const CUtensorMap* tmC_, const CUtensorMap* tmC2_) {
+  if (p.tma_store && tmC_ == nullptr) return cudaErrorInvalidValue;
+  // unused maps still travel as kernel parameters: any valid descriptor will do
+  const CUtensorMap& tmC = tmC_ != nullptr ? *tmC_ : tmA;
+  const CUtensorMap& tmC2 = tmC2_ != nullptr ? *tmC2_ : tmC;
 #define ADB_DISPATCH(BN_)                                                                      \
   if (bn == BN_) {                                                                             \
-    if (!a_mn && !b_mn) return launch_one<BN_, false, false>(tmA, tmB, p, num_sms, stream);    \
-    if (!a_mn && b_mn) return launch_one<BN_, false, true>(tmA, tmB, p, num_sms, stream);      \
-    if (a_mn && !b_mn) return launch_one<BN_, true, false>(tmA, tmB, p, num_sms, stream);      \
-    return launch_one<BN_, true, true>(tmA, tmB, p, num_sms, stream);                          \
+    if (!a_mn && !b_mn) return launch_one<BN_, false, false>(tmA, tmB, p, num_sms, stream, tmC, tmC2);    \
+    if (!a_mn && b_mn) return launch_one<BN_, false, true>(tmA, tmB, p, num_sms, stream, tmC, tmC2);      \
+    if (a_mn && !b_mn) return launch_one<BN_, true, false>(tmA, tmB, p, num_sms, stream, tmC, tmC2);      \
+    return launch_one<BN_, true, true>(tmA, tmB, p, num_sms, stream, tmC, tmC2);                          \
   }
   ADB_DISPATCH(256)
   ADB_DISPATCH(128)

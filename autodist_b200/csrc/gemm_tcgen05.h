@@ -30,6 +30,8 @@ struct GemmParams {
   unsigned long long drop_seed;
   const long long* drop_step;  // device step counter mixed into the seed (null = none)
   int b_shard_rows;            // > 0: B is split by rows into shards of this many rows, shard s read through tmB.m[s]
+  int tma_store;               // 1: the output goes through shared memory and TMA (maps tmC / tmC2 of the launch are valid)
+  long long* trace;            // optional tuning aid of the two-CTA kernel: [grid, 8] nanosecond marks per CTA, or null
 };
 
 // B operand maps: one for an ordinary GEMM; one per owner rank when the rows of B (a weight matrix sharded along
@@ -41,12 +43,14 @@ struct TmapArray {
 // `bn` is the N extent of the tile (64, 128 or 256). The tensor maps must be 4-D bf16 maps with 128-byte swizzle:
 //   K-major operand : dims (K, rows, batch_lo, batch_hi), box (64, 128 for A / bn for B, 1, 1)
 //   MN-major operand: dims (rows, K, batch_lo, batch_hi), box (64, 64, 1, 1)
+// With p.tma_store, `tmC` (and `tmC2` for EPI_BIAS_GELU) map the output: same element type as C, box (128 bytes of columns,
+// 32 rows, 1, 1), 128-byte swizzle; fp32 outputs need beta 0 or 1. Otherwise both may be null.
 cudaError_t launch_gemm(const CUtensorMap& tmA, const TmapArray& tmB, const GemmParams& p, int bn, bool a_mn,
-                        bool b_mn, int num_sms, cudaStream_t stream);
+                        bool b_mn, int num_sms, cudaStream_t stream, const CUtensorMap* tmC = nullptr, const CUtensorMap* tmC2 = nullptr);
 
 // The same product on pairs of SMs (tcgen05.mma.cta_group::2, 256 x 256 tiles; gemm_tcgen05_2cta.cu). Maps as above
 // with boxes of 128 rows for a K-major operand. No fused softmax, no row-sharded B.
 cudaError_t launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, bool a_mn, bool b_mn, int num_sms,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const CUtensorMap* tmC = nullptr, const CUtensorMap* tmC2 = nullptr);
 
 }  // namespace adb200

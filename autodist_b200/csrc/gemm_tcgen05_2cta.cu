@@ -36,7 +36,8 @@ constexpr int BN2 = 256;                 // tile width; each CTA stages BN2 / 2 
 constexpr int B2_BYTES = (BN2 / 2) * BK * 2;
 constexpr int STAGES2 = 6;
 constexpr int TMEM_COLS2 = 2 * BN2;
-constexpr int SMEM2 = STAGES2 * (A_BYTES + B2_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int STAGING2 = 4 * 2 * 4096;   // TMA-store staging: two 4 KB buffers per epilogue warp
+constexpr int SMEM2 = STAGES2 * (A_BYTES + B2_BYTES) + STAGING2 + 1024 /*align*/ + 256 /*barriers*/;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -74,6 +75,11 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t da, uint64_t db,
 __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
+__device__ __forceinline__ long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return (long long)t;
+}
 __device__ __forceinline__ uint32_t make_idesc2(bool a_mn, bool b_mn) {
   uint32_t d = 0;
   d |= 1u << 4;                       // D format: f32
@@ -88,13 +94,15 @@ __device__ __forceinline__ uint32_t make_idesc2(bool a_mn, bool b_mn) {
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+             const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared memory starts at the same offset in both CTAs, so the aligned layouts coincide
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES2 * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * (A_BYTES + B2_BYTES));
+  uint8_t* staging = smem + STAGES2 * (A_BYTES + B2_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STAGING2);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES2;
   uint64_t* tfull = bars + 2 * STAGES2;
@@ -104,6 +112,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // trace (when given): 0 entry, 1 set-up done, 2 first stage full, 3 last MMA committed, 4 ns the MMA thread waited for
+  // full stages, 5 ns it waited for a free accumulator, 6 ns the first epilogue warp spent draining, 7 end
+  long long* trace = p.trace != nullptr ? p.trace + (long long)blockIdx.x * 8 : nullptr;
+  if (trace != nullptr && threadIdx.x == 0) trace[0] = now_ns();
   const uint32_t rank = cluster_ctarank();            // 0 = leader
   const bool leader = rank == 0;
 
@@ -124,6 +136,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_sync();       // everything above touched only shared and tensor memory; global memory is read from here on
+  if (trace != nullptr && threadIdx.x == 0) trace[1] = now_ns();
 
   const int tiles_m = (p.M + 255) / 256;
   const int tiles_n = (p.N + BN2 - 1) / BN2;
@@ -174,11 +187,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const uint32_t idesc = make_idesc2(A_MN, B_MN);
       int stage = 0; uint32_t phase = 0; int as = 0; uint32_t aphase = 0; bool ok = true;
       for (long long t = pair; t < total && ok; t += pairs) {
+        const long long w0 = trace != nullptr ? now_ns() : 0;
         if (!mbar_wait(&tempty[as], aphase ^ 1, abort_flag)) { ok = false; break; }
+        if (trace != nullptr) trace[5] += now_ns() - w0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN2);
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long w1 = trace != nullptr ? now_ns() : 0;
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (trace != nullptr) { const long long w2 = now_ns(); trace[4] += w2 - w1; if (trace[2] == 0) trace[2] = w2; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * B2_BYTES);
@@ -198,6 +215,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (!ok) break;
         umma2_commit(smem_u32(&tfull[as]));            // accumulator complete -> both CTAs' epilogues
         umma2_commit(map_to_cta(smem_u32(&tfull[as]), 1));
+        if (trace != nullptr) trace[3] = now_ns();
         if (++as == 2) { as = 0; aphase ^= 1; }
       }
       if (!ok) {
@@ -210,6 +228,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int q = warp & 3;
     int as = 0; uint32_t aphase = 0; bool ok = true;
     const bool vec_ok = (p.ldc % 8 == 0);
+    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)q * 8192u, 0};
     for (long long t = pair; t < total && ok; t += pairs) {
       const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
       const int tn = rem / tiles_m, tm = rem % tiles_m;
@@ -217,21 +236,26 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int row = tm * 256 + (int)rank * 128 + q * 32 + lane;
       const int n0 = tn * BN2;
       if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
+      const long long e0 = trace != nullptr ? now_ns() : 0;
       tc_fence_after();
       const long long coff = (long long)b_hi * p.strideC_hi + (long long)b_lo * p.strideC_lo + (long long)row * p.ldc;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN2);
-      gemm_epilogue_row<BN2>(p, t_row, row, n0, coff, vec_ok);
+      if (p.tma_store) gemm_epilogue_row_tma<BN2>(p, est, t_row, row, tm * 256 + (int)rank * 128 + q * 32, n0, b_lo, b_hi, coff, vec_ok, lane);
+      else gemm_epilogue_row<BN2>(p, t_row, row, n0, coff, vec_ok);
       __syncwarp();
       tc_fence_before();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[as]), 0));
+      if (trace != nullptr && threadIdx.x == 64) trace[6] += now_ns() - e0;
       if (++as == 2) { as = 0; aphase ^= 1; }
     }
+    if (p.tma_store && lane == 0) bulk_wait_all();       // this warp's output copies have landed
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (p.error_flag) atomicExch(p.error_flag, 43);
     }
   }
 
+  if (trace != nullptr && threadIdx.x == 0) trace[7] = now_ns();
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                                  // neither CTA leaves, or frees TMEM, while the other still works
@@ -242,7 +266,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 }
 
 template <bool A_MN, bool B_MN>
-cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int num_sms, cudaStream_t stream) {
+cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int num_sms, cudaStream_t stream,
+                        const CUtensorMap& tmC, const CUtensorMap& tmC2) {
   auto kern = gemm2_kernel<A_MN, B_MN>;
   static int max_pairs = 0;
   if (max_pairs == 0) {
@@ -276,7 +301,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr; cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmC2, p);
 }
 
 }  // namespace
@@ -284,12 +309,15 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
 // The pair kernel: `tmA` / `tmB` are the maps of launch_gemm with boxes of 128 rows for a K-major operand (64 x 64
 // for an MN-major one). No fused softmax and no row-sharded B here.
 cudaError_t launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, bool a_mn, bool b_mn, int num_sms,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const CUtensorMap* tmC_, const CUtensorMap* tmC2_) {
+  if (p.tma_store && tmC_ == nullptr) return cudaErrorInvalidValue;
+  const CUtensorMap& tmC = tmC_ != nullptr ? *tmC_ : tmA;
+  const CUtensorMap& tmC2 = tmC2_ != nullptr ? *tmC2_ : tmC;
   if (p.b_shard_rows > 0 || p.epilogue == EPI_SOFTMAX || p.epilogue == EPI_SOFTMAX_GRAD) return cudaErrorInvalidValue;
-  if (!a_mn && !b_mn) return launch_pair<false, false>(tmA, tmB, p, num_sms, stream);
-  if (!a_mn && b_mn) return launch_pair<false, true>(tmA, tmB, p, num_sms, stream);
-  if (a_mn && !b_mn) return launch_pair<true, false>(tmA, tmB, p, num_sms, stream);
-  return launch_pair<true, true>(tmA, tmB, p, num_sms, stream);
+  if (!a_mn && !b_mn) return launch_pair<false, false>(tmA, tmB, p, num_sms, stream, tmC, tmC2);
+  if (!a_mn && b_mn) return launch_pair<false, true>(tmA, tmB, p, num_sms, stream, tmC, tmC2);
+  if (a_mn && !b_mn) return launch_pair<true, false>(tmA, tmB, p, num_sms, stream, tmC, tmC2);
+  return launch_pair<true, true>(tmA, tmB, p, num_sms, stream, tmC, tmC2);
 }
 
 }  // namespace adb200
