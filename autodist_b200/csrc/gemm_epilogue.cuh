@@ -62,8 +62,9 @@ __device__ __forceinline__ void gemm_epilogue_math16(const GemmParams& p, float*
 struct EpiStage {
   const CUtensorMap* tmC;      // output map, box (128 bytes of columns, 32 rows, 1, 1), 128-byte swizzle
   const CUtensorMap* tmC2;     // second output of EPI_BIAS_GELU
-  uint32_t smem;               // shared address of this warp's two 4 KB staging buffers (1024-byte aligned)
+  uint32_t smem;               // shared address of this warp's 4 KB staging buffers (1024-byte aligned)
   int units;                   // copies issued so far by this warp (picks the buffer)
+  int bufs;                    // 2: staging of one box overlaps the copy of the one before; 1: they alternate
 };
 
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
@@ -86,23 +87,25 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 }
 
 // box_row: first output row of this warp's 32 rows; lane = row inside the box. Other arguments as gemm_epilogue_row.
-template <int BN>
+// BNW: columns this warp drains (the tile's width, or half of it when two warps share a TMEM lane quarter).
+template <int BNW>
 __device__ __forceinline__ void gemm_epilogue_row_tma(const GemmParams& p, EpiStage& st, uint32_t t_row, int row, int box_row, int n0, int b_lo,
                                                       int b_hi, long long coff, bool vec_ok, int lane) {
   const bool f32 = p.c_is_fp32 != 0;
   const int gcols = f32 ? 32 : 64;                   // columns in one 128-byte staging row
-  const bool two = p.epilogue == EPI_BIAS_GELU;      // two outputs: both buffers are filled for one group
+  const bool two = p.epilogue == EPI_BIAS_GELU;      // two outputs (bf16): the pre-activation, then its GELU
   const uint32_t swz = (uint32_t)(lane & 7);
 #pragma unroll 1
-  for (int g = 0; g * gcols < BN; ++g) {
+  for (int g = 0; g * gcols < BNW; ++g) {
     const int gcol0 = n0 + g * gcols;
     if (gcol0 >= p.N) break;                          // uniform over the CTA
-    if (lane == 0) {                                  // the buffer(s) about to be written are no longer being read
-      if (two) bulk_wait_read<0>(); else bulk_wait_read<1>();
+    if (lane == 0) {                                  // the buffer about to be written is no longer being read
+      if (st.bufs < 2) bulk_wait_read<0>(); else bulk_wait_read<1>();
     }
     __syncwarp();
-    const uint32_t buf = st.smem + (uint32_t)(st.units & 1) * 4096u + (uint32_t)lane * 128u;
-    const uint32_t buf2 = st.smem + (uint32_t)((st.units + 1) & 1) * 4096u + (uint32_t)lane * 128u;
+    const uint32_t base = st.smem + (st.bufs < 2 ? 0u : (uint32_t)(st.units & 1)) * 4096u;
+    const uint32_t buf = base + (uint32_t)lane * 128u;
+    uint32_t act[32];                                 // packed GELU values of the group (two outputs only)
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) {
       if (f32 && cc >= 2) break;
@@ -124,24 +127,37 @@ __device__ __forceinline__ void gemm_epilogue_row_tma(const GemmParams& p, EpiSt
                        pack_bf16x2(v[8 * h + 4], v[8 * h + 5]), pack_bf16x2(v[8 * h + 6], v[8 * h + 7]));
         if (two) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-            st_shared_v4(buf2 + (((uint32_t)(cc * 2 + h) ^ swz) << 4), pack_bf16x2(v[8 * h], v[8 * h + 1]), pack_bf16x2(v[8 * h + 2], v[8 * h + 3]),
-                         pack_bf16x2(v[8 * h + 4], v[8 * h + 5]), pack_bf16x2(v[8 * h + 6], v[8 * h + 7]));
+          for (int j = 0; j < 8; ++j) act[cc * 8 + j] = pack_bf16x2(gelu_tanh(v[2 * j]), gelu_tanh(v[2 * j + 1]));
         }
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the staged rows are visible to the TMA unit
     __syncwarp();
     if (lane == 0) {
-      const uint32_t base = st.smem + (uint32_t)(st.units & 1) * 4096u;
       if (f32 && p.beta != 0.0f) tma_reduce_add_4d(st.tmC, base, gcol0, box_row, b_lo, b_hi);
       else tma_store_4d(st.tmC, base, gcol0, box_row, b_lo, b_hi);
-      if (two) tma_store_4d(st.tmC2, st.smem + (uint32_t)((st.units + 1) & 1) * 4096u, gcol0, box_row, b_lo, b_hi);
       bulk_commit();
     }
-    st.units += two ? 2 : 1;
+    st.units += 1;
+    if (two) {
+      // second output from the values kept in registers, through the other buffer (or the same one once it has been read)
+      if (lane == 0) {
+        if (st.bufs < 2) bulk_wait_read<0>(); else bulk_wait_read<1>();
+      }
+      __syncwarp();
+      const uint32_t base2 = st.smem + (st.bufs < 2 ? 0u : (uint32_t)(st.units & 1)) * 4096u;
+      const uint32_t buf2 = base2 + (uint32_t)lane * 128u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        st_shared_v4(buf2 + (((uint32_t)j ^ swz) << 4), act[4 * j], act[4 * j + 1], act[4 * j + 2], act[4 * j + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_4d(st.tmC2, base2, gcol0, box_row, b_lo, b_hi);
+        bulk_commit();
+      }
+      st.units += 1;
+    }
   }
 }
 

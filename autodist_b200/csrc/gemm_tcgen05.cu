@@ -32,14 +32,21 @@ using namespace tc;
 
 template <int BN> struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (BN == 256) ? 3 : (BN == 128 ? 6 : 8);
+  // Epilogue warps: four cover the TMEM lane quarters; the widest tile has eight, two per quarter with half of the
+  // columns each, because 128 threads cannot apply a bias or an activation to 32768 outputs in the time of one tile.
+  static constexpr int EPI_WARPS = (BN == 256) ? 8 : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int CW = BN / (EPI_WARPS / 4);          // columns per epilogue warp
   static constexpr int TMEM_COLS = 2 * BN;              // double-buffered fp32 accumulator
-  static constexpr int STAGING = (BN == 256) ? 4 * 2 * 4096 : 0;   // TMA-store staging (widest tile only): two 4 KB buffers per epilogue warp
+  // TMA-store staging (widest tile only): one 4 KB buffer per epilogue warp. The whole CTA stays near 208 KB so that the
+  // blocks of a small kernel launched behind it (programmatic dependent launch) still fit beside it on the SM.
+  static constexpr int STAGING = (BN == 256) ? EPI_WARPS * 4096 : 0;
   static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + STAGING + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmapArray tmBs, const __grid_constant__ CUtensorMap tmC,
             const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
   using C = Cfg<BN>;
@@ -61,7 +68,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 128); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 32 * C::EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -169,9 +176,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 -> TMEM lane quarter warp % 4)
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;                  // 0, or 1 for the second warp of a lane quarter
     int as = 0; uint32_t aphase = 0; bool ok = true;
     const bool vec_ok = (p.ldc % 8 == 0);
-    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)q * 8192u, 0};
+    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)(warp - 2) * 4096u, 0, 1};
     for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
       const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
       const int tn = rem / tiles_m, tm = rem % tiles_m;
@@ -250,8 +258,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ Tma
         }
       }
       if (!handled) {
-        if (BN == 256 && p.tma_store) gemm_epilogue_row_tma<BN>(p, est, t_row, row, tm * BM + q * 32, n0, b_lo, b_hi, coff, vec_ok, lane);
-        else gemm_epilogue_row<BN>(p, t_row, row, n0, coff, vec_ok);
+        const uint32_t t_w = t_row + (uint32_t)(half * C::CW);
+        const int n_w = n0 + half * C::CW;
+        if (BN == 256 && p.tma_store) gemm_epilogue_row_tma<C::CW>(p, est, t_w, row, tm * BM + q * 32, n_w, b_lo, b_hi, coff, vec_ok, lane);
+        else gemm_epilogue_row<C::CW>(p, t_w, row, n_w, coff, vec_ok);
       }
       __syncwarp();
       tc_fence_before();
@@ -286,7 +296,7 @@ cudaError_t launch_one(const CUtensorMap& tmA, const TmapArray& tmB, const GemmP
   }
   const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch_lo * p.batch_hi;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, tmA, tmB, tmC, tmC2, p);
+  launch_pdl(kern, dim3(grid), dim3(C::THREADS), C::SMEM, stream, tmA, tmB, tmC, tmC2, p);
   return cudaGetLastError();
 }
 

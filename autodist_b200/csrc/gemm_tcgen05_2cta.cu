@@ -12,7 +12,7 @@
 //   empty[s]   one per CTA: the leader's MMA thread commits to both (two tcgen05.commit, the second to the peer's
 //              address), releasing the stage in each CTA for that CTA's producer.
 //   tfull[a]   one per CTA, committed to in the same way when an accumulator is complete.
-//   tempty[a]  leader only: the four epilogue warps of both CTAs arrive on it (remote mbarrier.arrive for the peer).
+//   tempty[a]  leader only: the eight epilogue warps of both CTAs arrive on it (remote mbarrier.arrive for the peer).
 // TMEM is allocated and freed by warp 1 of both CTAs with the cta_group::2 forms; a cluster barrier after the barrier
 // initialisation and another before the deallocation keep either CTA from touching the other too early or leaving
 // while the other still reads its shared memory. Every mbarrier wait is bounded as in the one-CTA kernel; both CTAs
@@ -34,9 +34,11 @@ using namespace tc;
 
 constexpr int BN2 = 256;                 // tile width; each CTA stages BN2 / 2 rows of B
 constexpr int B2_BYTES = (BN2 / 2) * BK * 2;
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 5;              // 5 x 32 KB + 32 KB of output staging: the CTA stays at 193 KB (room for a dependent kernel's blocks)
 constexpr int TMEM_COLS2 = 2 * BN2;
-constexpr int STAGING2 = 4 * 2 * 4096;   // TMA-store staging: two 4 KB buffers per epilogue warp
+constexpr int EPI_WARPS2 = 8;            // two per TMEM lane quarter, half of the tile's columns each
+constexpr int kThreads2 = 64 + 32 * EPI_WARPS2;
+constexpr int STAGING2 = EPI_WARPS2 * 4096;   // TMA-store staging: one 4 KB buffer per epilogue warp
 constexpr int SMEM2 = STAGES2 * (A_BYTES + B2_BYTES) + STAGING2 + 1024 /*align*/ + 256 /*barriers*/;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -93,7 +95,7 @@ __device__ __forceinline__ uint32_t make_idesc2(bool a_mn, bool b_mn) {
 }
 
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads2, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
              const __grid_constant__ CUtensorMap tmC2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -121,7 +123,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 8); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * EPI_WARPS2); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -226,9 +228,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 -> TMEM lane quarter warp % 4)
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;                  // which half of the tile's columns this warp drains
     int as = 0; uint32_t aphase = 0; bool ok = true;
     const bool vec_ok = (p.ldc % 8 == 0);
-    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)q * 8192u, 0};
+    EpiStage est{&tmC, &tmC2, smem_u32(staging) + (uint32_t)(warp - 2) * 4096u, 0, 1};
     for (long long t = pair; t < total && ok; t += pairs) {
       const int b = (int)(t / per_batch), rem = (int)(t % per_batch);
       const int tn = rem / tiles_m, tm = rem % tiles_m;
@@ -240,8 +243,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       tc_fence_after();
       const long long coff = (long long)b_hi * p.strideC_hi + (long long)b_lo * p.strideC_lo + (long long)row * p.ldc;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN2);
-      if (p.tma_store) gemm_epilogue_row_tma<BN2>(p, est, t_row, row, tm * 256 + (int)rank * 128 + q * 32, n0, b_lo, b_hi, coff, vec_ok, lane);
-      else gemm_epilogue_row<BN2>(p, t_row, row, n0, coff, vec_ok);
+      const uint32_t t_w = t_row + (uint32_t)(half * (BN2 / 2));
+      const int n_w = n0 + half * (BN2 / 2);
+      if (p.tma_store) gemm_epilogue_row_tma<BN2 / 2>(p, est, t_w, row, tm * 256 + (int)rank * 128 + q * 32, n_w, b_lo, b_hi, coff, vec_ok, lane);
+      else gemm_epilogue_row<BN2 / 2>(p, t_w, row, n_w, coff, vec_ok);
       __syncwarp();
       tc_fence_before();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[as]), 0));
@@ -276,7 +281,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
     // how many pairs the GPU holds at once: SM pairs of one cluster sit in one GPC, so it can be fewer than SMs / 2
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3(num_sms & ~1);
-    q.blockDim = dim3(kThreads);
+    q.blockDim = dim3(kThreads2);
     q.dynamicSmemBytes = SMEM2;
     cudaLaunchAttribute a[1];
     a[0].id = cudaLaunchAttributeClusterDimension;
@@ -292,7 +297,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
   if (pairs <= 0) return cudaSuccess;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreads2);
   cfg.dynamicSmemBytes = SMEM2;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
