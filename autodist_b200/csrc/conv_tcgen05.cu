@@ -31,6 +31,11 @@ template <int BN, int MODE> struct ConvCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN;
+  // Eight epilogue warps: two per TMEM lane quarter, half of the tile's columns each. Layers with a short contraction
+  // (1 x 1 convolutions) spend longer draining a tile than multiplying it, and four warps could not keep up.
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int CHUNKS = BN / 16 / (EPI_WARPS / 4);      // 16-column chunks per epilogue warp
   static constexpr int STAT_BYTES = (MODE == CONV_FPROP) ? 2 * kMaxStatChannels * 4 : 0;
   static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/ + STAT_BYTES;
 };
@@ -93,7 +98,7 @@ __device__ __forceinline__ float warp_column_sums16(float* v, int lane) {
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(ConvCfg<BN, MODE>::THREADS, 1)
 conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvParams p) {
   using C = ConvCfg<BN, MODE>;
   constexpr bool A_MN = MODE == CONV_WGRAD;
@@ -117,13 +122,13 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 128); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 32 * C::EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (MODE == CONV_FPROP) {
-    if (do_stats) for (int i = threadIdx.x; i < 2 * p.Nc; i += kThreads) s_stat[i] = 0.f;
+    if (do_stats) for (int i = threadIdx.x; i < 2 * p.Nc; i += C::THREADS) s_stat[i] = 0.f;
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
@@ -266,6 +271,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 -> TMEM lane quarter warp % 4)
     const int q = warp & 3;
+    const int c_lo = ((warp - 2) >> 2) * C::CHUNKS;      // first 16-column chunk of this warp's share of the tile
     int as = 0; uint32_t aphase = 0; bool ok = true;
     const int r = q * 32 + lane;
     for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -291,23 +297,24 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
           // The gradient another consumer of the same tensor produced (a residual fork) is added to this tile. Its whole
           // row segment is requested before the wait for the accumulator, so the loads overlap the tile's MMAs, and
           // the chunk loop below is unrolled so that the prefetched vectors stay in registers.
-          uint4 pre[BN / 8];
-          const __nv_bfloat16* src = p.addend + off + tc_.c0;
+          uint4 pre[2 * C::CHUNKS];
+          const int cw0 = tc_.c0 + c_lo * 16;
+          const __nv_bfloat16* src = p.addend + off + cw0;
 #pragma unroll
-          for (int h = 0; h < BN / 8; ++h) {
+          for (int h = 0; h < 2 * C::CHUNKS; ++h) {
             pre[h] = make_uint4(0, 0, 0, 0);
-            if (valid && tc_.c0 + h * 8 < p.Nc) pre[h] = *reinterpret_cast<const uint4*>(src + h * 8);
+            if (valid && cw0 + h * 8 < p.Nc) pre[h] = *reinterpret_cast<const uint4*>(src + h * 8);
           }
           if (!mbar_wait(&tfull[as], aphase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
 #pragma unroll
-          for (int c = 0; c < BN / 16; ++c) {
-            const int col0 = tc_.c0 + c * 16;
-            if (col0 < p.Nc) {                     // uniform over the CTA
+          for (int c = 0; c < C::CHUNKS; ++c) {
+            const int col0 = cw0 + c * 16;
+            if (col0 < p.Nc) {                     // uniform over the warp
               float v[16], a[16];
               __syncwarp();
-              tmem_ld16(t_row + c * 16, v);
+              tmem_ld16(t_row + (c_lo + c) * 16, v);
               unpack8_bf16(pre[2 * c], a);
               unpack8_bf16(pre[2 * c + 1], a + 8);
 #pragma unroll
@@ -331,9 +338,9 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
+      for (int c = c_lo; c < c_lo + C::CHUNKS; ++c) {
         const int col0 = tc_.c0 + c * 16;
-        if (col0 >= p.Nc) break;                 // uniform over the CTA
+        if (col0 >= p.Nc) break;                 // uniform over the warp
         float v[16];
         __syncwarp();
         tmem_ld16(t_row + c * 16, v);
@@ -421,7 +428,7 @@ conv_kernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvP
   }
   if (MODE == CONV_FPROP) {
     if (do_stats) {
-      for (int i = threadIdx.x; i < 2 * p.Nc; i += kThreads) {
+      for (int i = threadIdx.x; i < 2 * p.Nc; i += C::THREADS) {
         const float x = s_stat[i];
         if (x != 0.f) atomicAdd(p.stats + i, x);
       }
@@ -445,7 +452,7 @@ cudaError_t launch_one(const ConvMaps& maps, const ConvParams& p, int num_sms, c
   else tiles = (long long)((p.Mc + BM - 1) / BM) * c_tiles * p.ntaps * p.ksplit;
   if (tiles <= 0) return cudaSuccess;
   const int grid = (int)(tiles < num_sms ? tiles : num_sms);
-  launch_pdl(kern, dim3(grid), dim3(kThreads), C::SMEM, stream, maps, p);
+  launch_pdl(kern, dim3(grid), dim3(C::THREADS), C::SMEM, stream, maps, p);
   return cudaGetLastError();
 }
 
