@@ -74,6 +74,8 @@ class Remapper:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._last_chunk = {}
+        self._prefetched = {}          # id(fed value) -> (value, placeholder name, device tensor, copy event, batch chunk)
+        self._copy_stream = None
 
     # ------------------------------------------------------------------ feeds
     @property
@@ -95,27 +97,61 @@ class Remapper:
             return t.to(self._device, non_blocking=True)
         return t.to(self._device)
 
+    def _remap_one(self, key, value):
+        """One fed value -> (placeholder name, this replica's slice on the device in the placeholder's dtype)."""
+        info = self._item.placeholder_of(key)
+        if not isinstance(value, (torch.Tensor, np.ndarray)):
+            value = np.asarray(value)
+        if isinstance(value, np.ndarray) and value.dtype == np.float64 and info.dtype == torch.float32:
+            value = value.astype(np.float32)
+        dim = info.batch_dim
+        if dim is not None and self._num_local > 1:
+            lo, hi = _chunk_bounds(value.shape[dim], self._num_local, self._local_index)
+            index = [slice(None)] * value.ndim
+            index[dim] = slice(lo, hi)
+            value = value[tuple(index)]
+        if dim is not None:
+            self._last_chunk[info.name] = value.shape[dim]
+        t = self._to_device(info.name, value)
+        if t.dtype != info.dtype and t.is_floating_point() and info.dtype.is_floating_point:
+            t = t.to(info.dtype)
+        return info.name, t
+
     def remap_feed(self, feed_dict):
         feeds = {}
         for key, value in (feed_dict or {}).items():
-            info = self._item.placeholder_of(key)
-            if not isinstance(value, (torch.Tensor, np.ndarray)):
-                value = np.asarray(value)
-            if isinstance(value, np.ndarray) and value.dtype == np.float64 and info.dtype == torch.float32:
-                value = value.astype(np.float32)
-            dim = info.batch_dim
-            if dim is not None and self._num_local > 1:
-                lo, hi = _chunk_bounds(value.shape[dim], self._num_local, self._local_index)
-                index = [slice(None)] * value.ndim
-                index[dim] = slice(lo, hi)
-                value = value[tuple(index)]
-            if dim is not None:
-                self._last_chunk[info.name] = value.shape[dim]
-            t = self._to_device(info.name, value)
-            if t.dtype != info.dtype and t.is_floating_point() and info.dtype.is_floating_point:
-                t = t.to(info.dtype)
-            feeds[info.name] = t
+            staged = self._prefetched.pop(id(value), None)
+            if staged is not None and staged[0] is value:
+                # uploaded by `prefetch` while the previous step ran: the step only waits for that copy
+                name, t, ev, chunk = staged[1], staged[2], staged[3], staged[4]
+                torch.cuda.current_stream(self._device).wait_event(ev)
+                t.record_stream(torch.cuda.current_stream(self._device))
+                if chunk is not None:
+                    self._last_chunk[name] = chunk
+                feeds[name] = t
+                continue
+            name, t = self._remap_one(key, value)
+            feeds[name] = t
+        self._prefetched.clear()
         return feeds
+
+    def prefetch(self, feed_dict):
+        """Starts the upload of a later step's feed on a copy stream of its own, so that it overlaps the step that is
+        running; ``remap_feed`` recognises the same value objects when they are fed and skips their copy. Values that
+        are not fed next are simply dropped."""
+        self._prefetched.clear()
+        if self._device.type != "cuda" or not feed_dict:
+            return
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self._device)
+        current = dict(self._last_chunk)           # the running step's fetches are still cut with its own batch sizes
+        with torch.cuda.stream(self._copy_stream):
+            for key, value in feed_dict.items():
+                name, t = self._remap_one(key, value)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_stream)
+                self._prefetched[id(value)] = (value, name, t, ev, self._last_chunk.get(name))
+        self._last_chunk = current
 
     # ------------------------------------------------------------------ fetches
     def flatten_fetches(self, fetches):

@@ -196,7 +196,10 @@ class WrappedSession:
     def rank(self):
         return self._engine.rank
 
-    def run(self, fetches, feed_dict=None, options=None, run_metadata=None):
+    def run(self, fetches, feed_dict=None, options=None, run_metadata=None, prefetch=None):
+        """Runs one step (reference: ``autodist/runner.py`` ``WrappedSession.run``). ``prefetch``, an extension: the feed
+        of the next step; its host-to-device copies start as soon as this step is launched and overlap it, and the next
+        ``run`` that is fed the same value objects does not copy them again."""
         if self._closed:
             raise RuntimeError("session is closed")
         if not self._is_built():
@@ -215,7 +218,7 @@ class WrappedSession:
                 self._watchdog.arm(self._engine.global_step)
             try:
                 with nvtx.annotate(f"step {self._engine.global_step}"):
-                    result = self._run(fetches, feed_dict)
+                    result = self._run(fetches, feed_dict, prefetch)
             finally:
                 if self._watchdog is not None:
                     self._watchdog.disarm()
@@ -233,7 +236,7 @@ class WrappedSession:
                     run_metadata.step_stats = prof.key_averages()
         return result
 
-    def _run(self, fetches, feed_dict):
+    def _run(self, fetches, feed_dict, prefetch=None):
         rm, eng = self._remapper, self._engine
         single = not isinstance(fetches, (list, tuple, dict))
         leaves, rebuild = rm.flatten_fetches([fetches] if single else fetches)
@@ -251,6 +254,8 @@ class WrappedSession:
             values = eng.forward(nodes, feeds, grad=False)
         else:
             values = []
+        if prefetch is not None:
+            rm.prefetch(prefetch)            # the step is launched; the next feed's copies run beside it
         out = [None] * len(leaves)
         for i, v in zip(tensor_idx, values):
             out[i] = rm.remap_fetch(v)

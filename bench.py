@@ -216,7 +216,9 @@ def run_ours(model_name, args, n_gpus, world, rank):
             sess.run(train_op, feed(dev_batches, i))
 
         def step_host(i):
-            return sess.run([loss, train_op], feed(host_batches, i))[0]
+            # every step uploads one batch from pinned host memory and reads the loss back; the upload of batch i + 1 is
+            # started as soon as step i is launched (the session's `prefetch` argument), so it overlaps the step
+            return sess.run([loss, train_op], feed(host_batches, i), prefetch=feed(host_batches, i + 1))[0]
 
         # this extension's launches inside the device-timed region: eager launches are counted directly, a replayed CUDA graph
         # by the launches of its capture
