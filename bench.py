@@ -73,10 +73,10 @@ class ClockSampler(threading.Thread):
 def reference_arm(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return 0                      # one line per job, from rank 0
-    print(json.dumps({
+    _emit({
         "impl": "reference",
         "unavailable": "petuum/autodist needs TensorFlow 1.15-2.2 (CUDA 10, no sm_100 code) and protoc at install time; "
-                       "neither is present offline: the offline pip install of the reference stops in its setup.py generate_proto step"}))
+                       "neither is present offline: the offline pip install of the reference stops in its setup.py generate_proto step"})
     return 0
 
 
@@ -386,6 +386,29 @@ def run_library(model_name, args, n_gpus, world, rank):
     }
 
 
+_RESULT_FD = None
+
+
+def _own_stdout():
+    """The result line must be the only thing on stdout, but libraries write there too (NCCL prints its version banner
+    when its first communicator comes up): point file descriptor 1 at stderr for the rest of the process and keep the
+    original for `_emit`."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(record):
+    line = (json.dumps(record) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, line)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -407,6 +430,7 @@ def main():
                     help="also time every gradient flight of the last step with CUDA events (the step then runs as eager launches, "
                          "not as a CUDA graph) and write the table to PATH; implies --only")
     args = ap.parse_args()
+    _own_stdout()
     if args.impl == "reference":
         return reference_arm(args)
     if args.comm:
@@ -426,7 +450,7 @@ def main():
     if args.impl == "library":
         out = run_library(args.model, args, n_gpus, world, rank)
         if rank == 0:
-            print(json.dumps(out))
+            _emit(out)
         return 0
 
     out = run_ours(args.model, args, n_gpus, world, rank)
@@ -457,7 +481,7 @@ def main():
             out["resnet101"]["vs_library"] = {"value": round(out["resnet101"]["value"] / lib["resnet101"]["value"], 3),
                                               "e2e": round(out["resnet101"]["e2e"]["value"] / lib["resnet101"]["e2e_value"], 3)}
     if rank == 0:
-        print(json.dumps(out))
+        _emit(out)
     return 0
 
 
