@@ -154,15 +154,101 @@ def _conv_rows(E, dev, flush, peaks, iters, only=""):
     return rows
 
 
+def _layer_rows(E, dev, iters, trace):
+    """The twelve GEMMs of one BERT-large encoder layer (4096 tokens, hidden 1024, FFN 4096) with the epilogues the model
+    uses, each launched ``iters`` times back to back with warm caches (no L2 flush: the training step runs them that way);
+    the kernel is the one the binding picks (``bn = 0``). ``trace``: also print the phase marks of the two-CTA kernel for the
+    FFN1 product (nanoseconds per CTA, median / maximum over the CTAs)."""
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    T, H, F = 4096, 1024, 4096
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)
+    x, wqkv, wo, w1, w2 = bf(T, H), bf(3 * H, H), bf(H, H), bf(F, H), bf(H, F)
+    qkv, att, o = torch.empty(T, 3 * H, dtype=torch.bfloat16, device=dev), bf(T, H), torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    u = torch.empty(T, F, dtype=torch.bfloat16, device=dev)
+    g, y = torch.empty_like(u), torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    bq, bo, b1, b2 = (torch.randn(n, device=dev) for n in (3 * H, H, F, H))
+    dy, dg, dx = bf(T, H), torch.empty(T, F, dtype=torch.bfloat16, device=dev), torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    gw1, gw2, gwo, gwq = (torch.zeros(*s, device=dev) for s in ((F, H), (H, F), (H, H), (3 * H, H)))
+    datt, dqkv = torch.empty(T, H, dtype=torch.bfloat16, device=dev), bf(T, 3 * H)
+
+    def G(a, b, c, a_mn=False, b_mn=False, epi=0, bias=None, c2=None, aux=None, beta=0.0):
+        E.gemm(a, b, c, a_mn, b_mn, epi, bias, c2, aux, 1.0, beta, err, 0)
+
+    products = [("QKV forward (bias)", lambda: G(x, wqkv, qkv, epi=1, bias=bq)),
+                ("attention output forward (bias)", lambda: G(att, wo, o, epi=1, bias=bo)),
+                ("FFN1 forward (bias + GELU, two outputs)", lambda: G(x, w1, u, epi=2, bias=b1, c2=g)),
+                ("FFN2 forward (bias)", lambda: G(g, w2, y, epi=1, bias=b2)),
+                ("FFN2 dX (x GELU')", lambda: G(dy, w2, dg, b_mn=True, epi=3, aux=u)),
+                ("FFN2 dW (fp32 +=)", lambda: G(dy, g, gw2, a_mn=True, b_mn=True, beta=1.0)),
+                ("FFN1 dX", lambda: G(dg, w1, dx, b_mn=True)),
+                ("FFN1 dW (fp32 +=)", lambda: G(dg, x, gw1, a_mn=True, b_mn=True, beta=1.0)),
+                ("attention output dX", lambda: G(dy, wo, datt, b_mn=True)),
+                ("attention output dW (fp32 +=)", lambda: G(dy, att, gwo, a_mn=True, b_mn=True, beta=1.0)),
+                ("QKV dX (+ residual gradient)", lambda: G(dqkv, wqkv, dx, b_mn=True, epi=4, aux=dx)),
+                ("QKV dW (fp32 +=)", lambda: G(dqkv, x, gwq, a_mn=True, b_mn=True, beta=1.0))]
+
+    def hot(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters * 1e3
+
+    rows, total = [], 0.0
+    for name, fn in products:
+        us = hot(fn)
+        total += us
+        rows.append({"product": name, "us": round(us, 1)})
+    rows.append({"product": "sum of the twelve", "us": round(total, 1),
+                 "pair_kernel": os.environ.get("AUTODIST_GEMM_PAIR", "1") != "0", "tma_store": os.environ.get("AUTODIST_GEMM_TMA_STORE", "1") != "0"})
+    lib = [("cuBLAS addmm QKV forward", lambda: torch.addmm(bq.to(torch.bfloat16), x, wqkv.t(), out=qkv)),
+           ("cuBLAS addmm FFN1 forward (bias only)", lambda: torch.addmm(b1.to(torch.bfloat16), x, w1.t(), out=u)),
+           ("cuBLAS addmm FFN2 forward", lambda: torch.addmm(b2.to(torch.bfloat16), g, w2.t(), out=y))]
+    for name, fn in lib:
+        rows.append({"product": name, "us": round(hot(fn), 1)})
+    if trace:
+        import statistics
+        a, b, c = bf(T, H), bf(F, H), torch.empty(T, F, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            E.gemm(a, b, c, False, False, 0, None, None, None, 1.0, 0.0, err, 512)
+        marks = torch.zeros(torch.cuda.get_device_properties(0).multi_processor_count, 8, dtype=torch.int64, device=dev)
+        torch.cuda.synchronize()
+        E.gemm_set_trace(marks)
+        E.gemm(a, b, c, False, False, 0, None, None, None, 1.0, 0.0, err, 512)
+        torch.cuda.synchronize()
+        E.gemm_set_trace(None)
+        t = marks.cpu()
+        t = t[t[:, 0] > 0]
+        t0 = int(t[:, 0].min())
+        lead = t[0::2]
+        med = lambda xs: int(statistics.median(xs))
+        rows.append({"trace": "two-CTA kernel 4096x4096x1024, ns", "ctas": int(t.shape[0]),
+                     "set_up_done_median": med([int(v) - t0 for v in lead[:, 1]]),
+                     "first_stage_full_median": med([int(v) - t0 for v in lead[:, 2]]),
+                     "last_mma_committed_median_max": [med([int(v) - t0 for v in lead[:, 3]]), max(int(v) - t0 for v in lead[:, 3])],
+                     "mma_thread_waited_for_stages_median": med(lead[:, 4].tolist()),
+                     "mma_thread_waited_for_accumulator_median": med(lead[:, 5].tolist()),
+                     "first_epilogue_warp_busy_median": med(t[:, 6].tolist())})
+    assert err.item() == 0, f"a GEMM kernel gave up waiting (code {err.item()})"
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default="")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default="", help="run only the GEMM shapes whose label contains this text")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--group", default="all", choices=["all", "gemm", "bert", "cnn", "conv"],
+    ap.add_argument("--group", default="all", choices=["all", "gemm", "bert", "cnn", "conv", "layer"],
                     help="gemm: GEMM shapes; bert: LayerNorm / Adam; cnn: batch-norm, max-pool, row gather, sparse-row update; "
-                         "conv: implicit-GEMM convolution at the ResNet-101 / VGG-16 layer shapes")
+                         "conv: implicit-GEMM convolution at the ResNet-101 / VGG-16 layer shapes; layer: the twelve GEMMs of one "
+                         "BERT-large encoder layer with their epilogues, warm caches")
+    ap.add_argument("--trace", action="store_true", help="with --group layer: phase marks of the two-CTA kernel")
     args = ap.parse_args()
     from autodist_b200 import ops
     E = ops.ext(required=True)
@@ -184,6 +270,10 @@ def main():
         shapes = shapes[:2]
     if args.only:
         shapes = [s for s in shapes if args.only in s[0]]
+    if args.group == "layer":
+        for r in _layer_rows(E, dev, max(args.iters, 5), args.trace):
+            print(json.dumps(r))
+        return
     if args.group == "conv":
         rows = _conv_rows(E, dev, flush, peaks, args.iters, args.only)
         for r in rows:
@@ -198,7 +288,9 @@ def main():
         a = torch.randn((K, M) if a_mn else (M, K), device=dev).to(torch.bfloat16)
         b = torch.randn((K, N) if b_mn else (N, K), device=dev).to(torch.bfloat16)
         c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-        for bn in (256, 128):
+        for bn in (512, 256, 128):          # 512: the 256 x 256 tile of the two-CTA kernel
+            if bn == 512 and (M < 256 or N < 256):
+                continue
             ms = _time(lambda: E.gemm(a, b, c, a_mn, b_mn, 0, None, None, None, 1.0, 0.0, err, bn), iters=args.iters, flush=flush)
             A = a.t() if a_mn else a
             B = b if b_mn else b.t()
