@@ -12,7 +12,6 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr long long kWaitLimitCycles = 100000000LL;    // ~50 ms at 1.9 GHz: no legitimate wait is longer
 
