@@ -152,3 +152,29 @@ print("not reached")
     r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 70, r.stderr[-2000:]
     assert "not reached" not in r.stdout and "exceeded the 0.5 s deadline" in r.stderr
+
+
+def test_run_accepts_a_prefetched_feed_on_a_cpu_session():
+    """``prefetch=`` is an upload hint: on a CPU session nothing is copied ahead and the results are those of plain feeding."""
+    import torch
+    from autodist_b200.strategy import PS
+    values = []
+    for use in (False, True):
+        _reset_default_autodist()
+        ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=PS())
+        with ad.scope():
+            torch.manual_seed(0)
+            w = torch.nn.Parameter(torch.zeros(3))
+            x = ad.placeholder((None, 3), torch.float32, name="x")
+            loss = ((x * w).sum(1) - 1.0).pow(2).mean()
+            train_op = torch.optim.SGD([w], lr=0.1).minimize(loss)
+            sess = ad.create_distributed_session()
+            batches = [torch.full((4, 3), float(i + 1)) for i in range(4)]
+            out = []
+            for i, b in enumerate(batches):
+                nxt = {x: batches[i + 1]} if use and i + 1 < len(batches) else None
+                out.append(float(sess.run([loss, train_op], {x: b}, prefetch=nxt)[0]))
+            values.append((out, sess.run(w).tolist()))
+            sess.close()
+    _reset_default_autodist()
+    assert values[0] == values[1]

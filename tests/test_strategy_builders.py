@@ -146,3 +146,22 @@ def test_parallax(r0):
     assert by["emb:0"].WhichOneof("synchronizer") == "PSSynchronizer"
     assert not by["emb:0"].PSSynchronizer.local_replication        # sparse PS variables never get a proxy
     assert [by[v].AllReduceSynchronizer.group for v in ("w1:0", "b1:0", "w2:0", "b2:0")] == [0, 1, 1, 2]
+
+
+def test_parallax_with_gpu_owners_row_shards_the_sparse_table(r0):
+    """``reduction_devices="gpu"``: a row-sparse table becomes one row shard per GPU (each shard a parameter-server part on
+    its GPU), dense variables keep their all-reduce groups, and a sparse variable inside control flow stays whole."""
+    s = Parallax(chunk_size=2, reduction_devices="gpu").build(model(), r0)
+    by = {n.var_name: n for n in s.node_config}
+    emb = by["emb:0"]
+    assert emb.partitioner == "2,1"                                     # axis 0 cut in two, axis 1 whole
+    assert [p.var_name for p in emb.part_config] == ["emb/part_0:0", "emb/part_1:0"]
+    owners = [p.PSSynchronizer.reduction_destination for p in emb.part_config]
+    assert len(set(owners)) == 2 and all("GPU" in o.upper() for o in owners), owners
+    assert all(p.PSSynchronizer.sync and not p.PSSynchronizer.local_replication for p in emb.part_config)
+    assert [by[v].AllReduceSynchronizer.group for v in ("w1:0", "b1:0", "w2:0", "b2:0")] == [0, 1, 1, 2]
+    f = torch.float32
+    looped = FakeItem([VariableInfo("emb:0", (10000, 16), f, sparse_grad=True, in_control_flow=True), VariableInfo("w:0", (16, 16), f)])
+    s2 = Parallax(chunk_size=2, reduction_devices="gpu").build(looped, r0)
+    whole = {n.var_name: n for n in s2.node_config}["emb:0"]
+    assert not whole.partitioner and whole.WhichOneof("synchronizer") == "PSSynchronizer"
