@@ -381,6 +381,13 @@ class GraphItem:
 
     # ------------------------------------------------------------------ optimizer capture
     def extend_optimizer_info(self, optimizer, args, kwargs):
+        # `kwargs` are the defaults the base class received; keep those the subclass's constructor accepts (a subclass may pass
+        # its parent more than it takes itself: AdamW hands Adam `decoupled_weight_decay`), so that the engines can build
+        # the same optimizer again over their own parameter objects
+        import inspect
+        accepted = inspect.signature(type(optimizer).__init__).parameters
+        if not any(p.kind is inspect.Parameter.VAR_KEYWORD for p in accepted.values()):
+            kwargs = {k: v for k, v in kwargs.items() if k in accepted}
         self.optimizers.append(OptimizerInfo(optimizer, type(optimizer), args, kwargs,
                                              f"{type(optimizer).__name__}_{len(self.optimizers)}"))
         for group in optimizer.param_groups:

@@ -362,6 +362,10 @@ class FusedStepEngine(StepEngine):
             return False      # the hand-scheduled models fuse reduction and update per flight: no place for a global norm
         if type(graph_item.optimizers[0].optimizer).__name__ not in ("Adam", "AdamW", "SGD", "Adagrad"):
             return False
+        if len(graph_item.optimizers[0].optimizer.param_groups) > 1 and (plan.ps_entries or plan.sparse_all_reduce):
+            # several parameter groups (their own learning rate, weight decay, ...) are applied range by range of the flat
+            # buffer after an all-reduce; the owner-side update kernels take one set of hyper-parameters per launch
+            return False
         if plan.replica.world_size > 1:
             # A variable split into all-reduce parts (PartitionedAR, RandomAxisPartitionAR: any axis) is reduced as the one
             # range it occupies in the flat buffer: the mean is element-wise, so reducing the parts separately or together
@@ -469,29 +473,49 @@ class FusedStepEngine(StepEngine):
         self.opt_kind = type(info.optimizer).__name__
         n = self.flat.total
         dev = self.device
+        # parameter groups: runs of the flat buffer whose parameters share a group (adjacent parameters of one group merge)
+        groups = info.optimizer.param_groups
+        group_of = {id(p): gi for gi, g in enumerate(groups) for p in g["params"]}
+        fl = self.flat
+        self._group_runs = []                       # (lo, hi, group index), ascending
+        for name, p in zip(fl.names, fl.params):
+            lo = fl.offsets[name]
+            hi = lo + p.numel()
+            gi = group_of.get(id(p), 0)
+            if self._group_runs and self._group_runs[-1][2] == gi and self._group_runs[-1][1] == lo:
+                self._group_runs[-1] = (self._group_runs[-1][0], hi, gi)
+            else:
+                self._group_runs.append((lo, hi, gi))
         self.slot1 = torch.zeros(n, dtype=torch.float32, device=dev) if self._needs_slot1() else None
         if self.opt_kind == "Adagrad":
-            self.slot1.fill_(float(info.optimizer.param_groups[0].get("initial_accumulator_value", 0.0)))
+            for lo, hi, gi in self._group_runs:
+                self.slot1[lo:hi].fill_(float(groups[gi].get("initial_accumulator_value", 0.0)))
         self.slot2 = torch.zeros(n, dtype=torch.float32, device=dev) if self.opt_kind in ("Adam", "AdamW") else None
-        self.lr = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.lrs = torch.zeros(len(groups), dtype=torch.float32, device=dev)      # one learning rate per group, read by the kernels
+        self.lr = self.lrs[0:1]
         self._lr_host = None
         self.opt_step = torch.zeros(1, dtype=torch.int64, device=dev)
         self._sync_lr()
 
     def _needs_slot1(self):
-        g = self.opt_info.optimizer.param_groups[0]
-        return self.opt_kind != "SGD" or g.get("momentum", 0) != 0
+        return self.opt_kind != "SGD" or any(g.get("momentum", 0) != 0 for g in self.opt_info.optimizer.param_groups)
 
     def _sync_lr(self):
-        lr = float(self.opt_info.optimizer.param_groups[0]["lr"])
-        if lr != self._lr_host:
-            self.lr.fill_(lr)
-            self._lr_host = lr
+        lrs = [float(g["lr"]) for g in self.opt_info.optimizer.param_groups]
+        if lrs != self._lr_host:
+            for gi, lr in enumerate(lrs):                    # device-side fills: a schedule that moves every step never syncs
+                if self._lr_host is None or self._lr_host[gi] != lr:
+                    self.lrs[gi:gi + 1].fill_(lr)
+            self._lr_host = lrs
 
     def _update_range(self, lo, hi):
+        """Optimizer update of the flat range [lo, hi): one launch per parameter group that has parameters in it."""
         fl = self.flat
-        self._apply_optimizer(fl.master[lo:hi], fl.grad[lo:hi], self.slot1[lo:hi] if self.slot1 is not None else None,
-                              self.slot2[lo:hi] if self.slot2 is not None else None, fl.p16[lo:hi])
+        for glo, ghi, gi in self._group_runs:
+            a, b = max(lo, glo), min(hi, ghi)
+            if a < b:
+                self._apply_optimizer(fl.master[a:b], fl.grad[a:b], self.slot1[a:b] if self.slot1 is not None else None,
+                                      self.slot2[a:b] if self.slot2 is not None else None, fl.p16[a:b], gi)
 
     # ------------------------------------------------------------------ flights
     def _setup_flights(self):
@@ -736,15 +760,17 @@ class FusedStepEngine(StepEngine):
         for st in self.sharded_rows.values():
             st.update()
 
-    def _apply_optimizer(self, p, gr, s1, s2, p16):
-        g = self.opt_info.optimizer.param_groups[0]
+    def _apply_optimizer(self, p, gr, s1, s2, p16, group=0):
+        g = self.opt_info.optimizer.param_groups[group]
+        lr = self.lrs[group:group + 1]
         if self.opt_kind in ("Adam", "AdamW"):
             b1, b2 = g["betas"]
-            self.E.adam_update(p, gr, s1, s2, p16, self.lr, b1, b2, g["eps"], g["weight_decay"], self.opt_kind == "AdamW", self.opt_step, 1.0)
+            self.E.adam_update(p, gr, s1, s2, p16, lr, b1, b2, g["eps"], g["weight_decay"], self.opt_kind == "AdamW", self.opt_step, 1.0)
         elif self.opt_kind == "SGD":
-            self.E.sgd_update(p, gr, s1, p16, self.lr, g["momentum"], g["dampening"], g["weight_decay"], g["nesterov"], self.opt_step, 1.0)
+            self.E.sgd_update(p, gr, s1 if g.get("momentum", 0) != 0 else None, p16, lr, g["momentum"], g["dampening"], g["weight_decay"],
+                              g["nesterov"], self.opt_step, 1.0)
         else:
-            self.E.adagrad_update(p, gr, s1, p16, self.lr, g["eps"], g["weight_decay"], 1.0)
+            self.E.adagrad_update(p, gr, s1, p16, lr, g["eps"], g["weight_decay"], 1.0)
 
     def _ps_table(self, lo, hi):
         """Device tables of this rank's owned segments inside [lo, hi) (cached per flight)."""
@@ -1081,7 +1107,7 @@ class FlatAutogradEngine(FusedStepEngine):
 
     @staticmethod
     def supports_autograd(graph_item, plan):
-        if len(graph_item.optimizers) != 1 or len(graph_item.optimizers[0].optimizer.param_groups) != 1:
+        if len(graph_item.optimizers) != 1:
             return False
         params = [p for _, p in graph_item.named_parameters() if p.requires_grad]
         if not params or any(p.dtype != torch.float32 for p in params):

@@ -178,3 +178,45 @@ def test_run_accepts_a_prefetched_feed_on_a_cpu_session():
             sess.close()
     _reset_default_autodist()
     assert values[0] == values[1]
+
+
+def test_parameter_groups_keep_their_hyper_parameters_on_the_generic_engine():
+    """AdamW with two groups (weight decay on the weights only, a different learning rate on the biases) through a session
+    equals the same optimizer stepped by hand."""
+    import copy
+    import torch
+    from autodist_b200.strategy import AllReduce
+
+    def make_groups(net):
+        weights = [p for n, p in net.named_parameters() if n.endswith("weight")]
+        biases = [p for n, p in net.named_parameters() if n.endswith("bias")]
+        return [{"params": weights, "weight_decay": 0.5}, {"params": biases, "weight_decay": 0.0, "lr": 0.05}]
+
+    torch.manual_seed(1)
+    base = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 1))
+    g = torch.Generator().manual_seed(0)
+    data = [(torch.randn(8, 6, generator=g), torch.randn(8, 1, generator=g)) for _ in range(5)]
+
+    ref = copy.deepcopy(base)
+    opt = torch.optim.AdamW(make_groups(ref), lr=0.01)
+    for xb, yb in data:
+        opt.zero_grad()
+        ((ref(xb) - yb) ** 2).mean().backward()
+        opt.step()
+
+    _reset_default_autodist()
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=AllReduce())
+    with ad.scope():
+        net = copy.deepcopy(base)
+        x = ad.placeholder((None, 6), torch.float32, name="x")
+        y = ad.placeholder((None, 1), torch.float32, name="y")
+        loss = ((net(x) - y) ** 2).mean()
+        train_op = torch.optim.AdamW(make_groups(net), lr=0.01).minimize(loss)
+        sess = ad.create_distributed_session()
+        for xb, yb in data:
+            sess.run(train_op, {x: xb, y: yb})
+        got = {n: torch.from_numpy(sess.run(p)) for n, p in net.named_parameters()}
+        sess.close()
+    _reset_default_autodist()
+    for n, p in ref.named_parameters():
+        assert torch.allclose(got[n], p.detach(), atol=1e-6), n

@@ -111,3 +111,23 @@ def test_leaf_module_is_one_node():
         torch.optim.SGD(m.parameters(), lr=0.1).minimize(loss)
     assert [n.op for n in item.tracer.graph.nodes] == ["placeholder", "call_module"]
     assert item.updated_variable_names() == {"fc.weight:0", "fc.bias:0"}
+
+
+def test_captured_optimizer_arguments_rebuild_the_same_optimizer_class():
+    """The recorded constructor arguments must be accepted by the optimizer's own class (AdamW passes its parent an argument
+    it does not take itself), and groups keep their own hyper-parameters."""
+    import torch
+    from autodist_b200 import AutoDist
+    from autodist_b200.autodist import _reset_default_autodist
+    from autodist_b200.resource_spec import ResourceSpec
+    _reset_default_autodist()
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1))
+    with ad.scope():
+        a, b = torch.nn.Parameter(torch.zeros(2)), torch.nn.Parameter(torch.zeros(3))
+        for cls in (torch.optim.AdamW, torch.optim.Adam, torch.optim.SGD, torch.optim.Adagrad, torch.optim.RMSprop):
+            opt = cls([{"params": [a], "weight_decay": 0.5}, {"params": [b], "lr": 0.25}], lr=0.125)
+            info = ad.graph_item.optimizers[-1]
+            again = info.cls([{"params": [torch.nn.Parameter(torch.zeros(2))]}], **dict(info.kwargs))
+            assert type(again) is cls and again.defaults["lr"] == 0.125
+            assert opt.param_groups[0]["weight_decay"] == 0.5 and opt.param_groups[1]["lr"] == 0.25
+    _reset_default_autodist()
