@@ -1102,7 +1102,8 @@ class FlatAutogradEngine(FusedStepEngine):
     into those views in place, post-accumulate hooks report finished parameters, and as soon as a *flight* (a run
     of consecutive parameters, at least ``AUTODIST_FLIGHT_MB`` of gradients) is complete its all-reduce /
     reduce-scatter kernel and the fused optimizer kernel run on the communication stream while autograd continues.
-    This is how the CNN benchmarks (cuDNN convolutions) use the same synchronisation kernels as the fused models.
+    This is how the CNN benchmarks and LM1B (autograd programs over the hand-written kernels) use the same synchronisation
+    kernels as the hand-scheduled models.
     """
 
     @staticmethod
