@@ -139,7 +139,8 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
     // pairs pay off once their 256 x 256 tiles fill the SM pairs, or when a long contraction makes the shared-memory
     // fill per FLOP (what the pair halves for B) the limit
     const int64_t pair_tiles = (int64_t)((M + 255) / 256) * ((N + 255) / 256) * a.size(0) * a.size(1);
-    if (pair_default && bn == 256 && M >= 256 && !softmax_epi && (pair_tiles >= num_sms() / 2 || K >= 2048)) bn = 512;
+    static const int64_t pair_min_k = [] { const char* e = std::getenv("AUTODIST_GEMM_PAIR_MIN_K"); return e != nullptr ? std::atoll(e) : 2048LL; }();
+    if (pair_default && bn == 256 && M >= 256 && !softmax_epi && (pair_tiles >= num_sms() / 2 || K >= pair_min_k)) bn = 512;
   }
   TORCH_CHECK(bn == 64 || bn == 128 || bn == 256 || bn == 512, "bn must be 64, 128, 256 or 512 (two-CTA tile)");
   const bool pair = bn == 512;
