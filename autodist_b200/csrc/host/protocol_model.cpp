@@ -210,8 +210,11 @@ py::tuple simulate_staleness(int world, int steps, uint32_t staleness, std::vect
 
 }  // namespace
 
+void register_batch_feeder(py::module& m);      // batch_feeder.cpp
+
 PYBIND11_MODULE(_adb200_host, m) {
-  m.doc() = "host model of the symmetric-memory barrier protocol";
+  m.doc() = "host-side native components: model of the symmetric-memory barrier protocol, background batch feeder";
+  register_batch_feeder(m);
   m.def("simulate_allreduce", &simulate_allreduce, py::arg("world"), py::arg("blocks"), py::arg("n"), py::arg("iters") = 1,
         py::arg("absent") = std::vector<int>{}, py::arg("timeout_ms") = 200.0, py::arg("first_epoch") = 0u,
         py::arg("with_grid_barriers") = true);

@@ -62,7 +62,8 @@ def host_so_path():
 
 
 def build_host(verbose=False):
-    """Host-only extension (no device code): the C++ model of the synchronisation protocol under ``csrc/host``."""
+    """Host-only extension (no device code) under ``csrc/host``: the C++ model of the synchronisation protocol and the
+    background batch feeder."""
     from torch.utils import cpp_extension
     os.makedirs(EXT_DIR, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))

@@ -24,8 +24,34 @@ def fit_route(ad, images, labels):
         print("evaluate:", result)
 
 
+def feeder_route(ad, images, labels):
+    """The same training from a record file: native worker threads assemble the shuffled batches in pinned buffers, and
+    every ``run`` starts the upload of the batch after the one it trains on."""
+    import tempfile
+    from autodist_b200.utils.data import RecordFeeder, write_records
+    path = os.path.join(tempfile.mkdtemp(), "fashion.rec")
+    write_records(path, {"images": images, "labels": labels})
+    with ad.scope():
+        model = FashionCNN()
+        x = ad.placeholder((None, 1, 28, 28), torch.float32, name="images")
+        y = ad.placeholder((None,), torch.int64, name="labels")
+        loss = model(x, y)
+        train_op = torch.optim.SGD(model.parameters(), lr=0.05).minimize(loss)
+        sess = ad.create_distributed_session()
+        # every process feeds its node's batches; the session splits them between the node's replicas
+        batches = iter(RecordFeeder(path, 64, shuffle=True, seed=0, epochs=5, depth=3))
+        current, step = next(batches), 0
+        while current is not None:
+            upcoming = next(batches, None)
+            lv, _ = sess.run([loss, train_op], {x: current["images"], y: current["labels"]},
+                             prefetch=None if upcoming is None else {x: upcoming["images"], y: upcoming["labels"]})
+            if sess.rank == 0 and step % 4 == 0:
+                print(f"step {step} loss {float(lv):.4f}")
+            current, step = upcoming, step + 1
+
+
 def main():
-    args = [a for a in sys.argv[1:] if a != "--fit"]
+    args = [a for a in sys.argv[1:] if a not in ("--fit", "--feeder")]
     spec = ResourceSpec(args[0]) if args else ResourceSpec.local(num_cpus=2)
     ad = AutoDist(resource_spec=spec)                     # default builder: PSLoadBalancing
     rng = np.random.RandomState(0)
@@ -33,6 +59,8 @@ def main():
     labels = rng.randint(0, 10, size=256).astype(np.int64)
     if "--fit" in sys.argv:
         return fit_route(ad, images, labels)
+    if "--feeder" in sys.argv:
+        return feeder_route(ad, images, labels)
     with ad.scope():
         model = FashionCNN()
         x = ad.placeholder((None, 1, 28, 28), torch.float32, name="images")

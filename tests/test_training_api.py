@@ -90,3 +90,20 @@ def test_fit_route_of_the_example_on_two_self_launched_ranks():
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "epoch 3/3" in r.stdout and "evaluate:" in r.stdout
+
+
+@pytest.mark.integration
+def test_record_feeder_route_of_the_example_on_two_self_launched_ranks():
+    """Batches from the native feeder, each step prefetching the next batch, on two CPU replicas started by the chief."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "AUTODIST_WORKER",
+                                                            "AUTODIST_STRATEGY_ID")}
+    env["AUTODIST_MIN_LOG_LEVEL"] = "ERROR"
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "image_classifier.py"), "--feeder"], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    losses = [float(l.split()[-1]) for l in r.stdout.splitlines() if l.startswith("step ")]
+    assert len(losses) == 5 and losses[-1] < losses[0], r.stdout          # 20 steps, printed every fourth
