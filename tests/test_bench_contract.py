@@ -23,3 +23,21 @@ def test_only_rank_zero_of_a_multi_rank_reference_call_prints():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_flight_table_is_written_from_an_engines_report(tmp_path):
+    sys.path.insert(0, ROOT)
+    import bench
+
+    class Engine:
+        def flight_report(self):
+            return [(0, 1 << 20, 0.5, 0.25), (1 << 20, 3 << 20, 1.0, 0.5)]
+
+    path = str(tmp_path / "sub" / "flights.md")
+    bench._write_flights(path, Engine(), "bert-tiny", "allreduce", 4, 12.5, 0, 1, "cpu")
+    text = open(path).read()
+    rows = [l for l in text.splitlines() if l.startswith("| 0 |") or l.startswith("| 1 |")]
+    assert len(rows) == 2 and "| 1048576 | 4.0 | 0.50 | 0.250 |" in rows[0]
+    # bus bandwidth of a 4-rank all-reduce: 2 * 3 / 4 * bytes / time
+    assert rows[1].rstrip("|").split("|")[-1].strip() == str(round(1.5 * (2 << 20) * 4 / 0.5e-3 / 1e9))
+    assert "busy 0.75 ms of the 12.50 ms step" in text and "ends 1.50 ms" in text
