@@ -133,6 +133,8 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
   // bn: tile width 64 / 128 / 256 of the one-CTA kernel, or 512 = the 256 x 256 tile of the two-CTA kernel; 0 picks one
   // (two CTAs when both extents fill a pair's tile and AUTODIST_GEMM_PAIR is not 0)
   const bool softmax_epi = epilogue == adb200::EPI_SOFTMAX || epilogue == adb200::EPI_SOFTMAX_GRAD;
+  static bool pair_unavailable = false;        // set when a cluster launch was refused once (see below)
+  const bool auto_bn = bn <= 0;
   if (bn <= 0) {
     static const bool pair_default = [] { const char* e = std::getenv("AUTODIST_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
     bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
@@ -140,7 +142,8 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
     // fill per FLOP (what the pair halves for B) the limit
     const int64_t pair_tiles = (int64_t)((M + 255) / 256) * ((N + 255) / 256) * a.size(0) * a.size(1);
     static const int64_t pair_min_k = [] { const char* e = std::getenv("AUTODIST_GEMM_PAIR_MIN_K"); return e != nullptr ? std::atoll(e) : 2048LL; }();
-    if (pair_default && bn == 256 && M >= 256 && !softmax_epi && (pair_tiles >= num_sms() / 2 || K >= pair_min_k)) bn = 512;
+    if (pair_default && !pair_unavailable && bn == 256 && M >= 256 && !softmax_epi && (pair_tiles >= num_sms() / 2 || K >= pair_min_k))
+      bn = 512;
   }
   TORCH_CHECK(bn == 64 || bn == 128 || bn == 256 || bn == 512, "bn must be 64, 128, 256 or 512 (two-CTA tile)");
   const bool pair = bn == 512;
@@ -216,6 +219,16 @@ void gemm_impl(const Tensor& a_, const Tensor& b_, Tensor c_, bool a_mn, bool b_
                                                   p.tma_store ? &tmC : nullptr, p.tma_store ? &tmC2 : nullptr)
                        : adb200::launch_gemm(tmA, tmB, p, (int)bn, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream(),
                                              p.tma_store ? &tmC : nullptr, p.tma_store ? &tmC2 : nullptr);
+  if (pair && auto_bn && e != cudaSuccess) {
+    // A device (or partition of one) that cannot schedule clusters of two refuses the launch: remember it and run this and
+    // every later product on the one-CTA kernel.
+    (void)cudaGetLastError();
+    pair_unavailable = true;
+    tmB.m[0] = make_map(b, b_mn ? 64 : 256);
+    for (int i = 1; i < 8; ++i) tmB.m[i] = tmB.m[0];
+    e = adb200::launch_gemm(tmA, tmB, p, 256, a_mn, b_mn, num_sms(), at::cuda::getCurrentCUDAStream(), p.tma_store ? &tmC : nullptr,
+                            p.tma_store ? &tmC2 : nullptr);
+  }
   TORCH_CHECK(e == cudaSuccess, "GEMM launch failed: ", cudaGetErrorString(e));
 }
 
