@@ -210,6 +210,49 @@ class StepEngine:
         self.global_step += 1
         return [v.detach() if isinstance(v, torch.Tensor) else v for v in values[:len(nodes)]]
 
+    def train_step_multi(self, train_ops, nodes, feeds):
+        """Several train ops fetched by one ``run`` - one per optimizer, over disjoint sets of variables (two networks trained
+        against each other, a head with its own optimizer, ...). As in the reference's session, every gradient is taken at
+        the values the variables had before the call: one forward pass, each loss differentiated with respect to its own
+        optimizer's variables only, one round of gradient synchronisation, then every optimizer steps."""
+        if self._async is not None:
+            raise NotImplementedError("several train ops in one run() call under a bounded-staleness / asynchronous strategy")
+        if len({op.optimizer_index for op in train_ops}) != len(train_ops):
+            raise NotImplementedError("several train ops of one optimizer in one run() call")
+        owned, seen = [], set()
+        for op in train_ops:
+            info = self._local_optimizers[op.optimizer_index][0]
+            params = op.var_list if op.var_list is not None else [p for g in info.optimizer.param_groups for p in g["params"]]
+            if seen & {id(p) for p in params}:
+                raise NotImplementedError("train ops fetched together must update disjoint sets of variables")
+            seen |= {id(p) for p in params}
+            owned.append(list(params))
+        self.before_read()
+        all_nodes = list(nodes)
+        for op in train_ops:
+            if op.loss_node not in all_nodes:
+                all_nodes.append(op.loss_node)
+        for p in self._params.values():
+            p.grad = None
+        values = self.forward(all_nodes, feeds, grad=True)
+        for i, (op, params) in enumerate(zip(train_ops, owned)):
+            values[all_nodes.index(op.loss_node)].backward(inputs=params, retain_graph=i + 1 < len(train_ops))
+        if self.world_size > 1:
+            self._all_reduce_dense()
+            self._all_reduce_sparse()
+            self._reduce_ps_dense()
+            self._reduce_ps_sparse()
+        for op in train_ops:
+            self._clip(op)
+            self._apply_local(op)
+        if self.world_size > 1 and self.plan.ps_entries:
+            if all(e.local_replication for e in self.plan.ps_entries.values()):
+                self._publish_ps()
+            else:
+                self._pending_pull = True
+        self.global_step += 1
+        return [v.detach() if isinstance(v, torch.Tensor) else v for v in values[:len(nodes)]]
+
     def backward(self, loss):
         loss.backward()
 

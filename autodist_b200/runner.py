@@ -246,8 +246,12 @@ class WrappedSession:
         nodes = [rm.node_of(leaves[i]) for i in tensor_idx]
         train_ops = [leaves[i] for i, k in enumerate(kinds) if k == "train_op"]
         if len(train_ops) > 1:
-            raise NotImplementedError("one train_op per run() call")
-        if train_ops:
+            from autodist_b200.parallel.engine import StepEngine
+            if type(eng) is not StepEngine:
+                raise NotImplementedError("several train ops in one run() call run on the generic engine only "
+                                          f"(this session uses {type(eng).__name__}; on GPUs set AUTODIST_COMM=nccl)")
+            values = eng.train_step_multi(train_ops, nodes, feeds)
+        elif train_ops:
             values = eng.train_step(train_ops[0], nodes, feeds)
         elif nodes:
             eng.before_read()

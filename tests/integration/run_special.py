@@ -218,6 +218,45 @@ def scenario_hetero():
     _run_multi_node("hetero", spec, 3, lambda r: [0, 1] if r < 2 else [2])
 
 
+def scenario_twoopts():
+    """Two optimizers over disjoint variables, both train ops fetched by one run() on two replicas: the result equals the
+    single-process computation on the whole batch (gradients of both losses taken at the values before the step)."""
+    import copy
+    torch.manual_seed(2)
+    enc0, head0 = torch.nn.Linear(5, 4), torch.nn.Linear(4, 1)
+    g = torch.Generator().manual_seed(0)
+    data = [(torch.randn(8, 5, generator=g), torch.randn(8, 1, generator=g)) for _ in range(4)]
+    enc, head = copy.deepcopy(enc0), copy.deepcopy(head0)
+    o1, o2 = torch.optim.SGD(enc.parameters(), lr=0.1), torch.optim.Adam(head.parameters(), lr=0.01)
+    for xb, yb in data:
+        h = torch.tanh(enc(xb))
+        l1, l2 = (h ** 2).mean(), ((head(h) - yb) ** 2).mean()
+        o1.zero_grad()
+        o2.zero_grad()
+        l1.backward(inputs=list(enc.parameters()), retain_graph=True)
+        l2.backward(inputs=list(head.parameters()))
+        o1.step()
+        o2.step()
+    strategy = PS() if os.environ.get("AUTODIST_TWOOPTS", "ar") == "ps" else AllReduce(chunk_size=2)
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=2), strategy_builder=strategy)
+    with ad.scope():
+        e, hd = copy.deepcopy(enc0), copy.deepcopy(head0)
+        x = ad.placeholder((None, 5), torch.float32, name="x")
+        y = ad.placeholder((None, 1), torch.float32, name="y")
+        hidden = torch.tanh(e(x))
+        loss1, loss2 = (hidden ** 2).mean(), ((hd(hidden) - y) ** 2).mean()
+        op1 = torch.optim.SGD(e.parameters(), lr=0.1).minimize(loss1, var_list=list(e.parameters()))
+        op2 = torch.optim.Adam(hd.parameters(), lr=0.01).minimize(loss2, var_list=list(hd.parameters()))
+        sess = ad.create_distributed_session()
+        for xb, yb in data:
+            sess.run([loss1, loss2, op1, op2], {x: xb, y: yb})
+        got = [sess.run(p) for p in list(e.parameters()) + list(hd.parameters())]
+    want = [p.detach().numpy() for p in list(enc.parameters()) + list(head.parameters())]
+    for a, b in zip(got, want):
+        assert np.allclose(a, b, atol=2e-5), (a, b)
+    print(f"twoopts rank {sess.rank} ok", flush=True)
+
+
 def _spawn_ranks(name, nproc=2):
     """Start the ranks the way an external launcher would (RANK / WORLD_SIZE in the environment)."""
     import subprocess

@@ -220,3 +220,50 @@ def test_parameter_groups_keep_their_hyper_parameters_on_the_generic_engine():
     _reset_default_autodist()
     for n, p in ref.named_parameters():
         assert torch.allclose(got[n], p.detach(), atol=1e-6), n
+
+
+def test_two_train_ops_of_two_optimizers_in_one_run_call():
+    """Two networks with their own optimizers fetched together: both gradients are taken at the values before the call,
+    as when the same is written by hand; train ops over the same variables are refused."""
+    import copy
+    import torch
+    from autodist_b200.strategy import AllReduce
+    torch.manual_seed(2)
+    enc0, head0 = torch.nn.Linear(5, 4), torch.nn.Linear(4, 1)
+    g = torch.Generator().manual_seed(0)
+    data = [(torch.randn(8, 5, generator=g), torch.randn(8, 1, generator=g)) for _ in range(4)]
+
+    enc, head = copy.deepcopy(enc0), copy.deepcopy(head0)
+    o1, o2 = torch.optim.SGD(enc.parameters(), lr=0.1), torch.optim.Adam(head.parameters(), lr=0.01)
+    for xb, yb in data:
+        h = torch.tanh(enc(xb))
+        l1, l2 = (h ** 2).mean(), ((head(h) - yb) ** 2).mean()
+        o1.zero_grad(); o2.zero_grad()
+        l1.backward(inputs=list(enc.parameters()), retain_graph=True)
+        l2.backward(inputs=list(head.parameters()))
+        o1.step(); o2.step()
+
+    _reset_default_autodist()
+    ad = AutoDist(resource_spec=ResourceSpec.local(num_cpus=1), strategy_builder=AllReduce())
+    with ad.scope():
+        e, hd = copy.deepcopy(enc0), copy.deepcopy(head0)
+        x = ad.placeholder((None, 5), torch.float32, name="x")
+        y = ad.placeholder((None, 1), torch.float32, name="y")
+        hidden = torch.tanh(e(x))
+        loss1, loss2 = (hidden ** 2).mean(), ((hd(hidden) - y) ** 2).mean()
+        op1 = torch.optim.SGD(e.parameters(), lr=0.1).minimize(loss1, var_list=list(e.parameters()))
+        op2 = torch.optim.Adam(hd.parameters(), lr=0.01).minimize(loss2, var_list=list(hd.parameters()))
+        both = torch.optim.SGD(list(e.parameters()) + list(hd.parameters()), lr=0.1).minimize(loss2)
+        sess = ad.create_distributed_session()
+        for xb, yb in data:
+            l1v, l2v, _, _ = sess.run([loss1, loss2, op1, op2], {x: xb, y: yb})
+        got = {("e", n): torch.from_numpy(sess.run(p)) for n, p in e.named_parameters()}
+        got.update({("h", n): torch.from_numpy(sess.run(p)) for n, p in hd.named_parameters()})
+        with pytest.raises(NotImplementedError):
+            sess.run([op1, both], {x: data[0][0], y: data[0][1]})
+        sess.close()
+    _reset_default_autodist()
+    for n, p in enc.named_parameters():
+        assert torch.allclose(got[("e", n)], p.detach(), atol=1e-6), n
+    for n, p in head.named_parameters():
+        assert torch.allclose(got[("h", n)], p.detach(), atol=1e-6), n

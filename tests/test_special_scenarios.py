@@ -25,3 +25,10 @@ def _launch(name, tmp_path, expect_ok=2):
                                       ("crossload", 2), ("function", 2), ("twonode", 8), ("hetero", 3)])
 def test_scenario(name, oks, tmp_path):
     _launch(name, tmp_path, oks)
+
+
+@pytest.mark.integration
+@pytest.mark.parametrize("strategy", ["ar", "ps"])
+def test_two_train_ops_in_one_run_on_two_replicas(strategy, tmp_path, monkeypatch):
+    monkeypatch.setenv("AUTODIST_TWOOPTS", strategy)
+    _launch("twoopts", tmp_path, 2)
