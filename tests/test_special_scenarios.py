@@ -28,7 +28,8 @@ def test_scenario(name, oks, tmp_path):
 
 
 @pytest.mark.integration
-@pytest.mark.parametrize("strategy", ["ar", "ps"])
-def test_two_train_ops_in_one_run_on_two_replicas(strategy, tmp_path, monkeypatch):
-    monkeypatch.setenv("AUTODIST_TWOOPTS", strategy)
+def test_two_train_ops_in_one_run_on_two_replicas(tmp_path, monkeypatch):
+    """Parameter-server strategy (reduce to the owner, owner-side update, publish); the all-reduce form of the same program runs
+    with ``AUTODIST_TWOOPTS=ar`` and, on one process, in ``tests/test_autodist.py``."""
+    monkeypatch.setenv("AUTODIST_TWOOPTS", "ps")
     _launch("twoopts", tmp_path, 2)
